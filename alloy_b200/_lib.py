@@ -1,0 +1,99 @@
+"""ctypes binding of ``liballoy_b200.so`` — the only route from Python to the kernels.
+
+There is no fallback: if the shared library has not been built
+(``python -m alloy_b200.build``) loading raises, and every op raises with it.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import pathlib
+
+_HERE = pathlib.Path(__file__).resolve().parent
+LIB_PATH = _HERE / "liballoy_b200.so"
+
+F16, BF16, F32 = 0, 1, 2
+Q4_K, Q6_K, Q8_0 = 0, 1, 2
+ACT_SILU, ACT_GELU_TANH = 0, 1
+KV_F16, KV_Q8_SPLIT, KV_Q8_PAGED = 0, 1, 2
+
+
+class AlloyB200Error(RuntimeError):
+    """A C-ABI call returned a negative status."""
+
+
+class Weight(C.Structure):
+    """Mirror of ``alloyb_weight`` in ``include/alloy_b200.h``."""
+
+    _fields_ = [
+        ("format", C.c_int),
+        ("N", C.c_int),
+        ("data", C.c_void_p),
+        ("scales", C.c_void_p),
+        ("row_bytes", C.c_int64),
+        ("y", C.c_void_p),
+        ("ldy", C.c_int64),
+    ]
+
+
+_p, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
+
+# name -> (restype, argtypes); must list every symbol the header declares.
+SIGNATURES = {
+    "alloyb_version": (_i, []),
+    "alloyb_error_string": (C.c_char_p, [_i]),
+    "alloyb_last_cuda_error": (_i, []),
+    "alloyb_device_supported": (_i, []),
+    "alloyb_dequant_q4k": (_i, [_p, _p, _p, _i64, _i64, _i, _i, _p]),
+    "alloyb_dequant_q6k": (_i, [_p, _p, _p, _i64, _i64, _i, _i, _p]),
+    "alloyb_dequant_q8_0": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _i, _p]),
+    "alloyb_linear": (_i, [_p, _i, _i, _i, C.POINTER(Weight), _i, _p, _p]),
+    "alloyb_q4k_mm": (_i, [_p, _p, _p, _i, _i, _i, _i, _p]),
+    "alloyb_q6k_mm": (_i, [_p, _p, _p, _i, _i, _i, _i, _p]),
+    "alloyb_q8_0_mm": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p]),
+    "alloyb_gated_linear": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "alloyb_kv_quantize_q8": (_i, [_p, _i64, _i64, _i64, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "alloyb_kv_dequant_q8": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "alloyb_kv_append_q8_paged": (_i, [_p, _p, _i64, _i64, _p, _p, _i, _i64, _p, _i, _i, _i, _p, _p]),
+    "alloyb_attn_workspace_bytes": (_sz, [_i, _i, _i]),
+    "alloyb_attn_workspace_init": (_i, [_p, _sz, _i, _i, _p]),
+    "alloyb_attn_workspace_status": (_i, [_p, C.POINTER(C.c_int32), _p]),
+    "alloyb_attn_decode": (_i, [_i, _p, _i64, _i64, _i, _p, _p, _p, _p, _p, _p, _i64, _i64, _p, _i,
+                                _p, _i, _i, _i, _i, _i, _i64, _f, _i, _p, _sz, _p]),
+    "alloyb_rms_norm": (_i, [_p, _p, _p, _i, _i, _f, _i, _p]),
+    "alloyb_rope_inplace": (_i, [_p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _p]),
+    "alloyb_silu_mul": (_i, [_p, _p, _p, _i64, _i, _p]),
+    "alloyb_argmax": (_i, [_p, _p, _i, _i, _i, _p]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the shared library once and attach argument types."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise AlloyB200Error(
+            f"{LIB_PATH} is missing: build it with `python -m alloy_b200.build` "
+            "(there is no CPU or eager fallback for these ops)")
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(code: int, what: str) -> None:
+    """Raise on a negative status, naming the call."""
+    if code == 0:
+        return
+    lib = load()
+    msg = lib.alloyb_error_string(code).decode()
+    extra = ""
+    if code == -5:
+        extra = f" (cudaError {lib.alloyb_last_cuda_error()})"
+    raise AlloyB200Error(f"{what}: {msg}{extra}")

@@ -1,0 +1,411 @@
+// Single-query (decode) GQA attention over fp16, split-q8 and paged-q8 KV caches.
+//
+// Grid (SPLITS, KV_H, B); each CTA streams one token range of one KV head ONCE
+// and scores all G = H/KV_H query heads of the group against it.  Softmax runs
+// in the exp2 frame (scale*log2e folded into q).  Each CTA writes a normalised
+// partial output and its log-sum-exp; the last CTA of a (sequence, kv head) to
+// finish merges the partials, so no second launch is needed.
+#include "kv.cuh"
+
+namespace alloyb {
+
+constexpr int ATTN_MAX_SPLITS = 32;
+constexpr float NEG_BIG = -1.0e30f;
+
+struct AttnParams {
+    const void* q;
+    int64_t q_bs, q_hs;
+    int q_dtype;
+    KVPtrs kv;
+    const int32_t* pos;
+    int pos_count;
+    void* out;
+    int B, H, KV_H;
+    float scale_log2;    // softmax scale * log2(e)
+    int splits;
+    float* part_o;       // (B, H, splits, D)
+    float* part_lse;     // (B, H, splits), log2 frame
+    unsigned int* counters;  // (B, KV_H)
+    int* status;
+};
+
+__device__ __forceinline__ float load_q(const void* q, int dtype, int64_t i) {
+    if (dtype == ALLOYB_F16) return __half2float(static_cast<const __half*>(q)[i]);
+    if (dtype == ALLOYB_BF16) {
+        // the reference computes decode attention with q in fp16 (torch/ops/kv_quant.py:175-180)
+        return __half2float(__float2half_rn(__bfloat162float(static_cast<const __nv_bfloat16*>(q)[i])));
+    }
+    return __half2float(__float2half_rn(static_cast<const float*>(q)[i]));
+}
+
+__device__ __forceinline__ void store_out(void* out, int dtype, int64_t i, float v) {
+    if (dtype == ALLOYB_F16) static_cast<__half*>(out)[i] = __float2half_rn(v);
+    else if (dtype == ALLOYB_BF16) static_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(v);
+    else static_cast<float*>(out)[i] = v;
+}
+
+// Row base of token j for (b, h) in each layout.  Paged: returns nullptr for a bad page.
+template <int LAYOUT, int D>
+struct RowRef {
+    const uint8_t* codes;    // f16: the fp16 row; split: int8 codes; paged: 34-byte blocks
+    const __half* scales;    // split only
+};
+
+template <int LAYOUT, int D>
+__device__ __forceinline__ RowRef<LAYOUT, D> row_ref(const KVPtrs& kv, int which, int b, int h,
+                                                     int KV_H, int j, int* status) {
+    RowRef<LAYOUT, D> r;
+    r.scales = nullptr;
+    if (LAYOUT == ALLOYB_KV_F16) {
+        const __half* base = static_cast<const __half*>(which ? kv.v0 : kv.k0);
+        r.codes = reinterpret_cast<const uint8_t*>(
+            base + ((static_cast<int64_t>(b) * KV_H + h) * kv.S_max + j) * D);
+    } else if (LAYOUT == ALLOYB_KV_Q8_SPLIT) {
+        const int64_t row = (static_cast<int64_t>(b) * KV_H + h) * kv.S_max + j;
+        r.codes = static_cast<const uint8_t*>(which ? kv.v0 : kv.k0) + row * D;
+        r.scales = static_cast<const __half*>(which ? kv.v1 : kv.k1) + row * (D / 32);
+    } else {
+        const int32_t* table = static_cast<const int32_t*>(kv.k1);
+        const int64_t page = table[static_cast<int64_t>(b) * kv.max_pages + j / PAGE_TOKENS];
+        if (page < 0 || page >= kv.num_pages) {
+            if (status) atomicOr(status, KV_STATUS_PAGE_RANGE);
+            r.codes = nullptr;
+        } else {
+            r.codes = static_cast<const uint8_t*>(kv.k0) +
+                      paged_row_offset(page, which, h, j % PAGE_TOKENS, KV_H, D);
+        }
+    }
+    return r;
+}
+
+// s[g] = sum_d q[g][d] * K[j][d] for the lane's token (q pre-scaled, in shared memory).
+template <int LAYOUT, int D, int G>
+__device__ __forceinline__ void score_row(const RowRef<LAYOUT, D>& r, const float* __restrict__ qs,
+                                          float (&s)[G]) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) s[g] = 0.f;
+    if (r.codes == nullptr) return;
+    if (LAYOUT == ALLOYB_KV_F16) {
+        const uint4* p = reinterpret_cast<const uint4*>(r.codes);
+#pragma unroll 4
+        for (int i = 0; i < D / 8; ++i) {
+            const uint4 v = __ldg(p + i);
+            const __half2* h2 = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(h2[e]);
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    s[g] = fmaf(qs[g * D + i * 8 + 2 * e], f.x, s[g]);
+                    s[g] = fmaf(qs[g * D + i * 8 + 2 * e + 1], f.y, s[g]);
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int blk = 0; blk < D / 32; ++blk) {
+            float ks;
+            float part[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) part[g] = 0.f;
+            if (LAYOUT == ALLOYB_KV_Q8_SPLIT) {
+                ks = __half2float(__ldg(r.scales + blk));
+                const uint32_t* cw = reinterpret_cast<const uint32_t*>(r.codes + blk * 32);
+#pragma unroll
+                for (int w = 0; w < 8; ++w) {
+                    const uint32_t cv = __ldg(cw + w);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float c = static_cast<float>(static_cast<int8_t>((cv >> (8 * e)) & 0xffu));
+#pragma unroll
+                        for (int g = 0; g < G; ++g)
+                            part[g] = fmaf(qs[g * D + blk * 32 + w * 4 + e], c, part[g]);
+                    }
+                }
+            } else {
+                const uint16_t* bw = reinterpret_cast<const uint16_t*>(r.codes + blk * KV_BLOCK_BYTES);
+                ks = half_bits_to_f32(__ldg(bw));
+#pragma unroll
+                for (int w = 0; w < 16; ++w) {
+                    const uint32_t cv = __ldg(bw + 1 + w);
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const float c = static_cast<float>(static_cast<int8_t>((cv >> (8 * e)) & 0xffu));
+#pragma unroll
+                        for (int g = 0; g < G; ++g)
+                            part[g] = fmaf(qs[g * D + blk * 32 + w * 2 + e], c, part[g]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) s[g] = fmaf(ks, part[g], s[g]);
+        }
+    }
+}
+
+// Dequantised V values of token row r for this lane's DPL = D/32 consecutive dims.
+template <int LAYOUT, int D>
+__device__ __forceinline__ void load_v(const RowRef<LAYOUT, D>& r, int lane, float (&v)[D / 32]) {
+    constexpr int DPL = D / 32;
+    const int d0 = lane * DPL;
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) v[e] = 0.f;
+    if (r.codes == nullptr) return;
+    if (LAYOUT == ALLOYB_KV_F16) {
+        const __half* p = reinterpret_cast<const __half*>(r.codes) + d0;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) v[e] = __half2float(__ldg(p + e));
+    } else if (LAYOUT == ALLOYB_KV_Q8_SPLIT) {
+        const float s = __half2float(__ldg(r.scales + d0 / 32));
+        const int8_t* p = reinterpret_cast<const int8_t*>(r.codes) + d0;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) v[e] = s * static_cast<float>(__ldg(p + e));
+    } else {
+        const uint8_t* blk = r.codes + (d0 / 32) * KV_BLOCK_BYTES;
+        const float s = half_bits_to_f32(__ldg(reinterpret_cast<const uint16_t*>(blk)));
+        const int8_t* p = reinterpret_cast<const int8_t*>(blk + 2) + (d0 % 32);
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) v[e] = s * static_cast<float>(__ldg(p + e));
+    }
+}
+
+template <int LAYOUT, int D, int G>
+__global__ void __launch_bounds__(32) attn_decode_kernel(AttnParams P) {
+    constexpr int DPL = D / 32;
+    __shared__ float qs[G * D];
+    __shared__ int s_last;
+    const int lane = threadIdx.x;
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    pdl_wait();
+    int pos = P.pos[P.pos_count == 1 ? 0 : b];
+    if (pos >= P.kv.S_max) {
+        if (lane == 0 && P.status) atomicOr(P.status, KV_STATUS_POS_RANGE);
+        pos = P.kv.S_max - 1;
+    }
+    const int len = pos + 1;                  // positions [0, pos]; pos < 0 -> empty
+    for (int i = lane; i < G * D; i += 32) {
+        const int g = i / D, d = i - g * D;
+        qs[i] = load_q(P.q, P.q_dtype, b * P.q_bs + (kvh * G + g) * P.q_hs + d) * P.scale_log2;
+    }
+    __syncwarp();
+
+    int chunk = (len + P.splits - 1) / P.splits;
+    chunk = (chunk + 31) & ~31;
+    const int t0 = split * chunk;
+    const int t1 = min(len, t0 + chunk);
+
+    float m[G], l[G], o[G][DPL];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = NEG_BIG;
+        l[g] = 0.f;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) o[g][e] = 0.f;
+    }
+
+    for (int c0 = t0; c0 < t1; c0 += 32) {
+        const int j = c0 + lane;
+        const bool valid = j < t1;
+        float s[G];
+        if (valid) {
+            const RowRef<LAYOUT, D> kr = row_ref<LAYOUT, D>(P.kv, 0, b, kvh, P.KV_H, j, P.status);
+            score_row<LAYOUT, D, G>(kr, qs, s);
+        }
+        float p[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float sv = valid ? s[g] : NEG_BIG;
+            const float mn = fmaxf(m[g], warp_max(sv));
+            const float alpha = exp2f(m[g] - mn);
+            p[g] = valid ? exp2f(sv - mn) : 0.f;
+            l[g] = l[g] * alpha + warp_sum(p[g]);
+            m[g] = mn;
+#pragma unroll
+            for (int e = 0; e < DPL; ++e) o[g][e] *= alpha;
+        }
+        const int cnt = min(32, t1 - c0);
+        for (int tt = 0; tt < cnt; ++tt) {
+            const RowRef<LAYOUT, D> vr = row_ref<LAYOUT, D>(P.kv, 1, b, kvh, P.KV_H, c0 + tt, nullptr);
+            float v[DPL];
+            load_v<LAYOUT, D>(vr, lane, v);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float pt = __shfl_sync(0xffffffffu, p[g], tt);
+#pragma unroll
+                for (int e = 0; e < DPL; ++e) o[g][e] = fmaf(pt, v[e], o[g][e]);
+            }
+        }
+    }
+
+    // partial out: normalised o and lse (log2 frame); empty ranges write lse = NEG_BIG
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const int h = kvh * G + g;
+        const int64_t pi = (static_cast<int64_t>(b) * P.H + h) * P.splits + split;
+        const float inv = l[g] > 0.f ? 1.0f / l[g] : 0.f;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) P.part_o[pi * D + lane * DPL + e] = o[g][e] * inv;
+        if (lane == 0) P.part_lse[pi] = l[g] > 0.f ? m[g] + log2f(l[g]) : NEG_BIG;
+    }
+
+    // last CTA of this (b, kv head) merges
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) {
+        const unsigned int prev = atomicAdd(P.counters + b * P.KV_H + kvh, 1u);
+        s_last = (prev == static_cast<unsigned int>(P.splits) - 1u);
+        if (s_last) P.counters[b * P.KV_H + kvh] = 0u;   // ready for the next call
+    }
+    __syncwarp();
+    if (!s_last) return;
+    __threadfence();
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const int h = kvh * G + g;
+        const int64_t base = (static_cast<int64_t>(b) * P.H + h) * P.splits;
+        float mx = NEG_BIG;
+        for (int s2 = 0; s2 < P.splits; ++s2) mx = fmaxf(mx, __ldcg(P.part_lse + base + s2));
+        float acc[DPL];
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) acc[e] = 0.f;
+        float wsum = 0.f;
+        for (int s2 = 0; s2 < P.splits; ++s2) {
+            const float lse = __ldcg(P.part_lse + base + s2);
+            if (lse <= 0.5f * NEG_BIG) continue;
+            const float w = exp2f(lse - mx);
+            wsum += w;
+#pragma unroll
+            for (int e = 0; e < DPL; ++e)
+                acc[e] = fmaf(w, __ldcg(P.part_o + (base + s2) * D + lane * DPL + e), acc[e]);
+        }
+        const float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e)
+            store_out(P.out, P.q_dtype, (static_cast<int64_t>(b) * P.H + h) * D + lane * DPL + e,
+                      acc[e] * inv);
+    }
+}
+
+template <int LAYOUT, int D>
+static int launch_attn_g(const AttnParams& P, int G, cudaStream_t st) {
+    dim3 grid(P.splits, P.KV_H, P.B);
+    switch (G) {
+        case 1: attn_decode_kernel<LAYOUT, D, 1><<<grid, 32, 0, st>>>(P); break;
+        case 2: attn_decode_kernel<LAYOUT, D, 2><<<grid, 32, 0, st>>>(P); break;
+        case 4: attn_decode_kernel<LAYOUT, D, 4><<<grid, 32, 0, st>>>(P); break;
+        case 8: attn_decode_kernel<LAYOUT, D, 8><<<grid, 32, 0, st>>>(P); break;
+        default: return ALLOYB_E_SHAPE;
+    }
+    return check_launch();
+}
+
+template <int LAYOUT>
+static int launch_attn_d(const AttnParams& P, int D, int G, cudaStream_t st) {
+    switch (D) {
+        case 64: return launch_attn_g<LAYOUT, 64>(P, G, st);
+        case 128: return launch_attn_g<LAYOUT, 128>(P, G, st);
+        case 256: return launch_attn_g<LAYOUT, 256>(P, G, st);
+        default: return ALLOYB_E_SHAPE;
+    }
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace alloyb
+
+using namespace alloyb;
+
+// workspace: [status word + counters | part_lse | part_o]
+extern "C" size_t alloyb_attn_workspace_bytes(int B, int H, int D) {
+    if (B <= 0 || H <= 0 || D <= 0) return 0;
+    const size_t bh = static_cast<size_t>(B) * H;
+    return align_up(256 + bh * sizeof(unsigned int), 256) +
+           align_up(bh * ATTN_MAX_SPLITS * sizeof(float), 256) +
+           align_up(bh * ATTN_MAX_SPLITS * D * sizeof(float), 256);
+}
+
+extern "C" int alloyb_attn_decode(int layout, const void* q, int64_t q_batch_stride,
+                                  int64_t q_head_stride, int q_dtype, void* k0, void* k1, void* v0,
+                                  void* v1, const void* new_k, const void* new_v,
+                                  int64_t new_batch_stride, int64_t new_head_stride,
+                                  const int32_t* pos, int pos_count, void* out, int B, int H, int KV_H,
+                                  int D, int S_max, int64_t num_pages, float scale, int write_kv,
+                                  void* workspace, size_t workspace_bytes, void* stream) {
+    if (!q || !k0 || !pos || !out || !workspace) return ALLOYB_E_NULL;
+    if (B <= 0 || H <= 0 || KV_H <= 0 || H % KV_H || D <= 0 || D % 32 || S_max <= 0)
+        return ALLOYB_E_SHAPE;
+    if (pos_count != 1 && pos_count != B) return ALLOYB_E_SHAPE;
+    if (q_dtype != ALLOYB_F16 && q_dtype != ALLOYB_BF16 && q_dtype != ALLOYB_F32) return ALLOYB_E_DTYPE;
+    if (layout == ALLOYB_KV_F16) { if (!v0) return ALLOYB_E_NULL; }
+    else if (layout == ALLOYB_KV_Q8_SPLIT) { if (!k1 || !v0 || !v1) return ALLOYB_E_NULL; }
+    else if (layout == ALLOYB_KV_Q8_PAGED) {
+        if (!k1) return ALLOYB_E_NULL;
+        if (S_max % PAGE_TOKENS || num_pages <= 0) return ALLOYB_E_SHAPE;
+    } else return ALLOYB_E_SHAPE;
+    if (write_kv && (!new_k || !new_v)) return ALLOYB_E_NULL;
+    if (reinterpret_cast<uintptr_t>(workspace) % 256) return ALLOYB_E_ALIGN;
+    if (workspace_bytes < alloyb_attn_workspace_bytes(B, H, D)) return ALLOYB_E_WORKSPACE;
+    cudaStream_t st = as_stream(stream);
+
+    AttnParams P;
+    P.q = q; P.q_bs = q_batch_stride; P.q_hs = q_head_stride; P.q_dtype = q_dtype;
+    P.kv.k0 = k0; P.kv.k1 = k1; P.kv.v0 = v0; P.kv.v1 = v1;
+    P.kv.S_max = S_max;
+    P.kv.max_pages = S_max / PAGE_TOKENS;
+    P.kv.num_pages = num_pages;
+    P.pos = pos; P.pos_count = pos_count; P.out = out;
+    P.B = B; P.H = H; P.KV_H = KV_H;
+    const float sc = scale > 0.f ? scale : 1.0f / sqrtf(static_cast<float>(D));
+    P.scale_log2 = sc * 1.4426950408889634f;
+    const size_t bh = static_cast<size_t>(B) * H;
+    char* ws = static_cast<char*>(workspace);
+    P.status = reinterpret_cast<int*>(ws);
+    P.counters = reinterpret_cast<unsigned int*>(ws + 256);
+    ws += align_up(256 + bh * sizeof(unsigned int), 256);
+    P.part_lse = reinterpret_cast<float*>(ws);
+    ws += align_up(bh * ATTN_MAX_SPLITS * sizeof(float), 256);
+    P.part_o = reinterpret_cast<float*>(ws);
+
+    // enough CTAs to fill the machine several times over, at least 64 tokens per split
+    const int ctas = B * KV_H;
+    int splits = (148 * 16 + ctas - 1) / ctas;
+    const int by_len = (S_max + 63) / 64;
+    if (splits > by_len) splits = by_len;
+    if (splits > ATTN_MAX_SPLITS) splits = ATTN_MAX_SPLITS;
+    if (splits < 1) splits = 1;
+    P.splits = splits;
+
+    if (write_kv) {
+        int rc = launch_kv_append(layout, new_k, new_v, new_batch_stride, new_head_stride, P.kv, pos,
+                                  pos_count, B, KV_H, D, P.status, st);
+        if (rc != ALLOYB_OK) return rc;
+    }
+    const int G = H / KV_H;
+    switch (layout) {
+        case ALLOYB_KV_F16: return launch_attn_d<ALLOYB_KV_F16>(P, D, G, st);
+        case ALLOYB_KV_Q8_SPLIT: return launch_attn_d<ALLOYB_KV_Q8_SPLIT>(P, D, G, st);
+        default: return launch_attn_d<ALLOYB_KV_Q8_PAGED>(P, D, G, st);
+    }
+}
+
+// Zero the status word and completion counters of a fresh workspace (once after allocation).
+extern "C" int alloyb_attn_workspace_init(void* workspace, size_t workspace_bytes, int B, int H,
+                                          void* stream) {
+    if (!workspace) return ALLOYB_E_NULL;
+    const size_t head = 256 + static_cast<size_t>(B) * H * sizeof(unsigned int);
+    if (workspace_bytes < head) return ALLOYB_E_WORKSPACE;
+    const cudaError_t e = cudaMemsetAsync(workspace, 0, head, as_stream(stream));
+    if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
+    return ALLOYB_OK;
+}
+
+// Device status word of the workspace (bit 0: position out of range, bit 1: page id out of
+// range; offending accesses were skipped).  Synchronises the stream.
+extern "C" int alloyb_attn_workspace_status(const void* workspace, int32_t* status_out, void* stream) {
+    if (!workspace || !status_out) return ALLOYB_E_NULL;
+    cudaError_t e = cudaMemcpyAsync(status_out, workspace, sizeof(int32_t), cudaMemcpyDeviceToHost,
+                                    as_stream(stream));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(as_stream(stream));
+    if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
+    return ALLOYB_OK;
+}

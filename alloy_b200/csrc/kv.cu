@@ -1,0 +1,191 @@
+// q8_0 KV cache: quantise-on-append (split tensors and paged 34-byte blocks) and dequantise.
+//
+// Arithmetic per 32-element block of one token/head, all in fp32 with IEEE
+// division and no contraction, so codes and scales are bit-identical to the
+// NumPy statement in the reference's test (tests/kernels/test_kv_quant.py:19-30):
+//   m = max|x|; scale = fp16(m / 127); inv = m > 0 ? 127 / m : 0;
+//   code = int8(sign(x*inv) * floor(|x*inv| + 0.5))
+#include "kv.cuh"
+
+namespace alloyb {
+
+struct Q8Block {
+    int code;
+    __half scale;
+};
+
+// All 32 lanes of a warp hold one element each of the same block.
+__device__ __forceinline__ Q8Block quantize_block_q8(float x) {
+    const float m = warp_max(fabsf(x));
+    const float inv = (m > 0.f) ? __fdiv_rn(127.0f, m) : 0.f;
+    const float q = __fmul_rn(x, inv);
+    const float mag = floorf(__fadd_rn(fabsf(q), 0.5f));
+    Q8Block r;
+    r.code = static_cast<int>(copysignf(mag, q));
+    r.scale = __float2half_rn(__fdiv_rn(m, 127.0f));
+    return r;
+}
+
+// Range quantise into the split layout; one warp per (b, h, token, block).
+__global__ void kv_quantize_range_kernel(const __half* __restrict__ src, int64_t sb, int64_t sh,
+                                         int64_t stok, int8_t* __restrict__ codes,
+                                         __half* __restrict__ scales, int B, int KV_H, int S_max,
+                                         int D, int start, int n_tokens) {
+    const int lane = threadIdx.x & 31;
+    const int nblk = D / 32;
+    const int64_t warps_total = static_cast<int64_t>(B) * KV_H * n_tokens * nblk;
+    const int64_t wid = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+    if (wid >= warps_total) return;
+    int64_t r = wid;
+    const int blk = static_cast<int>(r % nblk); r /= nblk;
+    const int t = static_cast<int>(r % n_tokens); r /= n_tokens;
+    const int h = static_cast<int>(r % KV_H); r /= KV_H;
+    const int b = static_cast<int>(r);
+    const float x = __half2float(src[b * sb + h * sh + t * stok + blk * 32 + lane]);
+    const Q8Block qb = quantize_block_q8(x);
+    const int64_t row = (static_cast<int64_t>(b) * KV_H + h) * S_max + (start + t);
+    codes[row * D + blk * 32 + lane] = static_cast<int8_t>(qb.code);
+    if (lane == 0) scales[row * nblk + blk] = qb.scale;
+}
+
+// One new token per sequence, any layout; one warp per (b, h, K|V, block).
+template <int LAYOUT>
+__global__ void kv_append_kernel(const __half* __restrict__ new_k, const __half* __restrict__ new_v,
+                                 int64_t sb, int64_t sh, KVPtrs kv, const int32_t* __restrict__ pos,
+                                 int pos_count, int B, int KV_H, int D, int* __restrict__ status) {
+    const int lane = threadIdx.x & 31;
+    const int nblk = D / 32;
+    const int64_t warps_total = static_cast<int64_t>(B) * KV_H * nblk * 2;
+    const int64_t wid = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+    if (wid >= warps_total) return;
+    pdl_wait();
+    int64_t r = wid;
+    const int which = static_cast<int>(r & 1); r >>= 1;
+    const int blk = static_cast<int>(r % nblk); r /= nblk;
+    const int h = static_cast<int>(r % KV_H); r /= KV_H;
+    const int b = static_cast<int>(r);
+    const int p = pos[pos_count == 1 ? 0 : b];
+    if (p < 0 || p >= kv.S_max) {
+        if (lane == 0 && status) atomicOr(status, KV_STATUS_POS_RANGE);
+        return;
+    }
+    const __half xin = (which ? new_v : new_k)[b * sb + h * sh + blk * 32 + lane];
+    if (LAYOUT == ALLOYB_KV_F16) {
+        __half* cache = static_cast<__half*>(which ? kv.v0 : kv.k0);
+        cache[((static_cast<int64_t>(b) * KV_H + h) * kv.S_max + p) * D + blk * 32 + lane] = xin;
+        return;
+    }
+    const Q8Block qb = quantize_block_q8(__half2float(xin));
+    if (LAYOUT == ALLOYB_KV_Q8_SPLIT) {
+        const int64_t row = (static_cast<int64_t>(b) * KV_H + h) * kv.S_max + p;
+        static_cast<int8_t*>(which ? kv.v0 : kv.k0)[row * D + blk * 32 + lane] =
+            static_cast<int8_t>(qb.code);
+        if (lane == 0) static_cast<__half*>(which ? kv.v1 : kv.k1)[row * nblk + blk] = qb.scale;
+    } else {
+        const int32_t* table = static_cast<const int32_t*>(kv.k1);
+        const int64_t page = table[static_cast<int64_t>(b) * kv.max_pages + p / PAGE_TOKENS];
+        if (page < 0 || page >= kv.num_pages) {
+            if (lane == 0 && status) atomicOr(status, KV_STATUS_PAGE_RANGE);
+            return;
+        }
+        uint8_t* dst = static_cast<uint8_t*>(kv.k0) +
+                       paged_row_offset(page, which, h, p % PAGE_TOKENS, KV_H, D) +
+                       blk * KV_BLOCK_BYTES;
+        if (lane == 0) *reinterpret_cast<__half*>(dst) = qb.scale;
+        reinterpret_cast<int8_t*>(dst + 2)[lane] = static_cast<int8_t>(qb.code);
+    }
+}
+
+__global__ void kv_dequant_kernel(const int8_t* __restrict__ codes, const __half* __restrict__ scales,
+                                  __half* __restrict__ out, int64_t rows_total, int S_max, int D,
+                                  int end) {
+    const int64_t total = rows_total * D;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t row = i / D;
+        if (static_cast<int>(row % S_max) >= end) continue;
+        const int c = static_cast<int>(i - row * D);
+        const float s = __half2float(scales[row * (D / 32) + c / 32]);
+        out[i] = __float2half_rn(__fmul_rn(static_cast<float>(codes[i]), s));
+    }
+}
+
+int launch_kv_append(int layout, const void* new_k, const void* new_v, int64_t sb, int64_t sh,
+                     const KVPtrs& kv, const int32_t* pos, int pos_count, int B, int KV_H, int D,
+                     int* status, cudaStream_t st) {
+    const __half* nk = static_cast<const __half*>(new_k);
+    const __half* nv = static_cast<const __half*>(new_v);
+    const int64_t warps = static_cast<int64_t>(B) * KV_H * (D / 32) * 2;
+    const int blocks = static_cast<int>((warps * 32 + 255) / 256);
+    switch (layout) {
+        case ALLOYB_KV_F16:
+            kv_append_kernel<ALLOYB_KV_F16><<<blocks, 256, 0, st>>>(nk, nv, sb, sh, kv, pos, pos_count,
+                                                                    B, KV_H, D, status);
+            break;
+        case ALLOYB_KV_Q8_SPLIT:
+            kv_append_kernel<ALLOYB_KV_Q8_SPLIT><<<blocks, 256, 0, st>>>(nk, nv, sb, sh, kv, pos,
+                                                                         pos_count, B, KV_H, D, status);
+            break;
+        case ALLOYB_KV_Q8_PAGED:
+            kv_append_kernel<ALLOYB_KV_Q8_PAGED><<<blocks, 256, 0, st>>>(nk, nv, sb, sh, kv, pos,
+                                                                         pos_count, B, KV_H, D, status);
+            break;
+        default:
+            return ALLOYB_E_SHAPE;
+    }
+    return check_launch();
+}
+
+}  // namespace alloyb
+
+using namespace alloyb;
+
+extern "C" int alloyb_kv_quantize_q8(const void* src, int64_t src_batch_stride,
+                                     int64_t src_head_stride, int64_t src_tok_stride, void* codes,
+                                     void* scales, int B, int KV_H, int S_max, int D, int start,
+                                     int n_tokens, void* stream) {
+    if (!src || !codes || !scales) return ALLOYB_E_NULL;
+    if (B <= 0 || KV_H <= 0 || S_max <= 0 || D <= 0 || D % 32) return ALLOYB_E_SHAPE;
+    if (n_tokens < 0 || start < 0 || start + n_tokens > S_max) return ALLOYB_E_SHAPE;
+    if (n_tokens == 0) return ALLOYB_OK;
+    const int64_t warps = static_cast<int64_t>(B) * KV_H * n_tokens * (D / 32);
+    const int64_t blocks = (warps * 32 + 255) / 256;
+    if (blocks > 0x7fffffff) return ALLOYB_E_SHAPE;
+    kv_quantize_range_kernel<<<static_cast<int>(blocks), 256, 0, as_stream(stream)>>>(
+        static_cast<const __half*>(src), src_batch_stride, src_head_stride, src_tok_stride,
+        static_cast<int8_t*>(codes), static_cast<__half*>(scales), B, KV_H, S_max, D, start, n_tokens);
+    return check_launch();
+}
+
+extern "C" int alloyb_kv_dequant_q8(const void* codes, const void* scales, void* out, int B, int KV_H,
+                                    int S_max, int D, int end, void* stream) {
+    if (!codes || !scales || !out) return ALLOYB_E_NULL;
+    if (B <= 0 || KV_H <= 0 || S_max <= 0 || D <= 0 || D % 32 || end < 0 || end > S_max)
+        return ALLOYB_E_SHAPE;
+    if (end == 0) return ALLOYB_OK;
+    const int64_t rows = static_cast<int64_t>(B) * KV_H * S_max;
+    const int64_t want = (rows * D + 255) / 256;
+    const int blocks = static_cast<int>(want < 148 * 32 ? want : 148 * 32);
+    kv_dequant_kernel<<<blocks, 256, 0, as_stream(stream)>>>(
+        static_cast<const int8_t*>(codes), static_cast<const __half*>(scales),
+        static_cast<__half*>(out), rows, S_max, D, end);
+    return check_launch();
+}
+
+extern "C" int alloyb_kv_append_q8_paged(const void* new_k, const void* new_v, int64_t batch_stride,
+                                         int64_t head_stride, void* pool, const int32_t* page_table,
+                                         int max_pages, int64_t num_pages, const int32_t* seq_pos,
+                                         int B, int KV_H, int D, int32_t* status, void* stream) {
+    if (!new_k || !new_v || !pool || !page_table || !seq_pos) return ALLOYB_E_NULL;
+    if (B <= 0 || KV_H <= 0 || D <= 0 || D % 32 || max_pages <= 0 || num_pages <= 0)
+        return ALLOYB_E_SHAPE;
+    KVPtrs kv;
+    kv.k0 = pool;
+    kv.k1 = const_cast<int32_t*>(page_table);
+    kv.v0 = kv.v1 = nullptr;
+    kv.S_max = max_pages * PAGE_TOKENS;
+    kv.max_pages = max_pages;
+    kv.num_pages = num_pages;
+    return launch_kv_append(ALLOYB_KV_Q8_PAGED, new_k, new_v, batch_stride, head_stride, kv, seq_pos,
+                            B, B, KV_H, D, status, as_stream(stream));
+}

@@ -1,0 +1,28 @@
+// Internal interfaces of the quantised-linear family.
+#pragma once
+#include "common.cuh"
+
+namespace alloyb {
+
+constexpr int MAX_SEGS = 4;            // weight matrices per launch (q/k/v + one spare)
+constexpr int ALLOYB_NOT_TAKEN = 1;    // a fast path declined the shape; use the row kernels
+
+struct WeightSeg {
+    int format;
+    int N;
+    const void* data;
+    const void* scales;
+    int64_t row_bytes;
+    void* y;
+    int64_t ldy;
+};
+
+// Tensor-core GEMV family / tcgen05 GEMM.  Return ALLOYB_NOT_TAKEN when the
+// shape, type or alignment is outside what they are built for.
+int try_linear_fast(const void* x, int M, int K, int dtype, const WeightSeg* seg, int n_seg,
+                    const void* residual, cudaStream_t st);
+int try_gated_fast(const void* x, const void* gate, const void* gate_scales, const void* up,
+                   const void* up_scales, void* y, int M, int N, int K, int format, int act,
+                   int dtype, cudaStream_t st);
+
+}  // namespace alloyb

@@ -1,0 +1,530 @@
+"""``torch.ops.alloy.*`` — the operator surface of the quantised-LLM hot path.
+
+The schemas are the ones the reference declares in
+``packages/alloy-torch/src/alloy_torch/custom_ops.py`` (``gguf_q4_k_mm`` :47-49,
+``batched_gguf_q4_k_mm`` :50-52, ``gguf_q4_k_silu`` / ``_gelu`` :53-58,
+``gguf_q4_k_embedding`` :67-69, ``gguf_q6_k_*`` :96-102, ``gguf_q8_0_*`` :103-111,
+``attention_cache`` :136-140, ``attention_cache_q8`` :144-150), so modules
+written against the reference call these unchanged.  The reference registers
+only ``Meta`` kernels and executes the ops on Metal through an FX handler
+table (``packages/alloy-torch/src/alloy_torch/ops/registry.py:280-330``); here
+each op has a ``CUDA`` kernel that calls the C ABI of ``liballoy_b200.so`` on
+the current stream, plus the same ``Meta`` shape functions.  There is no CPU
+implementation, as in the reference: a CPU call raises ``NotImplementedError``.
+
+Two ops have no reference schema: ``attention_cache_q8_paged`` (decode
+attention over the 16-token-paged pool of 34-byte q8_0 blocks) and
+``linear_residual`` (row-parallel projection with the residual add fused).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import math
+from collections.abc import Sequence
+
+import torch
+
+from . import _lib
+from ._lib import Weight, check
+
+_DTYPES = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
+
+lib = torch.library.Library("alloy", "DEF")
+
+lib.define("gguf_q4_k_mm(Tensor activations, Tensor blocks) -> Tensor")
+lib.define("batched_gguf_q4_k_mm(Tensor activations, Tensor[] blocks) -> Tensor[]")
+lib.define("gguf_q4_k_silu(Tensor activations, Tensor gate_blocks, Tensor up_blocks) -> Tensor")
+lib.define("gguf_q4_k_gelu(Tensor activations, Tensor gate_blocks, Tensor up_blocks) -> Tensor")
+lib.define("gguf_q4_k_embedding(Tensor input_ids, Tensor blocks) -> Tensor")
+lib.define("gguf_q6_k_mm(Tensor activations, Tensor packed_weights) -> Tensor")
+lib.define("gguf_q6_k_embedding(Tensor input_ids, Tensor packed_weights) -> Tensor")
+lib.define("batched_gguf_q6_k_mm(Tensor activations, Tensor[] packed_weights) -> Tensor[]")
+lib.define("gguf_q8_0_embedding(Tensor input_ids, Tensor qweight, Tensor scales) -> Tensor")
+lib.define("gguf_q8_0_mm(Tensor activations, Tensor qweight, Tensor scales) -> Tensor")
+lib.define("batched_gguf_q8_0_mm(Tensor activations, Tensor[] qweights, Tensor[] scales) -> Tensor[]")
+lib.define(
+    "gguf_q8_0_silu(Tensor activations, Tensor gate_qweight, Tensor gate_scales, "
+    "Tensor up_qweight, Tensor up_scales) -> Tensor"
+)
+lib.define(
+    "attention_cache(Tensor q, Tensor new_k, Tensor new_v, "
+    "Tensor cache_pos, Tensor k_cache, Tensor v_cache, float scale, "
+    "int sliding_window=0, bool write_kv=True, Tensor? last_real=None) -> Tensor"
+)
+lib.define(
+    "attention_cache_q8(Tensor q, Tensor new_k, Tensor new_v, "
+    "Tensor cache_pos, Tensor k_codes, Tensor k_scales, "
+    "Tensor v_codes, Tensor v_scales, "
+    "float scale=-1.0, int sliding_window=0, bool write_kv=True, "
+    "Tensor? last_real=None) -> Tensor"
+)
+# New ops (no reference schema).
+lib.define(
+    "attention_cache_q8_paged(Tensor q, Tensor new_k, Tensor new_v, Tensor seq_pos, "
+    "Tensor page_table, Tensor kv_pool, float scale=-1.0, bool write_kv=True) -> Tensor"
+)
+lib.define(
+    "linear_residual(Tensor activations, Tensor weight, Tensor? scales, Tensor residual, "
+    "str format) -> Tensor"
+)
+
+_FORMATS = {"q4_k": _lib.Q4_K, "q6_k": _lib.Q6_K, "q8_0": _lib.Q8_0}
+_BLOCK_BYTES = {_lib.Q4_K: 144, _lib.Q6_K: 210}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"activations must be float16, bfloat16 or float32, got {t.dtype}") from None
+
+
+def _k_of(fmt: int, w: torch.Tensor) -> int:
+    if w.ndim != 2:
+        raise ValueError(f"packed weight must be rank-2, got {tuple(w.shape)}")
+    if fmt == _lib.Q8_0:
+        if w.dtype != torch.int8:
+            raise TypeError(f"q8_0 qweight requires torch.int8, got {w.dtype}")
+        return w.shape[1]
+    if w.dtype != torch.uint8:
+        raise TypeError(f"packed blocks require torch.uint8, got {w.dtype}")
+    bb = _BLOCK_BYTES[fmt]
+    if w.shape[1] % bb:
+        raise ValueError(f"packed row of {w.shape[1]} bytes is not a whole number of {bb}-byte blocks")
+    return w.shape[1] // bb * 256
+
+
+def _check_acts(x: torch.Tensor, k: int) -> torch.Tensor:
+    if x.ndim != 2:
+        raise ValueError(f"activations must be (M, K), got {tuple(x.shape)}")
+    if x.shape[1] != k:
+        raise ValueError(f"activations K={x.shape[1]} does not match the weight's K={k}")
+    return x.contiguous()
+
+
+def _linear(x: torch.Tensor, fmt: int, weights: Sequence[torch.Tensor],
+            scales: Sequence[torch.Tensor] | None, residual: torch.Tensor | None = None):
+    """One launch for ``len(weights)`` sibling matrices of one format."""
+    if len(weights) == 0:
+        return []
+    k = _k_of(fmt, weights[0])
+    x = _check_acts(x, k)
+    m = x.shape[0]
+    outs = []
+    descs = (Weight * len(weights))()
+    keep = []
+    for i, w in enumerate(weights):
+        if _k_of(fmt, w) != k:
+            raise ValueError("batched matrices must share K")
+        w = w.contiguous()
+        y = torch.empty((m, w.shape[0]), dtype=x.dtype, device=x.device)
+        s_ptr = None
+        if fmt == _lib.Q8_0:
+            s = scales[i]
+            if s.dtype != torch.float16 or tuple(s.shape) != (w.shape[0], k // 32):
+                raise ValueError(f"q8_0 scales must be float16 {(w.shape[0], k // 32)}, "
+                                 f"got {s.dtype} {tuple(s.shape)}")
+            s = s.contiguous()
+            keep.append(s)
+            s_ptr = s.data_ptr()
+        keep.append(w)
+        descs[i] = Weight(fmt, w.shape[0], w.data_ptr(), s_ptr, 0, y.data_ptr(), 0)
+        outs.append(y)
+    r_ptr = None
+    if residual is not None:
+        residual = residual.contiguous()
+        if residual.shape != outs[0].shape or residual.dtype != x.dtype:
+            raise ValueError("residual must match the output's shape and dtype")
+        r_ptr = residual.data_ptr()
+    L = _lib.load()
+    check(L.alloyb_linear(x.data_ptr(), m, k, _dtype_code(x), descs, len(weights), r_ptr, _stream()),
+          "alloyb_linear")
+    return outs
+
+
+def linear_multi(x: torch.Tensor, specs: Sequence[tuple[str, torch.Tensor, torch.Tensor | None]]):
+    """Sibling projections of possibly different formats in ONE launch.
+
+    ``specs``: (format name, weight, scales-or-None) per matrix, all with the
+    same K.  Used for q/k/v where v is Q6_K while q and k are Q4_K.
+    """
+    fm0 = _FORMATS[specs[0][0]]
+    k = _k_of(fm0, specs[0][1])
+    x = _check_acts(x, k)
+    m = x.shape[0]
+    descs = (Weight * len(specs))()
+    outs = []
+    for i, (name, w, s) in enumerate(specs):
+        fmt = _FORMATS[name]
+        if _k_of(fmt, w) != k:
+            raise ValueError("matrices must share K")
+        y = torch.empty((m, w.shape[0]), dtype=x.dtype, device=x.device)
+        descs[i] = Weight(fmt, w.shape[0], w.data_ptr(), s.data_ptr() if s is not None else None, 0,
+                          y.data_ptr(), 0)
+        outs.append(y)
+    L = _lib.load()
+    check(L.alloyb_linear(x.data_ptr(), m, k, _dtype_code(x), descs, len(specs), None, _stream()),
+          "alloyb_linear")
+    return outs
+
+
+# ------------------------------------------------------------------------------- linear ops
+
+
+@torch.library.impl(lib, "gguf_q4_k_mm", "CUDA")
+def _q4k_mm(activations, blocks):
+    return _linear(activations, _lib.Q4_K, [blocks], None)[0]
+
+
+@torch.library.impl(lib, "gguf_q6_k_mm", "CUDA")
+def _q6k_mm(activations, packed_weights):
+    return _linear(activations, _lib.Q6_K, [packed_weights], None)[0]
+
+
+@torch.library.impl(lib, "gguf_q8_0_mm", "CUDA")
+def _q8_mm(activations, qweight, scales):
+    return _linear(activations, _lib.Q8_0, [qweight], [scales])[0]
+
+
+@torch.library.impl(lib, "batched_gguf_q4_k_mm", "CUDA")
+def _bq4k_mm(activations, blocks):
+    return _batched(activations, _lib.Q4_K, blocks, None)
+
+
+@torch.library.impl(lib, "batched_gguf_q6_k_mm", "CUDA")
+def _bq6k_mm(activations, packed_weights):
+    return _batched(activations, _lib.Q6_K, packed_weights, None)
+
+
+@torch.library.impl(lib, "batched_gguf_q8_0_mm", "CUDA")
+def _bq8_mm(activations, qweights, scales):
+    return _batched(activations, _lib.Q8_0, qweights, scales)
+
+
+def _batched(x, fmt, ws, ss, group: int = 4):
+    out = []
+    for i in range(0, len(ws), group):
+        out += _linear(x, fmt, ws[i:i + group], ss[i:i + group] if ss is not None else None)
+    return out
+
+
+@torch.library.impl(lib, "linear_residual", "CUDA")
+def _linear_residual(activations, weight, scales, residual, format):
+    fmt = _FORMATS[format]
+    return _linear(activations, fmt, [weight], [scales] if scales is not None else None, residual)[0]
+
+
+def _gated(x, gate, gs, up, us, fmt, act):
+    k = _k_of(fmt, gate)
+    if _k_of(fmt, up) != k or gate.shape[0] != up.shape[0]:
+        raise ValueError("gate and up must have the same shape")
+    x = _check_acts(x, k)
+    gate, up = gate.contiguous(), up.contiguous()
+    y = torch.empty((x.shape[0], gate.shape[0]), dtype=x.dtype, device=x.device)
+    L = _lib.load()
+    check(L.alloyb_gated_linear(x.data_ptr(), gate.data_ptr(), gs.data_ptr() if gs is not None else None,
+                                up.data_ptr(), us.data_ptr() if us is not None else None,
+                                y.data_ptr(), x.shape[0], gate.shape[0], k, fmt, act,
+                                _dtype_code(x), _stream()), "alloyb_gated_linear")
+    return y
+
+
+@torch.library.impl(lib, "gguf_q4_k_silu", "CUDA")
+def _q4k_silu(activations, gate_blocks, up_blocks):
+    return _gated(activations, gate_blocks, None, up_blocks, None, _lib.Q4_K, _lib.ACT_SILU)
+
+
+@torch.library.impl(lib, "gguf_q4_k_gelu", "CUDA")
+def _q4k_gelu(activations, gate_blocks, up_blocks):
+    return _gated(activations, gate_blocks, None, up_blocks, None, _lib.Q4_K, _lib.ACT_GELU_TANH)
+
+
+@torch.library.impl(lib, "gguf_q8_0_silu", "CUDA")
+def _q8_silu(activations, gate_qweight, gate_scales, up_qweight, up_scales):
+    return _gated(activations, gate_qweight, gate_scales.contiguous(), up_qweight,
+                  up_scales.contiguous(), _lib.Q8_0, _lib.ACT_SILU)
+
+
+# ------------------------------------------------------------------------------- embeddings
+
+
+def _embedding(ids: torch.Tensor, fmt: int, w: torch.Tensor, scales: torch.Tensor | None,
+               out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    k = _k_of(fmt, w)
+    w = w.contiguous()
+    flat = ids.reshape(-1).to(torch.int64).contiguous()
+    out = torch.empty((flat.numel(), k), dtype=out_dtype, device=w.device)
+    L = _lib.load()
+    if fmt == _lib.Q4_K:
+        rc = L.alloyb_dequant_q4k(w.data_ptr(), flat.data_ptr(), out.data_ptr(), flat.numel(),
+                                  w.shape[0], k, _DTYPES[out_dtype], _stream())
+    elif fmt == _lib.Q6_K:
+        rc = L.alloyb_dequant_q6k(w.data_ptr(), flat.data_ptr(), out.data_ptr(), flat.numel(),
+                                  w.shape[0], k, _DTYPES[out_dtype], _stream())
+    else:
+        scales = scales.contiguous()
+        rc = L.alloyb_dequant_q8_0(w.data_ptr(), scales.data_ptr(), flat.data_ptr(), out.data_ptr(),
+                                   flat.numel(), w.shape[0], k, _DTYPES[out_dtype], _stream())
+    check(rc, "alloyb_dequant")
+    return out.reshape(tuple(ids.shape) + (k,))
+
+
+@torch.library.impl(lib, "gguf_q4_k_embedding", "CUDA")
+def _q4k_emb(input_ids, blocks):
+    return _embedding(input_ids, _lib.Q4_K, blocks, None)
+
+
+@torch.library.impl(lib, "gguf_q6_k_embedding", "CUDA")
+def _q6k_emb(input_ids, packed_weights):
+    return _embedding(input_ids, _lib.Q6_K, packed_weights, None)
+
+
+@torch.library.impl(lib, "gguf_q8_0_embedding", "CUDA")
+def _q8_emb(input_ids, qweight, scales):
+    return _embedding(input_ids, _lib.Q8_0, qweight, scales)
+
+
+def dequantize(fmt: str, w: torch.Tensor, scales: torch.Tensor | None = None,
+               out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Decode a whole packed matrix on the device (test hook; bit-exact fp32)."""
+    code = _FORMATS[fmt]
+    k = _k_of(code, w)
+    w = w.contiguous()
+    out = torch.empty((w.shape[0], k), dtype=out_dtype, device=w.device)
+    L = _lib.load()
+    if code == _lib.Q4_K:
+        rc = L.alloyb_dequant_q4k(w.data_ptr(), None, out.data_ptr(), w.shape[0], w.shape[0], k,
+                                  _DTYPES[out_dtype], _stream())
+    elif code == _lib.Q6_K:
+        rc = L.alloyb_dequant_q6k(w.data_ptr(), None, out.data_ptr(), w.shape[0], w.shape[0], k,
+                                  _DTYPES[out_dtype], _stream())
+    else:
+        scales = scales.contiguous()
+        rc = L.alloyb_dequant_q8_0(w.data_ptr(), scales.data_ptr(), None, out.data_ptr(), w.shape[0],
+                                   w.shape[0], k, _DTYPES[out_dtype], _stream())
+    check(rc, "alloyb_dequant")
+    return out
+
+
+# ------------------------------------------------------------------------------- attention
+
+_workspaces: dict[tuple[int, int, int, int], torch.Tensor] = {}
+
+
+def attn_workspace(device: torch.device, b: int, h: int, d: int) -> torch.Tensor:
+    """Cached, initialised split-K workspace for (device, B, H, D).
+
+    One workspace serves every call of that shape on the device; calls that
+    may overlap on the GPU (different streams) need workspaces of their own
+    (``new_attn_workspace``).
+    """
+    key = (device.index if device.index is not None else torch.cuda.current_device(), b, h, d)
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = new_attn_workspace(device, b, h, d)
+        _workspaces[key] = ws
+    return ws
+
+
+def new_attn_workspace(device: torch.device, b: int, h: int, d: int) -> torch.Tensor:
+    L = _lib.load()
+    n = L.alloyb_attn_workspace_bytes(b, h, d)
+    ws = torch.empty(n, dtype=torch.uint8, device=device)
+    check(L.alloyb_attn_workspace_init(ws.data_ptr(), n, b, h, _stream()), "alloyb_attn_workspace_init")
+    return ws
+
+
+def attn_status(ws: torch.Tensor) -> int:
+    """Device status word of a workspace (0 = every position/page was in range)."""
+    L = _lib.load()
+    out = C.c_int32(0)
+    check(L.alloyb_attn_workspace_status(ws.data_ptr(), C.byref(out), _stream()),
+          "alloyb_attn_workspace_status")
+    return int(out.value)
+
+
+def _pos_i32(pos: torch.Tensor) -> torch.Tensor:
+    if pos.dtype != torch.int32:
+        pos = pos.to(torch.int32)
+    return pos.contiguous()
+
+
+def _decode_attention(layout, q, new_k, new_v, pos, k0, k1, v0, v1, s_max, num_pages, scale,
+                      write_kv, workspace=None):
+    if q.ndim != 4:
+        raise ValueError(f"attention expects 4D Q (B, H, S, D), got {q.ndim}D")
+    b, h, s, d = q.shape
+    if d % 32 != 0:
+        raise ValueError(f"attention needs head_dim % 32 == 0, got {d}")
+    if s != 1:
+        raise NotImplementedError(
+            "only the decode step (one query token per sequence) is implemented; "
+            f"got seq_len={s}")
+    kv_h = new_k.shape[1]
+    if q.stride(3) != 1:
+        q = q.contiguous()
+    for name, t in (("new_k", new_k), ("new_v", new_v)):
+        if t.dtype != torch.float16:
+            raise TypeError(f"{name} must be float16, got {t.dtype}")
+        if tuple(t.shape) != (b, kv_h, 1, d):
+            raise ValueError(f"{name} must be {(b, kv_h, 1, d)}, got {tuple(t.shape)}")
+    if new_k.stride(3) != 1 or new_v.stride(3) != 1 or new_k.stride() != new_v.stride():
+        new_k, new_v = new_k.contiguous(), new_v.contiguous()
+    out = torch.empty((b, 1, h, d), dtype=q.dtype, device=q.device)
+    ws = workspace if workspace is not None else attn_workspace(q.device, b, h, d)
+    L = _lib.load()
+    check(L.alloyb_attn_decode(
+        layout, q.data_ptr(), q.stride(0), q.stride(1), _dtype_code(q),
+        k0.data_ptr(), k1.data_ptr() if k1 is not None else None,
+        v0.data_ptr() if v0 is not None else None, v1.data_ptr() if v1 is not None else None,
+        new_k.data_ptr(), new_v.data_ptr(), new_k.stride(0), new_k.stride(1),
+        pos.data_ptr(), pos.numel(), out.data_ptr(), b, h, kv_h, d, s_max, num_pages,
+        float(scale) if scale is not None else -1.0, 1 if write_kv else 0,
+        ws.data_ptr(), ws.numel(), _stream()), "alloyb_attn_decode")
+    return out.transpose(1, 2)
+
+
+def _norm_scale(scale, d):
+    default = 1.0 / math.sqrt(d)
+    if scale is None or scale <= 0 or math.isclose(float(scale), default, rel_tol=1e-6, abs_tol=1e-6):
+        return -1.0
+    return float(scale)
+
+
+def _no_window(sliding_window, last_real):
+    if sliding_window:
+        raise NotImplementedError("sliding-window ring caches are outside this build's scope")
+
+
+@torch.library.impl(lib, "attention_cache", "CUDA")
+def _attention_cache(q, new_k, new_v, cache_pos, k_cache, v_cache, scale, sliding_window=0,
+                     write_kv=True, last_real=None):
+    _no_window(sliding_window, last_real)
+    if k_cache.dtype != torch.float16 or v_cache.dtype != torch.float16:
+        raise TypeError("attention_cache expects float16 K/V caches")
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError("K/V caches must be contiguous (B, KV_H, S, D)")
+    pos = _pos_i32(cache_pos.reshape(-1)[:1])
+    return _decode_attention(_lib.KV_F16, q, new_k, new_v, pos, k_cache, None, v_cache, None,
+                             k_cache.shape[2], 0, _norm_scale(scale, q.shape[-1]), write_kv)
+
+
+@torch.library.impl(lib, "attention_cache_q8", "CUDA")
+def _attention_cache_q8(q, new_k, new_v, cache_pos, k_codes, k_scales, v_codes, v_scales,
+                        scale=-1.0, sliding_window=0, write_kv=True, last_real=None):
+    _no_window(sliding_window, last_real)
+    for t, dt in ((k_codes, torch.int8), (v_codes, torch.int8), (k_scales, torch.float16),
+                  (v_scales, torch.float16)):
+        if t.dtype != dt or not t.is_contiguous():
+            raise TypeError("q8 cache tensors must be contiguous int8 codes / float16 scales")
+    pos = _pos_i32(cache_pos.reshape(-1)[:1])
+    return _decode_attention(_lib.KV_Q8_SPLIT, q, new_k, new_v, pos, k_codes, k_scales, v_codes,
+                             v_scales, k_codes.shape[2], 0, _norm_scale(scale, q.shape[-1]), write_kv)
+
+
+@torch.library.impl(lib, "attention_cache_q8_paged", "CUDA")
+def _attention_cache_q8_paged(q, new_k, new_v, seq_pos, page_table, kv_pool, scale=-1.0,
+                              write_kv=True):
+    if kv_pool.dtype != torch.uint8 or not kv_pool.is_contiguous() or kv_pool.ndim != 5:
+        raise TypeError("kv_pool must be contiguous uint8 (pages, 2, KV_H, 16, D/32*34)")
+    if page_table.dtype != torch.int32 or not page_table.is_contiguous() or page_table.ndim != 2:
+        raise TypeError("page_table must be contiguous int32 (B, max_pages)")
+    if page_table.shape[0] != q.shape[0]:
+        raise ValueError("page_table needs one row per sequence")
+    pos = _pos_i32(seq_pos.reshape(-1))
+    return _decode_attention(_lib.KV_Q8_PAGED, q, new_k, new_v, pos, kv_pool, page_table, None, None,
+                             page_table.shape[1] * 16, kv_pool.shape[0],
+                             _norm_scale(scale, q.shape[-1]), write_kv)
+
+
+# ------------------------------------------------------------------------------- Meta kernels
+# Same shape functions as the reference's Meta registrations
+# (packages/alloy-torch/src/alloy_torch/custom_ops.py:285-300, :666-673, :750-785).
+
+
+def _mm_meta(x, w):
+    return torch.empty((x.shape[0], w.shape[0]), dtype=x.dtype, device=x.device)
+
+
+torch.library.impl(lib, "gguf_q4_k_mm", "Meta")(lambda activations, blocks: _mm_meta(activations, blocks))
+torch.library.impl(lib, "gguf_q6_k_mm", "Meta")(
+    lambda activations, packed_weights: _mm_meta(activations, packed_weights))
+torch.library.impl(lib, "gguf_q8_0_mm", "Meta")(
+    lambda activations, qweight, scales: _mm_meta(activations, qweight))
+torch.library.impl(lib, "batched_gguf_q4_k_mm", "Meta")(
+    lambda activations, blocks: [_mm_meta(activations, w) for w in blocks])
+torch.library.impl(lib, "batched_gguf_q6_k_mm", "Meta")(
+    lambda activations, packed_weights: [_mm_meta(activations, w) for w in packed_weights])
+torch.library.impl(lib, "batched_gguf_q8_0_mm", "Meta")(
+    lambda activations, qweights, scales: [_mm_meta(activations, w) for w in qweights])
+torch.library.impl(lib, "gguf_q4_k_silu", "Meta")(
+    lambda activations, gate_blocks, up_blocks: _mm_meta(activations, gate_blocks))
+torch.library.impl(lib, "gguf_q4_k_gelu", "Meta")(
+    lambda activations, gate_blocks, up_blocks: _mm_meta(activations, gate_blocks))
+torch.library.impl(lib, "gguf_q8_0_silu", "Meta")(
+    lambda activations, gate_qweight, gate_scales, up_qweight, up_scales:
+    _mm_meta(activations, gate_qweight))
+torch.library.impl(lib, "linear_residual", "Meta")(
+    lambda activations, weight, scales, residual, format: torch.empty_like(residual))
+torch.library.impl(lib, "gguf_q4_k_embedding", "Meta")(
+    lambda input_ids, blocks: torch.empty(input_ids.shape + ((blocks.shape[1] // 144) * 256,),
+                                          dtype=torch.float32, device=input_ids.device))
+torch.library.impl(lib, "gguf_q6_k_embedding", "Meta")(
+    lambda input_ids, packed_weights: torch.empty(
+        input_ids.shape + ((packed_weights.shape[1] // 210) * 256,), dtype=torch.float32,
+        device=input_ids.device))
+torch.library.impl(lib, "gguf_q8_0_embedding", "Meta")(
+    lambda input_ids, qweight, scales: torch.empty(input_ids.shape + (qweight.shape[1],),
+                                                   dtype=torch.float32, device=input_ids.device))
+torch.library.impl(lib, "attention_cache", "Meta")(
+    lambda q, new_k, new_v, cache_pos, k_cache, v_cache, scale, sliding_window=0, write_kv=True,
+    last_real=None: torch.empty_like(q))
+torch.library.impl(lib, "attention_cache_q8", "Meta")(
+    lambda q, new_k, new_v, cache_pos, k_codes, k_scales, v_codes, v_scales, scale=-1.0,
+    sliding_window=0, write_kv=True, last_real=None: torch.empty_like(q))
+torch.library.impl(lib, "attention_cache_q8_paged", "Meta")(
+    lambda q, new_k, new_v, seq_pos, page_table, kv_pool, scale=-1.0, write_kv=True:
+    torch.empty_like(q))
+
+
+# ------------------------------------------------------------------------------- glue
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    y = torch.empty_like(x2)
+    L = _lib.load()
+    check(L.alloyb_rms_norm(x2.data_ptr(), weight.data_ptr(), y.data_ptr(), x2.shape[0], x2.shape[1],
+                            float(eps), _dtype_code(x2), _stream()), "alloyb_rms_norm")
+    return y.reshape(x.shape)
+
+
+def rope_inplace(q: torch.Tensor, k: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor) -> None:
+    """Rotate-half RoPE on contiguous q (B,H,D) and k (B,KV_H,D) at pos (int32 (1,) or (B,))."""
+    b, h, d = q.shape
+    L = _lib.load()
+    check(L.alloyb_rope_inplace(q.data_ptr(), k.data_ptr(), pos.data_ptr(), pos.numel(),
+                                inv_freq.data_ptr(), b, h, k.shape[1], d, _dtype_code(q), _stream()),
+          "alloyb_rope_inplace")
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    y = torch.empty_like(gate)
+    L = _lib.load()
+    check(L.alloyb_silu_mul(gate.data_ptr(), up.data_ptr(), y.data_ptr(), gate.numel(),
+                            _dtype_code(gate), _stream()), "alloyb_silu_mul")
+    return y
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    m, n = logits.shape
+    out = torch.empty((m,), dtype=torch.int64, device=logits.device)
+    L = _lib.load()
+    check(L.alloyb_argmax(logits.data_ptr(), out.data_ptr(), m, n, _dtype_code(logits), _stream()),
+          "alloyb_argmax")
+    return out

@@ -1,0 +1,202 @@
+/*
+ * alloy_b200 — C ABI of the B200 (sm_100a) quantised-LLM hot path.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the
+ * stream the caller passes (a cudaStream_t cast to void*; NULL = the legacy
+ * default stream), allocates nothing unless its comment says otherwise, never
+ * exits or aborts, and returns ALLOYB_OK (0) or a negative ALLOYB_E_* code
+ * (text via alloyb_error_string).  Shape and alignment problems are reported
+ * before anything is launched.
+ *
+ * Each declaration names the reference interface it stands in for; paths are
+ * relative to the rayanht/alloy checkout:
+ *   torch/  = packages/alloy-torch/src/alloy_torch/
+ *   metal/  = packages/alloy-metal/src/alloy/
+ *   server/ = packages/alloy-server/src/alloy_server/
+ */
+#ifndef ALLOY_B200_H
+#define ALLOY_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of activations / outputs */
+enum { ALLOYB_F16 = 0, ALLOYB_BF16 = 1, ALLOYB_F32 = 2 };
+/* weight formats */
+enum { ALLOYB_Q4_K = 0, ALLOYB_Q6_K = 1, ALLOYB_Q8_0 = 2 };
+/* gate activation of the fused gate/up op */
+enum { ALLOYB_ACT_SILU = 0, ALLOYB_ACT_GELU_TANH = 1 };
+/* KV cache layouts */
+enum { ALLOYB_KV_F16 = 0, ALLOYB_KV_Q8_SPLIT = 1, ALLOYB_KV_Q8_PAGED = 2 };
+
+enum {
+    ALLOYB_OK = 0,
+    ALLOYB_E_SHAPE = -1,      /* a dimension is not supported (message names it) */
+    ALLOYB_E_ALIGN = -2,      /* a pointer or row pitch misses the alignment the kernel needs */
+    ALLOYB_E_DTYPE = -3,
+    ALLOYB_E_NULL = -4,
+    ALLOYB_E_CUDA = -5,       /* a CUDA runtime call failed; see alloyb_last_cuda_error */
+    ALLOYB_E_WORKSPACE = -6,  /* caller-provided workspace too small */
+    ALLOYB_E_DEVICE = -7,     /* a bounded device-side wait ran out (status word set) */
+    ALLOYB_E_LIMIT = -8       /* a size exceeds a stated fixed maximum */
+};
+
+int alloyb_version(void);
+const char* alloyb_error_string(int code);
+/* cudaError_t of the most recent failed runtime call on this thread (0 if none). */
+int alloyb_last_cuda_error(void);
+/* 1 when the library was built for sm_100a and the current device is CC 10.x. */
+int alloyb_device_supported(void);
+
+/* ------------------------------------------------------------------ dequantisers / embeddings
+ * Bit-exact fp32 decode of packed rows.  ids == NULL decodes rows [0, n_rows);
+ * otherwise out row i = decode(row ids[i]) (ids int64).  Stand in for the
+ * embedding kernels metal/std/quant.py:836-884 (embedding_q4_k), :1201-1270
+ * (embedding_q6_k), :812-832 (embedding_q8_0) behind torch/custom_ops.py:67-69,
+ * :97-99, :103; also the test hook for the weight decode.
+ *   blocks: Q4_K (rows, K/256*144) u8; Q6_K (rows, K/256*210) u8.
+ *   Q8_0 takes the normalised pair: int8 (rows,K) + fp16 (rows,K/32).
+ *   out: (n_rows, K) fp32 (out_dtype F32) or fp16/bf16 (rounded once from fp32). */
+int alloyb_dequant_q4k(const void* blocks, const int64_t* ids, void* out, int64_t n_rows,
+                       int64_t table_rows, int K, int out_dtype, void* stream);
+int alloyb_dequant_q6k(const void* blocks, const int64_t* ids, void* out, int64_t n_rows,
+                       int64_t table_rows, int K, int out_dtype, void* stream);
+int alloyb_dequant_q8_0(const void* qweight, const void* scales, const int64_t* ids, void* out,
+                        int64_t n_rows, int64_t table_rows, int K, int out_dtype, void* stream);
+
+/* ------------------------------------------------------------------ quantised linear
+ * y[m,n] = sum_k x[m,k] * deq(W)[n,k], fp32 accumulate, y in the activation
+ * dtype.  One descriptor per weight matrix lets several sibling projections
+ * (q/k/v; mixed formats allowed) run as ONE launch, which is what the
+ * reference's batched ops do by concatenating rows
+ * (torch/ops/linalg.py:555-669, torch/custom_ops.py:50-52, :100-102, :106-108).
+ *
+ * M routing inside the library replaces torch/ops/linalg.py:462-497 (Q4_K),
+ * :726-739 (Q6_K), :346-401 (Q8_0): small M runs the bandwidth-bound
+ * dequant-GEMV family (metal/std/quant.py:1356-1453 dot_q4_k_v2, :2201-2277
+ * _rows, :1995-2126 dot_q6_k_v2, :61-273 dot_q8_0_v2); large M with bf16/fp16
+ * activations runs the tcgen05 dequant-GEMM (metal/std/quant.py:768-808
+ * dot_q4_k, :1949-1990 dot_q6_k and the load stage
+ * metal/_compiler/msl/memory.py:441-879). */
+typedef struct alloyb_weight {
+    int format;              /* ALLOYB_Q4_K / Q6_K / Q8_0 */
+    int N;                   /* output rows of this matrix */
+    const void* data;        /* Q4_K/Q6_K: packed blocks (N, row_bytes); Q8_0: int8 (N,K) */
+    const void* scales;      /* Q8_0: fp16 (N, K/32); else NULL */
+    int64_t row_bytes;       /* pitch of `data` rows in bytes; 0 = dense */
+    void* y;                 /* output (M, N) for this matrix, row pitch ldy elements */
+    int64_t ldy;             /* 0 = N */
+} alloyb_weight;
+
+/* Generic entry: n_w matrices sharing activations x (M,K).
+ * residual (may be NULL): same shape/pitch as y of matrix 0, added in the
+ * epilogue as dtype(residual + dtype(acc)); only with n_w == 1. */
+int alloyb_linear(const void* x, int M, int K, int dtype, const alloyb_weight* w, int n_w,
+                  const void* residual, void* stream);
+
+/* Convenience forms with the reference ops' argument order
+ * (torch/custom_ops.py:47-49 gguf_q4_k_mm, :96 gguf_q6_k_mm, :104 gguf_q8_0_mm). */
+int alloyb_q4k_mm(const void* x, const void* blocks, void* y, int M, int N, int K, int dtype,
+                  void* stream);
+int alloyb_q6k_mm(const void* x, const void* blocks, void* y, int M, int N, int K, int dtype,
+                  void* stream);
+int alloyb_q8_0_mm(const void* x, const void* qweight, const void* scales, void* y, int M, int N,
+                   int K, int dtype, void* stream);
+
+/* y = act(x*G^T) * (x*U^T), one launch sharing the activation load
+ * (torch/custom_ops.py:53-58 gguf_q4_k_silu/_gelu, :109-111 gguf_q8_0_silu;
+ * kernels metal/std/quant.py:1458-1723, :358-695; policy torch/ops/linalg.py:758-802).
+ * format is ALLOYB_Q4_K or ALLOYB_Q8_0 (scales NULL for Q4_K). */
+int alloyb_gated_linear(const void* x, const void* gate, const void* gate_scales, const void* up,
+                        const void* up_scales, void* y, int M, int N, int K, int format, int act,
+                        int dtype, void* stream);
+
+/* ------------------------------------------------------------------ q8_0 KV cache
+ * Quantise n_tokens rows per (batch, kv head) of fp16 `src` into the split
+ * cache tensors at positions [start, start+n_tokens): codes int8 (B,KV_H,S_max,D),
+ * scales fp16 (B,KV_H,S_max,D/32).  Strides of src in elements.
+ * Replaces kv_quantize_q8_range (metal/std/kv_quant.py:24-70). */
+int alloyb_kv_quantize_q8(const void* src, int64_t src_batch_stride, int64_t src_head_stride,
+                          int64_t src_tok_stride, void* codes, void* scales, int B, int KV_H,
+                          int S_max, int D, int start, int n_tokens, void* stream);
+/* fp16(code*scale) for positions [0, end) into scratch (B,KV_H,S_max,D) fp16.
+ * Replaces kv_dequant_q8_range (metal/std/kv_quant.py:73-108). */
+int alloyb_kv_dequant_q8(const void* codes, const void* scales, void* out, int B, int KV_H,
+                         int S_max, int D, int end, void* stream);
+
+/* Paged pool: uint8 (num_pages, 2 [K,V], KV_H, 16 tokens, D/32 blocks, 34 bytes);
+ * a block is fp16 scale + 32 int8 codes.  page_table int32 (B, max_pages).
+ * Appends one new token per sequence at position seq_pos[b] (int32 (B,)):
+ * new_k/new_v fp16 (B, KV_H, D) with the given strides (elements).
+ * No reference counterpart as a kernel of its own (the reference fuses the
+ * write into its attention kernel, metal/std/kv_quant.py:212-246); same
+ * arithmetic as kv_quantize_q8_range.  A position or page id outside the
+ * table is skipped, not written; when status (device int32, may be NULL) is
+ * given, bit 0 / bit 1 is set there for a bad position / page id. */
+int alloyb_kv_append_q8_paged(const void* new_k, const void* new_v, int64_t batch_stride,
+                              int64_t head_stride, void* pool, const int32_t* page_table,
+                              int max_pages, int64_t num_pages, const int32_t* seq_pos, int B,
+                              int KV_H, int D, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------ decode attention
+ * One query token per sequence, GQA (head h reads kv head h / (H/KV_H)),
+ * causal over positions [0, pos_b]; split-K partials merged with log-sum-exp.
+ * Replaces attention_decode_vector_split_q8 (metal/std/kv_quant.py:111-414),
+ * attention_decode_vector_split (metal/std/attention.py:2126-2363) and the
+ * combine kernels (metal/std/attention.py:2367-2410, :2657-2722) behind
+ * attention_cache_q8 / attention_cache (torch/custom_ops.py:136-150;
+ * handlers torch/ops/kv_quant.py:58-249, torch/ops/attention.py:886-1089).
+ *
+ * layout selects how k0..v1 are read:
+ *   ALLOYB_KV_F16      k0 = K (B,KV_H,S_max,D) fp16, v0 = V, k1 = v1 = NULL
+ *   ALLOYB_KV_Q8_SPLIT k0 = K codes int8 (B,KV_H,S_max,D), k1 = K scales fp16
+ *                      (B,KV_H,S_max,D/32), v0/v1 likewise
+ *   ALLOYB_KV_Q8_PAGED k0 = pool (see above), k1 = page_table int32 (B,max_pages),
+ *                      S_max = max_pages*16, v0 = v1 = NULL
+ * q: (B,H,D) with strides in elements, dtype f16/bf16/f32 (computed as fp16
+ * like the reference, torch/ops/kv_quant.py:175-180).  out: (B,H,D) dense in
+ * q's dtype.  pos: int32 (pos_count,) newest position per sequence; when
+ * pos_count == 1 every sequence uses pos[0] (the reference's cache_pos[:1]).
+ * write_kv != 0: new_k/new_v fp16 (B,KV_H,D) are first stored (quantised for
+ * the q8 layouts) at position pos_b, then attended, as the reference's fused
+ * WRITE_KV does.  scale <= 0 selects 1/sqrt(D).
+ * workspace: at least alloyb_attn_workspace_bytes(B,H,D) bytes, 256-aligned;
+ * it holds a status word, completion counters and the fp32 split partials,
+ * must be cleared once with alloyb_attn_workspace_init before its first use,
+ * and must not be shared by calls that may overlap on the device.  Positions
+ * or page ids outside the cache are skipped on the device and recorded in the
+ * status word (bit 0 position, bit 1 page id), read back with
+ * alloyb_attn_workspace_status (which synchronises the stream). */
+size_t alloyb_attn_workspace_bytes(int B, int H, int D);
+int alloyb_attn_workspace_init(void* workspace, size_t workspace_bytes, int B, int H, void* stream);
+int alloyb_attn_workspace_status(const void* workspace, int32_t* status_out, void* stream);
+int alloyb_attn_decode(int layout, const void* q, int64_t q_batch_stride, int64_t q_head_stride,
+                       int q_dtype, void* k0, void* k1, void* v0, void* v1, const void* new_k,
+                       const void* new_v, int64_t new_batch_stride, int64_t new_head_stride,
+                       const int32_t* pos, int pos_count, void* out, int B, int H, int KV_H, int D,
+                       int S_max, int64_t num_pages, float scale, int write_kv, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------ decode-step glue
+ * Small fp16/bf16 ops of the decode step (not graded kernels):
+ * rms_norm metal/std/norm.py:40-73 (normalise in fp32, cast, then multiply by
+ * the weight), rotate-half RoPE metal/std/rope.py:28-84 applied in place to
+ * q (B,H,D) and k (B,KV_H,D) at position pos_b with angle = float(pos)*inv_freq[j]
+ * (inv_freq fp32 (D/2,)), silu_mul
+ * metal/std/elementwise.py:40-43, greedy argmax of
+ * server/generation/decode.py:22-61. */
+int alloyb_rms_norm(const void* x, const void* weight, void* y, int M, int K, float eps, int dtype,
+                    void* stream);
+int alloyb_rope_inplace(void* q, void* k, const int32_t* pos, int pos_count, const float* inv_freq,
+                        int B, int H, int KV_H, int D, int dtype, void* stream);
+int alloyb_silu_mul(const void* gate, const void* up, void* y, int64_t n, int dtype, void* stream);
+int alloyb_argmax(const void* logits, int64_t* out_ids, int M, int N, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ALLOY_B200_H */

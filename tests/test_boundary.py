@@ -1,0 +1,125 @@
+"""CPU checks of the drop-in boundary: the shared library loads and exports every
+symbol the header declares, the op schemas equal the reference's, and host-side
+validation behaves like the reference's."""
+
+import pathlib
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import alloy_b200
+from alloy_b200 import _lib, kv, quant, synth
+
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+
+
+def _declared():
+    text = (ROOT / "include" / "alloy_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(alloyb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = _declared()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/alloy_b200.h but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert set(_lib.SIGNATURES) == set(names)
+    assert lib.alloyb_version() >= 1
+    assert lib.alloyb_error_string(-2).decode().startswith("pointer")
+
+
+def test_workspace_size_is_pure_arithmetic():
+    lib = _lib.load()
+    assert lib.alloyb_attn_workspace_bytes(0, 1, 1) == 0
+    a = lib.alloyb_attn_workspace_bytes(2, 32, 128)
+    assert a % 256 == 0 and a > 2 * 32 * 128 * 4
+
+
+HOT_OPS = ["gguf_q4_k_mm", "batched_gguf_q4_k_mm", "gguf_q4_k_silu", "gguf_q4_k_gelu",
+           "gguf_q4_k_embedding", "gguf_q6_k_mm", "gguf_q6_k_embedding", "batched_gguf_q6_k_mm",
+           "gguf_q8_0_embedding", "gguf_q8_0_mm", "batched_gguf_q8_0_mm", "gguf_q8_0_silu",
+           "attention_cache", "attention_cache_q8"]
+
+
+def test_op_schemas_match_reference_source():
+    src = pathlib.Path("/root/reference/packages/alloy-torch/src/alloy_torch/custom_ops.py")
+    if not src.exists():
+        pytest.skip("reference checkout not present")
+    text = src.read_text()
+    defs = {}
+    for m in re.finditer(r"_alloy_lib\.define\(\s*((?:\"[^\"]*\"\s*)+)\)", text):
+        schema = "".join(re.findall(r"\"([^\"]*)\"", m.group(1)))
+        defs[schema.split("(")[0]] = schema
+    for name in HOT_OPS:
+        ours = str(getattr(torch.ops.alloy, name).default._schema)
+        theirs = torch._C.parse_schema("alloy::" + defs[name])
+        assert ours == str(theirs), name
+
+
+def test_ops_have_no_cpu_kernel():
+    x = torch.zeros(1, 256, dtype=torch.float16)
+    w = torch.zeros(4, 144, dtype=torch.uint8)
+    with pytest.raises(NotImplementedError):
+        torch.ops.alloy.gguf_q4_k_mm(x, w)
+    assert torch.ops.alloy.gguf_q4_k_mm(x.to("meta"), w.to("meta")).shape == (1, 4)
+    ids = torch.zeros((2, 3), dtype=torch.int64, device="meta")
+    assert torch.ops.alloy.gguf_q6_k_embedding(ids, torch.zeros(4, 420, dtype=torch.uint8, device="meta")
+                                               ).shape == (2, 3, 512)
+    q = torch.zeros((2, 8, 1, 64), dtype=torch.float16, device="meta")
+    assert torch.ops.alloy.attention_cache_q8(q, q, q, q, q, q, q, q).shape == q.shape
+
+
+def test_validate_quant_buffers_errors():
+    blk = torch.zeros((8, 288), dtype=torch.uint8)
+    quant.GGUFQ4_KLinear(in_features=512, out_features=8, blocks=blk)
+    with pytest.raises(ValueError, match="not divisible"):
+        quant.GGUFQ4_KLinear(in_features=500, out_features=8, blocks=blk)
+    with pytest.raises(ValueError, match="shape"):
+        quant.GGUFQ4_KLinear(in_features=512, out_features=9, blocks=blk)
+    with pytest.raises(TypeError):
+        quant.GGUFQ6_KLinear(in_features=256, out_features=8, qweight=torch.zeros((8, 210), dtype=torch.int8))
+    with pytest.raises(ValueError, match="expects buffers"):
+        quant.GGUFQ8_0Linear(in_features=64, out_features=8, qweight=torch.zeros((8, 64), dtype=torch.int8))
+
+
+def test_split_q8_0_weight_matches_oracle():
+    from oracle import blocks as O
+    wire = synth.q8_0_wire(np.random.default_rng(0), 6, 96)
+    q, s = quant.split_q8_0_weight(weights=wire, in_features=96, out_features=6)
+    oc, osc = O.split_q8_0(wire)
+    assert np.array_equal(q.numpy(), oc) and np.array_equal(s.numpy().view(np.uint16), osc.view(np.uint16))
+    with pytest.raises(ValueError):
+        quant.split_q8_0_weight(weights=wire, in_features=64, out_features=6)
+    with pytest.raises(TypeError):
+        quant.split_q8_0_weight(weights=wire.astype(np.int8), in_features=96, out_features=6)
+
+
+def test_kv_format_and_page_pool_host_logic():
+    assert kv.resolve_kv_format("none") is None and kv.resolve_kv_format("q8_0") is kv.Q8_0
+    with pytest.raises(ValueError):
+        kv.resolve_kv_format("q4")
+    assert kv.Q8_0.scale_count_per_row(128) == 4 and kv.Q8_0.code_bytes_per_row(128) == 128
+    pool = kv.PagedKVPool(6, 2, 128, 2, 3, "cpu", free_order=[4, 1, 5, 0, 2, 3])
+    assert pool.pool.shape == (6, 2, 2, 16, 136) and pool.bytes_per_token() == 544
+    pool.reserve(0, 17)
+    pool.reserve(1, 1)
+    assert pool.pages_of(0) == [4, 1] and pool.pages_of(1) == [5]
+    assert pool.page_table.tolist() == [[4, 1, -1], [5, -1, -1]]
+    pool.reserve(0, 33)
+    assert pool.pages_of(0) == [4, 1, 0]
+    with pytest.raises(ValueError):
+        pool.reserve(0, 49)
+    pool.release(0)
+    assert pool.page_table[0].tolist() == [-1, -1, -1]
+    pool.reserve(1, 48)
+    assert pool.pages_of(1) == [5, 4, 1]
+    pool.reserve(0, 48)
+    assert pool.pages_of(0) == [0, 2, 3]
+    small = kv.PagedKVPool(2, 2, 128, 1, 3, "cpu")
+    with pytest.raises(MemoryError):
+        small.reserve(0, 48)

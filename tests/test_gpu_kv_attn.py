@@ -1,0 +1,242 @@
+"""GPU parity: q8_0 KV quantise/append (bit-exact) and decode attention (tolerance)
+vs the oracle, through torch.ops.alloy.* and the C ABI."""
+
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from alloy_b200 import _lib, kv, ops, synth
+from oracle import blocks as O
+from tests._util import assert_close, to_np
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def _quantize_range(src, codes, scales, start, n):
+    b, h, s_max, d = codes.shape
+    L = _lib.load()
+    _lib.check(L.alloyb_kv_quantize_q8(src.data_ptr(), src.stride(0), src.stride(1), src.stride(2),
+                                       codes.data_ptr(), scales.data_ptr(), b, h, s_max, d, start, n,
+                                       torch.cuda.current_stream().cuda_stream), "kv_quantize")
+
+
+def test_kv_quantize_golden_bit_exact(golden):
+    g = golden["kv_q8"]
+    h, s, d = g["k"].shape
+    for name in ("k", "v"):
+        src = _dev(g[name]).reshape(1, h, s, d)
+        codes = torch.full((1, h, 64, d), 99, dtype=torch.int8, device=DEV)
+        scales = torch.full((1, h, 64, d // 32), 7.0, dtype=torch.float16, device=DEV)
+        _quantize_range(src, codes, scales, 5, s)
+        assert np.array_equal(codes[0, :, 5:5 + s].cpu().numpy(), g[f"{name}_codes"])
+        assert np.array_equal(scales[0, :, 5:5 + s].cpu().numpy().view(np.uint16),
+                              g[f"{name}_scales"].view(np.uint16))
+        # rows outside [start, start+n) untouched
+        assert (codes[0, :, :5] == 99).all() and (codes[0, :, 5 + s:] == 99).all()
+        assert (scales[0, :, :5] == 7.0).all()
+
+
+def test_kv_quantize_seeded_strided_and_dequant():
+    rng = np.random.default_rng(3)
+    b, h, s, d = 2, 3, 37, 128
+    big = synth.kv_rows(rng, (b, s, h, d), 3.0)          # (B, S, H, D) storage, viewed (B, H, S, D)
+    big[0, 0, 0, :32] = 0
+    src = _dev(big).permute(0, 2, 1, 3)
+    codes = torch.zeros((b, h, 48, d), dtype=torch.int8, device=DEV)
+    scales = torch.zeros((b, h, 48, d // 32), dtype=torch.float16, device=DEV)
+    _quantize_range(src, codes, scales, 0, s)
+    rc, rs = O.kv_quantize_q8_0(big.transpose(0, 2, 1, 3))
+    assert np.array_equal(codes[:, :, :s].cpu().numpy(), rc)
+    assert np.array_equal(scales[:, :, :s].cpu().numpy().view(np.uint16), rs.view(np.uint16))
+    out = torch.zeros((b, h, 48, d), dtype=torch.float16, device=DEV)
+    L = _lib.load()
+    _lib.check(L.alloyb_kv_dequant_q8(codes.data_ptr(), scales.data_ptr(), out.data_ptr(), b, h, 48, d,
+                                      s, torch.cuda.current_stream().cuda_stream), "kv_dequant")
+    ref = O.kv_dequant_q8_0(rc, rs).astype(np.float16)
+    assert np.array_equal(out[:, :, :s].cpu().numpy().view(np.uint16), ref.view(np.uint16))
+    assert not out[:, :, s:].any()
+    # round-trip bound of the reference's test: |x - deq| <= d*(1/2 + 127*2^-11) + |x|*2^-10
+    x = big.transpose(0, 2, 1, 3).astype(np.float32)
+    dd = np.repeat(rs.astype(np.float32), 32, axis=-1)
+    assert (np.abs(x - ref.astype(np.float32)) <= dd * (0.5 + 127 * 2.0**-11) + np.abs(x) * 2.0**-10).all()
+
+
+def _ref_decode(k_rows, v_rows, q, pos_list, scale=None):
+    """k_rows/v_rows: per sequence (KV_H, S, D) fp32 dequantised; q (B,H,D)."""
+    return np.stack([O.attention_decode_ref(k_rows[b], v_rows[b], q[b], pos_list[b], scale)
+                     for b in range(q.shape[0])])
+
+
+@pytest.mark.parametrize("d,group,kv_h,s_max,pos", [(128, 4, 2, 512, 400), (64, 2, 2, 512, 400),
+                                                     (128, 1, 3, 256, 0), (256, 8, 1, 512, 511),
+                                                     (128, 4, 8, 2048, 2047)])
+def test_attention_cache_q8_fused_write(d, group, kv_h, s_max, pos):
+    rng = np.random.default_rng([d, group, pos])
+    b, h = 2, kv_h * group
+    hist_k = synth.kv_rows(rng, (b, kv_h, s_max, d), 2.0)
+    hist_v = synth.kv_rows(rng, (b, kv_h, s_max, d), 2.0)
+    kc, ks = O.kv_quantize_q8_0(hist_k)
+    vc, vs = O.kv_quantize_q8_0(hist_v)
+    new_k = synth.kv_rows(rng, (b, kv_h, 1, d), 2.0)
+    new_v = synth.kv_rows(rng, (b, kv_h, 1, d), 2.0)
+    q = synth.activations(rng, b * h, d).reshape(b, h, 1, d)
+    t = [_dev(a) for a in (kc, ks, vc, vs)]
+    out = torch.ops.alloy.attention_cache_q8(_dev(q), _dev(new_k), _dev(new_v),
+                                             torch.tensor([pos], device=DEV), *t)
+    assert out.shape == (b, h, 1, d) and out.dtype == torch.float16
+    # the write is bit-exact and only touches row `pos`
+    nkc, nks = O.kv_quantize_q8_0(new_k)
+    nvc, nvs = O.kv_quantize_q8_0(new_v)
+    kc2, ks2, vc2, vs2 = kc.copy(), ks.copy(), vc.copy(), vs.copy()
+    kc2[:, :, pos], ks2[:, :, pos] = nkc[:, :, 0], nks[:, :, 0]
+    vc2[:, :, pos], vs2[:, :, pos] = nvc[:, :, 0], nvs[:, :, 0]
+    for got, ref in zip(t, (kc2, ks2, vc2, vs2)):
+        assert np.array_equal(got.cpu().numpy().view(np.uint8), ref.view(np.uint8))
+    ref = _ref_decode(O.kv_dequant_q8_0(kc2, ks2), O.kv_dequant_q8_0(vc2, vs2), q[:, :, 0], [pos] * b)
+    assert np.abs(to_np(out)[:, :, 0] - ref).max() < 2e-3          # the reference test's bound
+    assert_close(to_np(out)[:, :, 0], ref, torch.float16, "attention_cache_q8")
+
+
+def test_attention_golden(golden):
+    g = golden["kv_q8"]
+    kv_h, s, d = g["k"].shape
+    pos, group = int(g["pos"]), int(g["group"])
+    t = [_dev(g[n][None]) for n in ("k_codes", "k_scales", "v_codes", "v_scales")]
+    q = _dev(g["q"]).reshape(1, kv_h * group, 1, d)
+    dummy = torch.zeros((1, kv_h, 1, d), dtype=torch.float16, device=DEV)
+    out = torch.ops.alloy.attention_cache_q8(q, dummy, dummy, torch.tensor([pos], device=DEV), *t,
+                                             write_kv=False)
+    assert np.abs(to_np(out)[0, :, 0] - g["attn"]).max() < 2e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_attention_cache_f16(dtype):
+    rng = np.random.default_rng(9)
+    b, kv_h, group, d, s_max, pos = 3, 2, 4, 128, 300, 257
+    h = kv_h * group
+    k = synth.kv_rows(rng, (b, kv_h, s_max, d))
+    v = synth.kv_rows(rng, (b, kv_h, s_max, d))
+    new_k = synth.kv_rows(rng, (b, 1, kv_h, d))
+    new_v = synth.kv_rows(rng, (b, 1, kv_h, d))
+    q = synth.activations(rng, b * h, d).reshape(b, h, 1, d)
+    kd, vd = _dev(k), _dev(v)
+    # new_k/new_v arrive as transposed views of (B, 1, KV_H, D), as the model produces them
+    out = torch.ops.alloy.attention_cache(_dev(q).to(dtype), _dev(new_k).transpose(1, 2),
+                                          _dev(new_v).transpose(1, 2),
+                                          torch.tensor([pos], device=DEV, dtype=torch.int64), kd, vd,
+                                          1.0 / np.sqrt(d))
+    k2, v2 = k.copy(), v.copy()
+    k2[:, :, pos], v2[:, :, pos] = new_k[:, 0], new_v[:, 0]
+    assert np.array_equal(kd.cpu().numpy().view(np.uint16), k2.view(np.uint16))
+    assert np.array_equal(vd.cpu().numpy().view(np.uint16), v2.view(np.uint16))
+    ref = _ref_decode(k2.astype(np.float32), v2.astype(np.float32), q[:, :, 0], [pos] * b)
+    assert out.dtype == dtype
+    assert_close(to_np(out)[:, :, 0], ref, dtype, "attention_cache f16")
+
+
+def _build_paged(rng, b, kv_h, d, lens, extra_pages=5):
+    """Random page placement; returns pool store, the oracle's per-sequence rows."""
+    pages_per = [(n + 1 + 15) // 16 for n in lens]
+    total = sum(pages_per) + extra_pages
+    order = rng.permutation(total).tolist()
+    store = kv.PagedKVPool(total, kv_h, d, b, max(pages_per), DEV, free_order=order)
+    host = np.zeros(tuple(store.pool.shape), np.uint8)
+    seq_rows = []
+    for s in range(b):
+        store.reserve(s, lens[s] + 1)
+        n_tok = pages_per[s] * 16
+        k = synth.kv_rows(rng, (kv_h, n_tok, d), 1.0)
+        v = synth.kv_rows(rng, (kv_h, n_tok, d), 1.0)
+        kc, ks = O.kv_quantize_q8_0(k)
+        vc, vs = O.kv_quantize_q8_0(v)
+        kraw, vraw = O.kv_pack_blocks(kc, ks), O.kv_pack_blocks(vc, vs)
+        for i, pg in enumerate(store.pages_of(s)):
+            host[pg, 0] = kraw[:, i * 16:(i + 1) * 16]
+            host[pg, 1] = vraw[:, i * 16:(i + 1) * 16]
+        seq_rows.append((kc, ks, vc, vs))
+    store.pool.copy_(torch.from_numpy(host))
+    return store, host, seq_rows
+
+
+@pytest.mark.parametrize("b,kv_h,group,d,lo,hi", [(4, 2, 4, 128, 1, 700), (3, 8, 4, 128, 900, 2100),
+                                                   (2, 1, 8, 64, 15, 17)])
+def test_attention_paged_q8(b, kv_h, group, d, lo, hi):
+    rng = np.random.default_rng([b, kv_h, hi])
+    h = kv_h * group
+    lens = rng.integers(lo, hi + 1, size=b).tolist()     # tokens already cached; new token at pos=len
+    store, host, seq_rows = _build_paged(rng, b, kv_h, d, lens)
+    new_k = synth.kv_rows(rng, (b, kv_h, 1, d))
+    new_v = synth.kv_rows(rng, (b, kv_h, 1, d))
+    q = synth.activations(rng, b * h, d).reshape(b, h, 1, d)
+    pos = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    out = torch.ops.alloy.attention_cache_q8_paged(_dev(q), _dev(new_k), _dev(new_v), pos,
+                                                   store.page_table, store.pool)
+    assert ops.attn_status(ops.attn_workspace(torch.device(DEV, 0), b, h, d)) == 0
+    nkc, nks = O.kv_quantize_q8_0(new_k)
+    nvc, nvs = O.kv_quantize_q8_0(new_v)
+    got_pool = store.pool.cpu().numpy()
+    k_rows, v_rows = [], []
+    for s in range(b):
+        kc, ks, vc, vs = (a.copy() for a in seq_rows[s])
+        p = lens[s]
+        kc[:, p], ks[:, p], vc[:, p], vs[:, p] = nkc[s, :, 0], nks[s, :, 0], nvc[s, :, 0], nvs[s, :, 0]
+        pg = store.pages_of(s)[p // 16]
+        host[pg, 0, :, p % 16] = O.kv_pack_blocks(nkc[s, :, 0], nks[s, :, 0])
+        host[pg, 1, :, p % 16] = O.kv_pack_blocks(nvc[s, :, 0], nvs[s, :, 0])
+        k_rows.append(O.kv_dequant_q8_0(kc, ks))
+        v_rows.append(O.kv_dequant_q8_0(vc, vs))
+    assert np.array_equal(got_pool, host)                 # append bit-exact, nothing else touched
+    # the oracle gathers pages to contiguous rows and runs the same attention math
+    s0 = 0
+    gathered = O.gather_pages(got_pool[:, 0], store.pages_of(s0), lens[s0] + 1)
+    gc, gs = O.kv_unpack_blocks(gathered)
+    assert np.array_equal(O.kv_dequant_q8_0(gc, gs), k_rows[s0][:, :lens[s0] + 1])
+    ref = _ref_decode(k_rows, v_rows, q[:, :, 0], lens)
+    assert np.abs(to_np(out)[:, :, 0] - ref).max() < 2e-3
+    assert_close(to_np(out)[:, :, 0], ref, torch.float16, "paged q8")
+
+
+def test_paged_append_entry_and_bad_page_is_skipped():
+    rng = np.random.default_rng(5)
+    b, kv_h, d = 2, 2, 128
+    store = kv.PagedKVPool(8, kv_h, d, b, 2, DEV)
+    store.reserve(0, 20)
+    store.reserve(1, 3)
+    new_k = _dev(synth.kv_rows(rng, (b, kv_h, d)))
+    new_v = _dev(synth.kv_rows(rng, (b, kv_h, d)))
+    pos = torch.tensor([19, 2], dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    L = _lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    args = (new_k.data_ptr(), new_v.data_ptr(), new_k.stride(0), new_k.stride(1), store.pool.data_ptr(),
+            store.page_table.data_ptr(), 2, 8, pos.data_ptr(), b, kv_h, d, status.data_ptr(), st)
+    _lib.check(L.alloyb_kv_append_q8_paged(*args), "append")
+    assert int(status.item()) == 0
+    kc, ks = O.kv_quantize_q8_0(new_k.cpu().numpy())
+    pg = store.pages_of(0)[1]
+    assert np.array_equal(store.pool[pg, 0, :, 3].cpu().numpy(), O.kv_pack_blocks(kc[0], ks[0]))
+    # sequence 1 asks for position 20 whose page is unmapped (-1): skipped, flagged, no fault
+    before = store.pool.clone()
+    pos2 = torch.tensor([19, 20], dtype=torch.int32, device=DEV)
+    args2 = args[:8] + (pos2.data_ptr(),) + args[9:]
+    _lib.check(L.alloyb_kv_append_q8_paged(*args2), "append")
+    assert int(status.item()) == 2
+    assert torch.equal(before[store.pages_of(1)[0]], store.pool[store.pages_of(1)[0]])
+
+
+def test_attention_argument_errors():
+    q = torch.zeros((1, 4, 1, 100), dtype=torch.float16, device=DEV)
+    z = torch.zeros((1, 2, 1, 100), dtype=torch.float16, device=DEV)
+    c = torch.zeros((1, 2, 8, 100), dtype=torch.int8, device=DEV)
+    s = torch.zeros((1, 2, 8, 3), dtype=torch.float16, device=DEV)
+    with pytest.raises(ValueError):
+        torch.ops.alloy.attention_cache_q8(q, z, z, torch.tensor([0], device=DEV), c, s, c, s)
+    with pytest.raises(ValueError):
+        torch.ops.alloy.attention_cache_q8(q[0], z, z, torch.tensor([0], device=DEV), c, s, c, s)

@@ -1,0 +1,187 @@
+"""GPU parity: dequantisers (bit-exact) and quantised linears (tolerance) vs the oracle,
+through torch.ops.alloy.* -> ctypes -> C ABI."""
+
+import numpy as np
+import pytest
+import torch
+
+from alloy_b200 import ops, quant, synth
+from oracle import blocks as O
+from tests._util import assert_close, same_bits_f32, to_np
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+# ------------------------------------------------------------------ dequant: bit-exact
+
+
+def test_dequant_golden_bit_exact(golden):
+    g = golden["q4k"]
+    for blk, w in ((g["blocks_signed"], g["w_signed"]), (g["blocks"], g["w"])):
+        got = ops.dequantize("q4_k", _dev(blk)).cpu().numpy()
+        assert same_bits_f32(got, w)
+    g6 = golden["q6k"]
+    assert same_bits_f32(ops.dequantize("q6_k", _dev(g6["blocks"])).cpu().numpy(), g6["w"])
+    g8 = golden["q8_0"]
+    codes, scales = O.split_q8_0(g8["wire"])
+    assert same_bits_f32(ops.dequantize("q8_0", _dev(codes), _dev(scales)).cpu().numpy(), g8["w"])
+
+
+@pytest.mark.parametrize("fmt,n,k", [("q4_k", 256, 4096), ("q6_k", 192, 4096), ("q4_k", 33, 2560),
+                                     ("q6_k", 17, 14336)])
+def test_dequant_seeded_bit_exact(fmt, n, k):
+    rng = np.random.default_rng(7)
+    if fmt == "q4_k":
+        blk = np.concatenate([synth.q4k_blocks(rng, n // 2 + 1, k), synth.q4k_blocks_signed(rng, n // 2, k)])
+        ref = O.dequant_q4_k(blk)
+    else:
+        blk = synth.q6k_blocks(rng, n, k)
+        ref = O.dequant_q6_k(blk)
+    got = ops.dequantize(fmt, _dev(blk)).cpu().numpy()
+    assert same_bits_f32(got, ref)
+    # bf16 output = the fp32 value rounded once
+    got_bf = ops.dequantize(fmt, _dev(blk), out_dtype=torch.bfloat16).cpu()
+    assert torch.equal(got_bf, torch.from_numpy(ref).to(torch.bfloat16))
+
+
+def test_embedding_ops():
+    rng = np.random.default_rng(8)
+    ids = torch.tensor([[3, 0], [31, 7]], device=DEV)
+    b4 = synth.q4k_blocks(rng, 32, 512)
+    e4 = torch.ops.alloy.gguf_q4_k_embedding(ids, _dev(b4))
+    assert e4.dtype == torch.float32 and e4.shape == (2, 2, 512)
+    assert same_bits_f32(e4.cpu().numpy().reshape(4, 512), O.dequant_q4_k(b4)[[3, 0, 31, 7]])
+    b6 = synth.q6k_blocks(rng, 32, 512)
+    e6 = torch.ops.alloy.gguf_q6_k_embedding(ids, _dev(b6))
+    assert same_bits_f32(e6.cpu().numpy().reshape(4, 512), O.dequant_q6_k(b6)[[3, 0, 31, 7]])
+    c8, s8 = O.split_q8_0(synth.q8_0_wire(rng, 32, 512))
+    e8 = torch.ops.alloy.gguf_q8_0_embedding(ids, _dev(c8), _dev(s8))
+    assert same_bits_f32(e8.cpu().numpy().reshape(4, 512), O.dequant_q8_0(c8, s8)[[3, 0, 31, 7]])
+
+
+# ------------------------------------------------------------------ linear: tolerance
+
+TORCH_DT = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
+
+
+def _weights(fmt, rng, n, k):
+    if fmt == "q4_k":
+        blk = synth.q4k_blocks(rng, n, k)
+        return (_dev(blk),), O.dequant_q4_k(blk)
+    if fmt == "q6_k":
+        blk = synth.q6k_blocks(rng, n, k)
+        return (_dev(blk),), O.dequant_q6_k(blk)
+    codes, scales = O.split_q8_0(synth.q8_0_wire(rng, n, k))
+    return (_dev(codes), _dev(scales)), O.dequant_q8_0(codes, scales)
+
+
+_MM = {"q4_k": lambda x, w: torch.ops.alloy.gguf_q4_k_mm(x, *w),
+       "q6_k": lambda x, w: torch.ops.alloy.gguf_q6_k_mm(x, *w),
+       "q8_0": lambda x, w: torch.ops.alloy.gguf_q8_0_mm(x, *w)}
+
+
+@pytest.mark.parametrize("fmt", ["q4_k", "q6_k", "q8_0"])
+@pytest.mark.parametrize("m,n,k,dt", [
+    (1, 4096, 4096, "f16"),        # config 0 shape
+    (1, 64, 2560, "f16"),          # the reference test's NB=10 tail case
+    (5, 64, 2560, "f32"),          # the reference's rows test (M=5, fp32 activations)
+    (4, 1000, 4096, "f16"), (16, 1024, 4096, "f16"), (32, 520, 2048, "f16"),
+    (3, 77, 512, "bf16"), (8, 4096, 14336, "f16"), (1, 1024, 8192, "bf16"),
+    (64, 256, 1024, "f16"),
+])
+def test_mm_matches_oracle(fmt, m, n, k, dt):
+    rng = np.random.default_rng([m, n, k, {'q4_k': 4, 'q6_k': 6, 'q8_0': 8}[fmt]])
+    w_dev, w = _weights(fmt, rng, n, k)
+    tdt = TORCH_DT[dt]
+    x = torch.from_numpy(synth.activations(rng, m, k, np.float32)).to(tdt)
+    y = _MM[fmt](x.to(DEV), w_dev)
+    assert y.shape == (m, n) and y.dtype == tdt
+    ref = O.mm_ref_f64(x.float().numpy(), w)
+    assert_close(to_np(y), ref, tdt, f"{fmt} m={m} n={n} k={k} {dt}")
+
+
+def test_q4k_mm_golden(golden):
+    g = golden["q4k"]
+    y = torch.ops.alloy.gguf_q4_k_mm(_dev(g["x"]), _dev(g["blocks"]))
+    assert_close(to_np(y), g["y"].astype(np.float64), torch.float16, "golden q4k")
+
+
+@pytest.mark.parametrize("m", [1, 3, 8])
+def test_batched_and_mixed(m):
+    rng = np.random.default_rng(21)
+    k = 2048
+    x = torch.from_numpy(synth.activations(rng, m, k)).to(DEV)
+    ws = [synth.q4k_blocks(rng, n, k) for n in (512, 128, 136, 40, 72)]
+    outs = torch.ops.alloy.batched_gguf_q4_k_mm(x, [_dev(w) for w in ws])
+    assert len(outs) == 5
+    for w, y in zip(ws, outs):
+        assert_close(to_np(y), O.mm_ref_f64(x.cpu().float().numpy(), O.dequant_q4_k(w)), torch.float16)
+    w6 = [synth.q6k_blocks(rng, n, k) for n in (128, 64)]
+    for w, y in zip(w6, torch.ops.alloy.batched_gguf_q6_k_mm(x, [_dev(w) for w in w6])):
+        assert_close(to_np(y), O.mm_ref_f64(x.cpu().float().numpy(), O.dequant_q6_k(w)), torch.float16)
+    w8 = [O.split_q8_0(synth.q8_0_wire(rng, n, k)) for n in (96, 32)]
+    outs8 = torch.ops.alloy.batched_gguf_q8_0_mm(x, [_dev(c) for c, _ in w8], [_dev(s) for _, s in w8])
+    for (c, s), y in zip(w8, outs8):
+        assert_close(to_np(y), O.mm_ref_f64(x.cpu().float().numpy(), O.dequant_q8_0(c, s)), torch.float16)
+    # q/k (Q4_K) + v (Q6_K) in one launch
+    mixed = ops.linear_multi(x, [("q4_k", _dev(ws[0]), None), ("q4_k", _dev(ws[1]), None),
+                                 ("q6_k", _dev(w6[0]), None)])
+    for y, wf in zip(mixed, (O.dequant_q4_k(ws[0]), O.dequant_q4_k(ws[1]), O.dequant_q6_k(w6[0]))):
+        assert_close(to_np(y), O.mm_ref_f64(x.cpu().float().numpy(), wf), torch.float16)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 14336, 4096), (4, 1024, 2560), (16, 512, 1024), (5, 64, 2560)])
+@pytest.mark.parametrize("act", ["silu", "gelu"])
+def test_q4k_gated(m, n, k, act):
+    rng = np.random.default_rng(31 + m)
+    g, u = synth.q4k_blocks(rng, n, k), synth.q4k_blocks(rng, n, k)
+    x = synth.activations(rng, m, k)
+    op = torch.ops.alloy.gguf_q4_k_silu if act == "silu" else torch.ops.alloy.gguf_q4_k_gelu
+    y = op(_dev(x), _dev(g), _dev(u))
+    gate = O.mm_ref_f64(x, O.dequant_q4_k(g))
+    up = O.mm_ref_f64(x, O.dequant_q4_k(u))
+    ref = (O.silu(gate) if act == "silu" else O.gelu_tanh(gate)) * up
+    assert_close(to_np(y), ref, torch.float16, f"gated {act} m={m}")
+
+
+def test_q8_gated():
+    rng = np.random.default_rng(41)
+    n, k, m = 256, 1024, 3
+    (gc, gs), (uc, us) = (O.split_q8_0(synth.q8_0_wire(rng, n, k)) for _ in range(2))
+    x = synth.activations(rng, m, k)
+    y = torch.ops.alloy.gguf_q8_0_silu(_dev(x), _dev(gc), _dev(gs), _dev(uc), _dev(us))
+    ref = O.silu(O.mm_ref_f64(x, O.dequant_q8_0(gc, gs))) * O.mm_ref_f64(x, O.dequant_q8_0(uc, us))
+    assert_close(to_np(y), ref, torch.float16, "q8 gated")
+
+
+def test_linear_residual():
+    rng = np.random.default_rng(51)
+    n, k, m = 512, 1024, 4
+    w = synth.q6k_blocks(rng, n, k)
+    x, r = synth.activations(rng, m, k), synth.activations(rng, m, n)
+    y = torch.ops.alloy.linear_residual(_dev(x), _dev(w), None, _dev(r), "q6_k")
+    lin = torch.from_numpy(O.mm_ref_f64(x, O.dequant_q6_k(w))).to(torch.float16).double().numpy()
+    assert_close(to_np(y), lin + r.astype(np.float64), torch.float16, "residual")
+
+
+def test_modules_and_errors():
+    rng = np.random.default_rng(61)
+    blk = synth.q4k_blocks(rng, 64, 512)
+    lin = quant.GGUFQ4_KLinear(in_features=512, out_features=64, blocks=torch.from_numpy(blk)).to(DEV)
+    x = torch.from_numpy(synth.activations(rng, 6, 512)).to(DEV).reshape(2, 3, 512)
+    y = lin(x)
+    assert y.shape == (2, 3, 64)
+    assert_close(to_np(y).reshape(6, 64),
+                 O.mm_ref_f64(x.cpu().float().numpy().reshape(6, 512), O.dequant_q4_k(blk)), torch.float16)
+    with pytest.raises(ValueError):
+        quant.GGUFQ4_KLinear(in_features=500, out_features=64, blocks=torch.from_numpy(blk))
+    with pytest.raises(TypeError):
+        quant.GGUFQ4_KLinear(in_features=512, out_features=64, blocks=torch.from_numpy(blk).to(torch.int8))
+    with pytest.raises(ValueError):
+        torch.ops.alloy.gguf_q4_k_mm(x.reshape(6, 512)[:, :256].contiguous(), lin.blocks)
+    assert torch.ops.alloy.gguf_q4_k_mm(x.reshape(6, 512)[:0], lin.blocks).shape == (0, 64)
