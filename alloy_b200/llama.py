@@ -1,0 +1,232 @@
+"""Llama-shape quantised decode step on the ``torch.ops.alloy`` surface.
+
+A thin harness, not a model zoo: it strings the hot-path ops together the way
+the reference's patched HF Llama forward does
+(``packages/alloy-server/src/alloy_server/models/attention.py:845-886`` for the
+attention block, ``packages/alloy-server/src/alloy_server/generation/decode.py:22-61``
+for the greedy next-token head) with the Q4_K_M tensor-type mix: Q4_K for
+q/k/o/gate/up and the token embedding, Q6_K for v/down and the output head.
+One decode step can be captured in a CUDA graph and replayed.
+
+Tensor parallelism (``tp_rank``/``tp_size``): q/k/v/gate/up and the head are
+split by output rows, o_proj/down by input columns on super-block boundaries;
+the row-parallel partial outputs are summed by ``all_reduce`` (NCCL) before the
+residual add.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import ops, synth
+
+
+@dataclass(frozen=True)
+class LlamaShape:
+    layers: int
+    hidden: int
+    ffn: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    vocab: int
+    rope_theta: float = 500000.0
+    eps: float = 1e-5
+
+    def weight_bytes(self) -> int:
+        """Packed bytes one decode step streams: every linear once, norms, no embedding table."""
+        q4 = lambda n, k: n * (k // 256) * 144
+        q6 = lambda n, k: n * (k // 256) * 210
+        hd = self.heads * self.head_dim
+        kvd = self.kv_heads * self.head_dim
+        layer = (q4(hd, self.hidden) + q4(kvd, self.hidden) + q6(kvd, self.hidden) +
+                 q4(self.hidden, hd) + 2 * q4(self.ffn, self.hidden) + q6(self.hidden, self.ffn))
+        norms = (2 * self.layers + 1) * self.hidden * 2
+        return layer * self.layers + q6(self.vocab, self.hidden) + norms
+
+
+LLAMA3_8B = LlamaShape(layers=32, hidden=4096, ffn=14336, heads=32, kv_heads=8, head_dim=128,
+                       vocab=128256)
+LLAMA3_70B = LlamaShape(layers=80, hidden=8192, ffn=28672, heads=64, kv_heads=8, head_dim=128,
+                        vocab=128256)
+
+
+def _slice_cols(blocks: torch.Tensor, block_bytes: int, rank: int, size: int) -> torch.Tensor:
+    """Row-parallel shard: super-blocks [rank*nb/size, (rank+1)*nb/size) of every row."""
+    n = blocks.shape[0]
+    nb = blocks.shape[1] // block_bytes
+    if nb % size:
+        raise ValueError(f"{nb} super-blocks per row do not split {size} ways")
+    per = nb // size
+    return blocks.view(n, nb, block_bytes)[:, rank * per:(rank + 1) * per].reshape(n, per * block_bytes).contiguous()
+
+
+class LayerWeights:
+    __slots__ = ("wq", "wk", "wv", "wo", "wg", "wu", "wd", "norm_in", "norm_post")
+
+
+class QuantLlamaDecoder:
+    """Random-init (seeded) Q4_K_M Llama-shape decoder for one decode step per call."""
+
+    def __init__(self, shape: LlamaShape, batch: int, context: int, *, device="cuda", seed: int = 0,
+                 kv: str = "f16", tp_rank: int = 0, tp_size: int = 1, process_group=None,
+                 dtype: torch.dtype = torch.float16, d_scale: float = 1.0) -> None:
+        if kv not in ("f16", "q8_paged"):
+            raise ValueError(f"kv must be 'f16' or 'q8_paged', got {kv!r}")
+        if shape.heads % tp_size or shape.kv_heads % tp_size or shape.ffn % (256 * tp_size) \
+                or (shape.heads * shape.head_dim) % (256 * tp_size) or shape.vocab % tp_size:
+            raise ValueError(f"shape does not shard {tp_size} ways")
+        self.shape, self.batch, self.context = shape, int(batch), int(context)
+        self.device, self.dtype, self.kv_kind = torch.device(device), dtype, kv
+        self.tp_rank, self.tp_size, self.pg = tp_rank, tp_size, process_group
+        s = shape
+        self.heads_l = s.heads // tp_size
+        self.kv_heads_l = s.kv_heads // tp_size
+        self.ffn_l = s.ffn // tp_size
+        self.vocab_l = s.vocab // tp_size
+        hd_l, kvd_l = self.heads_l * s.head_dim, self.kv_heads_l * s.head_dim
+
+        # every rank draws the FULL matrices from the same seed and keeps its shard, so the
+        # sharded model equals the unsharded one by construction
+        gen = torch.Generator(device=self.device)
+        gen.manual_seed(seed)
+        r, n = tp_rank, tp_size
+
+        def rows(t, per):
+            return t[r * per:(r + 1) * per].contiguous()
+
+        self.embed = synth.q4k_blocks_device(s.vocab, s.hidden, gen, self.device, d_scale)
+        self.layers: list[LayerWeights] = []
+        for _ in range(s.layers):
+            lw = LayerWeights()
+            lw.wq = rows(synth.q4k_blocks_device(s.heads * s.head_dim, s.hidden, gen, self.device, d_scale), hd_l)
+            lw.wk = rows(synth.q4k_blocks_device(s.kv_heads * s.head_dim, s.hidden, gen, self.device, d_scale), kvd_l)
+            lw.wv = rows(synth.q6k_blocks_device(s.kv_heads * s.head_dim, s.hidden, gen, self.device, d_scale), kvd_l)
+            lw.wo = _slice_cols(synth.q4k_blocks_device(s.hidden, s.heads * s.head_dim, gen, self.device, d_scale), 144, r, n)
+            lw.wg = rows(synth.q4k_blocks_device(s.ffn, s.hidden, gen, self.device, d_scale), self.ffn_l)
+            lw.wu = rows(synth.q4k_blocks_device(s.ffn, s.hidden, gen, self.device, d_scale), self.ffn_l)
+            lw.wd = _slice_cols(synth.q6k_blocks_device(s.hidden, s.ffn, gen, self.device, d_scale), 210, r, n)
+            lw.norm_in = self._norm_weight(gen)
+            lw.norm_post = self._norm_weight(gen)
+            self.layers.append(lw)
+        self.norm_final = self._norm_weight(gen)
+        self.head = rows(synth.q6k_blocks_device(s.vocab, s.hidden, gen, self.device, d_scale), self.vocab_l)
+        self.inv_freq = (1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, dtype=torch.float32) /
+                                                 s.head_dim))).to(self.device)
+        self._init_kv(gen)
+        # static step inputs/outputs (CUDA-graph friendly)
+        self.ids = torch.zeros(self.batch, dtype=torch.int64, device=self.device)
+        self.pos = torch.full((1,), self.context - 1, dtype=torch.int32, device=self.device)
+        self.seq_pos = torch.full((self.batch,), self.context - 1, dtype=torch.int32, device=self.device)
+        self.next_ids = torch.zeros(self.batch, dtype=torch.int64, device=self.device)
+        self.logits: torch.Tensor | None = None
+        self._graph: torch.cuda.CUDAGraph | None = None
+        self.launches_per_step = 0
+
+    def _norm_weight(self, gen) -> torch.Tensor:
+        w = torch.empty(self.shape.hidden, dtype=torch.float32, device=self.device)
+        w.normal_(0.0, 0.02, generator=gen).add_(1.0)
+        return w.to(self.dtype)
+
+    def _init_kv(self, gen) -> None:
+        s, b, ctx = self.shape, self.batch, self.context
+        full = (b, s.kv_heads, ctx, s.head_dim)
+        lo, hi = self.tp_rank * self.kv_heads_l, (self.tp_rank + 1) * self.kv_heads_l
+        self.k_cache, self.v_cache, self.pools = [], [], []
+        if self.kv_kind == "f16":
+            for _ in range(s.layers):
+                k = torch.empty(full, dtype=torch.float32, device=self.device).normal_(generator=gen)
+                v = torch.empty(full, dtype=torch.float32, device=self.device).normal_(generator=gen)
+                self.k_cache.append(k[:, lo:hi].to(torch.float16).contiguous())
+                self.v_cache.append(v[:, lo:hi].to(torch.float16).contiguous())
+                del k, v
+        else:
+            from .kv import PagedKVPool
+            pages_per = (ctx + 15) // 16
+            total = b * pages_per
+            order = torch.randperm(total, generator=torch.Generator().manual_seed(1234)).tolist()
+            table = None
+            for _ in range(s.layers):
+                pool = PagedKVPool(total, self.kv_heads_l, s.head_dim, b, pages_per, self.device,
+                                   page_table=table, free_order=order)
+                if table is None:
+                    for i in range(b):
+                        pool.reserve(i, ctx)
+                    table = pool.page_table
+                # random codes, scales ~ |N(0,1)| max / 127 magnitude
+                pool.pool.copy_(torch.randint(0, 256, pool.pool.shape, dtype=torch.uint8,
+                                              device=self.device, generator=gen))
+                blocks = pool.pool.view(-1, 34)
+                sc = torch.empty(blocks.shape[0], dtype=torch.float32, device=self.device).uniform_(
+                    0.015, 0.03, generator=gen).to(torch.float16)
+                blocks[:, 0:2] = sc.view(torch.uint8).view(-1, 2)
+                self.pools.append(pool)
+
+    # ------------------------------------------------------------------ one decode step
+
+    def _all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        if self.tp_size > 1:
+            torch.distributed.all_reduce(t, group=self.pg)
+        return t
+
+    def _step(self) -> None:
+        s, b = self.shape, self.batch
+        n0 = ops.launch_count()
+        h = ops._embedding(self.ids, 0, self.embed, None, out_dtype=self.dtype)
+        scale = 1.0 / (s.head_dim ** 0.5)
+        for li, lw in enumerate(self.layers):
+            xn = ops.rms_norm(h, lw.norm_in, s.eps)
+            q, k, v = ops.linear_multi(xn, [("q4_k", lw.wq, None), ("q4_k", lw.wk, None),
+                                            ("q6_k", lw.wv, None)])
+            q3 = q.view(b, self.heads_l, s.head_dim)
+            k3 = k.view(b, self.kv_heads_l, s.head_dim)
+            ops.rope_inplace(q3, k3, self.pos, self.inv_freq)
+            q4 = q3.unsqueeze(2)
+            k4 = k3.unsqueeze(2)
+            v4 = v.view(b, self.kv_heads_l, 1, s.head_dim)
+            if self.kv_kind == "f16":
+                a = torch.ops.alloy.attention_cache(q4, k4, v4, self.pos, self.k_cache[li],
+                                                    self.v_cache[li], scale)
+            else:
+                pool = self.pools[li]
+                a = torch.ops.alloy.attention_cache_q8_paged(q4, k4, v4, self.seq_pos, pool.page_table,
+                                                             pool.pool)
+            a2 = a.transpose(1, 2).reshape(b, self.heads_l * s.head_dim)
+            if self.tp_size == 1:
+                h = torch.ops.alloy.linear_residual(a2, lw.wo, None, h, "q4_k")
+            else:
+                h = h + self._all_reduce(torch.ops.alloy.gguf_q4_k_mm(a2, lw.wo))
+            xn = ops.rms_norm(h, lw.norm_post, s.eps)
+            act = torch.ops.alloy.gguf_q4_k_silu(xn, lw.wg, lw.wu)
+            if self.tp_size == 1:
+                h = torch.ops.alloy.linear_residual(act, lw.wd, None, h, "q6_k")
+            else:
+                h = h + self._all_reduce(torch.ops.alloy.gguf_q6_k_mm(act, lw.wd))
+        xn = ops.rms_norm(h, self.norm_final, s.eps)
+        logits = torch.ops.alloy.gguf_q6_k_mm(xn, self.head)
+        if self.tp_size > 1:
+            parts = [torch.empty_like(logits) for _ in range(self.tp_size)]
+            torch.distributed.all_gather(parts, logits, group=self.pg)
+            logits = torch.cat(parts, dim=1)
+        self.logits = logits
+        self.next_ids.copy_(ops.argmax(logits))
+        self.launches_per_step = ops.launch_count() - n0
+
+    def capture(self) -> None:
+        """Warm up once eagerly, then record the step into a CUDA graph."""
+        self._step()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._step()
+        self._graph = g
+
+    def step(self) -> torch.Tensor:
+        """Run one decode step on ``self.ids`` at ``self.pos``; returns ``self.next_ids``."""
+        if self._graph is not None:
+            self._graph.replay()
+        else:
+            self._step()
+        return self.next_ids

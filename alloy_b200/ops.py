@@ -73,7 +73,17 @@ _FORMATS = {"q4_k": _lib.Q4_K, "q6_k": _lib.Q6_K, "q8_0": _lib.Q8_0}
 _BLOCK_BYTES = {_lib.Q4_K: 144, _lib.Q6_K: 210}
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Number of C-ABI kernel-launching calls made so far (each launches 1-2 kernels)."""
+    return _launches
+
+
 def _stream() -> int:
+    global _launches
+    _launches += 1
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -115,6 +125,8 @@ def _linear(x: torch.Tensor, fmt: int, weights: Sequence[torch.Tensor],
     k = _k_of(fmt, weights[0])
     x = _check_acts(x, k)
     m = x.shape[0]
+    if m == 0:
+        return [x.new_empty((0, w.shape[0])) for w in weights]
     outs = []
     descs = (Weight * len(weights))()
     keep = []
@@ -157,6 +169,8 @@ def linear_multi(x: torch.Tensor, specs: Sequence[tuple[str, torch.Tensor, torch
     k = _k_of(fm0, specs[0][1])
     x = _check_acts(x, k)
     m = x.shape[0]
+    if m == 0:
+        return [x.new_empty((0, w.shape[0])) for _, w, _ in specs]
     descs = (Weight * len(specs))()
     outs = []
     for i, (name, w, s) in enumerate(specs):
@@ -226,6 +240,8 @@ def _gated(x, gate, gs, up, us, fmt, act):
     x = _check_acts(x, k)
     gate, up = gate.contiguous(), up.contiguous()
     y = torch.empty((x.shape[0], gate.shape[0]), dtype=x.dtype, device=x.device)
+    if x.shape[0] == 0:
+        return y
     L = _lib.load()
     check(L.alloyb_gated_linear(x.data_ptr(), gate.data_ptr(), gs.data_ptr() if gs is not None else None,
                                 up.data_ptr(), us.data_ptr() if us is not None else None,
@@ -259,6 +275,8 @@ def _embedding(ids: torch.Tensor, fmt: int, w: torch.Tensor, scales: torch.Tenso
     w = w.contiguous()
     flat = ids.reshape(-1).to(torch.int64).contiguous()
     out = torch.empty((flat.numel(), k), dtype=out_dtype, device=w.device)
+    if flat.numel() == 0:
+        return out.reshape(tuple(ids.shape) + (k,))
     L = _lib.load()
     if fmt == _lib.Q4_K:
         rc = L.alloyb_dequant_q4k(w.data_ptr(), flat.data_ptr(), out.data_ptr(), flat.numel(),

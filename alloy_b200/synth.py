@@ -91,27 +91,29 @@ def kv_rows(rng: np.random.Generator, shape, scale: float = 1.0) -> np.ndarray:
 # --------------------------------------------------------------------------- torch (device)
 
 
-def _uniform_f16_bytes(shape, gen: torch.Generator, device) -> torch.Tensor:
+def _uniform_f16_bytes(shape, gen: torch.Generator, device, d_scale: float = 1.0) -> torch.Tensor:
     d = torch.empty(shape, dtype=torch.float32, device=device).uniform_(D_LO, D_HI, generator=gen)
-    return d.to(torch.float16).view(torch.uint8)
+    return (d * d_scale).to(torch.float16).view(torch.uint8)
 
 
-def q4k_blocks_device(n: int, k: int, gen: torch.Generator, device="cuda") -> torch.Tensor:
-    """Device-side Q4_K blocks with the benchmark distribution."""
+def q4k_blocks_device(n: int, k: int, gen: torch.Generator, device="cuda",
+                      d_scale: float = 1.0) -> torch.Tensor:
+    """Device-side Q4_K blocks with the benchmark distribution (d, dmin times ``d_scale``)."""
     nb = _check_k(k)
     blk = torch.randint(0, 256, (n, nb, Q4K_BLOCK_BYTES), dtype=torch.uint8, device=device,
                         generator=gen)
-    blk[:, :, 0:2] = _uniform_f16_bytes((n, nb), gen, device).view(n, nb, 2)
-    blk[:, :, 2:4] = _uniform_f16_bytes((n, nb), gen, device).view(n, nb, 2)
+    blk[:, :, 0:2] = _uniform_f16_bytes((n, nb), gen, device, d_scale).view(n, nb, 2)
+    blk[:, :, 2:4] = _uniform_f16_bytes((n, nb), gen, device, d_scale).view(n, nb, 2)
     return blk.view(n, nb * Q4K_BLOCK_BYTES)
 
 
-def q6k_blocks_device(n: int, k: int, gen: torch.Generator, device="cuda") -> torch.Tensor:
-    """Device-side Q6_K blocks with the benchmark distribution."""
+def q6k_blocks_device(n: int, k: int, gen: torch.Generator, device="cuda",
+                      d_scale: float = 1.0) -> torch.Tensor:
+    """Device-side Q6_K blocks with the benchmark distribution (d times ``d_scale``)."""
     nb = _check_k(k)
     blk = torch.randint(0, 256, (n, nb, Q6K_BLOCK_BYTES), dtype=torch.uint8, device=device,
                         generator=gen)
-    blk[:, :, 208:210] = _uniform_f16_bytes((n, nb), gen, device).view(n, nb, 2)
+    blk[:, :, 208:210] = _uniform_f16_bytes((n, nb), gen, device, d_scale).view(n, nb, 2)
     return blk.view(n, nb * Q6K_BLOCK_BYTES)
 
 

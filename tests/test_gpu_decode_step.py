@@ -1,0 +1,63 @@
+"""GPU parity of the Llama-shape decode step (eager and CUDA-graph replay) vs the CPU oracle."""
+
+import numpy as np
+import pytest
+import torch
+
+from alloy_b200 import llama
+from oracle import blocks as O
+from oracle import decode_step as OD
+from tests._util import rel_errors, to_np
+
+pytestmark = pytest.mark.gpu
+
+TINY = llama.LlamaShape(layers=2, hidden=512, ffn=1024, heads=8, kv_heads=2, head_dim=64, vocab=640,
+                        rope_theta=10000.0, eps=1e-5)
+
+
+def _oracle_inputs(dec):
+    layers = []
+    for lw in dec.layers:
+        layers.append({
+            "wq": O.dequant_q4_k(lw.wq.cpu().numpy()), "wk": O.dequant_q4_k(lw.wk.cpu().numpy()),
+            "wv": O.dequant_q6_k(lw.wv.cpu().numpy()), "wo": O.dequant_q4_k(lw.wo.cpu().numpy()),
+            "wg": O.dequant_q4_k(lw.wg.cpu().numpy()), "wu": O.dequant_q4_k(lw.wu.cpu().numpy()),
+            "wd": O.dequant_q6_k(lw.wd.cpu().numpy()),
+            "norm_in": lw.norm_in.cpu().numpy(), "norm_post": lw.norm_post.cpu().numpy()})
+    return layers
+
+
+@pytest.mark.parametrize("batch", [1, 4])
+def test_decode_step_matches_oracle(batch):
+    ctx = 96
+    # d, dmin scaled down so that fp16 activations stay far from overflow in the oracle too
+    dec = llama.QuantLlamaDecoder(TINY, batch, ctx, seed=3, d_scale=0.05)
+    rng = np.random.default_rng(0)
+    ids = rng.integers(0, TINY.vocab, size=batch)
+    dec.ids.copy_(torch.from_numpy(ids))
+    kc = [k.float().cpu().numpy() for k in dec.k_cache]
+    vc = [v.float().cpu().numpy() for v in dec.v_cache]
+    layers = _oracle_inputs(dec)
+    ref_logits, ref_next, ref_h = OD.decode_step(
+        ids, ctx - 1, O.dequant_q4_k(dec.embed.cpu().numpy()), layers, dec.norm_final.cpu().numpy(),
+        O.dequant_q6_k(dec.head.cpu().numpy()), dec.inv_freq.cpu().numpy(), kc, vc, TINY.heads,
+        TINY.kv_heads, TINY.head_dim, TINY.eps)
+    assert np.isfinite(ref_logits.astype(np.float32)).all()
+    dec.step()
+    torch.cuda.synchronize()
+    got = to_np(dec.logits)
+    # Each op is held to max 1e-2 / mean 1e-3 in its own test.  Through a whole step an fp16
+    # rounding that flips in one op is amplified by the ops after it, so the composed step is
+    # held to a wider bound: max 5e-2, mean 2e-3.
+    mx, mean = rel_errors(got, ref_logits.astype(np.float64), torch.float16)
+    assert mx <= 5e-2 and mean <= 2e-3, (mx, mean)
+    # the KV rows written at pos are the oracle's rows (fp16, same rounding points)
+    mx, mean = rel_errors(to_np(dec.k_cache[0][:, :, ctx - 1]), kc[0][:, :, ctx - 1].astype(np.float64),
+                          torch.float16)
+    assert mx <= 1e-2 and mean <= 1e-3, (mx, mean)
+    # graph replay gives the same logits as eager
+    dec.capture()
+    dec.step()
+    torch.cuda.synchronize()
+    assert torch.equal(dec.logits, torch.from_numpy(got).to(dec.logits))
+    assert dec.launches_per_step > 0

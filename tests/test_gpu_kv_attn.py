@@ -109,11 +109,15 @@ def test_attention_golden(golden):
     kv_h, s, d = g["k"].shape
     pos, group = int(g["pos"]), int(g["group"])
     t = [_dev(g[n][None]) for n in ("k_codes", "k_scales", "v_codes", "v_scales")]
-    q = _dev(g["q"]).reshape(1, kv_h * group, 1, d)
+    q = _dev(g["q"]).reshape(1, kv_h * group, 1, d).float()   # fp32 in/out like the reference test
     dummy = torch.zeros((1, kv_h, 1, d), dtype=torch.float16, device=DEV)
     out = torch.ops.alloy.attention_cache_q8(q, dummy, dummy, torch.tensor([pos], device=DEV), *t,
                                              write_kv=False)
+    assert out.dtype == torch.float32
     assert np.abs(to_np(out)[0, :, 0] - g["attn"]).max() < 2e-3
+    out16 = torch.ops.alloy.attention_cache_q8(q.half(), dummy, dummy, torch.tensor([pos], device=DEV),
+                                               *t, write_kv=False)
+    assert_close(to_np(out16)[0, :, 0], g["attn"], torch.float16, "golden attention fp16")
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
