@@ -44,6 +44,7 @@ SIGNATURES = {
     "alloyb_error_string": (C.c_char_p, [_i]),
     "alloyb_last_cuda_error": (_i, []),
     "alloyb_device_supported": (_i, []),
+    "alloyb_device_error": (_i, [_i]),
     "alloyb_dequant_q4k": (_i, [_p, _p, _p, _i64, _i64, _i, _i, _p]),
     "alloyb_dequant_q6k": (_i, [_p, _p, _p, _i64, _i64, _i, _i, _p]),
     "alloyb_dequant_q8_0": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _i, _p]),

@@ -51,6 +51,10 @@ const char* alloyb_error_string(int code);
 int alloyb_last_cuda_error(void);
 /* 1 when the library was built for sm_100a and the current device is CC 10.x. */
 int alloyb_device_supported(void);
+/* Sticky device-side error word of the current device: non-zero after a kernel's bounded
+ * wait (mbarrier) ran out; the kernel then finished with undefined results instead of
+ * hanging.  clear != 0 resets it.  Synchronises the device.  Negative = ALLOYB_E_*. */
+int alloyb_device_error(int clear);
 
 /* ------------------------------------------------------------------ dequantisers / embeddings
  * Bit-exact fp32 decode of packed rows.  ids == NULL decodes rows [0, n_rows);

@@ -46,11 +46,13 @@ def test_decode_step_matches_oracle(batch):
     dec.step()
     torch.cuda.synchronize()
     got = to_np(dec.logits)
-    # Each op is held to max 1e-2 / mean 1e-3 in its own test.  Through a whole step an fp16
-    # rounding that flips in one op is amplified by the ops after it, so the composed step is
-    # held to a wider bound: max 5e-2, mean 2e-3.
-    mx, mean = rel_errors(got, ref_logits.astype(np.float64), torch.float16)
-    assert mx <= 5e-2 and mean <= 2e-3, (mx, mean)
+    # Each op is held to max 1e-2 / mean 1e-3 element-wise in its own test.  Through a whole
+    # step an fp16 rounding that flips in one op is carried through the ops after it, so the
+    # composed step is held to: max |err| <= 1e-2 * rms(logits), mean element-wise rel <= 2e-3.
+    _, mean = rel_errors(got, ref_logits.astype(np.float64), torch.float16)
+    ref64 = ref_logits.astype(np.float64)
+    worst = np.abs(got - ref64).max() / np.sqrt((ref64 ** 2).mean())
+    assert worst <= 1e-2 and mean <= 2e-3, (worst, mean)
     # the KV rows written at pos are the oracle's rows (fp16, same rounding points)
     mx, mean = rel_errors(to_np(dec.k_cache[0][:, :, ctx - 1]), kc[0][:, :, ctx - 1].astype(np.float64),
                           torch.float16)

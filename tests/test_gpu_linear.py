@@ -185,3 +185,9 @@ def test_modules_and_errors():
     with pytest.raises(ValueError):
         torch.ops.alloy.gguf_q4_k_mm(x.reshape(6, 512)[:, :256].contiguous(), lin.blocks)
     assert torch.ops.alloy.gguf_q4_k_mm(x.reshape(6, 512)[:0], lin.blocks).shape == (0, 64)
+
+
+def test_no_device_error_recorded():
+    """No kernel of this module ran out a bounded wait."""
+    from alloy_b200 import _lib
+    assert _lib.load().alloyb_device_error(0) == 0
