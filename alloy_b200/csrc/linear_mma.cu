@@ -66,7 +66,6 @@ struct MmaParams {
     int magic_f16;        // 1: fp16 quants as (1024+q)-1024 instead of fp16 subnormals
     int stage_bytes;
     int n_stages;         // ring depth actually used (<= MMA_STAGES)
-    int total_tiles;
 };
 
 // ------------------------------------------------------------------------------- PTX helpers
@@ -156,7 +155,7 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
 template <>
 __device__ __forceinline__ void mma16816<__half>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
                                                  uint32_t b1) {
-    asm(
+    asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -165,7 +164,7 @@ __device__ __forceinline__ void mma16816<__half>(float (&c)[4], const uint32_t (
 template <>
 __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4],
                                                         uint32_t b0, uint32_t b1) {
-    asm(
+    asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -209,27 +208,18 @@ __device__ __forceinline__ uint2 ldx4(const XT* x, int M, int K, int tok, int k)
 }
 
 // One Q4_K super-block for RT row tiles and NT token groups.
-//   stage: the stage's rows (rt*16.. at stride Q4_STRIDE), sb: block within the chunk
+//   stage: shared address of the stage (rows rt*16.. at stride Q4_STRIDE), sb: block within the chunk
 //   tbl:   this warp's scale table, RT*16 rows x 4 pairs x float4 {dsc_lo, dsc_hi, dm_lo, dm_hi}
 template <typename XT, int RT, int NT, bool SUBNORMAL>
-__device__ __forceinline__ void q4k_superblock(const uint8_t* stage, int sb, float4* tbl, const XT* x,
-                                               int M, int K, int kbase, float (&acc)[RT][NT][4]) {
+__device__ __forceinline__ void q4k_superblock(uint32_t stage, int sb, float4* tbl, const XT* x, int M,
+                                               int K, int kbase, float (&acc)[RT][NT][4]) {
     using E = QuantEnc<XT>;
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    // ---- activations of the whole super-block first, so their latency hides behind the table
-    uint4 xl[4][NT], xh[4][NT];
-#pragma unroll
-    for (int gp = 0; gp < 4; ++gp)
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            xl[gp][nt] = ldx8<XT>(x, M, K, nt * 8 + g, kbase + gp * 64 + 8 * t);
-            xh[gp][nt] = ldx8<XT>(x, M, K, nt * 8 + g, kbase + gp * 64 + 8 * t + 32);
-        }
     // ---- scale table: lane -> row (lane>>1), sub-block pairs 2*(lane&1), 2*(lane&1)+1
 #pragma unroll
     for (int rt = 0; rt < RT; ++rt) {
         const int r = rt * 16 + (lane >> 1);
-        const uint4 hdr = *reinterpret_cast<const uint4*>(stage + r * Q4_STRIDE + sb * Q4K_BYTES);
+        const uint4 hdr = lds128(stage + r * Q4_STRIDE + sb * Q4K_BYTES);
         const float d = half_bits_to_f32(hdr.x & 0xffffu);
         const float dmin = half_bits_to_f32(hdr.x >> 16);
         uint32_t scw, mw;
@@ -258,21 +248,26 @@ __device__ __forceinline__ void q4k_superblock(const uint8_t* stage, int sb, flo
     const uint32_t ones[4] = {E::ONE2, E::ONE2, E::ONE2, E::ONE2};
 #pragma unroll
     for (int gp = 0; gp < 4; ++gp) {
+        // activations: sub-block 2gp (lo nibbles) and 2gp+1 (hi nibbles), 8 elements each per lane
+        uint4 xl[NT], xh[NT];
         float sx_lo[NT][4], sx_hi[NT][4];
+        const int k0 = kbase + gp * 64 + 8 * t;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
+            xl[nt] = ldx8<XT>(x, M, K, nt * 8 + g, k0);
+            xh[nt] = ldx8<XT>(x, M, K, nt * 8 + g, k0 + 32);
 #pragma unroll
             for (int i = 0; i < 4; ++i) sx_lo[nt][i] = sx_hi[nt][i] = 0.f;
-            mma16816<XT>(sx_lo[nt], ones, xl[gp][nt].x, xl[gp][nt].y);
-            mma16816<XT>(sx_lo[nt], ones, xl[gp][nt].z, xl[gp][nt].w);
-            mma16816<XT>(sx_hi[nt], ones, xh[gp][nt].x, xh[gp][nt].y);
-            mma16816<XT>(sx_hi[nt], ones, xh[gp][nt].z, xh[gp][nt].w);
+            mma16816<XT>(sx_lo[nt], ones, xl[nt].x, xl[nt].y);
+            mma16816<XT>(sx_lo[nt], ones, xl[nt].z, xl[nt].w);
+            mma16816<XT>(sx_hi[nt], ones, xh[nt].x, xh[nt].y);
+            mma16816<XT>(sx_hi[nt], ones, xh[nt].z, xh[nt].w);
         }
 #pragma unroll
         for (int rt = 0; rt < RT; ++rt) {
-            const uint8_t* base = stage + sb * Q4K_BYTES + 16 + gp * 32 + 8 * t;
-            const uint2 w0 = *reinterpret_cast<const uint2*>(base + (rt * 16 + g) * Q4_STRIDE);
-            const uint2 w1 = *reinterpret_cast<const uint2*>(base + (rt * 16 + g + 8) * Q4_STRIDE);
+            const uint32_t base = stage + sb * Q4K_BYTES + 16 + gp * 32 + 8 * t;
+            const uint2 w0 = lds64(base + (rt * 16 + g) * Q4_STRIDE);
+            const uint2 w1 = lds64(base + (rt * 16 + g + 8) * Q4_STRIDE);
             const float4 s0 = tbl[(rt * 16 + g) * 4 + gp];
             const float4 s1 = tbl[(rt * 16 + g + 8) * 4 + gp];
             uint32_t alo[2][4], ahi[2][4];     // [j][fragment register]
@@ -300,10 +295,10 @@ __device__ __forceinline__ void q4k_superblock(const uint8_t* stage, int sb, flo
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 float cl[4] = {0.f, 0.f, 0.f, 0.f}, ch[4] = {0.f, 0.f, 0.f, 0.f};
-                mma16816<XT>(cl, alo[0], xl[gp][nt].x, xl[gp][nt].y);
-                mma16816<XT>(cl, alo[1], xl[gp][nt].z, xl[gp][nt].w);
-                mma16816<XT>(ch, ahi[0], xh[gp][nt].x, xh[gp][nt].y);
-                mma16816<XT>(ch, ahi[1], xh[gp][nt].z, xh[gp][nt].w);
+                mma16816<XT>(cl, alo[0], xl[nt].x, xl[nt].y);
+                mma16816<XT>(cl, alo[1], xl[nt].z, xl[nt].w);
+                mma16816<XT>(ch, ahi[0], xh[nt].x, xh[nt].y);
+                mma16816<XT>(ch, ahi[1], xh[nt].z, xh[nt].w);
                 float* a = acc[rt][nt];
                 a[0] += s0.x * cl[0] + s0.y * ch[0] - s0.z * sx_lo[nt][0] - s0.w * sx_hi[nt][0];
                 a[1] += s0.x * cl[1] + s0.y * ch[1] - s0.z * sx_lo[nt][1] - s0.w * sx_hi[nt][1];
@@ -315,42 +310,21 @@ __device__ __forceinline__ void q4k_superblock(const uint8_t* stage, int sb, flo
     __syncwarp();
 }
 
-// 32 bits at a 2-byte-aligned shared address.
-__device__ __forceinline__ uint32_t ld32_align2(const uint8_t* p) {
-    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-    if (a & 2u) {
-        const uint32_t* w = reinterpret_cast<const uint32_t*>(a - 2u);
-        return __funnelshift_r(w[0], w[1], 16);
-    }
-    return *reinterpret_cast<const uint32_t*>(p);
-}
-
 // One Q6_K super-block.  tbl: RT*16 rows x 16 floats d*sc, stored [row][h][lhalf][j].
 template <typename XT, int RT, int NT>
-__device__ __forceinline__ void q6k_superblock(const uint8_t* stage, int sb, float4* tbl, const XT* x,
-                                               int M, int K, int kbase, float (&acc)[RT][NT][4]) {
+__device__ __forceinline__ void q6k_superblock(uint32_t stage, int sb, float4* tbl, const XT* x, int M,
+                                               int K, int kbase, float (&acc)[RT][NT][4]) {
     using E = QuantEnc<XT>;
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    uint2 xv[2][2][NT][4];
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int lh = 0; lh < 2; ++lh)
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    xv[h][lh][nt][j] =
-                        ldx4<XT>(x, M, K, nt * 8 + g, kbase + h * 128 + lh * 16 + 4 * t + j * 32);
 #pragma unroll
     for (int rt = 0; rt < RT; ++rt) {
         const int r = rt * 16 + (lane >> 1), h = lane & 1;
-        const uint8_t* blk = stage + r * Q6_STRIDE + sb * Q6K_BYTES;
-        const float d = half_bits_to_f32(*reinterpret_cast<const uint16_t*>(blk + 208));
+        const uint32_t blk = stage + r * Q6_STRIDE + sb * Q6K_BYTES;
+        const float d = half_bits_to_f32(lds16(blk + 208));
         float s[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const uint32_t two = *reinterpret_cast<const uint16_t*>(blk + 192 + h * 8 + 2 * i);
+            const uint32_t two = lds16(blk + 192 + h * 8 + 2 * i);
             s[2 * i] = d * static_cast<float>(static_cast<int8_t>(two & 0xffu));
             s[2 * i + 1] = d * static_cast<float>(static_cast<int8_t>(two >> 8));
         }
@@ -365,6 +339,12 @@ __device__ __forceinline__ void q6k_superblock(const uint8_t* stage, int sb, flo
     for (int h = 0; h < 2; ++h) {
 #pragma unroll
         for (int lh = 0; lh < 2; ++lh) {
+            uint2 xv[NT][4];
+            const int k0 = kbase + h * 128 + lh * 16 + 4 * t;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) xv[nt][j] = ldx4<XT>(x, M, K, nt * 8 + g, k0 + j * 32);
 #pragma unroll
             for (int rt = 0; rt < RT; ++rt) {
                 uint32_t a[4][4];                 // [j][fragment register]
@@ -372,10 +352,10 @@ __device__ __forceinline__ void q6k_superblock(const uint8_t* stage, int sb, flo
 #pragma unroll
                 for (int rr = 0; rr < 2; ++rr) {
                     const int r = rt * 16 + g + 8 * rr;
-                    const uint8_t* blk = stage + r * Q6_STRIDE + sb * Q6K_BYTES;
-                    const uint32_t qla = ld32_align2(blk + h * 64 + lh * 16 + 4 * t);
-                    const uint32_t qlb = ld32_align2(blk + h * 64 + 32 + lh * 16 + 4 * t);
-                    const uint32_t qh = ld32_align2(blk + 128 + h * 32 + lh * 16 + 4 * t);
+                    const uint32_t blk = stage + r * Q6_STRIDE + sb * Q6K_BYTES;
+                    const uint32_t qla = lds32_align2(blk + h * 64 + lh * 16 + 4 * t);
+                    const uint32_t qlb = lds32_align2(blk + h * 64 + 32 + lh * 16 + 4 * t);
+                    const uint32_t qh = lds32_align2(blk + 128 + h * 32 + lh * 16 + 4 * t);
                     sc[rr] = tbl[r * 4 + h * 2 + lh];
                     uint32_t q[4];
                     q[0] = (qla & 0x0f0f0f0fu) | ((qh << 4) & 0x30303030u);
@@ -395,7 +375,7 @@ __device__ __forceinline__ void q6k_superblock(const uint8_t* stage, int sb, flo
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         float c[4] = {0.f, 0.f, 0.f, 0.f};
-                        mma16816<XT>(c, a[j], xv[h][lh][nt][j].x, xv[h][lh][nt][j].y);
+                        mma16816<XT>(c, a[j], xv[nt][j].x, xv[nt][j].y);
                         float* o = acc[rt][nt];
                         o[0] = fmaf(s0[j], c[0], o[0]);
                         o[1] = fmaf(s0[j], c[1], o[1]);
@@ -416,33 +396,29 @@ struct SmemHeader {
     uint64_t empty[MMA_STAGES];
 };
 
-struct TileRef {
-    int seg;     // matrix index (plain) or 0 (gated)
-    int row0;
-};
-__device__ __forceinline__ TileRef tile_ref(const MmaParams& P, int tile) {
-    TileRef r;
-    r.seg = 0;
-    if (!P.gated)
-        while (r.seg + 1 < P.n_seg && tile >= P.seg[r.seg + 1].tile0) ++r.seg;
-    r.row0 = (tile - P.seg[r.seg].tile0) * 16;
-    return r;
-}
-
-// Persistent CTAs: CTA b owns tiles b, b + gridDim.x, ...; the producer warp keeps the stage
-// ring full across tile boundaries, so there is no per-tile pipeline ramp.
 template <typename XT, int RT, int NT>
 __global__ void __launch_bounds__(MMA_THREADS) linear_mma_kernel(const MmaParams P) {
     extern __shared__ __align__(128) uint8_t smem[];
     SmemHeader* hdr = reinterpret_cast<SmemHeader*>(smem);
     float4* tbl_all = reinterpret_cast<float4*>(smem + 128);              // per consumer warp: RT KB
-    constexpr int RED_FLOATS = MMA_CONSUMERS * RT * 16 * 8 * NT;
-    float* red_all = reinterpret_cast<float*>(smem + 128 + MMA_CONSUMERS * RT * 1024);   // 2 buffers
-    uint8_t* stages = smem + 128 + MMA_CONSUMERS * RT * 1024 + 2 * RED_FLOATS * 4;
+    float* red = reinterpret_cast<float*>(smem + 128 + MMA_CONSUMERS * RT * 1024);
+    uint8_t* stages = smem + 128 + MMA_CONSUMERS * RT * 1024 + MMA_CONSUMERS * RT * 16 * 8 * NT * 4;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // which matrix / tile
+    int si = 0;
+    if (!P.gated) {
+        while (si + 1 < P.n_seg && static_cast<int>(blockIdx.x) >= P.seg[si + 1].tile0) ++si;
+    }
+    const MmaSeg& sg = P.seg[si];
+    const int tile = blockIdx.x - sg.tile0;
+    const int row0 = tile * 16;
+    const int fmt = sg.format;
     const int nsb = P.K / QK_K;
     const int nchunks = (nsb + MMA_CH - 1) / MMA_CH;
+    const int blk_bytes = (fmt == ALLOYB_Q4_K) ? Q4K_BYTES : Q6K_BYTES;
+    const int stride = (fmt == ALLOYB_Q4_K) ? Q4_STRIDE : Q6_STRIDE;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < P.n_stages; ++s) {
@@ -457,32 +433,25 @@ __global__ void __launch_bounds__(MMA_THREADS) linear_mma_kernel(const MmaParams
     if (warp == MMA_CONSUMERS) {
         // ---------------- producer: one row per lane (RT*16 rows), weights only -> no pdl_wait
         bool ok = true;
-        int it = 0;                                   // chunk counter across this CTA's tiles
-        for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x) {
-            const TileRef tr = tile_ref(P, tile);
-            const int fmt = P.seg[tr.seg].format;
-            const int blk_bytes = (fmt == ALLOYB_Q4_K) ? Q4K_BYTES : Q6K_BYTES;
-            const int stride = (fmt == ALLOYB_Q4_K) ? Q4_STRIDE : Q6_STRIDE;
-            for (int c = 0; c < nchunks; ++c, ++it) {
-                const int s = it % P.n_stages;
-                if (it >= P.n_stages) ok = mbar_wait(&hdr->empty[s], ((it / P.n_stages) - 1) & 1);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                const int sb_n = min(MMA_CH, nsb - c * MMA_CH);
-                const uint32_t bytes = (static_cast<uint32_t>(sb_n * blk_bytes) + 15u) & ~15u;
-                if (lane == 0) mbar_arrive_expect_tx(&hdr->full[s], bytes * RT * 16);
-                __syncwarp();
-                uint8_t* dst_stage = stages + static_cast<size_t>(s) * P.stage_bytes;
+        for (int c = 0; c < nchunks && ok; ++c) {
+            const int s = c % P.n_stages;
+            if (c >= P.n_stages) ok = mbar_wait(&hdr->empty[s], ((c / P.n_stages) - 1) & 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const int sb_n = min(MMA_CH, nsb - c * MMA_CH);
+            const uint32_t bytes = (static_cast<uint32_t>(sb_n * blk_bytes) + 15u) & ~15u;
+            if (lane == 0) mbar_arrive_expect_tx(&hdr->full[s], bytes * RT * 16);
+            __syncwarp();
+            uint8_t* dst_stage = stages + static_cast<size_t>(s) * P.stage_bytes;
 #pragma unroll
-                for (int rt = 0; rt < RT; ++rt) {
-                    if (lane < 16) {
-                        const MmaSeg& src = P.gated ? P.seg[rt] : P.seg[tr.seg];
-                        int r = tr.row0 + lane;
-                        if (r >= src.n_rows) r = src.n_rows - 1;  // tail tile: re-read the last row
-                        const uint8_t* gp = src.data + static_cast<int64_t>(r) * src.row_bytes +
-                                            static_cast<int64_t>(c) * MMA_CH * blk_bytes;
-                        bulk_g2s(dst_stage + (rt * 16 + lane) * stride, gp, bytes, &hdr->full[s]);
-                    }
+            for (int rt = 0; rt < RT; ++rt) {
+                if (lane < 16) {
+                    const MmaSeg& src = P.gated ? P.seg[rt] : sg;
+                    int r = row0 + lane;
+                    if (r >= src.n_rows) r = src.n_rows - 1;      // tail tile: re-read the last row
+                    const uint8_t* gp = src.data + static_cast<int64_t>(r) * src.row_bytes +
+                                        static_cast<int64_t>(c) * MMA_CH * blk_bytes;
+                    bulk_g2s(dst_stage + (rt * 16 + lane) * stride, gp, bytes, &hdr->full[s]);
                 }
             }
         }
@@ -490,89 +459,83 @@ __global__ void __launch_bounds__(MMA_THREADS) linear_mma_kernel(const MmaParams
     }
 
     // ---------------- consumers
+    float acc[RT][NT][4];
+#pragma unroll
+    for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[rt][nt][i] = 0.f;
     float4* tbl = tbl_all + warp * RT * 64;
     const XT* x = static_cast<const XT*>(P.x);
-    const int g = lane >> 2, t = lane & 3;
 
     pdl_wait();      // activations (and the output buffer) belong to the previous kernel until here
 
     bool ok = true;
-    int it = 0, n_done = 0;
-    for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x, ++n_done) {
-        const TileRef tr = tile_ref(P, tile);
-        const MmaSeg& sg = P.seg[tr.seg];
-        const int fmt = sg.format;
-        float acc[RT][NT][4];
-#pragma unroll
-        for (int rt = 0; rt < RT; ++rt)
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) acc[rt][nt][i] = 0.f;
-
-        for (int c = 0; c < nchunks; ++c, ++it) {
-            const int s = it % P.n_stages;
-            if (ok) ok = mbar_wait(&hdr->full[s], (it / P.n_stages) & 1);
-            if (!ok) continue;       // error word is set; skip the math, keep the control flow
-            const uint8_t* stage = stages + static_cast<size_t>(s) * P.stage_bytes;
-            const int sb_n = min(MMA_CH, nsb - c * MMA_CH);
-            for (int sb = warp; sb < sb_n; sb += MMA_CONSUMERS) {
-                const int kbase = (c * MMA_CH + sb) * QK_K;
-                if (fmt == ALLOYB_Q4_K) {
-                    if (P.magic_f16 || !std::is_same<XT, __half>::value)
-                        q4k_superblock<XT, RT, NT, false>(stage, sb, tbl, x, P.M, P.K, kbase, acc);
-                    else
-                        q4k_superblock<XT, RT, NT, true>(stage, sb, tbl, x, P.M, P.K, kbase, acc);
-                } else {
-                    q6k_superblock<XT, RT, NT>(stage, sb, tbl, x, P.M, P.K, kbase, acc);
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&hdr->empty[s]);
-        }
-
-        // ---------------- cross-warp reduction + epilogue (double-buffered: one barrier per tile)
-        float* red = red_all + (n_done & 1) * RED_FLOATS;
-#pragma unroll
-        for (int rt = 0; rt < RT; ++rt)
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                float* o = red + ((warp * RT + rt) * 16) * (8 * NT);
-                o[(g) * (8 * NT) + nt * 8 + 2 * t] = acc[rt][nt][0];
-                o[(g) * (8 * NT) + nt * 8 + 2 * t + 1] = acc[rt][nt][1];
-                o[(g + 8) * (8 * NT) + nt * 8 + 2 * t] = acc[rt][nt][2];
-                o[(g + 8) * (8 * NT) + nt * 8 + 2 * t + 1] = acc[rt][nt][3];
-            }
-        consumer_sync();
-        const int out_tiles = P.gated ? 1 : RT;
-        for (int idx = threadIdx.x; idx < out_tiles * 16 * 8 * NT; idx += MMA_CONSUMERS * 32) {
-            const int row = idx & 15;
-            const int tok = (idx >> 4) % (8 * NT);
-            const int rt = idx / (16 * 8 * NT);
-            if (tok >= P.M || tr.row0 + row >= sg.n_rows) continue;
-            float v = 0.f, u = 0.f;
-#pragma unroll
-            for (int w = 0; w < MMA_CONSUMERS; ++w) {
-                v += red[((w * RT + rt) * 16 + row) * (8 * NT) + tok];
-                if (RT == 2) u += red[((w * RT + 1) * 16 + row) * (8 * NT) + tok];
-            }
-            const int64_t o = static_cast<int64_t>(tok) * sg.ldy + tr.row0 + row;
-            XT* y = static_cast<XT*>(sg.y);
-            if (P.gated) {
-                const float a = (P.act == ALLOYB_ACT_SILU) ? act_silu(v) : act_gelu_tanh(v);
-                y[o] = from_f32<XT>(a * u);
+    for (int c = 0; c < nchunks; ++c) {
+        const int s = c % P.n_stages;
+        ok = mbar_wait(&hdr->full[s], (c / P.n_stages) & 1);
+        if (!ok) break;
+        const uint32_t stage = smem_u32(stages + static_cast<size_t>(s) * P.stage_bytes);
+        const int sb_n = min(MMA_CH, nsb - c * MMA_CH);
+        for (int sb = warp; sb < sb_n; sb += MMA_CONSUMERS) {
+            const int kbase = (c * MMA_CH + sb) * QK_K;
+            if (fmt == ALLOYB_Q4_K) {
+                if (P.magic_f16 || sizeof(XT) != 2 || !std::is_same<XT, __half>::value)
+                    q4k_superblock<XT, RT, NT, false>(stage, sb, tbl, x, P.M, P.K, kbase, acc);
+                else
+                    q4k_superblock<XT, RT, NT, true>(stage, sb, tbl, x, P.M, P.K, kbase, acc);
             } else {
-                XT r = from_f32<XT>(v);
-                if (P.residual)
-                    r = from_f32<XT>(to_f32<XT>(static_cast<const XT*>(P.residual)[o]) + to_f32<XT>(r));
-                y[o] = r;
+                q6k_superblock<XT, RT, NT>(stage, sb, tbl, x, P.M, P.K, kbase, acc);
             }
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&hdr->empty[s]);
     }
     if (!ok) {
-        // A wait ran out.  Give copies already in flight time to land before the CTA's shared
-        // memory is released.
+        // A wait ran out (the sticky error word is set; results of this CTA are garbage).  Give
+        // copies already in flight time to land before the CTA's shared memory is released, then
+        // fall through so that the other warps are not left at the barrier below.
         for (uint32_t i = 0; i < 2048; ++i) __nanosleep(512);
+    }
+
+    // ---------------- cross-warp reduction + epilogue
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            float* o = red + ((warp * RT + rt) * 16) * (8 * NT);
+            o[(g) * (8 * NT) + nt * 8 + 2 * t] = acc[rt][nt][0];
+            o[(g) * (8 * NT) + nt * 8 + 2 * t + 1] = acc[rt][nt][1];
+            o[(g + 8) * (8 * NT) + nt * 8 + 2 * t] = acc[rt][nt][2];
+            o[(g + 8) * (8 * NT) + nt * 8 + 2 * t + 1] = acc[rt][nt][3];
+        }
+    consumer_sync();
+    const int out_tiles = P.gated ? 1 : RT;
+    const int tid = threadIdx.x;
+    for (int idx = tid; idx < out_tiles * 16 * 8 * NT; idx += MMA_CONSUMERS * 32) {
+        const int row = idx & 15;
+        const int tok = (idx >> 4) % (8 * NT);
+        const int rt = idx / (16 * 8 * NT);
+        if (tok >= P.M || row0 + row >= sg.n_rows) continue;
+        float v = 0.f, u = 0.f;
+#pragma unroll
+        for (int w = 0; w < MMA_CONSUMERS; ++w) {
+            v += red[((w * RT + rt) * 16 + row) * (8 * NT) + tok];
+            if (RT == 2) u += red[((w * RT + 1) * 16 + row) * (8 * NT) + tok];
+        }
+        const int64_t o = static_cast<int64_t>(tok) * sg.ldy + row0 + row;
+        XT* y = static_cast<XT*>(sg.y);
+        if (P.gated) {
+            const float a = (P.act == ALLOYB_ACT_SILU) ? act_silu(v) : act_gelu_tanh(v);
+            y[o] = from_f32<XT>(a * u);
+        } else {
+            XT r = from_f32<XT>(v);
+            if (P.residual)
+                r = from_f32<XT>(to_f32<XT>(static_cast<const XT*>(P.residual)[o]) + to_f32<XT>(r));
+            y[o] = r;
+        }
     }
 }
 
@@ -586,37 +549,17 @@ static int magic_f16_flag() {
     return flag;
 }
 
-static int sm_count() {
-    static const int n = [] {
-        int dev = 0, v = 148;
-        if (cudaGetDevice(&dev) == cudaSuccess)
-            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-        return v > 0 ? v : 148;
-    }();
-    return n;
-}
-
 template <typename XT, int RT, int NT>
-static int launch_mma(MmaParams& P, int tiles, int smem_bytes, cudaStream_t st) {
+static int launch_mma(const MmaParams& P, int grid, int smem_bytes, cudaStream_t st) {
     static bool configured = false;   // per template instance
-    static int occ_smem = -1, occ_blocks = 1;
     auto kern = linear_mma_kernel<XT, RT, NT>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
         configured = true;
     }
-    if (occ_smem != smem_bytes) {
-        int nb = 1;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, MMA_THREADS, smem_bytes);
-        if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
-        occ_blocks = nb > 0 ? nb : 1;
-        occ_smem = smem_bytes;
-    }
-    P.total_tiles = tiles;
-    const int resident = sm_count() * occ_blocks;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(tiles < resident ? tiles : resident);
+    cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(MMA_THREADS);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = st;
@@ -625,7 +568,7 @@ static int launch_mma(MmaParams& P, int tiles, int smem_bytes, cudaStream_t st) 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<const MmaParams>(P));
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, P);
     if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
     return ALLOYB_OK;
 }
@@ -634,7 +577,7 @@ template <typename XT, int RT>
 static int launch_mma_nt(MmaParams& P, int grid, int stage_rows_bytes, cudaStream_t st) {
     const int nt = (P.M + 7) / 8;
     const int NTt = nt <= 1 ? 1 : (nt == 2 ? 2 : 4);
-    const int fixed = 128 + MMA_CONSUMERS * RT * 1024 + 2 * MMA_CONSUMERS * RT * 16 * 8 * NTt * 4;
+    const int fixed = 128 + MMA_CONSUMERS * RT * 1024 + MMA_CONSUMERS * RT * 16 * 8 * NTt * 4;
     int stages = (MMA_SMEM_TARGET - fixed) / stage_rows_bytes;
     if (stages > MMA_STAGES) stages = MMA_STAGES;
     if (stages < 2) stages = 2;
