@@ -1,7 +1,7 @@
 // Single-query (decode) GQA attention over fp16, split-q8 and paged-q8 KV caches.
 //
-// Grid (SPLITS, KV_H, B); each CTA streams one token range of one KV head ONCE
-// and scores all G = H/KV_H query heads of the group against it.  Softmax runs
+// Grid (SPLITS, KV_H, B); each CTA (4 warps) streams one token range of one KV head
+// ONCE and scores all G = H/KV_H query heads of the group against it.  Softmax runs
 // in the exp2 frame (scale*log2e folded into q).  Each CTA writes a normalised
 // partial output and its log-sum-exp; the last CTA of a (sequence, kv head) to
 // finish merges the partials, so no second launch is needed.
@@ -9,7 +9,7 @@
 
 namespace alloyb {
 
-constexpr int ATTN_MAX_SPLITS = 32;
+constexpr int ATTN_MAX_SPLITS = 64;
 constexpr float NEG_BIG = -1.0e30f;
 
 struct AttnParams {
@@ -169,25 +169,32 @@ __device__ __forceinline__ void load_v(const RowRef<LAYOUT, D>& r, int lane, flo
     }
 }
 
+constexpr int ATTN_WARPS = 4;
+
+// CTA = 4 warps.  The CTA's token range is cut into 32-token chunks dealt round-robin to the
+// warps; each warp keeps its own online-softmax state, the four states are merged through
+// shared memory, and the CTA writes ONE partial per query head.
 template <int LAYOUT, int D, int G>
-__global__ void __launch_bounds__(32) attn_decode_kernel(AttnParams P) {
+__global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(AttnParams P) {
     constexpr int DPL = D / 32;
     __shared__ float qs[G * D];
+    __shared__ float sm_m[ATTN_WARPS][G], sm_l[ATTN_WARPS][G];
+    __shared__ float sm_o[ATTN_WARPS][G][D];
     __shared__ int s_last;
-    const int lane = threadIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     pdl_wait();
     int pos = P.pos[P.pos_count == 1 ? 0 : b];
     if (pos >= P.kv.S_max) {
-        if (lane == 0 && P.status) atomicOr(P.status, KV_STATUS_POS_RANGE);
+        if (threadIdx.x == 0 && P.status) atomicOr(P.status, KV_STATUS_POS_RANGE);
         pos = P.kv.S_max - 1;
     }
     const int len = pos + 1;                  // positions [0, pos]; pos < 0 -> empty
-    for (int i = lane; i < G * D; i += 32) {
+    for (int i = threadIdx.x; i < G * D; i += ATTN_WARPS * 32) {
         const int g = i / D, d = i - g * D;
         qs[i] = load_q(P.q, P.q_dtype, b * P.q_bs + (kvh * G + g) * P.q_hs + d) * P.scale_log2;
     }
-    __syncwarp();
+    __syncthreads();
 
     int chunk = (len + P.splits - 1) / P.splits;
     chunk = (chunk + 31) & ~31;
@@ -203,7 +210,7 @@ __global__ void __launch_bounds__(32) attn_decode_kernel(AttnParams P) {
         for (int e = 0; e < DPL; ++e) o[g][e] = 0.f;
     }
 
-    for (int c0 = t0; c0 < t1; c0 += 32) {
+    for (int c0 = t0 + warp * 32; c0 < t1; c0 += ATTN_WARPS * 32) {
         const int j = c0 + lane;
         const bool valid = j < t1;
         float s[G];
@@ -237,52 +244,59 @@ __global__ void __launch_bounds__(32) attn_decode_kernel(AttnParams P) {
         }
     }
 
-    // partial out: normalised o and lse (log2 frame); empty ranges write lse = NEG_BIG
+    // merge the four warps
 #pragma unroll
     for (int g = 0; g < G; ++g) {
+        if (lane == 0) { sm_m[warp][g] = m[g]; sm_l[warp][g] = l[g]; }
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) sm_o[warp][g][lane * DPL + e] = o[g][e];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * D; i += ATTN_WARPS * 32) {
+        const int g = i / D, d = i - g * D;
+        float mx = NEG_BIG;
+#pragma unroll
+        for (int w = 0; w < ATTN_WARPS; ++w) mx = fmaxf(mx, sm_m[w][g]);
+        float lt = 0.f, ot = 0.f;
+#pragma unroll
+        for (int w = 0; w < ATTN_WARPS; ++w) {
+            const float sc = exp2f(sm_m[w][g] - mx);
+            lt = fmaf(sm_l[w][g], sc, lt);
+            ot = fmaf(sm_o[w][g][d], sc, ot);
+        }
         const int h = kvh * G + g;
         const int64_t pi = (static_cast<int64_t>(b) * P.H + h) * P.splits + split;
-        const float inv = l[g] > 0.f ? 1.0f / l[g] : 0.f;
-#pragma unroll
-        for (int e = 0; e < DPL; ++e) P.part_o[pi * D + lane * DPL + e] = o[g][e] * inv;
-        if (lane == 0) P.part_lse[pi] = l[g] > 0.f ? m[g] + log2f(l[g]) : NEG_BIG;
+        P.part_o[pi * D + d] = lt > 0.f ? ot / lt : 0.f;
+        if (d == 0) P.part_lse[pi] = lt > 0.f ? mx + log2f(lt) : NEG_BIG;
     }
 
-    // last CTA of this (b, kv head) merges
+    // last CTA of this (b, kv head) merges the splits
     __threadfence();
-    __syncwarp();
-    if (lane == 0) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
         const unsigned int prev = atomicAdd(P.counters + b * P.KV_H + kvh, 1u);
         s_last = (prev == static_cast<unsigned int>(P.splits) - 1u);
         if (s_last) P.counters[b * P.KV_H + kvh] = 0u;   // ready for the next call
     }
-    __syncwarp();
+    __syncthreads();
     if (!s_last) return;
     __threadfence();
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
+    for (int i = threadIdx.x; i < G * D; i += ATTN_WARPS * 32) {
+        const int g = i / D, d = i - g * D;
         const int h = kvh * G + g;
         const int64_t base = (static_cast<int64_t>(b) * P.H + h) * P.splits;
         float mx = NEG_BIG;
         for (int s2 = 0; s2 < P.splits; ++s2) mx = fmaxf(mx, __ldcg(P.part_lse + base + s2));
-        float acc[DPL];
-#pragma unroll
-        for (int e = 0; e < DPL; ++e) acc[e] = 0.f;
-        float wsum = 0.f;
+        float acc = 0.f, wsum = 0.f;
         for (int s2 = 0; s2 < P.splits; ++s2) {
             const float lse = __ldcg(P.part_lse + base + s2);
             if (lse <= 0.5f * NEG_BIG) continue;
             const float w = exp2f(lse - mx);
             wsum += w;
-#pragma unroll
-            for (int e = 0; e < DPL; ++e)
-                acc[e] = fmaf(w, __ldcg(P.part_o + (base + s2) * D + lane * DPL + e), acc[e]);
+            acc = fmaf(w, __ldcg(P.part_o + (base + s2) * D + d), acc);
         }
-        const float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
-#pragma unroll
-        for (int e = 0; e < DPL; ++e)
-            store_out(P.out, P.q_dtype, (static_cast<int64_t>(b) * P.H + h) * D + lane * DPL + e,
-                      acc[e] * inv);
+        store_out(P.out, P.q_dtype, (static_cast<int64_t>(b) * P.H + h) * D + d,
+                  wsum > 0.f ? acc / wsum : 0.f);
     }
 }
 
@@ -290,10 +304,10 @@ template <int LAYOUT, int D>
 static int launch_attn_g(const AttnParams& P, int G, cudaStream_t st) {
     dim3 grid(P.splits, P.KV_H, P.B);
     switch (G) {
-        case 1: attn_decode_kernel<LAYOUT, D, 1><<<grid, 32, 0, st>>>(P); break;
-        case 2: attn_decode_kernel<LAYOUT, D, 2><<<grid, 32, 0, st>>>(P); break;
-        case 4: attn_decode_kernel<LAYOUT, D, 4><<<grid, 32, 0, st>>>(P); break;
-        case 8: attn_decode_kernel<LAYOUT, D, 8><<<grid, 32, 0, st>>>(P); break;
+        case 1: attn_decode_kernel<LAYOUT, D, 1><<<grid, ATTN_WARPS * 32, 0, st>>>(P); break;
+        case 2: attn_decode_kernel<LAYOUT, D, 2><<<grid, ATTN_WARPS * 32, 0, st>>>(P); break;
+        case 4: attn_decode_kernel<LAYOUT, D, 4><<<grid, ATTN_WARPS * 32, 0, st>>>(P); break;
+        case 8: attn_decode_kernel<LAYOUT, D, 8><<<grid, ATTN_WARPS * 32, 0, st>>>(P); break;
         default: return ALLOYB_E_SHAPE;
     }
     return check_launch();
@@ -366,10 +380,11 @@ extern "C" int alloyb_attn_decode(int layout, const void* q, int64_t q_batch_str
     ws += align_up(bh * ATTN_MAX_SPLITS * sizeof(float), 256);
     P.part_o = reinterpret_cast<float*>(ws);
 
-    // enough CTAs to fill the machine several times over, at least 64 tokens per split
+    // enough CTAs (4 warps each) to fill the machine about four times over, at least 128 tokens
+    // (one 32-token chunk per warp) per split
     const int ctas = B * KV_H;
-    int splits = (148 * 16 + ctas - 1) / ctas;
-    const int by_len = (S_max + 63) / 64;
+    int splits = (148 * 4 + ctas - 1) / ctas;
+    const int by_len = (S_max + 127) / 128;
     if (splits > by_len) splits = by_len;
     if (splits > ATTN_MAX_SPLITS) splits = ATTN_MAX_SPLITS;
     if (splits < 1) splits = 1;
