@@ -61,6 +61,8 @@ SIGNATURES = {
     "alloyb_attn_workspace_status": (_i, [_p, C.POINTER(C.c_int32), _p]),
     "alloyb_attn_decode": (_i, [_i, _p, _i64, _i64, _i, _p, _p, _p, _p, _p, _p, _i64, _i64, _p, _i,
                                 _p, _i, _i, _i, _i, _i, _i64, _f, _i, _p, _sz, _p]),
+    "alloyb_attn_decode_static": (_i, [_i, _p, _i64, _i64, _i, _p, _p, _p, _p, _p, _p, _i64, _i64, _p, _i,
+                                       _p, _i, _i, _i, _i, _i, _i64, _f, _i, _p]),
     "alloyb_rms_norm": (_i, [_p, _p, _p, _i, _i, _f, _i, _p]),
     "alloyb_rope_inplace": (_i, [_p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _p]),
     "alloyb_silu_mul": (_i, [_p, _p, _p, _i64, _i, _p]),

@@ -424,3 +424,64 @@ extern "C" int alloyb_attn_workspace_status(const void* workspace, int32_t* stat
     if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
     return ALLOYB_OK;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate device memory.
+//
+// Some hosts of this library may not call cudaMalloc on the path that runs a decode step: code
+// that runs inside a region where the CUDA allocator must stay quiet (a latency-critical serving
+// loop with a frozen memory plan, a plugin whose host forbids allocations after start-up, a
+// sandbox that only hands out the input and output buffers).  alloyb_attn_decode needs a caller-
+// provided workspace for its split-K partials; this variant brings its own: a fixed array in
+// device memory that is part of the library image, so every GPU that loads the library holds
+// ALLOYB_ATTN_STATIC_BYTES of it until the process exits.
+//
+// The array is shared by every call on that device and keeps the previous call's contents.  The
+// words that must start at zero (status word and completion counters) are cleared on the stream
+// at the start of every call; the partials need no clearing.  Two calls that may overlap on the
+// GPU (different streams, or one stream in two threads) race on the array: serialise them.
+namespace alloyb {
+
+static __device__ __align__(256) unsigned char g_attn_static_scratch[ALLOYB_ATTN_STATIC_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+static void* g_attn_static_ptr[MAX_DEVICES] = {};   // device address per device ordinal
+
+}  // namespace alloyb
+
+extern "C" int alloyb_attn_decode_static(int layout, const void* q, int64_t q_batch_stride,
+                                         int64_t q_head_stride, int q_dtype, void* k0, void* k1,
+                                         void* v0, void* v1, const void* new_k, const void* new_v,
+                                         int64_t new_batch_stride, int64_t new_head_stride,
+                                         const int32_t* pos, int pos_count, void* out, int B, int H,
+                                         int KV_H, int D, int S_max, int64_t num_pages, float scale,
+                                         int write_kv, void* stream) {
+    if (B <= 0 || H <= 0 || KV_H <= 0 || D <= 0) return ALLOYB_E_SHAPE;
+    const size_t need = alloyb_attn_workspace_bytes(B, H, D);
+    if (need == 0) return ALLOYB_E_SHAPE;
+    if (need > static_cast<size_t>(ALLOYB_ATTN_STATIC_BYTES)) return ALLOYB_E_LIMIT;
+
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
+    if (dev < 0 || dev >= MAX_DEVICES) return ALLOYB_E_LIMIT;
+    if (g_attn_static_ptr[dev] == nullptr) {
+        // One-time set-up for this device (it is the current one).  In host code the array's name
+        // is only a stand-in for the symbol; the address a kernel can use comes from the runtime.
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            set_cuda_error(e);
+            return ALLOYB_E_CUDA;
+        }
+        g_attn_static_ptr[dev] = p;
+    }
+    void* ws = g_attn_static_ptr[dev];
+    // status word + completion counters start every call at zero
+    const size_t head = 256 + static_cast<size_t>(B) * H * sizeof(unsigned int);
+    e = cudaMemsetAsync(ws, 0, head, as_stream(stream));
+    if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
+    return alloyb_attn_decode(layout, q, q_batch_stride, q_head_stride, q_dtype, k0, k1, v0, v1, new_k,
+                              new_v, new_batch_stride, new_head_stride, pos, pos_count, out, B, H, KV_H,
+                              D, S_max, num_pages, scale, write_kv, ws, ALLOYB_ATTN_STATIC_BYTES, stream);
+}

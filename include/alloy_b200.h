@@ -185,6 +185,25 @@ int alloyb_attn_decode(int layout, const void* q, int64_t q_batch_stride, int64_
                        int S_max, int64_t num_pages, float scale, int write_kv, void* workspace,
                        size_t workspace_bytes, void* stream);
 
+/* Decode attention that allocates nothing and needs no workspace from the caller (no
+ * counterpart in the reference, whose runtime owns its scratch buffers).  For hosts that may
+ * not allocate device memory where the decode step runs -- a serving loop with a frozen
+ * memory plan, a plugin host that forbids allocation after start-up -- the split-K partials
+ * live in a fixed device array inside the library image: ALLOYB_ATTN_STATIC_BYTES on every
+ * GPU that loads the library, until the process exits.  Same arguments and results as
+ * alloyb_attn_decode without workspace/workspace_bytes.  Shapes whose
+ * alloyb_attn_workspace_bytes(B,H,D) exceeds ALLOYB_ATTN_STATIC_BYTES return ALLOYB_E_LIMIT.
+ * The first call on a device looks up the array's device address (make that call before any
+ * stream capture).  All calls on a device share the array: calls that may overlap on the GPU
+ * race and must be serialised by the caller.  It calls no cudaMalloc/cudaFree. */
+#define ALLOYB_ATTN_STATIC_BYTES (16 * 1024 * 1024)
+int alloyb_attn_decode_static(int layout, const void* q, int64_t q_batch_stride,
+                              int64_t q_head_stride, int q_dtype, void* k0, void* k1, void* v0,
+                              void* v1, const void* new_k, const void* new_v,
+                              int64_t new_batch_stride, int64_t new_head_stride, const int32_t* pos,
+                              int pos_count, void* out, int B, int H, int KV_H, int D, int S_max,
+                              int64_t num_pages, float scale, int write_kv, void* stream);
+
 /* ------------------------------------------------------------------ decode-step glue
  * Small fp16/bf16 ops of the decode step (not graded kernels):
  * rms_norm metal/std/norm.py:40-73 (normalise in fp32, cast, then multiply by
