@@ -20,7 +20,7 @@ from dataclasses import dataclass
 
 import torch
 
-from . import ops, synth
+from . import ops, synth, tp
 
 
 @dataclass(frozen=True)
@@ -51,16 +51,6 @@ LLAMA3_8B = LlamaShape(layers=32, hidden=4096, ffn=14336, heads=32, kv_heads=8, 
                        vocab=128256)
 LLAMA3_70B = LlamaShape(layers=80, hidden=8192, ffn=28672, heads=64, kv_heads=8, head_dim=128,
                         vocab=128256)
-
-
-def _slice_cols(blocks: torch.Tensor, block_bytes: int, rank: int, size: int) -> torch.Tensor:
-    """Row-parallel shard: super-blocks [rank*nb/size, (rank+1)*nb/size) of every row."""
-    n = blocks.shape[0]
-    nb = blocks.shape[1] // block_bytes
-    if nb % size:
-        raise ValueError(f"{nb} super-blocks per row do not split {size} ways")
-    per = nb // size
-    return blocks.view(n, nb, block_bytes)[:, rank * per:(rank + 1) * per].reshape(n, per * block_bytes).contiguous()
 
 
 class LayerWeights:
@@ -95,7 +85,7 @@ class QuantLlamaDecoder:
         r, n = tp_rank, tp_size
 
         def rows(t, per):
-            return t[r * per:(r + 1) * per].contiguous()
+            return tp.shard_rows(t, r, n)
 
         self.embed = synth.q4k_blocks_device(s.vocab, s.hidden, gen, self.device, d_scale)
         self.layers: list[LayerWeights] = []
@@ -104,10 +94,10 @@ class QuantLlamaDecoder:
             lw.wq = rows(synth.q4k_blocks_device(s.heads * s.head_dim, s.hidden, gen, self.device, d_scale), hd_l)
             lw.wk = rows(synth.q4k_blocks_device(s.kv_heads * s.head_dim, s.hidden, gen, self.device, d_scale), kvd_l)
             lw.wv = rows(synth.q6k_blocks_device(s.kv_heads * s.head_dim, s.hidden, gen, self.device, d_scale), kvd_l)
-            lw.wo = _slice_cols(synth.q4k_blocks_device(s.hidden, s.heads * s.head_dim, gen, self.device, d_scale), 144, r, n)
+            lw.wo = tp.shard_cols(synth.q4k_blocks_device(s.hidden, s.heads * s.head_dim, gen, self.device, d_scale), "q4_k", r, n)
             lw.wg = rows(synth.q4k_blocks_device(s.ffn, s.hidden, gen, self.device, d_scale), self.ffn_l)
             lw.wu = rows(synth.q4k_blocks_device(s.ffn, s.hidden, gen, self.device, d_scale), self.ffn_l)
-            lw.wd = _slice_cols(synth.q6k_blocks_device(s.hidden, s.ffn, gen, self.device, d_scale), 210, r, n)
+            lw.wd = tp.shard_cols(synth.q6k_blocks_device(s.hidden, s.ffn, gen, self.device, d_scale), "q6_k", r, n)
             lw.norm_in = self._norm_weight(gen)
             lw.norm_post = self._norm_weight(gen)
             self.layers.append(lw)
@@ -166,11 +156,6 @@ class QuantLlamaDecoder:
 
     # ------------------------------------------------------------------ one decode step
 
-    def _all_reduce(self, t: torch.Tensor) -> torch.Tensor:
-        if self.tp_size > 1:
-            torch.distributed.all_reduce(t, group=self.pg)
-        return t
-
     def _step(self) -> None:
         s, b = self.shape, self.batch
         n0 = ops.launch_count()
@@ -197,19 +182,17 @@ class QuantLlamaDecoder:
             if self.tp_size == 1:
                 h = torch.ops.alloy.linear_residual(a2, lw.wo, None, h, "q4_k")
             else:
-                h = h + self._all_reduce(torch.ops.alloy.gguf_q4_k_mm(a2, lw.wo))
+                h = h + tp.row_parallel(a2, lambda t: torch.ops.alloy.gguf_q4_k_mm(t, lw.wo), self.pg)
             xn = ops.rms_norm(h, lw.norm_post, s.eps)
             act = torch.ops.alloy.gguf_q4_k_silu(xn, lw.wg, lw.wu)
             if self.tp_size == 1:
                 h = torch.ops.alloy.linear_residual(act, lw.wd, None, h, "q6_k")
             else:
-                h = h + self._all_reduce(torch.ops.alloy.gguf_q6_k_mm(act, lw.wd))
+                h = h + tp.row_parallel(act, lambda t: torch.ops.alloy.gguf_q6_k_mm(t, lw.wd), self.pg)
         xn = ops.rms_norm(h, self.norm_final, s.eps)
         logits = torch.ops.alloy.gguf_q6_k_mm(xn, self.head)
         if self.tp_size > 1:
-            parts = [torch.empty_like(logits) for _ in range(self.tp_size)]
-            torch.distributed.all_gather(parts, logits, group=self.pg)
-            logits = torch.cat(parts, dim=1)
+            logits = tp.gather_columns(logits, self.pg)
         self.logits = logits
         self.next_ids.copy_(ops.argmax(logits))
         self.launches_per_step = ops.launch_count() - n0
