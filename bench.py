@@ -227,10 +227,21 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
     shape = getattr(llama, shape_name)
     dev = torch.device("cuda", local)
 
+    t_start = time.perf_counter()
+
+    def note(msg):
+        if args.verbose:
+            print(f"[bench rank {rank} +{time.perf_counter() - t_start:6.1f}s] {msg}", file=sys.stderr, flush=True)
+
     def build(batch):
+        note(f"building decoder batch={batch}")
         d = llama.QuantLlamaDecoder(shape, batch, wl["context"], device=dev, seed=0, kv=wl["kv"],
                                     tp_rank=rank, tp_size=world, process_group=pg)
+        torch.cuda.synchronize()
+        note("weights ready; capturing")
         d.capture()
+        torch.cuda.synchronize()
+        note("captured")
         return d
 
     def timed(dec, steps, warmup):
@@ -270,7 +281,9 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
     dec = build(args.batch)
     with ClockSampler(local) as clocks:
         ms = timed(dec, args.steps, args.warmup)
+        note(f"timed: {ms / args.steps:.3f} ms/step")
         e2e_ms, h2d, d2h = timed_e2e(dec, args.steps, args.warmup)
+        note("e2e timed")
     value = args.batch * args.steps / (ms * 1e-3)
     e2e_val = args.batch * args.steps / (e2e_ms * 1e-3)
     w_bytes = shape.weight_bytes()
@@ -297,8 +310,7 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
             r["frac_of_weight_plus_kv_bound"] = ((w_bytes + kv_bytes) / (peak * 1e9)) / (r["ms_per_step"] * 1e-3)
 
     if rank != 0:
-        if world > 1:
-            torch.distributed.destroy_process_group()
+        _leave(world)
         return
     cpu = cpu_layer_sample(shape, args.batch) if world == 1 and not args.no_cpu else None
     line = {
@@ -327,9 +339,20 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
     if cpu is not None:
         line["cpu_baseline"] = {"value": cpu["tok_s"], "unit": "tokens/s", "cores": cpu["cores"],
                                 "kind": "port", "sample": cpu["sample"]}
-    print(json.dumps(line))
+    print(json.dumps(line), flush=True)
+    _leave(world)
+
+
+def _leave(world: int) -> None:
+    """End a multi-rank run.  The process group is NOT destroyed: with NCCL collectives
+    captured in a live CUDA graph, ``destroy_process_group`` blocked for minutes on this
+    stack, so the ranks meet at a barrier and exit directly."""
     if world > 1:
-        torch.distributed.destroy_process_group()
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main() -> None:
@@ -342,6 +365,7 @@ def main() -> None:
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--no-sweep", action="store_true", help="skip the batch 1/4/16/32 sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
+    ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
