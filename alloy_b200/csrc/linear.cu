@@ -165,6 +165,16 @@ extern "C" int alloyb_linear(const void* x, int M, int K, int dtype, const alloy
     if (M == 0) return ALLOYB_OK;
     cudaStream_t st = as_stream(stream);
 
+    if (M >= 64 && !residual) {
+        // prefill-sized M: one tcgen05 GEMM per matrix
+        bool all = true;
+        for (int i = 0; i < segs.n_seg && all; ++i) {
+            rc = try_gemm_tc(x, M, K, dtype, segs.seg[i], st);
+            if (rc == ALLOYB_NOT_TAKEN) all = false;
+            else if (rc != ALLOYB_OK) return rc;
+        }
+        if (all) return ALLOYB_OK;
+    }
     rc = try_linear_fast(x, M, K, dtype, segs.seg, segs.n_seg, residual, st);
     if (rc != ALLOYB_NOT_TAKEN) return rc;
 

@@ -25,4 +25,8 @@ int try_gated_fast(const void* x, const void* gate, const void* gate_scales, con
                    const void* up_scales, void* y, int M, int N, int K, int format, int act,
                    int dtype, cudaStream_t st);
 
+// tcgen05 dequant-GEMM for prefill-sized M (one matrix).
+int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, cudaStream_t st);
+int gemm_tc_device_error(int clear);
+
 }  // namespace alloyb

@@ -694,10 +694,11 @@ extern "C" int alloyb_device_error(int clear) {
     int v = 0;
     cudaError_t e = cudaMemcpyFromSymbol(&v, alloyb::g_device_error, sizeof(int));
     if (e != cudaSuccess) { alloyb::set_cuda_error(e); return ALLOYB_E_CUDA; }
+    const int v_tc = alloyb::gemm_tc_device_error(clear);
     if (clear && v) {
         const int z = 0;
         e = cudaMemcpyToSymbol(alloyb::g_device_error, &z, sizeof(int));
         if (e != cudaSuccess) { alloyb::set_cuda_error(e); return ALLOYB_E_CUDA; }
     }
-    return v;
+    return v | v_tc;
 }

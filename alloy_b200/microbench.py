@@ -12,6 +12,7 @@ graph; the figure printed is the mean device time per launch and the algorithmic
     python -m alloy_b200.microbench --op gated  --n 14336 --k 4096 --m 1
     python -m alloy_b200.microbench --op q6k_mm --n 4096 --k 14336 --m 4
     python -m alloy_b200.microbench --op attn_paged --batch 64 --ctx-lo 4096 --ctx-hi 32768
+    python -m alloy_b200.microbench --op gemm_q4k --m 4096 --n 14336 --k 4096 --dtype bf16
 """
 
 from __future__ import annotations
@@ -78,6 +79,26 @@ def bench_linear(op: str, n: int, k: int, m: int, ring_mb: int, sweeps: int, dty
             "gbs_median": alg / med / 1e3, "gbs_best": alg / min(us) / 1e3}
 
 
+def bench_gemm(fmt: str, m: int, n: int, k: int, sweeps: int, dtype) -> dict:
+    """Prefill dequant-GEMM (tcgen05 path): M tokens against one packed matrix."""
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    if fmt == "q6k":
+        blk = synth.q6k_blocks_device(n, k, gen)
+        op = torch.ops.alloy.gguf_q6_k_mm
+        wbytes = n * (k // 256) * 210
+    else:
+        blk = synth.q4k_blocks_device(n, k, gen)
+        op = torch.ops.alloy.gguf_q4_k_mm
+        wbytes = n * (k // 256) * 144
+    x = torch.randn((m, k), device="cuda").to(dtype)
+    ms = _time_graph(lambda: op(x, blk), sweeps)
+    med = statistics.median(ms)
+    flop = 2.0 * m * n * k
+    return {"op": f"gemm_{fmt}", "m": m, "n": n, "k": k, "flop": flop, "bytes": wbytes + 2 * m * k + 2 * m * n,
+            "ms_median": med, "ms_min": min(ms), "tflops_median": flop / med / 1e9,
+            "tflops_best": flop / min(ms) / 1e9}
+
+
 def bench_attn_paged(batch: int, lo: int, hi: int, sweeps: int, kv_heads: int = 8, group: int = 4,
                      d: int = 128) -> dict:
     from .kv import PagedKVPool
@@ -115,7 +136,8 @@ def bench_attn_paged(batch: int, lo: int, hi: int, sweeps: int, kv_heads: int = 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["q4k_mm", "q6k_mm", "gated", "attn_paged"])
+    ap.add_argument("--op", required=True,
+                    choices=["q4k_mm", "q6k_mm", "gated", "attn_paged", "gemm_q4k", "gemm_q6k"])
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--m", type=int, default=1)
@@ -126,8 +148,11 @@ def main() -> None:
     ap.add_argument("--ctx-lo", type=int, default=4096)
     ap.add_argument("--ctx-hi", type=int, default=32768)
     a = ap.parse_args()
+    dt = torch.float16 if a.dtype == "f16" else torch.bfloat16
     if a.op == "attn_paged":
         res = bench_attn_paged(a.batch, a.ctx_lo, a.ctx_hi, a.sweeps)
+    elif a.op.startswith("gemm_"):
+        res = bench_gemm(a.op[5:], a.m, a.n, a.k, a.sweeps, dt)
     else:
         res = bench_linear(a.op, a.n, a.k, a.m, a.ring_mb, a.sweeps,
                            torch.float16 if a.dtype == "f16" else torch.bfloat16)

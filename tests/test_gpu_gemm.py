@@ -1,0 +1,94 @@
+"""GPU parity of the prefill dequant-GEMM (tcgen05 path, M >= 64) against the oracle.
+
+The GEMM's definition includes ONE rounding of the exactly-decoded fp32 weight to the activation
+type (bf16 / fp16) before the tensor-core product, so the oracle here is
+float64( X ) @ float64( round_to_type( dequant_fp32(W) ) ).T, rounded to the output type.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from alloy_b200 import _lib, synth
+from oracle import blocks as O
+from tests._util import assert_close, to_np
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DT = {"bf16": torch.bfloat16, "f16": torch.float16}
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def _ref(x_t, w_f32, dt):
+    w_r = torch.from_numpy(w_f32).to(dt).double().numpy()      # one rounding of the decoded weight
+    return x_t.double().cpu().numpy() @ w_r.T
+
+
+# Q6_K rows are 16-byte aligned (what the bulk copies need) only when K is a multiple of 2048;
+# other Q6_K shapes take the exact-weight row kernels and are covered in test_gpu_linear.py.
+@pytest.mark.parametrize("fmt,m,n,k,dt", [
+    ("q4_k", 256, 128, 256, "bf16"), ("q4_k", 64, 256, 512, "bf16"), ("q4_k", 300, 200, 1024, "bf16"),
+    ("q4_k", 512, 384, 2048, "f16"), ("q4_k", 1000, 136, 4096, "bf16"),
+    ("q6_k", 256, 128, 2048, "bf16"), ("q6_k", 64, 256, 2048, "bf16"), ("q6_k", 300, 200, 4096, "bf16"),
+    ("q6_k", 512, 384, 2048, "f16"), ("q6_k", 1000, 136, 6144, "bf16")])
+def test_gemm_matches_oracle(fmt, m, n, k, dt):
+    rng = np.random.default_rng([m, n, k, len(fmt)])
+    tdt = DT[dt]
+    if fmt == "q4_k":
+        blk = synth.q4k_blocks(rng, n, k)
+        w = O.dequant_q4_k(blk)
+        op = torch.ops.alloy.gguf_q4_k_mm
+    else:
+        blk = synth.q6k_blocks(rng, n, k)
+        w = O.dequant_q6_k(blk)
+        op = torch.ops.alloy.gguf_q6_k_mm
+    x = torch.from_numpy(synth.activations(rng, m, k, np.float32)).to(tdt).to(DEV)
+    y = op(x, _dev(blk))
+    assert y.shape == (m, n) and y.dtype == tdt
+    assert_close(to_np(y), _ref(x, w, tdt), tdt, f"gemm {fmt} {m}x{n}x{k} {dt}")
+    assert _lib.load().alloyb_device_error(0) == 0
+
+
+def test_gemm_rows_agree_with_gemv_path():
+    """The same matrix through the GEMV family (M=8) and the GEMM (M=64, first 8 rows equal inputs)."""
+    rng = np.random.default_rng(77)
+    n, k = 256, 1024
+    blk = _dev(synth.q4k_blocks(rng, n, k))
+    x = torch.from_numpy(synth.activations(rng, 64, k)).to(DEV)
+    big = torch.ops.alloy.gguf_q4_k_mm(x, blk)
+    small = torch.ops.alloy.gguf_q4_k_mm(x[:8].contiguous(), blk)
+    # GEMV keeps fp32-exact weights, the GEMM rounds them to fp16 once: close, not identical
+    a, b = to_np(big[:8]).astype(np.float64), to_np(small).astype(np.float64)
+    assert np.abs(a - b).max() <= 1e-2 * np.sqrt((b * b).mean())
+
+
+def test_gated_prefill_two_gemms():
+    rng = np.random.default_rng(78)
+    m, n, k = 128, 256, 512
+    g, u = synth.q4k_blocks(rng, n, k), synth.q4k_blocks(rng, n, k)
+    x = torch.from_numpy(synth.activations(rng, m, k, np.float32)).to(torch.bfloat16).to(DEV)
+    y = torch.ops.alloy.gguf_q4_k_silu(x, _dev(g), _dev(u))
+    gate = torch.from_numpy(_ref(x, O.dequant_q4_k(g), torch.bfloat16)).to(torch.bfloat16).double().numpy()
+    up = torch.from_numpy(_ref(x, O.dequant_q4_k(u), torch.bfloat16)).to(torch.bfloat16).double().numpy()
+    assert_close(to_np(y), O.silu(gate) * up, torch.bfloat16, "prefill gate/up")
+
+
+@pytest.mark.parametrize("fmt,n,k", [("q4_k", 14336, 4096), ("q6_k", 4096, 14336)])
+def test_gemm_full_size_sampled_columns(fmt, n, k):
+    """The benchmark-sized prefill GEMM (4096 tokens), checked on 48 sampled output columns."""
+    rng = np.random.default_rng(5)
+    m = 4096
+    gen = torch.Generator(device=DEV).manual_seed(3)
+    blk = (synth.q4k_blocks_device if fmt == "q4_k" else synth.q6k_blocks_device)(n, k, gen, DEV)
+    x = torch.randn((m, k), device=DEV, generator=gen).to(torch.bfloat16)
+    op = torch.ops.alloy.gguf_q4_k_mm if fmt == "q4_k" else torch.ops.alloy.gguf_q6_k_mm
+    y = op(x, blk)
+    cols = np.sort(rng.choice(n, size=48, replace=False))
+    sub = blk[torch.from_numpy(cols).to(DEV)].cpu().numpy()
+    w = O.dequant_q4_k(sub) if fmt == "q4_k" else O.dequant_q6_k(sub)
+    assert_close(to_np(y[:, torch.from_numpy(cols).to(DEV)]), _ref(x, w, torch.bfloat16), torch.bfloat16,
+                 f"full-size {fmt}")
+    assert _lib.load().alloyb_device_error(0) == 0
