@@ -153,13 +153,27 @@ __device__ __forceinline__ void load_v(const RowRef<LAYOUT, D>& r, int lane, flo
     if (r.codes == nullptr) return;
     if (LAYOUT == ALLOYB_KV_F16) {
         const __half* p = reinterpret_cast<const __half*>(r.codes) + d0;
+        if (DPL == 4) {
+            const uint2 w = __ldg(reinterpret_cast<const uint2*>(p));
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+            const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+            v[0] = a.x; v[1] = a.y; v[2 % DPL] = c.x; v[3 % DPL] = c.y;
+        } else {
 #pragma unroll
-        for (int e = 0; e < DPL; ++e) v[e] = __half2float(__ldg(p + e));
+            for (int e = 0; e < DPL; ++e) v[e] = __half2float(__ldg(p + e));
+        }
     } else if (LAYOUT == ALLOYB_KV_Q8_SPLIT) {
         const float s = __half2float(__ldg(r.scales + d0 / 32));
         const int8_t* p = reinterpret_cast<const int8_t*>(r.codes) + d0;
+        if (DPL == 4) {
+            const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(p));
 #pragma unroll
-        for (int e = 0; e < DPL; ++e) v[e] = s * static_cast<float>(__ldg(p + e));
+            for (int e = 0; e < DPL; ++e)
+                v[e] = s * static_cast<float>(static_cast<int8_t>((w >> (8 * (e & 3))) & 0xffu));
+        } else {
+#pragma unroll
+            for (int e = 0; e < DPL; ++e) v[e] = s * static_cast<float>(__ldg(p + e));
+        }
     } else {
         const uint8_t* blk = r.codes + (d0 / 32) * KV_BLOCK_BYTES;
         const float s = half_bits_to_f32(__ldg(reinterpret_cast<const uint16_t*>(blk)));
@@ -230,16 +244,30 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(AttnParams
 #pragma unroll
             for (int e = 0; e < DPL; ++e) o[g][e] *= alpha;
         }
+        // P*V: the lanes own DPL dims each; token rows are fetched eight at a time so that eight
+        // independent loads are in flight before the first multiply-add needs its data
         const int cnt = min(32, t1 - c0);
-        for (int tt = 0; tt < cnt; ++tt) {
-            const RowRef<LAYOUT, D> vr = row_ref<LAYOUT, D>(P.kv, 1, b, kvh, P.KV_H, c0 + tt, nullptr);
-            float v[DPL];
-            load_v<LAYOUT, D>(vr, lane, v);
+        for (int tb = 0; tb < cnt; tb += 8) {
+            float v[8][DPL];
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float pt = __shfl_sync(0xffffffffu, p[g], tt);
+            for (int u = 0; u < 8; ++u) {
+                if (tb + u < cnt) {
+                    const RowRef<LAYOUT, D> vr =
+                        row_ref<LAYOUT, D>(P.kv, 1, b, kvh, P.KV_H, c0 + tb + u, nullptr);
+                    load_v<LAYOUT, D>(vr, lane, v[u]);
+                } else {
 #pragma unroll
-                for (int e = 0; e < DPL; ++e) o[g][e] = fmaf(pt, v[e], o[g][e]);
+                    for (int e = 0; e < DPL; ++e) v[u][e] = 0.f;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float pt = __shfl_sync(0xffffffffu, p[g], (tb + u) & 31);
+#pragma unroll
+                    for (int e = 0; e < DPL; ++e) o[g][e] = fmaf(pt, v[u][e], o[g][e]);
+                }
             }
         }
     }
@@ -380,14 +408,21 @@ extern "C" int alloyb_attn_decode(int layout, const void* q, int64_t q_batch_str
     ws += align_up(bh * ATTN_MAX_SPLITS * sizeof(float), 256);
     P.part_o = reinterpret_cast<float*>(ws);
 
-    // enough CTAs (4 warps each) to fill the machine about four times over, at least 128 tokens
-    // (one 32-token chunk per warp) per split
+    // Split count: the (b, kv head) pairs times the splits run in waves of about three CTAs per
+    // SM; a split costs its tokens (whole 64-token passes of the four warps) plus a fixed start-up
+    // and merge share, and every extra split lengthens the final merge.  Take the cheapest.
     const int ctas = B * KV_H;
-    int splits = (148 * 4 + ctas - 1) / ctas;
-    const int by_len = (S_max + 127) / 128;
-    if (splits > by_len) splits = by_len;
-    if (splits > ATTN_MAX_SPLITS) splits = ATTN_MAX_SPLITS;
-    if (splits < 1) splits = 1;
+    const int by_len = (S_max + 63) / 64;
+    int max_s = by_len < ATTN_MAX_SPLITS ? by_len : ATTN_MAX_SPLITS;
+    if (max_s < 1) max_s = 1;
+    int splits = 1;
+    int64_t best = INT64_MAX;
+    for (int s = 1; s <= max_s; ++s) {
+        const int64_t waves = (static_cast<int64_t>(ctas) * s + 148 * 3 - 1) / (148 * 3);
+        const int64_t per = ((S_max + s - 1) / s + 63) / 64 * 64 + 256;
+        const int64_t cost = waves * per + 8 * s;
+        if (cost < best) { best = cost; splits = s; }
+    }
     P.splits = splits;
 
     if (write_kv) {
@@ -396,6 +431,9 @@ extern "C" int alloyb_attn_decode(int layout, const void* q, int64_t q_batch_str
         if (rc != ALLOYB_OK) return rc;
     }
     const int G = H / KV_H;
+    if (D == 128 && G <= 8)
+        return launch_attn_mma(layout, q, q_batch_stride, q_head_stride, q_dtype, P.kv, pos, pos_count, out, B, H,
+                               KV_H, P.scale_log2, P.splits, P.part_o, P.part_lse, P.counters, P.status, st);
     switch (layout) {
         case ALLOYB_KV_F16: return launch_attn_d<ALLOYB_KV_F16>(P, D, G, st);
         case ALLOYB_KV_Q8_SPLIT: return launch_attn_d<ALLOYB_KV_Q8_SPLIT>(P, D, G, st);

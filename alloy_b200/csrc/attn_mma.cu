@@ -1,0 +1,522 @@
+// Tensor-core decode attention (head_dim 128, up to 8 query heads per KV head).
+//
+// A warp takes 16-token tiles.  Scores: S[head, token] = Q[head, d] * K[token, d]^T as
+// mma.sync.m16n8k16 with the group's query heads as the (padded) M rows, eight tokens as N and the
+// head dimension as K; the C fragment of two such products is exactly the A fragment of the
+// P * V product (M = heads, K = 16 tokens, N = 8 output dims), so probabilities never leave
+// registers.  The contraction index of either product may be permuted freely as long as both
+// operands agree, which is used to make every thread's loads contiguous:
+//   * K operand: thread (g, t) reads 8 consecutive dims of token g -> two k-steps of the S product;
+//   * V operand: thread (g, t) reads 4 consecutive dims (4g..4g+3 of a 32-dim block) of its four
+//     tokens and transposes them in registers; output column g of the e-th product of the block
+//     is dim 32*kp + 4g + e.
+// q8_0 caches: codes enter the MMA as unsigned bytes u = code + 128 in fp16 SUBNORMAL form
+// (u * 2^-24, no int->float conversion); the block scale multiplies the block's partial sum
+// afterwards and the +128 is taken out with sum(q) resp. sum(P') -- all in fp32.
+// The paged layout (34-byte blocks, 2-byte aligned) is staged per 16-token page through shared
+// memory with two bulk copies per tile; the other layouts are read straight from global memory.
+#include "kv.cuh"
+
+namespace alloyb {
+
+namespace am {
+
+constexpr int D = 128;
+constexpr int NKP = D / 32;
+constexpr int WARPS = 4;
+constexpr float NEG_BIG = -1.0e30f;
+constexpr int SLAB = PAGE_TOKENS * NKP * KV_BLOCK_BYTES;     // 2176 bytes: one page of K (or V) of one head
+constexpr uint32_t SPIN = 1u << 22;
+
+__device__ int g_attn_error = 0;
+
+struct Params {
+    const void* q;
+    int64_t q_bs, q_hs;
+    int q_dtype;
+    KVPtrs kv;
+    const int32_t* pos;
+    int pos_count;
+    void* out;
+    int B, H, KV_H, G;
+    float scale_log2;
+    int splits;
+    float* part_o;
+    float* part_lse;
+    unsigned int* counters;
+    int* status;
+};
+
+__device__ __forceinline__ uint32_t s32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+__device__ __forceinline__ void mma(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    // rows 8..15 of A are zero (at most 8 query heads): a1 = a3 = 0
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t lds32(const void* p) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(s32(p)));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(const void* p) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(s32(p)));
+    return v;
+}
+// n (1 or 2) 32-bit words starting at a 2-byte-aligned shared address
+__device__ __forceinline__ void lds_words_align2(const uint8_t* p, uint32_t& w0, uint32_t& w1, bool two) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const uint8_t* base = reinterpret_cast<const uint8_t*>(a & ~uintptr_t(3));
+    const uint32_t x0 = lds32(base), x1 = lds32(base + 4);
+    if (a & 2u) {
+        w0 = __funnelshift_r(x0, x1, 16);
+        if (two) w1 = __funnelshift_r(x1, lds32(base + 8), 16);
+    } else {
+        w0 = x0;
+        if (two) w1 = x1;
+    }
+}
+__device__ __forceinline__ void bar_init(uint64_t* b, uint32_t n) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(n));
+}
+__device__ __forceinline__ void bar_expect(uint64_t* b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_wait(uint64_t* b, uint32_t parity) {
+    for (uint32_t i = 0; i < SPIN; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(s32(b)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (i > 32) __nanosleep(64);
+    }
+    atomicExch(&g_attn_error, 4);
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     s32(dst)),
+                 "l"(src), "r"(bytes), "r"(s32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ float2 unpack_h2(uint32_t v) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&v));
+}
+__device__ __forceinline__ float q_elem(const void* q, int dtype, int64_t i) {
+    if (dtype == ALLOYB_F16) return __half2float(static_cast<const __half*>(q)[i]);
+    if (dtype == ALLOYB_BF16)
+        return __half2float(__float2half_rn(__bfloat162float(static_cast<const __nv_bfloat16*>(q)[i])));
+    return __half2float(__float2half_rn(static_cast<const float*>(q)[i]));
+}
+__device__ __forceinline__ void out_elem(void* out, int dtype, int64_t i, float v) {
+    if (dtype == ALLOYB_F16) static_cast<__half*>(out)[i] = __float2half_rn(v);
+    else if (dtype == ALLOYB_BF16) static_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(v);
+    else static_cast<float*>(out)[i] = v;
+}
+
+struct WarpStage {                       // paged layout only
+    uint8_t k[2][SLAB];
+    uint8_t v[2][SLAB];
+};
+
+template <int LAYOUT>
+__global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
+    constexpr bool Q8 = LAYOUT != ALLOYB_KV_F16;
+    constexpr bool PAGED = LAYOUT == ALLOYB_KV_Q8_PAGED;
+    __shared__ float sm_m[WARPS][8], sm_l[WARPS][8];
+    __shared__ int s_last;
+    // the page stages (paged layout) and, after the tile loop, the per-warp output rows share one buffer
+    constexpr int O_BYTES = WARPS * 8 * D * 4;
+    constexpr int STAGE_BYTES = PAGED ? WARPS * static_cast<int>(sizeof(WarpStage)) : 0;
+    __shared__ __align__(16) uint8_t sm_buf[O_BYTES > STAGE_BYTES ? O_BYTES : STAGE_BYTES];
+    __shared__ __align__(8) uint64_t sm_bar[WARPS][2];
+    uint8_t* sm_stage = sm_buf;
+    float (*sm_o)[8][D] = reinterpret_cast<float (*)[8][D]>(sm_buf);
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int G = P.G;
+    if (PAGED && lane == 0) {
+        bar_init(&sm_bar[warp][0], 1);
+        bar_init(&sm_bar[warp][1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    pdl_wait();
+    int pos = P.pos[P.pos_count == 1 ? 0 : b];
+    if (pos >= P.kv.S_max) {
+        if (threadIdx.x == 0 && P.status) atomicOr(P.status, KV_STATUS_POS_RANGE);
+        pos = P.kv.S_max - 1;
+    }
+    const int len = pos + 1;
+
+    // ---- Q fragments (rows = heads of this group; rows >= G are zero) and per-block sums of q
+    uint32_t qa[NKP][2][2];
+    float qsum[NKP];
+#pragma unroll
+    for (int kp = 0; kp < NKP; ++kp) {
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (g < G) {
+                const int64_t base = b * P.q_bs + static_cast<int64_t>(kvh * G + g) * P.q_hs + 32 * kp + 8 * t + 4 * j;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[e] = q_elem(P.q, P.q_dtype, base + e);
+            }
+            qa[kp][j][0] = pack_h2(v[0], v[1]);
+            qa[kp][j][1] = pack_h2(v[2], v[3]);
+            s += (v[0] + v[1]) + (v[2] + v[3]);
+        }
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        qsum[kp] = s;
+    }
+
+    // ---- this CTA's token range, in 16-token tiles
+    int chunk = (len + P.splits - 1) / P.splits;
+    chunk = (chunk + 63) & ~63;                       // whole tiles for each of the four warps
+    const int t0 = split * chunk;
+    const int t1 = min(len, t0 + chunk);
+    const int n_tiles = t1 > t0 ? (t1 - t0 + 15) / 16 : 0;
+
+    float m_run = NEG_BIG, l_run = 0.f;               // for head g (replicated over t)
+    float o[NKP * 4][2];                              // [(kp, e)][column 2t / 2t+1]
+    float ocorr[NKP];
+    float zz2 = 0.f, zz3 = 0.f;                       // rows 8..15 of every C fragment (always 0)
+#pragma unroll
+    for (int i = 0; i < NKP * 4; ++i) o[i][0] = o[i][1] = 0.f;
+#pragma unroll
+    for (int kp = 0; kp < NKP; ++kp) ocorr[kp] = 0.f;
+
+    const int64_t head_row = (static_cast<int64_t>(b) * P.KV_H + kvh) * P.kv.S_max;
+    WarpStage* st = reinterpret_cast<WarpStage*>(sm_stage) + (PAGED ? warp : 0);
+    const int32_t* table = static_cast<const int32_t*>(P.kv.k1) + static_cast<int64_t>(b) * P.kv.max_pages;
+
+    auto issue_page = [&](int tile_idx, int slot) {
+        // lane 0: both slabs of the page that holds tokens [tile*16, tile*16+16)
+        const int tok0 = t0 + tile_idx * 16;
+        int64_t page = table[tok0 / PAGE_TOKENS];
+        if (page < 0 || page >= P.kv.num_pages) {
+            if (P.status) atomicOr(P.status, KV_STATUS_PAGE_RANGE);
+            page = 0;                                  // stay in bounds; the tile's tokens are masked below
+        }
+        const uint8_t* pool = static_cast<const uint8_t*>(P.kv.k0);
+        bar_expect(&sm_bar[warp][slot], 2 * SLAB);
+        bulk_g2s(st->k[slot], pool + paged_row_offset(page, 0, kvh, 0, P.KV_H, D), SLAB, &sm_bar[warp][slot]);
+        bulk_g2s(st->v[slot], pool + paged_row_offset(page, 1, kvh, 0, P.KV_H, D), SLAB, &sm_bar[warp][slot]);
+    };
+
+    bool ok = true;
+    int n_mine = 0;
+    if (PAGED && warp < n_tiles && lane == 0) issue_page(warp, 0);
+    for (int tile = warp; tile < n_tiles; tile += WARPS, ++n_mine) {
+        const int tok0 = t0 + tile * 16;
+        const int slot = n_mine & 1;
+        if (PAGED) {
+            if (tile + WARPS < n_tiles && lane == 0) issue_page(tile + WARPS, slot ^ 1);
+            if (ok) ok = bar_wait(&sm_bar[warp][slot], (n_mine >> 1) & 1);
+            if (!ok) continue;
+        }
+        // ---------------- S = Q K^T
+        float s[2][2];
+#pragma unroll
+        for (int tb = 0; tb < 2; ++tb) {
+            const int tok = min(tok0 + 8 * tb + g, t1 - 1);          // B column of this thread (clamped)
+            float sc[2] = {0.f, 0.f};
+            if (!Q8) {
+                float c[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint4* kr = reinterpret_cast<const uint4*>(static_cast<const __half*>(P.kv.k0) + (head_row + tok) * D) + t;
+#pragma unroll
+                for (int kp = 0; kp < NKP; ++kp) {
+                    const uint4 kv = __ldg(kr + kp * 4);
+                    mma(c, qa[kp][0][0], qa[kp][0][1], kv.x, kv.y);
+                    mma(c, qa[kp][1][0], qa[kp][1][1], kv.z, kv.w);
+                }
+                sc[0] = c[0];
+                sc[1] = c[1];
+                zz2 = c[2];
+                zz3 = c[3];
+            } else {
+#pragma unroll
+                for (int kp = 0; kp < NKP; ++kp) {
+                    uint32_t w0, w1;
+                    float ks[2];
+                    if (PAGED) {
+                        lds_words_align2(st->k[slot] + (8 * tb + g) * (NKP * KV_BLOCK_BYTES) + kp * KV_BLOCK_BYTES + 2 + 8 * t,
+                                         w0, w1, true);
+#pragma unroll
+                        for (int e = 0; e < 2; ++e)
+                            ks[e] = tok0 + 8 * tb + 2 * t + e < t1
+                                        ? half_bits_to_f32(lds16(st->k[slot] + (8 * tb + 2 * t + e) * (NKP * KV_BLOCK_BYTES) + kp * KV_BLOCK_BYTES))
+                                        : 0.f;
+                    } else {
+                        const uint2 cw = __ldg(reinterpret_cast<const uint2*>(static_cast<const int8_t*>(P.kv.k0) + (head_row + tok) * D + 32 * kp + 8 * t));
+                        w0 = cw.x;
+                        w1 = cw.y;
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int tk = min(tok0 + 8 * tb + 2 * t + e, t1 - 1);
+                            ks[e] = __half2float(__ldg(static_cast<const __half*>(P.kv.k1) + (head_row + tk) * NKP + kp));
+                        }
+                    }
+                    const uint32_t u0 = w0 ^ 0x80808080u, u1 = w1 ^ 0x80808080u;
+                    float c[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma(c, qa[kp][0][0], qa[kp][0][1], prmt(u0, 0u, 0x4140u), prmt(u0, 0u, 0x4342u));
+                    mma(c, qa[kp][1][0], qa[kp][1][1], prmt(u1, 0u, 0x4140u), prmt(u1, 0u, 0x4342u));
+                    sc[0] = fmaf(ks[0], fmaf(c[0], 16777216.0f, -128.0f * qsum[kp]), sc[0]);
+                    sc[1] = fmaf(ks[1], fmaf(c[1], 16777216.0f, -128.0f * qsum[kp]), sc[1]);
+                    zz2 = c[2];
+                    zz3 = c[3];
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const bool valid = tok0 + 8 * tb + 2 * t + e < t1;
+                s[tb][e] = valid ? sc[e] * P.scale_log2 : NEG_BIG;
+            }
+        }
+        // ---------------- online softmax for head g (the four lanes of a group hold the 16 tokens)
+        float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const float alpha = exp2f(m_run - m_new);
+        float p[2][2];
+        float ls = 0.f;
+#pragma unroll
+        for (int tb = 0; tb < 2; ++tb)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                p[tb][e] = s[tb][e] > 0.5f * NEG_BIG ? exp2f(s[tb][e] - m_new) : 0.f;
+                ls += p[tb][e];
+            }
+        ls += __shfl_xor_sync(0xffffffffu, ls, 1);
+        ls += __shfl_xor_sync(0xffffffffu, ls, 2);
+        l_run = l_run * alpha + ls;
+        m_run = m_new;
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll
+            for (int i = 0; i < NKP * 4; ++i) {
+                o[i][0] *= alpha;
+                o[i][1] *= alpha;
+            }
+#pragma unroll
+            for (int kp = 0; kp < NKP; ++kp) ocorr[kp] *= alpha;
+        }
+        // ---------------- O += P V
+        int vtok[4];                                   // this thread's four contraction tokens
+#pragma unroll
+        for (int i = 0; i < 4; ++i) vtok[i] = min(tok0 + (i >> 1) * 8 + 2 * t + (i & 1), t1 - 1);
+        // P enters the tensor core as fp16 hi + lo halves (two products), which keeps ~22 bits of it
+        uint32_t pa0 = pack_h2(p[0][0], p[0][1]), pa2 = pack_h2(p[1][0], p[1][1]);
+        uint32_t pl0, pl2;
+        {
+            const float2 r0 = unpack_h2(pa0), r2 = unpack_h2(pa2);
+            pl0 = pack_h2(p[0][0] - r0.x, p[0][1] - r0.y);
+            pl2 = pack_h2(p[1][0] - r2.x, p[1][1] - r2.y);
+        }
+#pragma unroll
+        for (int kp = 0; kp < NKP; ++kp) {
+            uint32_t b0[4], b1[4];                     // B fragments of the four products e = 0..3
+            if (!Q8) {
+                uint2 w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    w[i] = __ldg(reinterpret_cast<const uint2*>(static_cast<const __half*>(P.kv.v0) + (head_row + vtok[i]) * D + 32 * kp + 4 * g));
+                b0[0] = prmt(w[0].x, w[1].x, 0x5410u); b0[1] = prmt(w[0].x, w[1].x, 0x7632u);
+                b0[2] = prmt(w[0].y, w[1].y, 0x5410u); b0[3] = prmt(w[0].y, w[1].y, 0x7632u);
+                b1[0] = prmt(w[2].x, w[3].x, 0x5410u); b1[1] = prmt(w[2].x, w[3].x, 0x7632u);
+                b1[2] = prmt(w[2].y, w[3].y, 0x5410u); b1[3] = prmt(w[2].y, w[3].y, 0x7632u);
+            } else {
+                uint32_t w[4];
+                float vs[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (PAGED) {
+                        const uint8_t* row = st->v[slot] + ((i >> 1) * 8 + 2 * t + (i & 1)) * (NKP * KV_BLOCK_BYTES) + kp * KV_BLOCK_BYTES;
+                        uint32_t dummy;
+                        lds_words_align2(row + 2 + 4 * g, w[i], dummy, false);
+                        vs[i] = tok0 + (i >> 1) * 8 + 2 * t + (i & 1) < t1 ? half_bits_to_f32(lds16(row)) : 0.f;
+                    } else {
+                        w[i] = __ldg(reinterpret_cast<const uint32_t*>(static_cast<const int8_t*>(P.kv.v0) + (head_row + vtok[i]) * D + 32 * kp + 4 * g));
+                        vs[i] = __half2float(__ldg(static_cast<const __half*>(P.kv.v1) + (head_row + vtok[i]) * NKP + kp));
+                    }
+                    w[i] ^= 0x80808080u;
+                }
+                // 4x4 byte transpose: T[e] = (w0.b[e], w1.b[e], w2.b[e], w3.b[e])
+                const uint32_t lo01 = prmt(w[0], w[1], 0x5140u), hi01 = prmt(w[0], w[1], 0x7362u);
+                const uint32_t lo23 = prmt(w[2], w[3], 0x5140u), hi23 = prmt(w[2], w[3], 0x7362u);
+                const uint32_t T[4] = {prmt(lo01, lo23, 0x5410u), prmt(lo01, lo23, 0x7632u),
+                                       prmt(hi01, hi23, 0x5410u), prmt(hi01, hi23, 0x7632u)};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    b0[e] = prmt(T[e], 0u, 0x4140u);
+                    b1[e] = prmt(T[e], 0u, 0x4342u);
+                }
+                // P' = p * (block scale of the token) as fp16 hi + lo; keep its sum for the +128
+                const float f0 = p[0][0] * vs[0], f1 = p[0][1] * vs[1], f2 = p[1][0] * vs[2], f3 = p[1][1] * vs[3];
+                pa0 = pack_h2(f0, f1);
+                pa2 = pack_h2(f2, f3);
+                const float2 r0 = unpack_h2(pa0), r2 = unpack_h2(pa2);
+                pl0 = pack_h2(f0 - r0.x, f1 - r0.y);
+                pl2 = pack_h2(f2 - r2.x, f3 - r2.y);
+                const float2 q0 = unpack_h2(pl0), q2 = unpack_h2(pl2);
+                ocorr[kp] += ((r0.x + r0.y) + (r2.x + r2.y)) + ((q0.x + q0.y) + (q2.x + q2.y));
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float c[4] = {o[kp * 4 + e][0], o[kp * 4 + e][1], zz2, zz3};
+                mma(c, pa0, pa2, b0[e], b1[e]);
+                mma(c, pl0, pl2, b0[e], b1[e]);
+                o[kp * 4 + e][0] = c[0];
+                o[kp * 4 + e][1] = c[1];
+                zz2 = c[2];
+                zz3 = c[3];
+            }
+        }
+        __syncwarp();
+    }
+    if (PAGED && !ok) {
+        for (uint32_t i = 0; i < 1024; ++i) __nanosleep(512);        // let copies in flight land
+    }
+
+    // ---- this warp's state -> shared memory (head g; the thread's dims are 32kp + 4(2t+c) + e)
+    if (Q8) {
+#pragma unroll
+        for (int kp = 0; kp < NKP; ++kp) {
+            float cs = ocorr[kp];
+            cs += __shfl_xor_sync(0xffffffffu, cs, 1);
+            cs += __shfl_xor_sync(0xffffffffu, cs, 2);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) o[kp * 4 + e][c] = fmaf(o[kp * 4 + e][c], 16777216.0f, -128.0f * cs);
+        }
+    }
+    __syncthreads();                                   // every warp is done with the page stages
+    if (t == 0) { sm_m[warp][g] = m_run; sm_l[warp][g] = l_run; }
+#pragma unroll
+    for (int kp = 0; kp < NKP; ++kp)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) sm_o[warp][g][32 * kp + 4 * (2 * t + c) + e] = o[kp * 4 + e][c];
+    __syncthreads();
+
+    // ---- merge the four warps, write the split's partial, let the last CTA combine the splits
+    for (int i = threadIdx.x; i < G * D; i += WARPS * 32) {
+        const int hg = i / D, d = i - hg * D;
+        float mx = NEG_BIG;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) mx = fmaxf(mx, sm_m[w][hg]);
+        float lt = 0.f, ot = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const float sc = exp2f(sm_m[w][hg] - mx);
+            lt = fmaf(sm_l[w][hg], sc, lt);
+            ot = fmaf(sm_o[w][hg][d], sc, ot);
+        }
+        const int h = kvh * G + hg;
+        const int64_t pi = (static_cast<int64_t>(b) * P.H + h) * P.splits + split;
+        P.part_o[pi * D + d] = lt > 0.f ? ot / lt : 0.f;
+        if (d == 0) P.part_lse[pi] = lt > 0.f ? mx + log2f(lt) : NEG_BIG;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int prev = atomicAdd(P.counters + b * P.KV_H + kvh, 1u);
+        s_last = (prev == static_cast<unsigned int>(P.splits) - 1u);
+        if (s_last) P.counters[b * P.KV_H + kvh] = 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // split weights once per head (into the now-free per-warp rows), then the weighted sums with
+    // eight independent loads in flight per thread
+    float* wgt = reinterpret_cast<float*>(sm_buf);            // [G][splits], splits <= 64
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * P.splits; i += WARPS * 32)
+        wgt[i] = __ldcg(P.part_lse + (static_cast<int64_t>(b) * P.H + kvh * G + i / P.splits) * P.splits + i % P.splits);
+    __syncthreads();
+    if (threadIdx.x < G) {
+        float* w = wgt + threadIdx.x * P.splits;
+        float mx = NEG_BIG;
+        for (int s2 = 0; s2 < P.splits; ++s2) mx = fmaxf(mx, w[s2]);
+        float sum = 0.f;
+        for (int s2 = 0; s2 < P.splits; ++s2) {
+            const float e = w[s2] > 0.5f * NEG_BIG ? exp2f(w[s2] - mx) : 0.f;
+            w[s2] = e;
+            sum += e;
+        }
+        const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+        for (int s2 = 0; s2 < P.splits; ++s2) w[s2] *= inv;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * D; i += WARPS * 32) {
+        const int hg = i / D, d = i - hg * D;
+        const int h = kvh * G + hg;
+        const float* po = P.part_o + (static_cast<int64_t>(b) * P.H + h) * P.splits * D + d;
+        const float* w = wgt + hg * P.splits;
+        float acc = 0.f;
+        int s2 = 0;
+        for (; s2 + 8 <= P.splits; s2 += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __ldcg(po + static_cast<int64_t>(s2 + u) * D);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc = fmaf(w[s2 + u], v[u], acc);
+        }
+        for (; s2 < P.splits; ++s2) acc = fmaf(w[s2], __ldcg(po + static_cast<int64_t>(s2) * D), acc);
+        out_elem(P.out, P.q_dtype, (static_cast<int64_t>(b) * P.H + h) * D + d, acc);
+    }
+}
+
+}  // namespace am
+
+// Launch the tensor-core kernel; the caller has validated shapes and laid the workspace out.
+int launch_attn_mma(int layout, const void* q, int64_t q_bs, int64_t q_hs, int q_dtype, const KVPtrs& kv,
+                    const int32_t* pos, int pos_count, void* out, int B, int H, int KV_H, float scale_log2,
+                    int splits, float* part_o, float* part_lse, unsigned int* counters, int* status,
+                    cudaStream_t st) {
+    am::Params P;
+    P.q = q; P.q_bs = q_bs; P.q_hs = q_hs; P.q_dtype = q_dtype;
+    P.kv = kv; P.pos = pos; P.pos_count = pos_count; P.out = out;
+    P.B = B; P.H = H; P.KV_H = KV_H; P.G = H / KV_H;
+    P.scale_log2 = scale_log2; P.splits = splits;
+    P.part_o = part_o; P.part_lse = part_lse; P.counters = counters; P.status = status;
+    const dim3 grid(splits, KV_H, B);
+    switch (layout) {
+        case ALLOYB_KV_F16: am::attn_mma_kernel<ALLOYB_KV_F16><<<grid, am::WARPS * 32, 0, st>>>(P); break;
+        case ALLOYB_KV_Q8_SPLIT: am::attn_mma_kernel<ALLOYB_KV_Q8_SPLIT><<<grid, am::WARPS * 32, 0, st>>>(P); break;
+        default: am::attn_mma_kernel<ALLOYB_KV_Q8_PAGED><<<grid, am::WARPS * 32, 0, st>>>(P); break;
+    }
+    return check_launch();
+}
+
+int attn_mma_device_error(int clear) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, am::g_attn_error, sizeof(int)) != cudaSuccess) return 0;
+    if (clear && v) {
+        const int z = 0;
+        cudaMemcpyToSymbol(am::g_attn_error, &z, sizeof(int));
+    }
+    return v;
+}
+
+}  // namespace alloyb

@@ -31,4 +31,11 @@ int launch_kv_append(int layout, const void* new_k, const void* new_v, int64_t s
                      const KVPtrs& kv, const int32_t* pos, int pos_count, int B, int KV_H, int D,
                      int* status, cudaStream_t st);
 
+// Tensor-core decode attention (head_dim 128, <= 8 query heads per KV head); see attn_mma.cu.
+int launch_attn_mma(int layout, const void* q, int64_t q_bs, int64_t q_hs, int q_dtype, const KVPtrs& kv,
+                    const int32_t* pos, int pos_count, void* out, int B, int H, int KV_H, float scale_log2,
+                    int splits, float* part_o, float* part_lse, unsigned int* counters, int* status,
+                    cudaStream_t st);
+int attn_mma_device_error(int clear);
+
 }  // namespace alloyb

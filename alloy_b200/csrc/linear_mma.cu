@@ -26,6 +26,7 @@
 #include <cstdlib>
 #include <type_traits>
 
+#include "kv.cuh"
 #include "linear.cuh"
 #include "linear_rows.cuh"
 
@@ -694,7 +695,7 @@ extern "C" int alloyb_device_error(int clear) {
     int v = 0;
     cudaError_t e = cudaMemcpyFromSymbol(&v, alloyb::g_device_error, sizeof(int));
     if (e != cudaSuccess) { alloyb::set_cuda_error(e); return ALLOYB_E_CUDA; }
-    const int v_tc = alloyb::gemm_tc_device_error(clear);
+    const int v_tc = alloyb::gemm_tc_device_error(clear) | alloyb::attn_mma_device_error(clear);
     if (clear && v) {
         const int z = 0;
         e = cudaMemcpyToSymbol(alloyb::g_device_error, &z, sizeof(int));
