@@ -60,7 +60,7 @@ def build_library(force: bool = False, verbose: bool = False) -> pathlib.Path:
                     print(out, file=sys.stderr)
     objs = [OBJ / (s.stem + ".o") for s in sources]
     if jobs or not LIB.exists():
-        cmd = [nvcc, *ARCH, "-shared", "-o", str(LIB), *map(str, objs), "-lcuda"]
+        cmd = [nvcc, *ARCH, "-shared", "-o", str(LIB), *map(str, objs)]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")

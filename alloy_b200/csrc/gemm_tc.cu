@@ -442,7 +442,23 @@ int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, cu
     const cuuint64_t gstr[1] = {static_cast<cuuint64_t>(K) * 2};
     const cuuint32_t box[2] = {BK, BM};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult cr = cuTensorMapEncodeTiled(
+    // The driver's tensor-map encoder is looked up through the runtime, so the library carries no
+    // link-time dependency on the driver and still loads (for symbol checks) on a machine without one.
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr);
+        if (e != cudaSuccess || qr != cudaDriverEntryPointSuccess || !fn) {
+            set_cuda_error(e != cudaSuccess ? e : cudaErrorNotSupported);
+            return ALLOYB_E_CUDA;
+        }
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    const CUresult cr = encode(
         &map, dtype == ALLOYB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
         const_cast<void*>(x), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
