@@ -41,6 +41,7 @@ constexpr int Q4_CHUNK = MMA_CH * Q4K_BYTES;     // 1152
 constexpr int Q6_CHUNK = MMA_CH * Q6K_BYTES;     // 1680
 constexpr int Q4_STRIDE = Q4_CHUNK + 32;         // words/row = 8 mod 32: conflict-free 64-bit reads
 constexpr int Q6_STRIDE = Q6_CHUNK;              // words/row = 4 mod 32: conflict-free 32-bit reads
+constexpr int Q4_STRIDE_SB = Q4_CHUNK + 16;      // one-token path: 16 mod 128 bytes, conflict-free 128-bit reads
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 __device__ int g_device_error = 0;               // sticky; read by alloyb_device_error()
@@ -311,6 +312,111 @@ __device__ __forceinline__ void q4k_superblock(uint32_t stage, int sb, float4* t
     __syncwarp();
 }
 
+// fp16 MMA with the accumulator passed as separate registers, and with a zero accumulator.
+__device__ __forceinline__ void mma_f16_acc(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                            uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_f16_zero(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "{\n\t.reg .f32 z;\n\tmov.f32 z, 0f00000000;\n\t"
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{z,z,z,z};\n\t}"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// One Q4_K super-block against ONE fp16 token, with the eight MMA columns used for the eight
+// sub-blocks instead of for tokens.
+//
+// Lane (g, t) reads the 32 quant bytes of group t (sub-block 2t in the low nibbles, 2t+1 in the
+// high ones) of rows g and g+8 with four 128-bit loads.  A 32-bit word gives four A registers with
+// one shift and four ANDs: the nibbles of bytes (0, 2) and of bytes (1, 3), low ones as n*2^-24,
+// high ones as 16n*2^-24 (fp16 subnormals, exact).  In the B operand column n carries the token's
+// activations of sub-block n in the k slots of the lanes that own that sub-block and zero
+// elsewhere, so that after the sixteen MMAs of a super-block C_lo[row][2t] and C_hi[row][2t+1] hold
+// the per-sub-block sums  sum nib*x  (the other columns hold cross terms nobody reads).  The
+// sub-block scales are then applied to eight numbers per lane instead of to every MMA's output,
+// and  sum x  per sub-block comes from eight MMAs with A = 1 shared by all row tiles.
+template <int RT>
+__device__ __forceinline__ void q4k_superblock_sb(uint32_t stage, int sb, const __half* x, int kbase,
+                                                  float (&acc)[RT][1][4]) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    uint32_t xb[8][2];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) xb[j][0] = xb[j][1] = 0u;
+    if ((g >> 1) == t) {
+        const uint4* xp = reinterpret_cast<const uint4*>(x + kbase + 32 * g);   // sub-block g
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint4 v = __ldg(xp + q);
+            xb[2 * q][0] = prmt(v.x, v.y, 0x5410u);          // (x[4j], x[4j+2])
+            xb[2 * q][1] = prmt(v.x, v.y, 0x7632u);          // (x[4j+1], x[4j+3])
+            xb[2 * q + 1][0] = prmt(v.z, v.w, 0x5410u);
+            xb[2 * q + 1][1] = prmt(v.z, v.w, 0x7632u);
+        }
+    }
+    constexpr uint32_t ONE2 = QuantEnc<__half>::ONE2;
+    float sx[4];                                                              // sx[0], sx[1]: sub-blocks 2t, 2t+1
+    mma_f16_zero(sx, ONE2, ONE2, ONE2, ONE2, xb[0][0], xb[0][1]);
+#pragma unroll
+    for (int j = 1; j < 8; ++j) mma_f16_acc(sx, ONE2, ONE2, ONE2, ONE2, xb[j][0], xb[j][1]);
+
+    const int sh = 16 * (t & 1);
+#pragma unroll
+    for (int rt = 0; rt < RT; ++rt) {
+        const uint32_t rb = stage + (rt * 16 + g) * Q4_STRIDE_SB + sb * Q4K_BYTES;
+        const uint4 h0 = lds128(rb), h1 = lds128(rb + 8 * Q4_STRIDE_SB);
+        const uint4 p0 = lds128(rb + 16 + 32 * t), p1 = lds128(rb + 32 + 32 * t);
+        const uint4 r0 = lds128(rb + 8 * Q4_STRIDE_SB + 16 + 32 * t), r1 = lds128(rb + 8 * Q4_STRIDE_SB + 32 + 32 * t);
+        const uint32_t wg[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+        const uint32_t wh[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+        float clo[4], chi[4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t ug = wg[j] >> 8, uh = wh[j] >> 8;
+            if (j == 0) {
+                mma_f16_zero(clo, wg[j] & 0x000f000fu, wh[j] & 0x000f000fu, ug & 0x000f000fu, uh & 0x000f000fu,
+                             xb[j][0], xb[j][1]);
+                mma_f16_zero(chi, wg[j] & 0x00f000f0u, wh[j] & 0x00f000f0u, ug & 0x00f000f0u, uh & 0x00f000f0u,
+                             xb[j][0], xb[j][1]);
+            } else {
+                mma_f16_acc(clo, wg[j] & 0x000f000fu, wh[j] & 0x000f000fu, ug & 0x000f000fu, uh & 0x000f000fu,
+                            xb[j][0], xb[j][1]);
+                mma_f16_acc(chi, wg[j] & 0x00f000f0u, wh[j] & 0x00f000f0u, ug & 0x00f000f0u, uh & 0x00f000f0u,
+                            xb[j][0], xb[j][1]);
+            }
+        }
+        // 6-bit scales and mins of sub-blocks 2t, 2t+1 (llama.cpp's get_scale_min_k4, two at a time)
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            const uint4 h = rr ? h1 : h0;
+            const uint32_t wy = h.y >> sh, wz = h.z >> sh, ww = h.w >> sh;
+            uint32_t scp, mp;
+            if (t < 2) {
+                scp = wy & 0x3f3fu;
+                mp = wz & 0x3f3fu;
+            } else {
+                scp = (ww & 0x0f0fu) | ((wy >> 2) & 0x3030u);
+                mp = ((ww >> 4) & 0x0f0fu) | ((wz >> 2) & 0x3030u);
+            }
+            const float d = half_bits_to_f32(h.x & 0xffffu) * 16777216.0f;     // undoes the 2^-24
+            const float dmin = half_bits_to_f32(h.x >> 16);
+            const float c_lo = clo[2 * rr], c_hi = chi[2 * rr + 1] * 0.0625f;
+            float a = static_cast<float>(scp & 0xffu) * c_lo;
+            a = fmaf(static_cast<float>(scp >> 8), c_hi, a);
+            float m = static_cast<float>(mp & 0xffu) * sx[0];
+            m = fmaf(static_cast<float>(mp >> 8), sx[1], m);
+            acc[rt][0][2 * rr] = fmaf(d, a, fmaf(-dmin, m, acc[rt][0][2 * rr]));
+        }
+    }
+}
+
 // One Q6_K super-block.  tbl: RT*16 rows x 16 floats d*sc, stored [row][h][lhalf][j].
 template <typename XT, int RT, int NT>
 __device__ __forceinline__ void q6k_superblock(uint32_t stage, int sb, float4* tbl, const XT* x, int M,
@@ -397,8 +503,9 @@ struct SmemHeader {
     uint64_t empty[MMA_STAGES];
 };
 
-template <typename XT, int RT, int NT>
+template <typename XT, int RT, int NT, bool SB>
 __global__ void __launch_bounds__(MMA_THREADS) linear_mma_kernel(const MmaParams P) {
+    static_assert(!SB || (std::is_same<XT, __half>::value && NT == 1), "one-token path: fp16, one token group");
     extern __shared__ __align__(128) uint8_t smem[];
     SmemHeader* hdr = reinterpret_cast<SmemHeader*>(smem);
     float4* tbl_all = reinterpret_cast<float4*>(smem + 128);              // per consumer warp: RT KB
@@ -419,7 +526,7 @@ __global__ void __launch_bounds__(MMA_THREADS) linear_mma_kernel(const MmaParams
     const int nsb = P.K / QK_K;
     const int nchunks = (nsb + MMA_CH - 1) / MMA_CH;
     const int blk_bytes = (fmt == ALLOYB_Q4_K) ? Q4K_BYTES : Q6K_BYTES;
-    const int stride = (fmt == ALLOYB_Q4_K) ? Q4_STRIDE : Q6_STRIDE;
+    const int stride = (fmt == ALLOYB_Q4_K) ? (SB ? Q4_STRIDE_SB : Q4_STRIDE) : Q6_STRIDE;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < P.n_stages; ++s) {
@@ -482,7 +589,9 @@ __global__ void __launch_bounds__(MMA_THREADS) linear_mma_kernel(const MmaParams
         for (int sb = warp; sb < sb_n; sb += MMA_CONSUMERS) {
             const int kbase = (c * MMA_CH + sb) * QK_K;
             if (fmt == ALLOYB_Q4_K) {
-                if (P.magic_f16 || sizeof(XT) != 2 || !std::is_same<XT, __half>::value)
+                if constexpr (SB)
+                    q4k_superblock_sb<RT>(stage, sb, x, kbase, acc);
+                else if (P.magic_f16 || sizeof(XT) != 2 || !std::is_same<XT, __half>::value)
                     q4k_superblock<XT, RT, NT, false>(stage, sb, tbl, x, P.M, P.K, kbase, acc);
                 else
                     q4k_superblock<XT, RT, NT, true>(stage, sb, tbl, x, P.M, P.K, kbase, acc);
@@ -502,6 +611,22 @@ __global__ void __launch_bounds__(MMA_THREADS) linear_mma_kernel(const MmaParams
 
     // ---------------- cross-warp reduction + epilogue
     const int g = lane >> 2, t = lane & 3;
+    if constexpr (SB) {
+        // the one-token path keeps one partial per lane for rows g and g+8: fold the four t lanes
+        // (Q6_K tiles of the same launch already hold column sums; their t > 0 columns are tokens
+        // that do not exist and are never read)
+        if (fmt == ALLOYB_Q4_K) {
+#pragma unroll
+            for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+                for (int i = 0; i < 4; i += 2) {
+                    float v = acc[rt][0][i];
+                    v += __shfl_xor_sync(0xffffffffu, v, 1);
+                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    acc[rt][0][i] = v;
+                }
+        }
+    }
 #pragma unroll
     for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
@@ -550,10 +675,10 @@ static int magic_f16_flag() {
     return flag;
 }
 
-template <typename XT, int RT, int NT>
+template <typename XT, int RT, int NT, bool SB = false>
 static int launch_mma(const MmaParams& P, int grid, int smem_bytes, cudaStream_t st) {
     static bool configured = false;   // per template instance
-    auto kern = linear_mma_kernel<XT, RT, NT>;
+    auto kern = linear_mma_kernel<XT, RT, NT, SB>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
@@ -584,6 +709,10 @@ static int launch_mma_nt(MmaParams& P, int grid, int stage_rows_bytes, cudaStrea
     if (stages < 2) stages = 2;
     P.n_stages = stages;
     const int smem = fixed + stages * stage_rows_bytes;
+    if constexpr (std::is_same<XT, __half>::value) {
+        static const bool no_sb = [] { const char* e = std::getenv("ALLOYB_NO_SB"); return e && e[0] == '1'; }();
+        if (P.M == 1 && !P.magic_f16 && !no_sb) return launch_mma<XT, RT, 1, true>(P, grid, smem, st);
+    }
     switch (NTt) {
         case 1: return launch_mma<XT, RT, 1>(P, grid, smem, st);
         case 2: return launch_mma<XT, RT, 2>(P, grid, smem, st);
