@@ -25,6 +25,11 @@ int try_gated_fast(const void* x, const void* gate, const void* gate_scales, con
                    const void* up_scales, void* y, int M, int N, int K, int format, int act,
                    int dtype, cudaStream_t st);
 
+// Persistent streaming GEMV for one fp16 token against Q4_K matrices.
+int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg, int n_seg, bool gated, int act,
+                    const void* residual, cudaStream_t stream);
+int gemv_stream_device_error(int clear);
+
 // tcgen05 dequant-GEMM for prefill-sized M (one matrix).
 int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, cudaStream_t st);
 int gemm_tc_device_error(int clear);

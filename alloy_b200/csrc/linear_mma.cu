@@ -675,6 +675,11 @@ static int magic_f16_flag() {
     return flag;
 }
 
+static bool no_stream_flag() {
+    static const bool flag = [] { const char* e = std::getenv("ALLOYB_NO_STREAM"); return e && e[0] == '1'; }();
+    return flag;
+}
+
 template <typename XT, int RT, int NT, bool SB = false>
 static int launch_mma(const MmaParams& P, int grid, int smem_bytes, cudaStream_t st) {
     static bool configured = false;   // per template instance
@@ -737,6 +742,10 @@ int try_linear_fast(const void* x, int M, int K, int dtype, const WeightSeg* seg
     if (dtype != ALLOYB_F16 && dtype != ALLOYB_BF16) return ALLOYB_NOT_TAKEN;
     if (reinterpret_cast<uintptr_t>(x) % 16 || K % 8) return ALLOYB_NOT_TAKEN;
     if (M > 128) return ALLOYB_NOT_TAKEN;
+    if (!no_stream_flag()) {
+        const int rc = try_gemv_stream(x, M, K, dtype, seg, n_seg, false, 0, residual, st);
+        if (rc != ALLOYB_NOT_TAKEN) return rc;
+    }
     int stage_bytes = 0;
     for (int i = 0; i < n_seg; ++i) {
         if (!seg_ok(seg[i], K)) return ALLOYB_NOT_TAKEN;
@@ -787,6 +796,11 @@ int try_gated_fast(const void* x, const void* gate, const void* gate_scales, con
     WeightSeg us = gs;
     us.data = up;
     if (!seg_ok(gs, K) || !seg_ok(us, K)) return ALLOYB_NOT_TAKEN;
+    if (!no_stream_flag()) {
+        const WeightSeg pair[2] = {gs, us};
+        const int rc = try_gemv_stream(x, M, K, dtype, pair, 2, true, act, nullptr, st);
+        if (rc != ALLOYB_NOT_TAKEN) return rc;
+    }
     const int stage_bytes = 32 * Q4_STRIDE;
     const int esz = 2;
     for (int m0 = 0; m0 < M; m0 += 32) {
@@ -824,7 +838,8 @@ extern "C" int alloyb_device_error(int clear) {
     int v = 0;
     cudaError_t e = cudaMemcpyFromSymbol(&v, alloyb::g_device_error, sizeof(int));
     if (e != cudaSuccess) { alloyb::set_cuda_error(e); return ALLOYB_E_CUDA; }
-    const int v_tc = alloyb::gemm_tc_device_error(clear) | alloyb::attn_mma_device_error(clear);
+    const int v_tc = alloyb::gemm_tc_device_error(clear) | alloyb::attn_mma_device_error(clear) |
+                     alloyb::gemv_stream_device_error(clear);
     if (clear && v) {
         const int z = 0;
         e = cudaMemcpyToSymbol(alloyb::g_device_error, &z, sizeof(int));

@@ -1,0 +1,562 @@
+// One-token dequant-GEMV as a persistent streaming kernel (fp16 activations, Q4_K weights).
+//
+// The decode step multiplies ONE token by every weight matrix, so the kernel's only job is to
+// pull packed rows out of HBM at full speed and to spend as few instructions per byte as it can.
+//
+// Work split.  One CTA per SM.  The output rows of a launch (all row-stacked matrices together)
+// are cut into one contiguous range per CTA, equal to within one row, so every SM streams the same
+// number of bytes; a CTA walks its range in 16-row tiles (the last tile of a range or of a matrix
+// is partial) and deals the tiles round-robin to its GROUPS of eight warps.  Inside a tile the K
+// dimension is cut into eight slices of whole super-blocks, one per warp of the group, the same
+// slice for every tile: a warp's activations (as MMA B fragments) and their per-sub-block sums
+// are loop invariants and live in registers when the slice is one stage long.
+//
+// Data movement.  Every warp has a PRIVATE ring of slots (16 rows x one or two 144-byte
+// super-blocks) with one mbarrier per slot.  A full tile's slot is filled by ONE 2-D TMA copy out
+// of the row-major packed matrix; a partial tile by one plain bulk copy per valid row.  The warp
+// refills a slot as soon as it has drained it, across tile boundaries, with no producer warp and
+// no CTA-wide barrier on the load path.  The ring is kept SHALLOW (one or two slots in flight per
+// warp): HBM delivers its peak with ~75 KB in flight per SM, and deeper queues of small strided
+// boxes measurably lose row-buffer locality.  Weight copies do not depend on the previous kernel
+// and start before griddepcontrol.wait.
+//
+// Arithmetic.  mma.sync.m16n8k16 with the 16 rows as M and the eight MMA columns used for the
+// eight SUB-BLOCKS of a super-block (the B operand carries the token's activations of sub-block n
+// in column n, zero elsewhere).  The A operand is the raw nibbles as fp16 subnormals (n * 2^-24,
+// high nibbles as 16n * 2^-24; one shift and four ANDs per 32-bit word give four A registers), so
+// after sixteen MMAs the accumulator tile holds  sum nib*x  per (row, sub-block) and the 6-bit
+// scales and mins are applied to eight numbers per lane.  Exact products, fp32 accumulation: the
+// factored form  sum_g d*sc_g*(sum nib*x) - dmin*m_g*(sum x)  of the reference's GEMV
+// (metal/std/quant.py:1312-1347).
+//
+// One group-wide named barrier per tile folds the eight K slices (double-buffered partials in
+// shared memory); 16 threads apply the activation / residual and store.
+#include <cuda.h>
+
+#include <cstdlib>
+
+#include "linear.cuh"
+#include "linear_rows.cuh"
+
+namespace alloyb {
+namespace st {
+
+constexpr int GW = 8;                        // warps per group (= K slices per tile)
+constexpr int MAX_GROUPS = 3;
+constexpr int MAX_D = 4;                     // ring slots per warp (upper bound)
+constexpr int SB_B = Q4K_BYTES;              // 144
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr int MAX_SEG = MAX_SEGS;
+
+// Row pitch of a slot holding SBS super-blocks per row: 16 mod 32 bytes, so that the 128-bit reads
+// of two rows x four lanes fall on 32 different banks (144; 288 + 16 spare bytes).
+template <int SBS> struct SlotGeom {
+    static constexpr int PITCH = SBS == 1 ? 144 : 304;
+    static constexpr int BYTES = 16 * PITCH;
+};
+
+__device__ int g_error = 0;                  // sticky: a bounded wait ran out
+
+struct Seg {
+    const uint8_t* data;
+    int64_t row_bytes;
+    void* y;
+    int n_rows;
+    int row_base;                            // first row of this matrix in the launch's stacked row space
+};
+struct Params {
+    const __half* x;
+    const __half* residual;
+    Seg seg[MAX_SEG];
+    int n_seg;                               // matrices walked row-wise (1 for a gate/up pair)
+    int total_rows;
+    int nsb;
+    int gated;                               // seg[0] = gate, seg[1] = up, y = act(gate) * up
+    int act;
+    int n_groups;
+    int depth;                               // ring slots per warp
+    int debug;
+};
+struct Maps {
+    CUtensorMap m[MAX_SEG];                  // (row_bytes / 4, n_rows) uint32, box PITCH/4 x 16
+};
+
+// Position in a CTA's row range: matrix, local row, local end of the range inside that matrix.
+struct Cursor {
+    int seg, row, lim;
+};
+__device__ __forceinline__ void cursor_enter(Cursor& c, const Params& P, int lo, int hi) {
+    while (c.seg < P.n_seg) {
+        const int base = P.seg[c.seg].row_base, n = P.seg[c.seg].n_rows;
+        const int a = lo > base ? lo - base : 0;
+        const int b = hi - base < n ? hi - base : n;
+        if (a < b) {
+            c.row = a;
+            c.lim = b;
+            return;
+        }
+        ++c.seg;
+    }
+}
+__device__ __forceinline__ void cursor_next(Cursor& c, const Params& P, int lo, int hi, int steps) {
+    for (int i = 0; i < steps && c.seg < P.n_seg; ++i) {
+        c.row += 16;
+        if (c.row >= c.lim) {
+            ++c.seg;
+            cursor_enter(c, P, lo, hi);
+        }
+    }
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 32) __nanosleep(32);
+    }
+    atomicExch(&g_error, 1);
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+__device__ __forceinline__ void mma_acc(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_zero(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm("{\n\t.reg .f32 z;\n\tmov.f32 z, 0f00000000;\n\t"
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {z,z,z,z};\n\t}"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// B fragments of one super-block of the token: lane (g, t) holds sub-block g's 32 activations when
+// it owns that sub-block's k slots (g >> 1 == t), zero otherwise; sx = per-sub-block sums (columns
+// 2t, 2t+1) from eight MMAs with A = 1.
+struct XFrag {
+    uint32_t b[8][2];
+    float sx0, sx1;
+};
+__device__ __forceinline__ void load_xfrag(XFrag& f, const __half* x, int sb, int g, int t) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f.b[j][0] = f.b[j][1] = 0u;
+    if ((g >> 1) == t) {
+        const uint4* xp = reinterpret_cast<const uint4*>(x + sb * QK_K + 32 * g);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint4 v = __ldg(xp + q);
+            f.b[2 * q][0] = prmt(v.x, v.y, 0x5410u);          // (x[4j], x[4j+2])
+            f.b[2 * q][1] = prmt(v.x, v.y, 0x7632u);          // (x[4j+1], x[4j+3])
+            f.b[2 * q + 1][0] = prmt(v.z, v.w, 0x5410u);
+            f.b[2 * q + 1][1] = prmt(v.z, v.w, 0x7632u);
+        }
+    }
+    constexpr uint32_t ONE2 = 0x3C003C00u;
+    float s[4];
+    mma_zero(s, ONE2, ONE2, ONE2, ONE2, f.b[0][0], f.b[0][1]);
+#pragma unroll
+    for (int j = 1; j < 8; ++j) mma_acc(s, ONE2, ONE2, ONE2, ONE2, f.b[j][0], f.b[j][1]);
+    f.sx0 = s[0];
+    f.sx1 = s[1];
+}
+
+// Lane-invariant constants of the 6-bit scale decode (sub-blocks 2t, 2t+1 of rows g and g+8 at once).
+struct ScaleSel {
+    uint32_t sel;        // PRMT selector: bytes 2(t&1), 2(t&1)+1 of row g | the same of row g+8
+    uint32_t m_a, m_b;   // t < 2: 0x3f3f3f3f, 0;  t >= 2: 0x0f0f0f0f, 0x30303030
+    bool high;           // t >= 2
+};
+__device__ __forceinline__ ScaleSel make_scale_sel(int t) {
+    ScaleSel s;
+    const uint32_t b = 2u * (t & 1);
+    s.sel = b | ((b + 1u) << 4) | ((b + 4u) << 8) | ((b + 5u) << 12);
+    s.high = t >= 2;
+    s.m_a = s.high ? 0x0f0f0f0fu : 0x3f3f3f3fu;
+    s.m_b = s.high ? 0x30303030u : 0u;
+    return s;
+}
+
+// One super-block of 16 rows at `blk` (row pitch PITCH): adds this lane's share of rows g and g+8.
+template <int PITCH>
+__device__ __forceinline__ void unit_q4k(uint32_t blk, const XFrag& f, const ScaleSel& ss, int g, int t, float& a0,
+                                         float& a1) {
+    const uint32_t rb = blk + g * PITCH;
+    const uint4 p0 = lds128(rb + 16 + 32 * t), p1 = lds128(rb + 32 + 32 * t);
+    const uint4 r0 = lds128(rb + 8 * PITCH + 16 + 32 * t), r1 = lds128(rb + 8 * PITCH + 32 + 32 * t);
+    const uint4 h0 = lds128(rb), h1 = lds128(rb + 8 * PITCH);
+    const uint32_t wg[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+    const uint32_t wh[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+    float clo[4], chi[4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t ug = wg[j] >> 8, uh = wh[j] >> 8;
+        if (j == 0) {
+            mma_zero(clo, wg[j] & 0x000f000fu, wh[j] & 0x000f000fu, ug & 0x000f000fu, uh & 0x000f000fu, f.b[j][0],
+                     f.b[j][1]);
+            mma_zero(chi, wg[j] & 0x00f000f0u, wh[j] & 0x00f000f0u, ug & 0x00f000f0u, uh & 0x00f000f0u, f.b[j][0],
+                     f.b[j][1]);
+        } else {
+            mma_acc(clo, wg[j] & 0x000f000fu, wh[j] & 0x000f000fu, ug & 0x000f000fu, uh & 0x000f000fu, f.b[j][0],
+                    f.b[j][1]);
+            mma_acc(chi, wg[j] & 0x00f000f0u, wh[j] & 0x00f000f0u, ug & 0x00f000f0u, uh & 0x00f000f0u, f.b[j][0],
+                    f.b[j][1]);
+        }
+    }
+    // 6-bit scales / mins (llama.cpp's get_scale_min_k4) of both rows in one register each:
+    // bytes = {row g: 2t, 2t+1; row g+8: 2t, 2t+1}
+    const uint32_t Y = prmt(h0.y, h1.y, ss.sel), Z = prmt(h0.z, h1.z, ss.sel), Wd = prmt(h0.w, h1.w, ss.sel);
+    const uint32_t sc4 = ((ss.high ? Wd : Y) & ss.m_a) | ((Y >> 2) & ss.m_b);
+    const uint32_t mn4 = ((ss.high ? (Wd >> 4) : Z) & ss.m_a) | ((Z >> 2) & ss.m_b);
+    const float2 dm0 = __half22float2(*reinterpret_cast<const __half2*>(&h0.x));
+    const float2 dm1 = __half22float2(*reinterpret_cast<const __half2*>(&h1.x));
+    // low nibbles entered as n * 2^-24, high ones as 16 n * 2^-24
+    float a = static_cast<float>(sc4 & 0xffu) * clo[0];
+    a = fmaf(static_cast<float>((sc4 >> 8) & 0xffu) * 0.0625f, chi[1], a);
+    float m = static_cast<float>(mn4 & 0xffu) * f.sx0;
+    m = fmaf(static_cast<float>((mn4 >> 8) & 0xffu), f.sx1, m);
+    a0 = fmaf(dm0.x * 16777216.0f, a, fmaf(-dm0.y, m, a0));
+    float b = static_cast<float>((sc4 >> 16) & 0xffu) * clo[2];
+    b = fmaf(static_cast<float>(sc4 >> 24) * 0.0625f, chi[3], b);
+    float n = static_cast<float>((mn4 >> 16) & 0xffu) * f.sx0;
+    n = fmaf(static_cast<float>(mn4 >> 24), f.sx1, n);
+    a1 = fmaf(dm1.x * 16777216.0f, b, fmaf(-dm1.y, n, a1));
+}
+
+// RT: matrices per tile (2 = gate/up pair).  SBS: super-blocks per slot row.  CACHE: the warp's
+// slice is exactly one slot long and its B fragments stay in registers for the whole launch.
+template <int RT, int SBS, bool CACHE, int NG>
+__global__ void __launch_bounds__(NG* GW * 32, 1)
+gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
+    constexpr int PITCH = SlotGeom<SBS>::PITCH, SLOT = SlotGeom<SBS>::BYTES;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int grp = warp / GW, wg = warp % GW;
+    const int n_warps = P.n_groups * GW, D = P.depth;
+    // [warps][D] slots | [groups][2][GW][RT][16] partials | [warps][MAX_D] barriers
+    float* red = reinterpret_cast<float*>(smem + n_warps * D * SLOT) + grp * (2 * GW * RT * 16);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + n_warps * D * SLOT + P.n_groups * 2 * GW * RT * 16 * 4);
+    const uint32_t ring = smem_u32(smem + warp * D * SLOT);
+    const uint32_t bar0 = smem_u32(bars + warp * MAX_D);
+
+    if (lane == 0) {
+        for (int s = 0; s < D; ++s) mbar_init(bar0 + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    pdl_launch_dependents();
+
+    // this CTA's rows, this group's tiles (every n_groups-th), this warp's K slice
+    const int lo = static_cast<int>(static_cast<int64_t>(P.total_rows) * blockIdx.x / gridDim.x);
+    const int hi = static_cast<int>(static_cast<int64_t>(P.total_rows) * (blockIdx.x + 1) / gridDim.x);
+    const int slice = P.nsb / GW;                                    // super-blocks per warp per tile
+    const int sb_lo = wg * slice;
+    const int spt = (slice / SBS) * RT;                              // stages per tile
+    int my_tiles = 0;
+    {
+        Cursor c = {0, 0, 0};
+        cursor_enter(c, P, lo, hi);
+        cursor_next(c, P, lo, hi, grp);
+        while (c.seg < P.n_seg) {
+            ++my_tiles;
+            cursor_next(c, P, lo, hi, P.n_groups);
+        }
+    }
+    const int n_stage = my_tiles * spt;
+
+    // producer side: stage sequence = for tile, for slot-sized step of the slice, for matrix
+    Cursor pc = {0, 0, 0};
+    cursor_enter(pc, P, lo, hi);
+    cursor_next(pc, P, lo, hi, grp);
+    int issued = 0, p_r = 0, p_slot = 0;
+    auto issue = [&]() {
+        const int sb = sb_lo + (p_r / RT) * SBS, mt = p_r % RT;
+        const int si = P.gated ? mt : pc.seg;
+        const int nvalid = pc.lim - pc.row < 16 ? pc.lim - pc.row : 16;
+        const uint32_t bar = bar0 + 8 * p_slot, dst = ring + p_slot * SLOT;
+        if (!(P.debug & 2)) {
+            if (nvalid == 16) {
+                if (lane == 0) {
+                    mbar_expect_tx(bar, SLOT);
+                    tma_2d(dst, &maps.m[si], sb * (SB_B / 4), pc.row, bar);
+                }
+            } else {
+                if (lane == 0) mbar_expect_tx(bar, nvalid * SBS * SB_B);
+                __syncwarp();
+                if (lane < nvalid)
+                    bulk_g2s(dst + lane * PITCH,
+                             P.seg[si].data + (pc.row + lane) * P.seg[si].row_bytes + static_cast<int64_t>(sb) * SB_B,
+                             SBS * SB_B, bar);
+            }
+        }
+        ++issued;
+        if (++p_slot == D) p_slot = 0;
+        if (++p_r == spt) {
+            p_r = 0;
+            cursor_next(pc, P, lo, hi, P.n_groups);
+        }
+    };
+    while (issued < n_stage && issued < D) issue();
+
+    pdl_wait();          // activations, residual and outputs belong to the previous kernel until here
+
+    const ScaleSel ss = make_scale_sel(t);
+    XFrag xc[CACHE ? SBS : 1];
+    if (CACHE) {
+#pragma unroll
+        for (int i = 0; i < SBS; ++i) load_xfrag(xc[i], P.x, sb_lo + i, g, t);
+    }
+
+    bool ok = true;
+    int c_slot = 0;
+    uint32_t c_ph = 0;
+    Cursor cc = {0, 0, 0};
+    cursor_enter(cc, P, lo, hi);
+    cursor_next(cc, P, lo, hi, grp);
+    for (int it = 0; it < my_tiles; ++it) {
+        float acc[RT][2];
+#pragma unroll
+        for (int m = 0; m < RT; ++m) acc[m][0] = acc[m][1] = 0.f;
+        for (int sb = sb_lo; sb < sb_lo + slice; sb += SBS) {
+            uint32_t slot[RT];
+#pragma unroll
+            for (int mt = 0; mt < RT; ++mt) {
+                slot[mt] = ring + c_slot * SLOT;
+                if (ok && !(P.debug & 2)) ok = mbar_wait(bar0 + 8 * c_slot, c_ph);
+                if (++c_slot == D) {
+                    c_slot = 0;
+                    c_ph ^= 1u;
+                }
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok && !(P.debug & 1)) {
+#pragma unroll
+                for (int i = 0; i < SBS; ++i) {
+                    if (!CACHE) load_xfrag(xc[0], P.x, sb + i, g, t);
+#pragma unroll
+                    for (int mt = 0; mt < RT; ++mt)
+                        unit_q4k<PITCH>(slot[mt] + i * SB_B, xc[CACHE ? i : 0], ss, g, t, acc[mt][0], acc[mt][1]);
+                }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int mt = 0; mt < RT; ++mt)
+                if (issued < n_stage) issue();                       // refills the slots just drained
+        }
+        // fold the four t lanes, then the eight K slices of the group
+        float* rbuf = red + (it & 1) * (GW * RT * 16);
+#pragma unroll
+        for (int m = 0; m < RT; ++m)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                float v = acc[m][i];
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                if (t == 0) rbuf[(wg * RT + m) * 16 + g + 8 * i] = v;
+            }
+        asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "n"(GW * 32) : "memory");
+        const int tl = threadIdx.x - grp * GW * 32;
+        if (tl < 16 && cc.row + tl < cc.lim) {
+            const Seg& sg = P.seg[cc.seg];
+            const int row = cc.row + tl;
+            float v = 0.f, u = 0.f;
+#pragma unroll
+            for (int w = 0; w < GW; ++w) {
+                v += rbuf[(w * RT) * 16 + tl];
+                if (RT == 2) u += rbuf[(w * RT + 1) * 16 + tl];
+            }
+            __half* y = static_cast<__half*>(sg.y);
+            if (RT == 2) {
+                const float a = (P.act == ALLOYB_ACT_SILU) ? act_silu(v) : act_gelu_tanh(v);
+                y[row] = __float2half_rn(a * u);
+            } else {
+                __half r = __float2half_rn(v);
+                if (P.residual) r = __float2half_rn(__half2float(P.residual[row]) + __half2float(r));
+                y[row] = r;
+            }
+        }
+        cursor_next(cc, P, lo, hi, P.n_groups);
+    }
+    if (!ok) {
+        // a wait ran out (sticky error word set; this CTA's results are garbage): let copies in
+        // flight land before the shared memory is released
+        for (uint32_t i = 0; i < 2048; ++i) __nanosleep(512);
+    }
+}
+
+template <int RT, int SBS, bool CACHE, int NG>
+static int launch_ng(const Maps& maps, const Params& P, cudaStream_t stream) {
+    static bool configured = false;
+    auto kern = gemv_stream_kernel<RT, SBS, CACHE, NG>;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
+        configured = true;
+    }
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    const int n_warps = P.n_groups * GW;
+    const int smem = n_warps * P.depth * SlotGeom<SBS>::BYTES + P.n_groups * 2 * GW * RT * 16 * 4 + n_warps * MAX_D * 8;
+    int grid = sms;
+    const int tiles = (P.total_rows + 15) / 16;
+    if (grid > tiles) grid = tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(n_warps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, maps, P);
+    if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
+    return ALLOYB_OK;
+}
+template <int RT, int SBS, bool CACHE>
+static int launch(const Maps& maps, const Params& P, cudaStream_t stream) {
+    return P.n_groups == 3 ? launch_ng<RT, SBS, CACHE, 3>(maps, P, stream) : launch_ng<RT, SBS, CACHE, 2>(maps, P, stream);
+}
+
+// The driver's tensor-map encoder, looked up through the runtime (no link-time dependency on the driver).
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeFn encoder() {
+    static EncodeFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) != cudaSuccess ||
+            qr != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    return fn;
+}
+
+}  // namespace st
+
+static int env_int(const char* name, int dflt) {
+    const char* e = std::getenv(name);
+    return e ? std::atoi(e) : dflt;
+}
+
+// One fp16 token against Q4_K matrices (plain: up to MAX_SEGS row-stacked outputs; gated: gate/up
+// pair with the activation fused).  NOT_TAKEN for anything else.
+int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg, int n_seg, bool gated, int act,
+                    const void* residual, cudaStream_t stream) {
+    using namespace st;
+    if (M != 1 || dtype != ALLOYB_F16 || K % QK_K || n_seg < 1 || n_seg > MAX_SEG) return ALLOYB_NOT_TAKEN;
+    if (reinterpret_cast<uintptr_t>(x) % 16) return ALLOYB_NOT_TAKEN;
+    const int nsb = K / QK_K;
+    if (nsb % GW) return ALLOYB_NOT_TAKEN;
+    if (gated && (n_seg != 2 || seg[0].N != seg[1].N)) return ALLOYB_NOT_TAKEN;
+    const int slice = nsb / GW;
+    static const int force_sbs = env_int("ALLOYB_ST_SBS", 0);
+    const int sbs = force_sbs == 1 ? 1 : ((slice % 2 == 0) ? 2 : 1);
+    Params P = {};
+    Maps maps;
+    P.x = static_cast<const __half*>(x);
+    P.residual = static_cast<const __half*>(residual);
+    P.n_seg = gated ? 1 : n_seg;
+    P.nsb = nsb;
+    P.gated = gated ? 1 : 0;
+    P.act = act;
+    static const int dbg = env_int("ALLOYB_ST_DEBUG", 0), groups = env_int("ALLOYB_ST_GROUPS", 2),
+                     depth = env_int("ALLOYB_ST_DEPTH", 0);
+    P.debug = dbg;
+    P.n_groups = groups == 3 ? 3 : 2;
+    P.depth = depth > 0 ? (depth > MAX_D ? MAX_D : depth) : (sbs == 2 ? 2 : 3);
+    int64_t rows = 0;
+    for (int i = 0; i < n_seg; ++i) {
+        if (seg[i].format != ALLOYB_Q4_K || seg[i].N <= 0) return ALLOYB_NOT_TAKEN;
+        if (reinterpret_cast<uintptr_t>(seg[i].data) % 16 || seg[i].row_bytes % 16) return ALLOYB_NOT_TAKEN;
+        if (seg[i].row_bytes < static_cast<int64_t>(nsb) * Q4K_BYTES) return ALLOYB_NOT_TAKEN;
+        P.seg[i].data = static_cast<const uint8_t*>(seg[i].data);
+        P.seg[i].row_bytes = seg[i].row_bytes;
+        P.seg[i].y = seg[i].y;
+        P.seg[i].n_rows = seg[i].N;
+        P.seg[i].row_base = gated ? 0 : static_cast<int>(rows);
+        if (!gated || i == 0) rows += seg[i].N;
+    }
+    if (rows > (1 << 30)) return ALLOYB_NOT_TAKEN;
+    P.total_rows = static_cast<int>(rows);
+    const EncodeFn encode = encoder();
+    if (!encode) { set_cuda_error(cudaErrorNotSupported); return ALLOYB_E_CUDA; }
+    const cuuint32_t box_w = (sbs == 2 ? SlotGeom<2>::PITCH : SlotGeom<1>::PITCH) / 4;
+    for (int i = 0; i < n_seg; ++i) {
+        const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(nsb) * (SB_B / 4), static_cast<cuuint64_t>(seg[i].N)};
+        const cuuint64_t gstr[1] = {static_cast<cuuint64_t>(seg[i].row_bytes)};
+        const cuuint32_t box[2] = {box_w, 16};
+        const cuuint32_t estr[2] = {1, 1};
+        const CUresult cr = encode(&maps.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(seg[i].data), gdim, gstr,
+                                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) { set_cuda_error(cudaErrorInvalidValue); return ALLOYB_E_CUDA; }
+    }
+    for (int i = n_seg; i < MAX_SEG; ++i) maps.m[i] = maps.m[0];
+    const bool cache = slice == sbs;
+    if (gated) {
+        if (sbs == 2) return cache ? launch<2, 2, true>(maps, P, stream) : launch<2, 2, false>(maps, P, stream);
+        return cache ? launch<2, 1, true>(maps, P, stream) : launch<2, 1, false>(maps, P, stream);
+    }
+    if (sbs == 2) return cache ? launch<1, 2, true>(maps, P, stream) : launch<1, 2, false>(maps, P, stream);
+    return cache ? launch<1, 1, true>(maps, P, stream) : launch<1, 1, false>(maps, P, stream);
+}
+
+int gemv_stream_device_error(int clear) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, st::g_error, sizeof(int)) != cudaSuccess) return 0;
+    if (clear && v) {
+        const int z = 0;
+        cudaMemcpyToSymbol(st::g_error, &z, sizeof(int));
+    }
+    return v;
+}
+
+}  // namespace alloyb
