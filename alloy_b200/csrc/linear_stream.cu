@@ -1,4 +1,4 @@
-// One-token dequant-GEMV as a persistent streaming kernel (fp16 activations, Q4_K weights).
+// One-token dequant-GEMV as a persistent streaming kernel (fp16 activations, Q4_K / Q6_K weights).
 //
 // The decode step multiplies ONE token by every weight matrix, so the kernel's only job is to
 // pull packed rows out of HBM at full speed and to spend as few instructions per byte as it can.
@@ -34,6 +34,7 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <type_traits>
 
 #include "linear.cuh"
 #include "linear_rows.cuh"
@@ -42,18 +43,25 @@ namespace alloyb {
 namespace st {
 
 constexpr int GW = 8;                        // warps per group (= K slices per tile)
-constexpr int MAX_GROUPS = 3;
+constexpr int MAX_GROUPS = 2;
 constexpr int MAX_D = 4;                     // ring slots per warp (upper bound)
-constexpr int SB_B = Q4K_BYTES;              // 144
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr int MAX_SEG = MAX_SEGS;
 
-// Row pitch of a slot holding SBS super-blocks per row: 16 mod 32 bytes, so that the 128-bit reads
-// of two rows x four lanes fall on 32 different banks (144; 288 + 16 spare bytes).
-template <int SBS> struct SlotGeom {
-    static constexpr int PITCH = SBS == 1 ? 144 : 304;
-    static constexpr int BYTES = 16 * PITCH;
-};
+// Slot geometries.  A slot holds 16 rows of one stage; its row pitch is chosen so that the lanes'
+// shared-memory reads fall on 32 different banks.
+//   Q4x1: one 144-byte Q4_K super-block per row; pitch 144 (16 mod 32 bytes: 128-bit reads of two
+//         rows x four lanes are conflict-free).
+//   Q4x2: two super-blocks per row; pitch 288 + 16 spare bytes (again 16 mod 32).
+//   Q6:   one 210-byte Q6_K super-block per row.  Blocks are only 2-byte aligned, copies need 16:
+//         the slot row is the 16-byte-aligned window [floor16(210 sb), +240) and the block sits
+//         at offset (210 sb) mod 16 inside it; pitch 240 = 60 words (28 mod 32: 32-bit reads of
+//         eight rows x four lanes are conflict-free).
+enum Kind { Q4x1 = 0, Q4x2 = 1, Q6 = 2 };
+template <int KIND> struct Geom;
+template <> struct Geom<Q4x1> { static constexpr int SBS = 1, PITCH = 144, BLK = Q4K_BYTES; };
+template <> struct Geom<Q4x2> { static constexpr int SBS = 2, PITCH = 304, BLK = Q4K_BYTES; };
+template <> struct Geom<Q6> { static constexpr int SBS = 1, PITCH = 240, BLK = Q6K_BYTES; };
 
 __device__ int g_error = 0;                  // sticky: a bounded wait ran out
 
@@ -151,6 +159,21 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+// 32 bits at a shared address that is 4-byte aligned (AL) or 2 bytes past a 4-byte boundary.
+template <bool AL> __device__ __forceinline__ uint32_t lds32_u(uint32_t addr) {
+    if (AL) return lds32(addr);
+    return __funnelshift_r(lds32(addr - 2u), lds32(addr + 2u), 16);
 }
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t d;
@@ -263,12 +286,102 @@ __device__ __forceinline__ void unit_q4k(uint32_t blk, const XFrag& f, const Sca
     a1 = fmaf(dm1.x * 16777216.0f, b, fmaf(-dm1.y, n, a1));
 }
 
-// RT: matrices per tile (2 = gate/up pair).  SBS: super-blocks per slot row.  CACHE: the warp's
+// ---- Q6_K ------------------------------------------------------------------------------------
+// A Q6_K super-block has 16 sub-blocks of 16 weights (int8 scale each), in two halves of 128.
+// Within a half, ql byte l (l < 32) holds codes l (low nibble, "plane" 0) and l + 64 (high nibble,
+// plane 2), ql byte 32 + l holds l + 32 (plane 1) and l + 96 (plane 3), qh byte l holds the four
+// codes' bits 4-5; sub-block 2p + i of the half is plane p, l in [16 i, 16 i + 16).
+//
+// MMA mapping for one token: the eight columns are the eight sub-blocks of a half.  MMA (p, i)
+// covers sub-block 2p + i: lane t supplies l = 16 i + 4t + {0, 2 | 1, 3} (bytes 0, 2 and 1, 3 of
+// one 32-bit word per row), so lane (g, t) of the B operand holds x[128 h + 16 g + 4t ..+3] --
+// each lane its own four activations -- for the MMA with 2p + i == g and zero for the other
+// seven.  Codes enter as fp16 bit patterns: planes 0/1 as code * 2^-24, planes 2/3 as
+// 16 code * 2^-24 (the high nibble stays in place, its two high bits go to bits 8-9); the -32
+// offset is applied through the per-sub-block activation sums (one MMA with A = 1 per half).
+struct XFrag6 {
+    uint32_t b[2][2];        // [half][k slots (0, 2) | (1, 3)]
+    float sx[2][2];          // [half][sub-block 2t, 2t+1 of the half]
+};
+__device__ __forceinline__ void load_xfrag6(XFrag6& f, const __half* x, int sb, int g, int t) {
+    constexpr uint32_t ONE2 = 0x3C003C00u;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint2 v = __ldg(reinterpret_cast<const uint2*>(x + sb * QK_K + 128 * h + 16 * g + 4 * t));
+        f.b[h][0] = prmt(v.x, v.y, 0x5410u);
+        f.b[h][1] = prmt(v.x, v.y, 0x7632u);
+        float s[4];
+        mma_zero(s, ONE2, ONE2, ONE2, ONE2, f.b[h][0], f.b[h][1]);
+        f.sx[h][0] = s[0];
+        f.sx[h][1] = s[1];
+    }
+}
+
+// One super-block of 16 rows; `blk` = slot + the block's offset inside the aligned window.
+template <bool AL>
+__device__ __forceinline__ void unit_q6k(uint32_t blk, const XFrag6& f, int g, int t, float& a0, float& a1) {
+    constexpr int PITCH = Geom<Q6>::PITCH;
+    const uint32_t rb = blk + g * PITCH + 4 * t;
+    const float fscale = t >= 2 ? 1048576.0f : 16777216.0f;          // planes 2, 3 carry a factor 16
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float c[4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            uint32_t qa[2], qb[2], qh[2];
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const uint32_t r = rb + rr * 8 * PITCH + 16 * i;
+                qa[rr] = lds32_u<AL>(r + 64 * h);
+                qb[rr] = lds32_u<AL>(r + 64 * h + 32);
+                qh[rr] = lds32_u<AL>(r + 128 + 32 * h);
+            }
+            uint32_t A[4][4];                                          // [plane][a0..a3]
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const uint32_t qa8 = qa[rr] >> 8, qb8 = qb[rr] >> 8;
+                const uint32_t u0 = qh[rr] << 4, v0 = qh[rr] << 2, u1 = qh[rr] >> 4, v1 = qh[rr] >> 6;
+                A[0][rr] = (qa[rr] & 0x000f000fu) | (u0 & 0x00300030u);
+                A[0][rr + 2] = (qa8 & 0x000f000fu) | (u1 & 0x00300030u);
+                A[1][rr] = (qb[rr] & 0x000f000fu) | (v0 & 0x00300030u);
+                A[1][rr + 2] = (qb8 & 0x000f000fu) | (v1 & 0x00300030u);
+                A[2][rr] = (qa[rr] & 0x00f000f0u) | (u0 & 0x03000300u);
+                A[2][rr + 2] = (qa8 & 0x00f000f0u) | (u1 & 0x03000300u);
+                A[3][rr] = (qb[rr] & 0x00f000f0u) | (v0 & 0x03000300u);
+                A[3][rr + 2] = (qb8 & 0x00f000f0u) | (v1 & 0x03000300u);
+            }
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                const bool mine = g == 2 * p + i;
+                const uint32_t b0 = mine ? f.b[h][0] : 0u, b1 = mine ? f.b[h][1] : 0u;
+                if (i == 0 && p == 0) mma_zero(c, A[p][0], A[p][1], A[p][2], A[p][3], b0, b1);
+                else mma_acc(c, A[p][0], A[p][1], A[p][2], A[p][3], b0, b1);
+            }
+        }
+        // int8 scales of sub-blocks 8h + 2t, 8h + 2t + 1 and the block scale, rows g and g+8
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            const uint32_t base = blk + (g + 8 * rr) * PITCH;
+            const uint32_t s2 = lds16(base + 192 + 8 * h + 2 * t);
+            const float d = half_bits_to_f32(lds16(base + 208));
+            const float s0 = static_cast<float>(static_cast<int8_t>(s2 & 0xffu));
+            const float s1 = static_cast<float>(static_cast<int8_t>(s2 >> 8));
+            const float e0 = fmaf(c[2 * rr], fscale, -32.0f * f.sx[h][0]);
+            const float e1 = fmaf(c[2 * rr + 1], fscale, -32.0f * f.sx[h][1]);
+            const float v = fmaf(s1, e1, s0 * e0);
+            if (rr == 0) a0 = fmaf(d, v, a0);
+            else a1 = fmaf(d, v, a1);
+        }
+    }
+}
+
+// KIND: slot geometry / weight format.  RT: matrices per tile (2 = gate/up pair).  CACHE: the warp's
 // slice is exactly one slot long and its B fragments stay in registers for the whole launch.
-template <int RT, int SBS, bool CACHE, int NG>
-__global__ void __launch_bounds__(NG* GW * 32, 1)
+template <int KIND, int RT, bool CACHE>
+__global__ void __launch_bounds__(MAX_GROUPS* GW * 32, 1)
 gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
-    constexpr int PITCH = SlotGeom<SBS>::PITCH, SLOT = SlotGeom<SBS>::BYTES;
+    constexpr int SBS = Geom<KIND>::SBS, PITCH = Geom<KIND>::PITCH, SLOT = 16 * PITCH, BLK = Geom<KIND>::BLK;
+    using XF = typename std::conditional<KIND == Q6, XFrag6, XFrag>::type;
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int grp = warp / GW, wg = warp % GW;
@@ -314,19 +427,23 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
         const int si = P.gated ? mt : pc.seg;
         const int nvalid = pc.lim - pc.row < 16 ? pc.lim - pc.row : 16;
         const uint32_t bar = bar0 + 8 * p_slot, dst = ring + p_slot * SLOT;
+        const int win = (sb * BLK) & ~15;                            // 16-byte-aligned start of the stage in a row
         if (!(P.debug & 2)) {
             if (nvalid == 16) {
                 if (lane == 0) {
                     mbar_expect_tx(bar, SLOT);
-                    tma_2d(dst, &maps.m[si], sb * (SB_B / 4), pc.row, bar);
+                    tma_2d(dst, &maps.m[si], win / 4, pc.row, bar);
                 }
             } else {
-                if (lane == 0) mbar_expect_tx(bar, nvalid * SBS * SB_B);
+                int bytes = SBS * BLK;
+                if (KIND == Q6) {
+                    const int left = static_cast<int>(P.seg[si].row_bytes) - win;
+                    bytes = left < PITCH ? left : PITCH;
+                }
+                if (lane == 0) mbar_expect_tx(bar, nvalid * bytes);
                 __syncwarp();
                 if (lane < nvalid)
-                    bulk_g2s(dst + lane * PITCH,
-                             P.seg[si].data + (pc.row + lane) * P.seg[si].row_bytes + static_cast<int64_t>(sb) * SB_B,
-                             SBS * SB_B, bar);
+                    bulk_g2s(dst + lane * PITCH, P.seg[si].data + (pc.row + lane) * P.seg[si].row_bytes + win, bytes, bar);
             }
         }
         ++issued;
@@ -341,10 +458,13 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     pdl_wait();          // activations, residual and outputs belong to the previous kernel until here
 
     const ScaleSel ss = make_scale_sel(t);
-    XFrag xc[CACHE ? SBS : 1];
+    XF xc[CACHE ? SBS : 1];
     if (CACHE) {
 #pragma unroll
-        for (int i = 0; i < SBS; ++i) load_xfrag(xc[i], P.x, sb_lo + i, g, t);
+        for (int i = 0; i < SBS; ++i) {
+            if constexpr (KIND == Q6) load_xfrag6(xc[i], P.x, sb_lo + i, g, t);
+            else load_xfrag(xc[i], P.x, sb_lo + i, g, t);
+        }
     }
 
     bool ok = true;
@@ -372,10 +492,17 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
             if (ok && !(P.debug & 1)) {
 #pragma unroll
                 for (int i = 0; i < SBS; ++i) {
-                    if (!CACHE) load_xfrag(xc[0], P.x, sb + i, g, t);
+                    if constexpr (KIND == Q6) {
+                        if (!CACHE) load_xfrag6(xc[0], P.x, sb, g, t);
+                        const uint32_t off = static_cast<uint32_t>(sb * BLK) & 15u;
+                        if (off & 2u) unit_q6k<false>(slot[0] + off, xc[0], g, t, acc[0][0], acc[0][1]);
+                        else unit_q6k<true>(slot[0] + off, xc[0], g, t, acc[0][0], acc[0][1]);
+                    } else {
+                        if (!CACHE) load_xfrag(xc[0], P.x, sb + i, g, t);
 #pragma unroll
-                    for (int mt = 0; mt < RT; ++mt)
-                        unit_q4k<PITCH>(slot[mt] + i * SB_B, xc[CACHE ? i : 0], ss, g, t, acc[mt][0], acc[mt][1]);
+                        for (int mt = 0; mt < RT; ++mt)
+                            unit_q4k<PITCH>(slot[mt] + i * BLK, xc[CACHE ? i : 0], ss, g, t, acc[mt][0], acc[mt][1]);
+                    }
                 }
             }
             __syncwarp();
@@ -424,10 +551,10 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     }
 }
 
-template <int RT, int SBS, bool CACHE, int NG>
-static int launch_ng(const Maps& maps, const Params& P, cudaStream_t stream) {
+template <int KIND, int RT, bool CACHE>
+static int launch(const Maps& maps, const Params& P, cudaStream_t stream) {
     static bool configured = false;
-    auto kern = gemv_stream_kernel<RT, SBS, CACHE, NG>;
+    auto kern = gemv_stream_kernel<KIND, RT, CACHE>;
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
@@ -440,7 +567,7 @@ static int launch_ng(const Maps& maps, const Params& P, cudaStream_t stream) {
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     }
     const int n_warps = P.n_groups * GW;
-    const int smem = n_warps * P.depth * SlotGeom<SBS>::BYTES + P.n_groups * 2 * GW * RT * 16 * 4 + n_warps * MAX_D * 8;
+    const int smem = n_warps * P.depth * 16 * Geom<KIND>::PITCH + P.n_groups * 2 * GW * RT * 16 * 4 + n_warps * MAX_D * 8;
     int grid = sms;
     const int tiles = (P.total_rows + 15) / 16;
     if (grid > tiles) grid = tiles;
@@ -457,10 +584,6 @@ static int launch_ng(const Maps& maps, const Params& P, cudaStream_t stream) {
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, maps, P);
     if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
     return ALLOYB_OK;
-}
-template <int RT, int SBS, bool CACHE>
-static int launch(const Maps& maps, const Params& P, cudaStream_t stream) {
-    return P.n_groups == 3 ? launch_ng<RT, SBS, CACHE, 3>(maps, P, stream) : launch_ng<RT, SBS, CACHE, 2>(maps, P, stream);
 }
 
 // The driver's tensor-map encoder, looked up through the runtime (no link-time dependency on the driver).
@@ -486,8 +609,8 @@ static int env_int(const char* name, int dflt) {
     return e ? std::atoi(e) : dflt;
 }
 
-// One fp16 token against Q4_K matrices (plain: up to MAX_SEGS row-stacked outputs; gated: gate/up
-// pair with the activation fused).  NOT_TAKEN for anything else.
+// One fp16 token against Q4_K or Q6_K matrices of one format (plain: up to MAX_SEGS row-stacked
+// outputs; gated: Q4_K gate/up pair with the activation fused).  NOT_TAKEN for anything else.
 int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg, int n_seg, bool gated, int act,
                     const void* residual, cudaStream_t stream) {
     using namespace st;
@@ -496,9 +619,13 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
     const int nsb = K / QK_K;
     if (nsb % GW) return ALLOYB_NOT_TAKEN;
     if (gated && (n_seg != 2 || seg[0].N != seg[1].N)) return ALLOYB_NOT_TAKEN;
+    const int fmt = seg[0].format;
+    if (fmt != ALLOYB_Q4_K && !(fmt == ALLOYB_Q6_K && !gated)) return ALLOYB_NOT_TAKEN;
     const int slice = nsb / GW;
-    static const int force_sbs = env_int("ALLOYB_ST_SBS", 0);
-    const int sbs = force_sbs == 1 ? 1 : ((slice % 2 == 0) ? 2 : 1);
+    const int kind = fmt == ALLOYB_Q6_K ? Q6 : ((slice % 2 == 0) ? Q4x2 : Q4x1);
+    const int sbs = kind == Q4x2 ? 2 : 1;
+    const int blk = fmt == ALLOYB_Q6_K ? Q6K_BYTES : Q4K_BYTES;
+    const int pitch = kind == Q6 ? Geom<Q6>::PITCH : (kind == Q4x2 ? Geom<Q4x2>::PITCH : Geom<Q4x1>::PITCH);
     Params P = {};
     Maps maps;
     P.x = static_cast<const __half*>(x);
@@ -507,16 +634,15 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
     P.nsb = nsb;
     P.gated = gated ? 1 : 0;
     P.act = act;
-    static const int dbg = env_int("ALLOYB_ST_DEBUG", 0), groups = env_int("ALLOYB_ST_GROUPS", 2),
-                     depth = env_int("ALLOYB_ST_DEPTH", 0);
+    static const int dbg = env_int("ALLOYB_ST_DEBUG", 0), depth = env_int("ALLOYB_ST_DEPTH", 0);
     P.debug = dbg;
-    P.n_groups = groups == 3 ? 3 : 2;
-    P.depth = depth > 0 ? (depth > MAX_D ? MAX_D : depth) : (sbs == 2 ? 2 : 3);
+    P.n_groups = MAX_GROUPS;
+    P.depth = depth > 0 ? (depth > MAX_D ? MAX_D : depth) : (kind == Q4x1 ? 3 : 2);
     int64_t rows = 0;
     for (int i = 0; i < n_seg; ++i) {
-        if (seg[i].format != ALLOYB_Q4_K || seg[i].N <= 0) return ALLOYB_NOT_TAKEN;
+        if (seg[i].format != fmt || seg[i].N <= 0) return ALLOYB_NOT_TAKEN;
         if (reinterpret_cast<uintptr_t>(seg[i].data) % 16 || seg[i].row_bytes % 16) return ALLOYB_NOT_TAKEN;
-        if (seg[i].row_bytes < static_cast<int64_t>(nsb) * Q4K_BYTES) return ALLOYB_NOT_TAKEN;
+        if (seg[i].row_bytes < static_cast<int64_t>(nsb) * blk) return ALLOYB_NOT_TAKEN;
         P.seg[i].data = static_cast<const uint8_t*>(seg[i].data);
         P.seg[i].row_bytes = seg[i].row_bytes;
         P.seg[i].y = seg[i].y;
@@ -528,11 +654,11 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
     P.total_rows = static_cast<int>(rows);
     const EncodeFn encode = encoder();
     if (!encode) { set_cuda_error(cudaErrorNotSupported); return ALLOYB_E_CUDA; }
-    const cuuint32_t box_w = (sbs == 2 ? SlotGeom<2>::PITCH : SlotGeom<1>::PITCH) / 4;
     for (int i = 0; i < n_seg; ++i) {
-        const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(nsb) * (SB_B / 4), static_cast<cuuint64_t>(seg[i].N)};
+        // the packed matrix as rows of 32-bit words; a box is one slot: pitch/4 words x 16 rows
+        const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(nsb) * blk / 4, static_cast<cuuint64_t>(seg[i].N)};
         const cuuint64_t gstr[1] = {static_cast<cuuint64_t>(seg[i].row_bytes)};
-        const cuuint32_t box[2] = {box_w, 16};
+        const cuuint32_t box[2] = {static_cast<cuuint32_t>(pitch / 4), 16};
         const cuuint32_t estr[2] = {1, 1};
         const CUresult cr = encode(&maps.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(seg[i].data), gdim, gstr,
                                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -541,12 +667,13 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
     }
     for (int i = n_seg; i < MAX_SEG; ++i) maps.m[i] = maps.m[0];
     const bool cache = slice == sbs;
+    if (kind == Q6) return cache ? launch<Q6, 1, true>(maps, P, stream) : launch<Q6, 1, false>(maps, P, stream);
     if (gated) {
-        if (sbs == 2) return cache ? launch<2, 2, true>(maps, P, stream) : launch<2, 2, false>(maps, P, stream);
-        return cache ? launch<2, 1, true>(maps, P, stream) : launch<2, 1, false>(maps, P, stream);
+        if (kind == Q4x2) return cache ? launch<Q4x2, 2, true>(maps, P, stream) : launch<Q4x2, 2, false>(maps, P, stream);
+        return cache ? launch<Q4x1, 2, true>(maps, P, stream) : launch<Q4x1, 2, false>(maps, P, stream);
     }
-    if (sbs == 2) return cache ? launch<1, 2, true>(maps, P, stream) : launch<1, 2, false>(maps, P, stream);
-    return cache ? launch<1, 1, true>(maps, P, stream) : launch<1, 1, false>(maps, P, stream);
+    if (kind == Q4x2) return cache ? launch<Q4x2, 1, true>(maps, P, stream) : launch<Q4x2, 1, false>(maps, P, stream);
+    return cache ? launch<Q4x1, 1, true>(maps, P, stream) : launch<Q4x1, 1, false>(maps, P, stream);
 }
 
 int gemv_stream_device_error(int clear) {

@@ -110,6 +110,47 @@ def test_mm_matches_oracle(fmt, m, n, k, dt):
     assert_close(to_np(y), ref, tdt, f"{fmt} m={m} n={n} k={k} {dt}")
 
 
+# One fp16 token takes the persistent streaming kernel when K is a multiple of 2048: full and
+# ragged row counts (partial last tile per SM and per matrix), one- and two-super-block slots
+# (K = 2048 / 4096), slices longer than one slot (K = 6144, 14336), stacked matrices, residual.
+@pytest.mark.parametrize("fmt", ["q4_k", "q6_k"])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (1000, 2048), (77, 4096), (4096, 14336), (50, 14336),
+                                 (2100, 6144), (5, 2048), (2367, 4096)])
+def test_one_token_stream(fmt, n, k):
+    rng = np.random.default_rng([n, k, len(fmt), 7])
+    w_dev, w = _weights(fmt, rng, n, k)
+    x = torch.from_numpy(synth.activations(rng, 1, k))
+    y = _MM[fmt](x.to(DEV), w_dev)
+    assert_close(to_np(y), O.mm_ref_f64(x.float().numpy(), w), torch.float16, f"stream {fmt} n={n} k={k}")
+
+
+@pytest.mark.parametrize("fmt", ["q4_k", "q6_k"])
+def test_one_token_stream_stacked_and_residual(fmt):
+    rng = np.random.default_rng(91)
+    k = 4096
+    x = torch.from_numpy(synth.activations(rng, 1, k)).to(DEV)
+    mk = synth.q4k_blocks if fmt == "q4_k" else synth.q6k_blocks
+    dq = O.dequant_q4_k if fmt == "q4_k" else O.dequant_q6_k
+    ws = [mk(rng, n, k) for n in (4096, 1024, 1000, 24)]
+    outs = ops.linear_multi(x, [(fmt, _dev(w), None) for w in ws])
+    for w, y in zip(ws, outs):
+        assert_close(to_np(y), O.mm_ref_f64(x.cpu().float().numpy(), dq(w)), torch.float16, f"stacked {fmt}")
+    r = synth.activations(rng, 1, 1000)
+    y = torch.ops.alloy.linear_residual(x, _dev(ws[2]), None, _dev(r), fmt)
+    lin = torch.from_numpy(O.mm_ref_f64(x.cpu().float().numpy(), dq(ws[2]))).to(torch.float16).double().numpy()
+    assert_close(to_np(y), lin + r.astype(np.float64), torch.float16, f"residual {fmt}")
+
+
+@pytest.mark.parametrize("n,k", [(1000, 2048), (14336, 4096), (333, 6144)])
+def test_one_token_stream_gated(n, k):
+    rng = np.random.default_rng([n, k, 13])
+    g, u = synth.q4k_blocks(rng, n, k), synth.q4k_blocks(rng, n, k)
+    x = synth.activations(rng, 1, k)
+    y = torch.ops.alloy.gguf_q4_k_silu(_dev(x), _dev(g), _dev(u))
+    ref = O.silu(O.mm_ref_f64(x, O.dequant_q4_k(g))) * O.mm_ref_f64(x, O.dequant_q4_k(u))
+    assert_close(to_np(y), ref, torch.float16, f"stream gated n={n} k={k}")
+
+
 def test_q4k_mm_golden(golden):
     g = golden["q4k"]
     y = torch.ops.alloy.gguf_q4_k_mm(_dev(g["x"]), _dev(g["blocks"]))
