@@ -190,6 +190,7 @@ constexpr int ATTN_WARPS = 4;
 // shared memory, and the CTA writes ONE partial per query head.
 template <int LAYOUT, int D, int G>
 __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(AttnParams P) {
+    pdl_launch_dependents();
     constexpr int DPL = D / 32;
     __shared__ float qs[G * D];
     __shared__ float sm_m[ATTN_WARPS][G], sm_l[ATTN_WARPS][G];
@@ -332,10 +333,10 @@ template <int LAYOUT, int D>
 static int launch_attn_g(const AttnParams& P, int G, cudaStream_t st) {
     dim3 grid(P.splits, P.KV_H, P.B);
     switch (G) {
-        case 1: attn_decode_kernel<LAYOUT, D, 1><<<grid, ATTN_WARPS * 32, 0, st>>>(P); break;
-        case 2: attn_decode_kernel<LAYOUT, D, 2><<<grid, ATTN_WARPS * 32, 0, st>>>(P); break;
-        case 4: attn_decode_kernel<LAYOUT, D, 4><<<grid, ATTN_WARPS * 32, 0, st>>>(P); break;
-        case 8: attn_decode_kernel<LAYOUT, D, 8><<<grid, ATTN_WARPS * 32, 0, st>>>(P); break;
+        case 1: launch_pdl(attn_decode_kernel<LAYOUT, D, 1>, dim3(grid), dim3(ATTN_WARPS * 32), 0, st, P); break;
+        case 2: launch_pdl(attn_decode_kernel<LAYOUT, D, 2>, dim3(grid), dim3(ATTN_WARPS * 32), 0, st, P); break;
+        case 4: launch_pdl(attn_decode_kernel<LAYOUT, D, 4>, dim3(grid), dim3(ATTN_WARPS * 32), 0, st, P); break;
+        case 8: launch_pdl(attn_decode_kernel<LAYOUT, D, 8>, dim3(grid), dim3(ATTN_WARPS * 32), 0, st, P); break;
         default: return ALLOYB_E_SHAPE;
     }
     return check_launch();

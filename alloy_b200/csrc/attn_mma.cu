@@ -136,6 +136,7 @@ struct WarpStage {                       // paged layout only
 
 template <int LAYOUT>
 __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
+    pdl_launch_dependents();
     constexpr bool Q8 = LAYOUT != ALLOYB_KV_F16;
     constexpr bool PAGED = LAYOUT == ALLOYB_KV_Q8_PAGED;
     __shared__ float sm_m[WARPS][8], sm_l[WARPS][8];
@@ -502,9 +503,9 @@ int launch_attn_mma(int layout, const void* q, int64_t q_bs, int64_t q_hs, int q
     P.part_o = part_o; P.part_lse = part_lse; P.counters = counters; P.status = status;
     const dim3 grid(splits, KV_H, B);
     switch (layout) {
-        case ALLOYB_KV_F16: am::attn_mma_kernel<ALLOYB_KV_F16><<<grid, am::WARPS * 32, 0, st>>>(P); break;
-        case ALLOYB_KV_Q8_SPLIT: am::attn_mma_kernel<ALLOYB_KV_Q8_SPLIT><<<grid, am::WARPS * 32, 0, st>>>(P); break;
-        default: am::attn_mma_kernel<ALLOYB_KV_Q8_PAGED><<<grid, am::WARPS * 32, 0, st>>>(P); break;
+        case ALLOYB_KV_F16: launch_pdl(am::attn_mma_kernel<ALLOYB_KV_F16>, dim3(grid), dim3(am::WARPS * 32), 0, st, P); break;
+        case ALLOYB_KV_Q8_SPLIT: launch_pdl(am::attn_mma_kernel<ALLOYB_KV_Q8_SPLIT>, dim3(grid), dim3(am::WARPS * 32), 0, st, P); break;
+        default: launch_pdl(am::attn_mma_kernel<ALLOYB_KV_Q8_PAGED>, dim3(grid), dim3(am::WARPS * 32), 0, st, P); break;
     }
     return check_launch();
 }

@@ -44,6 +44,8 @@ template <int FMT, typename OT>
 __global__ void dequant_rows_kernel(const uint8_t* __restrict__ data, const __half* __restrict__ scales,
                                     const int64_t* __restrict__ ids, OT* __restrict__ out,
                                     int64_t n_rows, int64_t table_rows, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t total = n_rows * static_cast<int64_t>(K);
     for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -87,15 +89,15 @@ static int launch_dequant(const void* data, const void* scales, const int64_t* i
     const __half* sc = static_cast<const __half*>(scales);
     switch (out_dtype) {
         case ALLOYB_F32:
-            dequant_rows_kernel<FMT, float><<<blocks, threads, 0, st>>>(
+            launch_pdl(dequant_rows_kernel<FMT, float>, dim3(blocks), dim3(threads), 0, st, 
                 d8, sc, ids, static_cast<float*>(out), n_rows, table_rows, K);
             break;
         case ALLOYB_F16:
-            dequant_rows_kernel<FMT, __half><<<blocks, threads, 0, st>>>(
+            launch_pdl(dequant_rows_kernel<FMT, __half>, dim3(blocks), dim3(threads), 0, st, 
                 d8, sc, ids, static_cast<__half*>(out), n_rows, table_rows, K);
             break;
         case ALLOYB_BF16:
-            dequant_rows_kernel<FMT, __nv_bfloat16><<<blocks, threads, 0, st>>>(
+            launch_pdl(dequant_rows_kernel<FMT, __nv_bfloat16>, dim3(blocks), dim3(threads), 0, st, 
                 d8, sc, ids, static_cast<__nv_bfloat16*>(out), n_rows, table_rows, K);
             break;
         default:

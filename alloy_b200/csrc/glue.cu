@@ -6,6 +6,7 @@ namespace alloyb {
 template <typename T>
 __global__ void __launch_bounds__(256) rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ w,
                                                        T* __restrict__ y, int K, float eps) {
+    pdl_launch_dependents();
     __shared__ float red[8];
     const int row = blockIdx.x;
     const T* xr = x + static_cast<int64_t>(row) * K;
@@ -34,6 +35,7 @@ template <typename T>
 __global__ void rope_kernel(T* __restrict__ q, T* __restrict__ k, const int32_t* __restrict__ pos,
                             int pos_count, const float* __restrict__ inv_freq, int B, int H, int KV_H,
                             int D) {
+    pdl_launch_dependents();
     const int half = D / 2;
     const int64_t total = static_cast<int64_t>(B) * (H + KV_H) * half;
     const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
@@ -57,6 +59,7 @@ __global__ void rope_kernel(T* __restrict__ q, T* __restrict__ k, const int32_t*
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ g, const T* __restrict__ u, T* __restrict__ y,
                                 int64_t n) {
+    pdl_launch_dependents();
     const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     if (i >= n) return;
     pdl_wait();
@@ -64,26 +67,45 @@ __global__ void silu_mul_kernel(const T* __restrict__ g, const T* __restrict__ u
     y[i] = from_f32<T>(gv / (1.0f + expf(-gv)) * to_f32<T>(u[i]));
 }
 
+// Greedy argmax of one row by a cluster of eight CTAs: every CTA scans an eighth of the row, the
+// eight (value, index) candidates meet in CTA 0 through distributed shared memory.  Ties go to
+// the smallest index.
+constexpr int ARGMAX_CLUSTER = 8;
+
+__device__ __forceinline__ void argmax_take(float& best, int& idx, float ov, int oi) {
+    if (ov > best || (ov == best && oi < idx)) {
+        best = ov;
+        idx = oi;
+    }
+}
+
 template <typename T>
-__global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logits,
-                                                      int64_t* __restrict__ out, int N) {
+__global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logits, int64_t* __restrict__ out, int N) {
+    pdl_launch_dependents();
     __shared__ float bv[32];
     __shared__ int bi[32];
-    const T* row = logits + static_cast<int64_t>(blockIdx.x) * N;
+    __shared__ float c_val;
+    __shared__ int c_idx;
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const T* row = logits + static_cast<int64_t>(blockIdx.y) * N;
+    const int chunk = (N + ARGMAX_CLUSTER - 1) / ARGMAX_CLUSTER;
+    const int lo = static_cast<int>(rank) * chunk;
+    const int hi = lo + chunk < N ? lo + chunk : N;
     pdl_wait();
     float best = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < N; i += blockDim.x) {
-        const float v = to_f32<T>(row[i]);
-        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
-    }
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) argmax_take(best, idx, to_f32<T>(row[i]), i);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
         const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+        argmax_take(best, idx, ov, oi);
     }
-    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+    if ((threadIdx.x & 31) == 0) {
+        bv[threadIdx.x >> 5] = best;
+        bi[threadIdx.x >> 5] = idx;
+    }
     __syncthreads();
     if (threadIdx.x < 32) {
         const int nw = blockDim.x >> 5;
@@ -93,10 +115,55 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logi
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best, o);
             const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-            if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+            argmax_take(best, idx, ov, oi);
         }
-        if (threadIdx.x == 0) out[blockIdx.x] = idx;
+        if (threadIdx.x == 0) {
+            c_val = best;
+            c_idx = idx;
+        }
     }
+    // every CTA's candidate is written; CTA 0 reads all eight through the cluster's shared window
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (rank == 0 && threadIdx.x < 32) {
+        best = -INFINITY;
+        idx = 0x7fffffff;
+        if (threadIdx.x < ARGMAX_CLUSTER) {
+            uint32_t va, ia;
+            const uint32_t lv = static_cast<uint32_t>(__cvta_generic_to_shared(&c_val));
+            const uint32_t li = static_cast<uint32_t>(__cvta_generic_to_shared(&c_idx));
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(va) : "r"(lv), "r"(threadIdx.x));
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ia) : "r"(li), "r"(threadIdx.x));
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(best) : "r"(va));
+            asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(idx) : "r"(ia));
+        }
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            argmax_take(best, idx, ov, oi);
+        }
+        if (threadIdx.x == 0) out[blockIdx.y] = idx;
+    }
+    // nobody leaves while CTA 0 may still read its shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <typename T>
+static cudaError_t launch_argmax(const void* logits, int64_t* out, int M, int N, cudaStream_t st) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ARGMAX_CLUSTER, M);
+    cfg.blockDim = dim3(1024);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ARGMAX_CLUSTER;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, argmax_kernel<T>, static_cast<const T*>(logits), out, N);
 }
 
 }  // namespace alloyb
@@ -111,17 +178,17 @@ extern "C" int alloyb_rms_norm(const void* x, const void* weight, void* y, int M
     cudaStream_t st = as_stream(stream);
     switch (dtype) {
         case ALLOYB_F16:
-            rms_norm_kernel<__half><<<M, 256, 0, st>>>(static_cast<const __half*>(x),
+            launch_pdl(rms_norm_kernel<__half>, dim3(M), dim3(256), 0, st, static_cast<const __half*>(x),
                                                        static_cast<const __half*>(weight),
                                                        static_cast<__half*>(y), K, eps);
             break;
         case ALLOYB_BF16:
-            rms_norm_kernel<__nv_bfloat16><<<M, 256, 0, st>>>(
+            launch_pdl(rms_norm_kernel<__nv_bfloat16>, dim3(M), dim3(256), 0, st, 
                 static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight),
                 static_cast<__nv_bfloat16*>(y), K, eps);
             break;
         case ALLOYB_F32:
-            rms_norm_kernel<float><<<M, 256, 0, st>>>(static_cast<const float*>(x),
+            launch_pdl(rms_norm_kernel<float>, dim3(M), dim3(256), 0, st, static_cast<const float*>(x),
                                                       static_cast<const float*>(weight),
                                                       static_cast<float*>(y), K, eps);
             break;
@@ -141,16 +208,16 @@ extern "C" int alloyb_rope_inplace(void* q, void* k, const int32_t* pos, int pos
     cudaStream_t st = as_stream(stream);
     switch (dtype) {
         case ALLOYB_F16:
-            rope_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<__half*>(q), static_cast<__half*>(k),
+            launch_pdl(rope_kernel<__half>, dim3(blocks), dim3(256), 0, st, static_cast<__half*>(q), static_cast<__half*>(k),
                                                         pos, pos_count, inv_freq, B, H, KV_H, D);
             break;
         case ALLOYB_BF16:
-            rope_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
+            launch_pdl(rope_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, st, 
                 static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), pos, pos_count,
                 inv_freq, B, H, KV_H, D);
             break;
         case ALLOYB_F32:
-            rope_kernel<float><<<blocks, 256, 0, st>>>(static_cast<float*>(q), static_cast<float*>(k),
+            launch_pdl(rope_kernel<float>, dim3(blocks), dim3(256), 0, st, static_cast<float*>(q), static_cast<float*>(k),
                                                        pos, pos_count, inv_freq, B, H, KV_H, D);
             break;
         default: return ALLOYB_E_DTYPE;
@@ -168,17 +235,17 @@ extern "C" int alloyb_silu_mul(const void* gate, const void* up, void* y, int64_
     cudaStream_t st = as_stream(stream);
     switch (dtype) {
         case ALLOYB_F16:
-            silu_mul_kernel<__half><<<static_cast<int>(blocks), 256, 0, st>>>(
+            launch_pdl(silu_mul_kernel<__half>, dim3(static_cast<int>(blocks)), dim3(256), 0, st, 
                 static_cast<const __half*>(gate), static_cast<const __half*>(up),
                 static_cast<__half*>(y), n);
             break;
         case ALLOYB_BF16:
-            silu_mul_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(
+            launch_pdl(silu_mul_kernel<__nv_bfloat16>, dim3(static_cast<int>(blocks)), dim3(256), 0, st, 
                 static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up),
                 static_cast<__nv_bfloat16*>(y), n);
             break;
         case ALLOYB_F32:
-            silu_mul_kernel<float><<<static_cast<int>(blocks), 256, 0, st>>>(
+            launch_pdl(silu_mul_kernel<float>, dim3(static_cast<int>(blocks)), dim3(256), 0, st, 
                 static_cast<const float*>(gate), static_cast<const float*>(up),
                 static_cast<float*>(y), n);
             break;
@@ -193,18 +260,13 @@ extern "C" int alloyb_argmax(const void* logits, int64_t* out_ids, int M, int N,
     if (M < 0 || N <= 0) return ALLOYB_E_SHAPE;
     if (M == 0) return ALLOYB_OK;
     cudaStream_t st = as_stream(stream);
+    cudaError_t e;
     switch (dtype) {
-        case ALLOYB_F16:
-            argmax_kernel<__half><<<M, 1024, 0, st>>>(static_cast<const __half*>(logits), out_ids, N);
-            break;
-        case ALLOYB_BF16:
-            argmax_kernel<__nv_bfloat16><<<M, 1024, 0, st>>>(
-                static_cast<const __nv_bfloat16*>(logits), out_ids, N);
-            break;
-        case ALLOYB_F32:
-            argmax_kernel<float><<<M, 1024, 0, st>>>(static_cast<const float*>(logits), out_ids, N);
-            break;
+        case ALLOYB_F16: e = launch_argmax<__half>(logits, out_ids, M, N, st); break;
+        case ALLOYB_BF16: e = launch_argmax<__nv_bfloat16>(logits, out_ids, M, N, st); break;
+        case ALLOYB_F32: e = launch_argmax<float>(logits, out_ids, M, N, st); break;
         default: return ALLOYB_E_DTYPE;
     }
+    if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
     return check_launch();
 }

@@ -31,6 +31,8 @@ __global__ void kv_quantize_range_kernel(const __half* __restrict__ src, int64_t
                                          int64_t stok, int8_t* __restrict__ codes,
                                          __half* __restrict__ scales, int B, int KV_H, int S_max,
                                          int D, int start, int n_tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int nblk = D / 32;
     const int64_t warps_total = static_cast<int64_t>(B) * KV_H * n_tokens * nblk;
@@ -53,6 +55,7 @@ template <int LAYOUT>
 __global__ void kv_append_kernel(const __half* __restrict__ new_k, const __half* __restrict__ new_v,
                                  int64_t sb, int64_t sh, KVPtrs kv, const int32_t* __restrict__ pos,
                                  int pos_count, int B, int KV_H, int D, int* __restrict__ status) {
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int nblk = D / 32;
     const int64_t warps_total = static_cast<int64_t>(B) * KV_H * nblk * 2;
@@ -99,6 +102,8 @@ __global__ void kv_append_kernel(const __half* __restrict__ new_k, const __half*
 __global__ void kv_dequant_kernel(const int8_t* __restrict__ codes, const __half* __restrict__ scales,
                                   __half* __restrict__ out, int64_t rows_total, int S_max, int D,
                                   int end) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t total = rows_total * D;
     for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -119,15 +124,15 @@ int launch_kv_append(int layout, const void* new_k, const void* new_v, int64_t s
     const int blocks = static_cast<int>((warps * 32 + 255) / 256);
     switch (layout) {
         case ALLOYB_KV_F16:
-            kv_append_kernel<ALLOYB_KV_F16><<<blocks, 256, 0, st>>>(nk, nv, sb, sh, kv, pos, pos_count,
+            launch_pdl(kv_append_kernel<ALLOYB_KV_F16>, dim3(blocks), dim3(256), 0, st, nk, nv, sb, sh, kv, pos, pos_count,
                                                                     B, KV_H, D, status);
             break;
         case ALLOYB_KV_Q8_SPLIT:
-            kv_append_kernel<ALLOYB_KV_Q8_SPLIT><<<blocks, 256, 0, st>>>(nk, nv, sb, sh, kv, pos,
+            launch_pdl(kv_append_kernel<ALLOYB_KV_Q8_SPLIT>, dim3(blocks), dim3(256), 0, st, nk, nv, sb, sh, kv, pos,
                                                                          pos_count, B, KV_H, D, status);
             break;
         case ALLOYB_KV_Q8_PAGED:
-            kv_append_kernel<ALLOYB_KV_Q8_PAGED><<<blocks, 256, 0, st>>>(nk, nv, sb, sh, kv, pos,
+            launch_pdl(kv_append_kernel<ALLOYB_KV_Q8_PAGED>, dim3(blocks), dim3(256), 0, st, nk, nv, sb, sh, kv, pos,
                                                                          pos_count, B, KV_H, D, status);
             break;
         default:
@@ -151,7 +156,7 @@ extern "C" int alloyb_kv_quantize_q8(const void* src, int64_t src_batch_stride,
     const int64_t warps = static_cast<int64_t>(B) * KV_H * n_tokens * (D / 32);
     const int64_t blocks = (warps * 32 + 255) / 256;
     if (blocks > 0x7fffffff) return ALLOYB_E_SHAPE;
-    kv_quantize_range_kernel<<<static_cast<int>(blocks), 256, 0, as_stream(stream)>>>(
+    launch_pdl(kv_quantize_range_kernel, dim3(static_cast<int>(blocks)), dim3(256), 0, as_stream(stream), 
         static_cast<const __half*>(src), src_batch_stride, src_head_stride, src_tok_stride,
         static_cast<int8_t*>(codes), static_cast<__half*>(scales), B, KV_H, S_max, D, start, n_tokens);
     return check_launch();
@@ -166,7 +171,7 @@ extern "C" int alloyb_kv_dequant_q8(const void* codes, const void* scales, void*
     const int64_t rows = static_cast<int64_t>(B) * KV_H * S_max;
     const int64_t want = (rows * D + 255) / 256;
     const int blocks = static_cast<int>(want < 148 * 32 ? want : 148 * 32);
-    kv_dequant_kernel<<<blocks, 256, 0, as_stream(stream)>>>(
+    launch_pdl(kv_dequant_kernel, dim3(blocks), dim3(256), 0, as_stream(stream), 
         static_cast<const int8_t*>(codes), static_cast<const __half*>(scales),
         static_cast<__half*>(out), rows, S_max, D, end);
     return check_launch();

@@ -17,6 +17,7 @@ template <typename XT>
 __global__ void __launch_bounds__(ROWS_WARPS * 32)
 linear_rows_kernel(const XT* __restrict__ x, int M, int K, RowSegs segs,
                    const XT* __restrict__ residual) {
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int row = blockIdx.x * ROWS_WARPS + warp;
     if (row >= segs.total_rows) return;
@@ -63,6 +64,7 @@ gated_rows_kernel(const XT* __restrict__ x, int M, int K, int N, int format,
                   const uint8_t* __restrict__ gate, const __half* __restrict__ gate_scales,
                   const uint8_t* __restrict__ up, const __half* __restrict__ up_scales,
                   int64_t row_bytes, XT* __restrict__ y, int act) {
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * ROWS_WARPS + warp;
     if (row >= N) return;
@@ -145,7 +147,7 @@ template <typename XT>
 static int launch_rows(const void* x, int M, int K, const RowSegs& segs, const void* residual,
                        cudaStream_t st) {
     const int blocks = (segs.total_rows + ROWS_WARPS - 1) / ROWS_WARPS;
-    linear_rows_kernel<XT><<<blocks, ROWS_WARPS * 32, 0, st>>>(
+    launch_pdl(linear_rows_kernel<XT>, dim3(blocks), dim3(ROWS_WARPS * 32), 0, st, 
         static_cast<const XT*>(x), M, K, segs, static_cast<const XT*>(residual));
     return check_launch();
 }
@@ -243,17 +245,17 @@ extern "C" int alloyb_gated_linear(const void* x, const void* gate, const void* 
     const __half* us = static_cast<const __half*>(up_scales);
     switch (dtype) {
         case ALLOYB_F16:
-            gated_rows_kernel<__half><<<blocks, ROWS_WARPS * 32, 0, st>>>(
+            launch_pdl(gated_rows_kernel<__half>, dim3(blocks), dim3(ROWS_WARPS * 32), 0, st, 
                 static_cast<const __half*>(x), M, K, N, format, g8, gs, u8, us, row_bytes,
                 static_cast<__half*>(y), act);
             break;
         case ALLOYB_BF16:
-            gated_rows_kernel<__nv_bfloat16><<<blocks, ROWS_WARPS * 32, 0, st>>>(
+            launch_pdl(gated_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(ROWS_WARPS * 32), 0, st, 
                 static_cast<const __nv_bfloat16*>(x), M, K, N, format, g8, gs, u8, us, row_bytes,
                 static_cast<__nv_bfloat16*>(y), act);
             break;
         case ALLOYB_F32:
-            gated_rows_kernel<float><<<blocks, ROWS_WARPS * 32, 0, st>>>(
+            launch_pdl(gated_rows_kernel<float>, dim3(blocks), dim3(ROWS_WARPS * 32), 0, st, 
                 static_cast<const float*>(x), M, K, N, format, g8, gs, u8, us, row_bytes,
                 static_cast<float*>(y), act);
             break;

@@ -42,8 +42,10 @@
 namespace alloyb {
 namespace st {
 
-constexpr int GW = 8;                        // warps per group (= K slices per tile)
-constexpr int MAX_GROUPS = 2;
+constexpr int WARPS = 16;                    // warps per CTA
+// Warps per group (= K slices per tile) is a kernel template parameter GW: 8 when an SM owns few
+// tiles (the K split is what keeps all its warps busy), 1 when it owns at least two tiles per warp
+// (every warp then runs whole tiles on its own, with no reduction and no barrier at all).
 constexpr int MAX_D = 4;                     // ring slots per warp (upper bound)
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr int MAX_SEG = MAX_SEGS;
@@ -81,7 +83,6 @@ struct Params {
     int nsb;
     int gated;                               // seg[0] = gate, seg[1] = up, y = act(gate) * up
     int act;
-    int n_groups;
     int depth;                               // ring slots per warp
     int debug;
 };
@@ -377,18 +378,19 @@ __device__ __forceinline__ void unit_q6k(uint32_t blk, const XFrag6& f, int g, i
 
 // KIND: slot geometry / weight format.  RT: matrices per tile (2 = gate/up pair).  CACHE: the warp's
 // slice is exactly one slot long and its B fragments stay in registers for the whole launch.
-template <int KIND, int RT, bool CACHE>
-__global__ void __launch_bounds__(MAX_GROUPS* GW * 32, 1)
+template <int KIND, int RT, bool CACHE, int GW>
+__global__ void __launch_bounds__(WARPS * 32, 1)
 gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     constexpr int SBS = Geom<KIND>::SBS, PITCH = Geom<KIND>::PITCH, SLOT = 16 * PITCH, BLK = Geom<KIND>::BLK;
     using XF = typename std::conditional<KIND == Q6, XFrag6, XFrag>::type;
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int grp = warp / GW, wg = warp % GW;
-    const int n_warps = P.n_groups * GW, D = P.depth;
+    constexpr int n_warps = WARPS, n_groups = WARPS / GW;
+    const int D = P.depth;
     // [warps][D] slots | [groups][2][GW][RT][16] partials | [warps][MAX_D] barriers
     float* red = reinterpret_cast<float*>(smem + n_warps * D * SLOT) + grp * (2 * GW * RT * 16);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + n_warps * D * SLOT + P.n_groups * 2 * GW * RT * 16 * 4);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + n_warps * D * SLOT + n_groups * 2 * GW * RT * 16 * 4);
     const uint32_t ring = smem_u32(smem + warp * D * SLOT);
     const uint32_t bar0 = smem_u32(bars + warp * MAX_D);
 
@@ -412,7 +414,7 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
         cursor_next(c, P, lo, hi, grp);
         while (c.seg < P.n_seg) {
             ++my_tiles;
-            cursor_next(c, P, lo, hi, P.n_groups);
+            cursor_next(c, P, lo, hi, n_groups);
         }
     }
     const int n_stage = my_tiles * spt;
@@ -450,7 +452,7 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
         if (++p_slot == D) p_slot = 0;
         if (++p_r == spt) {
             p_r = 0;
-            cursor_next(pc, P, lo, hi, P.n_groups);
+            cursor_next(pc, P, lo, hi, n_groups);
         }
     };
     while (issued < n_stage && issued < D) issue();
@@ -510,8 +512,7 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
             for (int mt = 0; mt < RT; ++mt)
                 if (issued < n_stage) issue();                       // refills the slots just drained
         }
-        // fold the four t lanes, then the eight K slices of the group
-        float* rbuf = red + (it & 1) * (GW * RT * 16);
+        // fold the four t lanes ...
 #pragma unroll
         for (int m = 0; m < RT; ++m)
 #pragma unroll
@@ -519,19 +520,12 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
                 float v = acc[m][i];
                 v += __shfl_xor_sync(0xffffffffu, v, 1);
                 v += __shfl_xor_sync(0xffffffffu, v, 2);
-                if (t == 0) rbuf[(wg * RT + m) * 16 + g + 8 * i] = v;
+                acc[m][i] = v;
             }
-        asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "n"(GW * 32) : "memory");
-        const int tl = threadIdx.x - grp * GW * 32;
-        if (tl < 16 && cc.row + tl < cc.lim) {
+        auto store = [&](int tl, float v, float u) {
+            if (cc.row + tl >= cc.lim) return;
             const Seg& sg = P.seg[cc.seg];
             const int row = cc.row + tl;
-            float v = 0.f, u = 0.f;
-#pragma unroll
-            for (int w = 0; w < GW; ++w) {
-                v += rbuf[(w * RT) * 16 + tl];
-                if (RT == 2) u += rbuf[(w * RT + 1) * 16 + tl];
-            }
             __half* y = static_cast<__half*>(sg.y);
             if (RT == 2) {
                 const float a = (P.act == ALLOYB_ACT_SILU) ? act_silu(v) : act_gelu_tanh(v);
@@ -541,8 +535,36 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
                 if (P.residual) r = __float2half_rn(__half2float(P.residual[row]) + __half2float(r));
                 y[row] = r;
             }
+        };
+        if constexpr (GW == 1) {
+            // ... and the tile is done: lanes t == 0 hold rows g and g + 8
+            if (t == 0) {
+                store(g, acc[0][0], RT == 2 ? acc[RT - 1][0] : 0.f);
+                store(g + 8, acc[0][1], RT == 2 ? acc[RT - 1][1] : 0.f);
+            }
+        } else {
+            // ... then the K slices of the group (double-buffered partials, one named barrier)
+            float* rbuf = red + (it & 1) * (GW * RT * 16);
+            if (t == 0) {
+#pragma unroll
+                for (int m = 0; m < RT; ++m) {
+                    rbuf[(wg * RT + m) * 16 + g] = acc[m][0];
+                    rbuf[(wg * RT + m) * 16 + g + 8] = acc[m][1];
+                }
+            }
+            asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "n"(GW * 32) : "memory");
+            const int tl = threadIdx.x - grp * GW * 32;
+            if (tl < 16) {
+                float v = 0.f, u = 0.f;
+#pragma unroll
+                for (int w = 0; w < GW; ++w) {
+                    v += rbuf[(w * RT) * 16 + tl];
+                    if (RT == 2) u += rbuf[(w * RT + 1) * 16 + tl];
+                }
+                store(tl, v, u);
+            }
         }
-        cursor_next(cc, P, lo, hi, P.n_groups);
+        cursor_next(cc, P, lo, hi, n_groups);
     }
     if (!ok) {
         // a wait ran out (sticky error word set; this CTA's results are garbage): let copies in
@@ -551,10 +573,10 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     }
 }
 
-template <int KIND, int RT, bool CACHE>
+template <int KIND, int RT, bool CACHE, int GW>
 static int launch(const Maps& maps, const Params& P, cudaStream_t stream) {
     static bool configured = false;
-    auto kern = gemv_stream_kernel<KIND, RT, CACHE>;
+    auto kern = gemv_stream_kernel<KIND, RT, CACHE, GW>;
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
@@ -566,8 +588,8 @@ static int launch(const Maps& maps, const Params& P, cudaStream_t stream) {
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     }
-    const int n_warps = P.n_groups * GW;
-    const int smem = n_warps * P.depth * 16 * Geom<KIND>::PITCH + P.n_groups * 2 * GW * RT * 16 * 4 + n_warps * MAX_D * 8;
+    constexpr int n_warps = WARPS, n_groups = WARPS / GW;
+    const int smem = n_warps * P.depth * 16 * Geom<KIND>::PITCH + n_groups * 2 * GW * RT * 16 * 4 + n_warps * MAX_D * 8;
     int grid = sms;
     const int tiles = (P.total_rows + 15) / 16;
     if (grid > tiles) grid = tiles;
@@ -617,11 +639,21 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
     if (M != 1 || dtype != ALLOYB_F16 || K % QK_K || n_seg < 1 || n_seg > MAX_SEG) return ALLOYB_NOT_TAKEN;
     if (reinterpret_cast<uintptr_t>(x) % 16) return ALLOYB_NOT_TAKEN;
     const int nsb = K / QK_K;
-    if (nsb % GW) return ALLOYB_NOT_TAKEN;
     if (gated && (n_seg != 2 || seg[0].N != seg[1].N)) return ALLOYB_NOT_TAKEN;
     const int fmt = seg[0].format;
     if (fmt != ALLOYB_Q4_K && !(fmt == ALLOYB_Q6_K && !gated)) return ALLOYB_NOT_TAKEN;
-    const int slice = nsb / GW;
+    int64_t all_rows = 0;
+    for (int i = 0; i < (gated ? 1 : n_seg); ++i) all_rows += seg[i].N;
+    // whole tiles per warp once every SM owns at least two tiles per warp, else an 8-way K split
+    static const int force_gw = env_int("ALLOYB_ST_GW", 0);
+    int gw = (all_rows / 16 >= static_cast<int64_t>(2) * WARPS * 148) ? 1 : 8;
+    if (force_gw == 1 || force_gw == 8) gw = force_gw;
+    if (nsb % gw) {
+        if (nsb % 8 == 0) gw = 8;
+        else if (all_rows / 16 >= 148) gw = 1;
+        else return ALLOYB_NOT_TAKEN;
+    }
+    const int slice = nsb / gw;
     const int kind = fmt == ALLOYB_Q6_K ? Q6 : ((slice % 2 == 0) ? Q4x2 : Q4x1);
     const int sbs = kind == Q4x2 ? 2 : 1;
     const int blk = fmt == ALLOYB_Q6_K ? Q6K_BYTES : Q4K_BYTES;
@@ -636,7 +668,6 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
     P.act = act;
     static const int dbg = env_int("ALLOYB_ST_DEBUG", 0), depth = env_int("ALLOYB_ST_DEPTH", 0);
     P.debug = dbg;
-    P.n_groups = MAX_GROUPS;
     P.depth = depth > 0 ? (depth > MAX_D ? MAX_D : depth) : (kind == Q4x1 ? 3 : 2);
     int64_t rows = 0;
     for (int i = 0; i < n_seg; ++i) {
@@ -667,13 +698,13 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
     }
     for (int i = n_seg; i < MAX_SEG; ++i) maps.m[i] = maps.m[0];
     const bool cache = slice == sbs;
-    if (kind == Q6) return cache ? launch<Q6, 1, true>(maps, P, stream) : launch<Q6, 1, false>(maps, P, stream);
-    if (gated) {
-        if (kind == Q4x2) return cache ? launch<Q4x2, 2, true>(maps, P, stream) : launch<Q4x2, 2, false>(maps, P, stream);
-        return cache ? launch<Q4x1, 2, true>(maps, P, stream) : launch<Q4x1, 2, false>(maps, P, stream);
-    }
-    if (kind == Q4x2) return cache ? launch<Q4x2, 1, true>(maps, P, stream) : launch<Q4x2, 1, false>(maps, P, stream);
-    return cache ? launch<Q4x1, 1, true>(maps, P, stream) : launch<Q4x1, 1, false>(maps, P, stream);
+#define ALLOYB_ST_LAUNCH(KIND, RT)                                                                              \
+    (gw == 1 ? launch<KIND, RT, false, 1>(maps, P, stream)                                                     \
+             : (cache ? launch<KIND, RT, true, 8>(maps, P, stream) : launch<KIND, RT, false, 8>(maps, P, stream)))
+    if (kind == Q6) return ALLOYB_ST_LAUNCH(Q6, 1);
+    if (gated) return kind == Q4x2 ? ALLOYB_ST_LAUNCH(Q4x2, 2) : ALLOYB_ST_LAUNCH(Q4x1, 2);
+    return kind == Q4x2 ? ALLOYB_ST_LAUNCH(Q4x2, 1) : ALLOYB_ST_LAUNCH(Q4x1, 1);
+#undef ALLOYB_ST_LAUNCH
 }
 
 int gemv_stream_device_error(int clear) {
