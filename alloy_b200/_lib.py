@@ -53,6 +53,8 @@ SIGNATURES = {
     "alloyb_q6k_mm": (_i, [_p, _p, _p, _i, _i, _i, _i, _p]),
     "alloyb_q8_0_mm": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p]),
     "alloyb_gated_linear": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "alloyb_linear_normed": (_i, [_p, _p, _f, _p, _i, _i, _i, C.POINTER(Weight), _i, _p]),
+    "alloyb_gated_linear_normed": (_i, [_p, _p, _f, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "alloyb_kv_quantize_q8": (_i, [_p, _i64, _i64, _i64, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "alloyb_kv_dequant_q8": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "alloyb_kv_append_q8_paged": (_i, [_p, _p, _i64, _i64, _p, _p, _i, _i64, _p, _i, _i, _i, _p, _p]),

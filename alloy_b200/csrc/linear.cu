@@ -264,3 +264,39 @@ extern "C" int alloyb_gated_linear(const void* x, const void* gate, const void* 
     }
     return check_launch();
 }
+
+// ---- RMSNorm fused into the activation load (one token), two launches otherwise
+
+extern "C" int alloyb_linear_normed(const void* x, const void* norm_weight, float eps, void* xn_scratch, int M, int K,
+                                    int dtype, const alloyb_weight* w, int n_w, void* stream) {
+    if (!x || !norm_weight || !xn_scratch) return ALLOYB_E_NULL;
+    if (M < 0 || K <= 0) return ALLOYB_E_SHAPE;
+    RowSegs segs;
+    int rc = validate_segs(w, n_w, K, segs);
+    if (rc != ALLOYB_OK) return rc;
+    if (M == 0) return ALLOYB_OK;
+    rc = try_gemv_stream_mixed(x, M, K, dtype, segs.seg, segs.n_seg, nullptr, norm_weight, eps, as_stream(stream));
+    if (rc != ALLOYB_NOT_TAKEN) return rc;
+    rc = alloyb_rms_norm(x, norm_weight, xn_scratch, M, K, eps, dtype, stream);
+    if (rc != ALLOYB_OK) return rc;
+    return alloyb_linear(xn_scratch, M, K, dtype, w, n_w, nullptr, stream);
+}
+
+extern "C" int alloyb_gated_linear_normed(const void* x, const void* norm_weight, float eps, void* xn_scratch,
+                                          const void* gate, const void* gate_scales, const void* up,
+                                          const void* up_scales, void* y, int M, int N, int K, int format, int act,
+                                          int dtype, void* stream) {
+    if (!x || !norm_weight || !xn_scratch || !gate || !up || !y) return ALLOYB_E_NULL;
+    if (M < 0 || N <= 0 || K <= 0) return ALLOYB_E_SHAPE;
+    if (act != ALLOYB_ACT_SILU && act != ALLOYB_ACT_GELU_TANH) return ALLOYB_E_SHAPE;
+    if (M == 0) return ALLOYB_OK;
+    if (format == ALLOYB_Q4_K && K % QK_K == 0 && M == 1) {
+        const int64_t rb = static_cast<int64_t>(K / QK_K) * Q4K_BYTES;
+        const WeightSeg pair[2] = {{ALLOYB_Q4_K, N, gate, nullptr, rb, y, N}, {ALLOYB_Q4_K, N, up, nullptr, rb, y, N}};
+        const int rc = try_gemv_stream(x, M, K, dtype, pair, 2, true, act, nullptr, norm_weight, eps, as_stream(stream));
+        if (rc != ALLOYB_NOT_TAKEN) return rc;
+    }
+    const int rc = alloyb_rms_norm(x, norm_weight, xn_scratch, M, K, eps, dtype, stream);
+    if (rc != ALLOYB_OK) return rc;
+    return alloyb_gated_linear(xn_scratch, gate, gate_scales, up, up_scales, y, M, N, K, format, act, dtype, stream);
+}

@@ -743,7 +743,7 @@ int try_linear_fast(const void* x, int M, int K, int dtype, const WeightSeg* seg
     if (reinterpret_cast<uintptr_t>(x) % 16 || K % 8) return ALLOYB_NOT_TAKEN;
     if (M > 128) return ALLOYB_NOT_TAKEN;
     if (!no_stream_flag()) {
-        const int rc = try_gemv_stream(x, M, K, dtype, seg, n_seg, false, 0, residual, st);
+        const int rc = try_gemv_stream_mixed(x, M, K, dtype, seg, n_seg, residual, nullptr, 0.f, st);
         if (rc != ALLOYB_NOT_TAKEN) return rc;
     }
     int stage_bytes = 0;
@@ -798,7 +798,7 @@ int try_gated_fast(const void* x, const void* gate, const void* gate_scales, con
     if (!seg_ok(gs, K) || !seg_ok(us, K)) return ALLOYB_NOT_TAKEN;
     if (!no_stream_flag()) {
         const WeightSeg pair[2] = {gs, us};
-        const int rc = try_gemv_stream(x, M, K, dtype, pair, 2, true, act, nullptr, st);
+        const int rc = try_gemv_stream(x, M, K, dtype, pair, 2, true, act, nullptr, nullptr, 0.f, st);
         if (rc != ALLOYB_NOT_TAKEN) return rc;
     }
     const int stage_bytes = 32 * Q4_STRIDE;

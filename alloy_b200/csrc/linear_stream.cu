@@ -77,6 +77,8 @@ struct Seg {
 struct Params {
     const __half* x;
     const __half* residual;
+    const __half* norm_w;                    // non-null: RMSNorm(x; norm_w, eps) is applied on the way in
+    float eps;
     Seg seg[MAX_SEG];
     int n_seg;                               // matrices walked row-wise (1 for a gate/up pair)
     int total_rows;
@@ -84,7 +86,6 @@ struct Params {
     int gated;                               // seg[0] = gate, seg[1] = up, y = act(gate) * up
     int act;
     int depth;                               // ring slots per warp
-    int debug;
 };
 struct Maps {
     CUtensorMap m[MAX_SEG];                  // (row_bytes / 4, n_rows) uint32, box PITCH/4 x 16
@@ -209,7 +210,7 @@ __device__ __forceinline__ void load_xfrag(XFrag& f, const __half* x, int sb, in
         const uint4* xp = reinterpret_cast<const uint4*>(x + sb * QK_K + 32 * g);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            const uint4 v = __ldg(xp + q);
+            const uint4 v = xp[q];
             f.b[2 * q][0] = prmt(v.x, v.y, 0x5410u);          // (x[4j], x[4j+2])
             f.b[2 * q][1] = prmt(v.x, v.y, 0x7632u);          // (x[4j+1], x[4j+3])
             f.b[2 * q + 1][0] = prmt(v.z, v.w, 0x5410u);
@@ -308,7 +309,7 @@ __device__ __forceinline__ void load_xfrag6(XFrag6& f, const __half* x, int sb, 
     constexpr uint32_t ONE2 = 0x3C003C00u;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        const uint2 v = __ldg(reinterpret_cast<const uint2*>(x + sb * QK_K + 128 * h + 16 * g + 4 * t));
+        const uint2 v = *reinterpret_cast<const uint2*>(x + sb * QK_K + 128 * h + 16 * g + 4 * t);
         f.b[h][0] = prmt(v.x, v.y, 0x5410u);
         f.b[h][1] = prmt(v.x, v.y, 0x7632u);
         float s[4];
@@ -393,6 +394,7 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + n_warps * D * SLOT + n_groups * 2 * GW * RT * 16 * 4);
     const uint32_t ring = smem_u32(smem + warp * D * SLOT);
     const uint32_t bar0 = smem_u32(bars + warp * MAX_D);
+    const int xs_off = n_warps * D * SLOT + n_groups * 2 * GW * RT * 16 * 4 + n_warps * MAX_D * 8;      // 16-byte aligned
 
     if (lane == 0) {
         for (int s = 0; s < D; ++s) mbar_init(bar0 + 8 * s, 1);
@@ -430,7 +432,7 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
         const int nvalid = pc.lim - pc.row < 16 ? pc.lim - pc.row : 16;
         const uint32_t bar = bar0 + 8 * p_slot, dst = ring + p_slot * SLOT;
         const int win = (sb * BLK) & ~15;                            // 16-byte-aligned start of the stage in a row
-        if (!(P.debug & 2)) {
+        {
             if (nvalid == 16) {
                 if (lane == 0) {
                     mbar_expect_tx(bar, SLOT);
@@ -459,13 +461,57 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
 
     pdl_wait();          // activations, residual and outputs belong to the previous kernel until here
 
+    // Fused RMSNorm: the CTA normalises the token once into shared memory (same arithmetic as the
+    // stand-alone kernel: fp32 sum of squares, x * r narrowed to fp16, then times the fp16 weight)
+    // and every warp builds its B fragments from there.
+    const __half* xsrc = P.x;
+    if (P.norm_w) {
+        const int K = P.nsb * QK_K;
+        __half* xs = reinterpret_cast<__half*>(smem + xs_off);
+        float* nred = reinterpret_cast<float*>(smem + xs_off + K * 2);
+        float ssq = 0.f;
+        for (int i = threadIdx.x * 8; i < K; i += WARPS * 32 * 8) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(P.x + i));
+            const __half2* h2 = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f2 = __half22float2(h2[j]);
+                ssq = fmaf(f2.x, f2.x, ssq);
+                ssq = fmaf(f2.y, f2.y, ssq);
+            }
+        }
+        ssq = warp_sum(ssq);
+        if (lane == 0) nred[warp] = ssq;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int i = 0; i < WARPS; ++i) tot += nred[i];
+        const float r = rsqrtf(tot / static_cast<float>(K) + P.eps);
+        for (int i = threadIdx.x * 8; i < K; i += WARPS * 32 * 8) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(P.x + i));
+            const uint4 w = __ldg(reinterpret_cast<const uint4*>(P.norm_w + i));
+            const __half* hv = reinterpret_cast<const __half*>(&v);
+            const __half* hw = reinterpret_cast<const __half*>(&w);
+            uint4 o;
+            __half* ho = reinterpret_cast<__half*>(&o);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const __half normed = __float2half_rn(__half2float(hv[j]) * r);
+                ho[j] = __float2half_rn(__half2float(hw[j]) * __half2float(normed));
+            }
+            *reinterpret_cast<uint4*>(xs + i) = o;
+        }
+        __syncthreads();
+        xsrc = xs;
+    }
+
     const ScaleSel ss = make_scale_sel(t);
     XF xc[CACHE ? SBS : 1];
     if (CACHE) {
 #pragma unroll
         for (int i = 0; i < SBS; ++i) {
-            if constexpr (KIND == Q6) load_xfrag6(xc[i], P.x, sb_lo + i, g, t);
-            else load_xfrag(xc[i], P.x, sb_lo + i, g, t);
+            if constexpr (KIND == Q6) load_xfrag6(xc[i], xsrc, sb_lo + i, g, t);
+            else load_xfrag(xc[i], xsrc, sb_lo + i, g, t);
         }
     }
 
@@ -484,23 +530,23 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
 #pragma unroll
             for (int mt = 0; mt < RT; ++mt) {
                 slot[mt] = ring + c_slot * SLOT;
-                if (ok && !(P.debug & 2)) ok = mbar_wait(bar0 + 8 * c_slot, c_ph);
+                if (ok) ok = mbar_wait(bar0 + 8 * c_slot, c_ph);
                 if (++c_slot == D) {
                     c_slot = 0;
                     c_ph ^= 1u;
                 }
             }
             ok = __all_sync(0xffffffffu, ok);
-            if (ok && !(P.debug & 1)) {
+            if (ok) {
 #pragma unroll
                 for (int i = 0; i < SBS; ++i) {
                     if constexpr (KIND == Q6) {
-                        if (!CACHE) load_xfrag6(xc[0], P.x, sb, g, t);
+                        if (!CACHE) load_xfrag6(xc[0], xsrc, sb, g, t);
                         const uint32_t off = static_cast<uint32_t>(sb * BLK) & 15u;
                         if (off & 2u) unit_q6k<false>(slot[0] + off, xc[0], g, t, acc[0][0], acc[0][1]);
                         else unit_q6k<true>(slot[0] + off, xc[0], g, t, acc[0][0], acc[0][1]);
                     } else {
-                        if (!CACHE) load_xfrag(xc[0], P.x, sb + i, g, t);
+                        if (!CACHE) load_xfrag(xc[0], xsrc, sb + i, g, t);
 #pragma unroll
                         for (int mt = 0; mt < RT; ++mt)
                             unit_q4k<PITCH>(slot[mt] + i * BLK, xc[CACHE ? i : 0], ss, g, t, acc[mt][0], acc[mt][1]);
@@ -589,7 +635,8 @@ static int launch(const Maps& maps, const Params& P, cudaStream_t stream) {
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     }
     constexpr int n_warps = WARPS, n_groups = WARPS / GW;
-    const int smem = n_warps * P.depth * 16 * Geom<KIND>::PITCH + n_groups * 2 * GW * RT * 16 * 4 + n_warps * MAX_D * 8;
+    const int smem = n_warps * P.depth * 16 * Geom<KIND>::PITCH + n_groups * 2 * GW * RT * 16 * 4 + n_warps * MAX_D * 8 +
+                     (P.norm_w ? P.nsb * QK_K * 2 + WARPS * 4 : 0);
     int grid = sms;
     const int tiles = (P.total_rows + 15) / 16;
     if (grid > tiles) grid = tiles;
@@ -634,10 +681,11 @@ static int env_int(const char* name, int dflt) {
 // One fp16 token against Q4_K or Q6_K matrices of one format (plain: up to MAX_SEGS row-stacked
 // outputs; gated: Q4_K gate/up pair with the activation fused).  NOT_TAKEN for anything else.
 int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg, int n_seg, bool gated, int act,
-                    const void* residual, cudaStream_t stream) {
+                    const void* residual, const void* norm_w, float eps, cudaStream_t stream) {
     using namespace st;
     if (M != 1 || dtype != ALLOYB_F16 || K % QK_K || n_seg < 1 || n_seg > MAX_SEG) return ALLOYB_NOT_TAKEN;
-    if (reinterpret_cast<uintptr_t>(x) % 16) return ALLOYB_NOT_TAKEN;
+    if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(norm_w) % 16) return ALLOYB_NOT_TAKEN;
+    if (norm_w && K > 16384) return ALLOYB_NOT_TAKEN;             // the normalised token lives in shared memory
     const int nsb = K / QK_K;
     if (gated && (n_seg != 2 || seg[0].N != seg[1].N)) return ALLOYB_NOT_TAKEN;
     const int fmt = seg[0].format;
@@ -662,12 +710,13 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
     Maps maps;
     P.x = static_cast<const __half*>(x);
     P.residual = static_cast<const __half*>(residual);
+    P.norm_w = static_cast<const __half*>(norm_w);
+    P.eps = eps;
     P.n_seg = gated ? 1 : n_seg;
     P.nsb = nsb;
     P.gated = gated ? 1 : 0;
     P.act = act;
-    static const int dbg = env_int("ALLOYB_ST_DEBUG", 0), depth = env_int("ALLOYB_ST_DEPTH", 0);
-    P.debug = dbg;
+    static const int depth = env_int("ALLOYB_ST_DEPTH", 0);     // tuning aid: ring slots per warp
     P.depth = depth > 0 ? (depth > MAX_D ? MAX_D : depth) : (kind == Q4x1 ? 3 : 2);
     int64_t rows = 0;
     for (int i = 0; i < n_seg; ++i) {
@@ -705,6 +754,32 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
     if (gated) return kind == Q4x2 ? ALLOYB_ST_LAUNCH(Q4x2, 2) : ALLOYB_ST_LAUNCH(Q4x1, 2);
     return kind == Q4x2 ? ALLOYB_ST_LAUNCH(Q4x2, 1) : ALLOYB_ST_LAUNCH(Q4x1, 1);
 #undef ALLOYB_ST_LAUNCH
+}
+
+int try_gemv_stream_mixed(const void* x, int M, int K, int dtype, const WeightSeg* seg, int n_seg, const void* residual,
+                          const void* norm_w, float eps, cudaStream_t stream) {
+    if (M != 1 || n_seg < 1 || n_seg > MAX_SEGS) return ALLOYB_NOT_TAKEN;
+    WeightSeg grp[2][MAX_SEGS];
+    int cnt[2] = {0, 0};
+    for (int i = 0; i < n_seg; ++i) {
+        const int f = seg[i].format == ALLOYB_Q4_K ? 0 : (seg[i].format == ALLOYB_Q6_K ? 1 : -1);
+        if (f < 0) return ALLOYB_NOT_TAKEN;
+        grp[f][cnt[f]++] = seg[i];
+    }
+    if (cnt[0] == 0 || cnt[1] == 0)
+        return try_gemv_stream(x, M, K, dtype, seg, n_seg, false, 0, residual, norm_w, eps, stream);
+    if (residual) return ALLOYB_NOT_TAKEN;
+    // both launches must be possible before the first one is made: probe with the cheap checks
+    if (dtype != ALLOYB_F16 || K % QK_K || (K / QK_K) % 8) return ALLOYB_NOT_TAKEN;
+    for (int i = 0; i < n_seg; ++i)
+        if (reinterpret_cast<uintptr_t>(seg[i].data) % 16 || seg[i].row_bytes % 16 || seg[i].N <= 0 ||
+            seg[i].row_bytes < static_cast<int64_t>(K / QK_K) * (seg[i].format == ALLOYB_Q4_K ? Q4K_BYTES : Q6K_BYTES))
+            return ALLOYB_NOT_TAKEN;
+    for (int f = 0; f < 2; ++f) {
+        const int rc = try_gemv_stream(x, M, K, dtype, grp[f], cnt[f], false, 0, nullptr, norm_w, eps, stream);
+        if (rc != ALLOYB_OK) return rc == ALLOYB_NOT_TAKEN ? ALLOYB_E_SHAPE : rc;
+    }
+    return ALLOYB_OK;
 }
 
 int gemv_stream_device_error(int clear) {

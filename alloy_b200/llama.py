@@ -57,6 +57,7 @@ class LayerWeights:
     __slots__ = ("wq", "wk", "wv", "wo", "wg", "wu", "wd", "norm_in", "norm_post")
 
 
+
 class QuantLlamaDecoder:
     """Random-init (seeded) Q4_K_M Llama-shape decoder for one decode step per call."""
 
@@ -162,6 +163,8 @@ class QuantLlamaDecoder:
         h = ops._embedding(self.ids, 0, self.embed, None, out_dtype=self.dtype)
         scale = 1.0 / (s.head_dim ** 0.5)
         for li, lw in enumerate(self.layers):
+            # q/k are Q4_K and v is Q6_K: one launch for the three projections beats the norm fused
+            # into one streaming launch per format (measured), so the norm stays its own kernel here
             xn = ops.rms_norm(h, lw.norm_in, s.eps)
             q, k, v = ops.linear_multi(xn, [("q4_k", lw.wq, None), ("q4_k", lw.wk, None),
                                             ("q6_k", lw.wv, None)])
@@ -183,14 +186,12 @@ class QuantLlamaDecoder:
                 h = torch.ops.alloy.linear_residual(a2, lw.wo, None, h, "q4_k")
             else:
                 h = h + tp.row_parallel(a2, lambda t: torch.ops.alloy.gguf_q4_k_mm(t, lw.wo), self.pg)
-            xn = ops.rms_norm(h, lw.norm_post, s.eps)
-            act = torch.ops.alloy.gguf_q4_k_silu(xn, lw.wg, lw.wu)
+            act = ops.gated_normed(h, lw.norm_post, s.eps, lw.wg, lw.wu)
             if self.tp_size == 1:
                 h = torch.ops.alloy.linear_residual(act, lw.wd, None, h, "q6_k")
             else:
                 h = h + tp.row_parallel(act, lambda t: torch.ops.alloy.gguf_q6_k_mm(t, lw.wd), self.pg)
-        xn = ops.rms_norm(h, self.norm_final, s.eps)
-        logits = torch.ops.alloy.gguf_q6_k_mm(xn, self.head)
+        logits = ops.linear_multi(h, [("q6_k", self.head, None)], norm=(self.norm_final, s.eps))[0]
         if self.tp_size > 1:
             logits = tp.gather_columns(logits, self.pg)
         self.logits = logits

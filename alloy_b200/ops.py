@@ -159,11 +159,13 @@ def _linear(x: torch.Tensor, fmt: int, weights: Sequence[torch.Tensor],
     return outs
 
 
-def linear_multi(x: torch.Tensor, specs: Sequence[tuple[str, torch.Tensor, torch.Tensor | None]]):
-    """Sibling projections of possibly different formats in ONE launch.
+def linear_multi(x: torch.Tensor, specs: Sequence[tuple[str, torch.Tensor, torch.Tensor | None]],
+                 norm: tuple[torch.Tensor, float] | None = None):
+    """Sibling projections of possibly different formats in ONE call.
 
     ``specs``: (format name, weight, scales-or-None) per matrix, all with the
     same K.  Used for q/k/v where v is Q6_K while q and k are Q4_K.
+    ``norm`` = (weight, eps): the projections see RMSNorm(x) (``alloyb_linear_normed``).
     """
     fm0 = _FORMATS[specs[0][0]]
     k = _k_of(fm0, specs[0][1])
@@ -182,9 +184,33 @@ def linear_multi(x: torch.Tensor, specs: Sequence[tuple[str, torch.Tensor, torch
                           y.data_ptr(), 0)
         outs.append(y)
     L = _lib.load()
+    if norm is not None:
+        nw, eps = norm
+        scratch = torch.empty_like(x)
+        check(L.alloyb_linear_normed(x.data_ptr(), nw.data_ptr(), float(eps), scratch.data_ptr(), m, k,
+                                     _dtype_code(x), descs, len(specs), _stream()), "alloyb_linear_normed")
+        return outs
     check(L.alloyb_linear(x.data_ptr(), m, k, _dtype_code(x), descs, len(specs), None, _stream()),
           "alloyb_linear")
     return outs
+
+
+def gated_normed(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, gate: torch.Tensor, up: torch.Tensor,
+                 act: str = "silu") -> torch.Tensor:
+    """act(RMSNorm(x) G^T) * (RMSNorm(x) U^T) for Q4_K gate/up (``alloyb_gated_linear_normed``)."""
+    k = _k_of(_lib.Q4_K, gate)
+    x = _check_acts(x, k)
+    y = torch.empty((x.shape[0], gate.shape[0]), dtype=x.dtype, device=x.device)
+    if x.shape[0] == 0:
+        return y
+    scratch = torch.empty_like(x)
+    L = _lib.load()
+    check(L.alloyb_gated_linear_normed(x.data_ptr(), norm_weight.data_ptr(), float(eps), scratch.data_ptr(),
+                                       gate.data_ptr(), None, up.data_ptr(), None, y.data_ptr(), x.shape[0],
+                                       gate.shape[0], k, _lib.Q4_K,
+                                       _lib.ACT_SILU if act == "silu" else _lib.ACT_GELU_TANH, _dtype_code(x),
+                                       _stream()), "alloyb_gated_linear_normed")
+    return y
 
 
 # ------------------------------------------------------------------------------- linear ops

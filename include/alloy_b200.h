@@ -119,6 +119,19 @@ int alloyb_gated_linear(const void* x, const void* gate, const void* gate_scales
                         const void* up_scales, void* y, int M, int N, int K, int format, int act,
                         int dtype, void* stream);
 
+/* RMSNorm folded into the linear that consumes it (no single counterpart op in the reference,
+ * which runs rms_norm -- metal/std/norm.py:58-73 -- and the quantised matmul as two graph nodes;
+ * the results are those of alloyb_rms_norm followed by alloyb_linear / alloyb_gated_linear).
+ * For one fp16 token on Q4_K / Q6_K weights the normalisation happens inside the GEMV launch;
+ * every other shape runs the two launches through xn_scratch (M*K elements of `dtype`, caller's
+ * memory, contents undefined afterwards). */
+int alloyb_linear_normed(const void* x, const void* norm_weight, float eps, void* xn_scratch, int M,
+                         int K, int dtype, const alloyb_weight* w, int n_w, void* stream);
+int alloyb_gated_linear_normed(const void* x, const void* norm_weight, float eps, void* xn_scratch,
+                               const void* gate, const void* gate_scales, const void* up,
+                               const void* up_scales, void* y, int M, int N, int K, int format,
+                               int act, int dtype, void* stream);
+
 /* ------------------------------------------------------------------ q8_0 KV cache
  * Quantise n_tokens rows per (batch, kv head) of fp16 `src` into the split
  * cache tensors at positions [start, start+n_tokens): codes int8 (B,KV_H,S_max,D),

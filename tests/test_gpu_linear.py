@@ -151,6 +151,34 @@ def test_one_token_stream_gated(n, k):
     assert_close(to_np(y), ref, torch.float16, f"stream gated n={n} k={k}")
 
 
+# RMSNorm folded into the consuming linear: fused inside the one-token streaming launch (m = 1,
+# fp16), two launches through the caller's scratch otherwise; the oracle is rms_norm_ref (fp16
+# out) followed by the float64 product.
+@pytest.mark.parametrize("m,dt", [(1, "f16"), (4, "f16"), (1, "bf16")])
+def test_linear_normed_qkv_and_gate_up(m, dt):
+    rng = np.random.default_rng([m, len(dt), 17])
+    k, eps = 4096, 1e-5
+    tdt = TORCH_DT[dt]
+    x = torch.from_numpy((3.0 * synth.activations(rng, m, k, np.float32))).to(tdt)
+    nw = torch.from_numpy((1.0 + 0.1 * rng.standard_normal(k)).astype(np.float32)).to(tdt)
+    xn = torch.from_numpy(O.rms_norm_ref(x.float().numpy().astype(np.float32), nw.float().numpy().astype(np.float32), eps))
+    # the oracle normalises in fp32 and narrows twice, as the kernels do
+    xr = (x.float() * torch.rsqrt((x.float() ** 2).mean(dim=1, keepdim=True) + eps)).to(tdt)
+    xn = (nw.float() * xr.float()).to(tdt).float().numpy()
+    wq, wk, wv = synth.q4k_blocks(rng, 1024, k), synth.q4k_blocks(rng, 200, k), synth.q6k_blocks(rng, 256, k)
+    outs = ops.linear_multi(x.to(DEV), [("q4_k", _dev(wq), None), ("q4_k", _dev(wk), None), ("q6_k", _dev(wv), None)],
+                            norm=(nw.to(DEV), eps))
+    for y, wf in zip(outs, (O.dequant_q4_k(wq), O.dequant_q4_k(wk), O.dequant_q6_k(wv))):
+        assert_close(to_np(y), O.mm_ref_f64(xn, wf), tdt, f"normed qkv m={m} {dt}")
+    head = synth.q6k_blocks(rng, 3000, k)
+    y = ops.linear_multi(x.to(DEV), [("q6_k", _dev(head), None)], norm=(nw.to(DEV), eps))[0]
+    assert_close(to_np(y), O.mm_ref_f64(xn, O.dequant_q6_k(head)), tdt, f"normed head m={m} {dt}")
+    g, u = synth.q4k_blocks(rng, 1000, k), synth.q4k_blocks(rng, 1000, k)
+    y = ops.gated_normed(x.to(DEV), nw.to(DEV), eps, _dev(g), _dev(u))
+    ref = O.silu(O.mm_ref_f64(xn, O.dequant_q4_k(g))) * O.mm_ref_f64(xn, O.dequant_q4_k(u))
+    assert_close(to_np(y), ref, tdt, f"normed gate/up m={m} {dt}")
+
+
 def test_q4k_mm_golden(golden):
     g = golden["q4k"]
     y = torch.ops.alloy.gguf_q4_k_mm(_dev(g["x"]), _dev(g["blocks"]))
