@@ -36,6 +36,17 @@ class Weight(C.Structure):
     ]
 
 
+class TP(C.Structure):
+    """Mirror of ``alloyb_tp`` in ``include/alloy_b200.h``."""
+
+    _fields_ = [
+        ("world", C.c_int),
+        ("rank", C.c_int),
+        ("max_n", C.c_int),
+        ("peer", C.c_void_p * 8),
+    ]
+
+
 _p, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 
 # name -> (restype, argtypes); must list every symbol the header declares.
@@ -55,6 +66,13 @@ SIGNATURES = {
     "alloyb_gated_linear": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "alloyb_linear_normed": (_i, [_p, _p, _f, _p, _i, _i, _i, C.POINTER(Weight), _i, _p]),
     "alloyb_gated_linear_normed": (_i, [_p, _p, _f, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "alloyb_tp_buffer_bytes": (_sz, [_i]),
+    "alloyb_tp_alloc": (_i, [_sz, C.POINTER(_p)]),
+    "alloyb_tp_free": (_i, [_p]),
+    "alloyb_tp_ipc_export": (_i, [_p, _p]),
+    "alloyb_tp_ipc_import": (_i, [_p, C.POINTER(_p)]),
+    "alloyb_tp_ipc_close": (_i, [_p]),
+    "alloyb_linear_allreduce": (_i, [_p, _i, _i, _i, C.POINTER(Weight), _p, C.POINTER(TP), _p]),
     "alloyb_kv_quantize_q8": (_i, [_p, _i64, _i64, _i64, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "alloyb_kv_dequant_q8": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "alloyb_kv_append_q8_paged": (_i, [_p, _p, _i64, _i64, _p, _p, _i, _i64, _p, _i, _i, _i, _p, _p]),

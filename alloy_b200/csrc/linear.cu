@@ -293,10 +293,27 @@ extern "C" int alloyb_gated_linear_normed(const void* x, const void* norm_weight
     if (format == ALLOYB_Q4_K && K % QK_K == 0 && M == 1) {
         const int64_t rb = static_cast<int64_t>(K / QK_K) * Q4K_BYTES;
         const WeightSeg pair[2] = {{ALLOYB_Q4_K, N, gate, nullptr, rb, y, N}, {ALLOYB_Q4_K, N, up, nullptr, rb, y, N}};
-        const int rc = try_gemv_stream(x, M, K, dtype, pair, 2, true, act, nullptr, norm_weight, eps, as_stream(stream));
+        const int rc = try_gemv_stream(x, M, K, dtype, pair, 2, true, act, nullptr, norm_weight, eps, as_stream(stream), nullptr);
         if (rc != ALLOYB_NOT_TAKEN) return rc;
     }
     const int rc = alloyb_rms_norm(x, norm_weight, xn_scratch, M, K, eps, dtype, stream);
     if (rc != ALLOYB_OK) return rc;
     return alloyb_gated_linear(xn_scratch, gate, gate_scales, up, up_scales, y, M, N, K, format, act, dtype, stream);
+}
+
+// ---- row-parallel linear with the all-reduce over peer memory inside the launch
+
+extern "C" int alloyb_linear_allreduce(const void* x, int M, int K, int dtype, const alloyb_weight* w,
+                                       const void* residual, const alloyb_tp* tp, void* stream) {
+    if (!x || !w || !tp) return ALLOYB_E_NULL;
+    if (M < 0 || K <= 0) return ALLOYB_E_SHAPE;
+    if (tp->world < 1 || tp->world > 8 || tp->rank < 0 || tp->rank >= tp->world) return ALLOYB_E_SHAPE;
+    for (int r = 0; r < tp->world; ++r)
+        if (!tp->peer[r]) return ALLOYB_E_NULL;
+    RowSegs segs;
+    const int rc = validate_segs(w, 1, K, segs);
+    if (rc != ALLOYB_OK) return rc;
+    if (segs.seg[0].N > tp->max_n) return ALLOYB_E_LIMIT;
+    if (M == 0) return ALLOYB_OK;
+    return try_gemv_stream(x, M, K, dtype, segs.seg, 1, false, 0, residual, nullptr, 0.f, as_stream(stream), tp);
 }

@@ -26,9 +26,11 @@ int try_gated_fast(const void* x, const void* gate, const void* gate_scales, con
                    int dtype, cudaStream_t st);
 
 // Persistent streaming GEMV for one fp16 token against Q4_K matrices.
-// norm_w != nullptr fuses RMSNorm(x; norm_w, eps) into the activation load.
+// norm_w != nullptr fuses RMSNorm(x; norm_w, eps) into the activation load; tp != nullptr sums the
+// (single) output over the ranks through peer memory inside the launch.
 int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg, int n_seg, bool gated, int act,
-                    const void* residual, const void* norm_w, float eps, cudaStream_t stream);
+                    const void* residual, const void* norm_w, float eps, cudaStream_t stream,
+                    const alloyb_tp* tp = nullptr);
 // One token, any mix of Q4_K / Q6_K matrices: one streaming launch per format present.
 int try_gemv_stream_mixed(const void* x, int M, int K, int dtype, const WeightSeg* seg, int n_seg, const void* residual,
                           const void* norm_w, float eps, cudaStream_t stream);

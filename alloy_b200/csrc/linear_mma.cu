@@ -798,7 +798,7 @@ int try_gated_fast(const void* x, const void* gate, const void* gate_scales, con
     if (!seg_ok(gs, K) || !seg_ok(us, K)) return ALLOYB_NOT_TAKEN;
     if (!no_stream_flag()) {
         const WeightSeg pair[2] = {gs, us};
-        const int rc = try_gemv_stream(x, M, K, dtype, pair, 2, true, act, nullptr, nullptr, 0.f, st);
+        const int rc = try_gemv_stream(x, M, K, dtype, pair, 2, true, act, nullptr, nullptr, 0.f, st, nullptr);
         if (rc != ALLOYB_NOT_TAKEN) return rc;
     }
     const int stage_bytes = 32 * Q4_STRIDE;

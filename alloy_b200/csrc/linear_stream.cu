@@ -67,6 +67,17 @@ template <> struct Geom<Q6> { static constexpr int SBS = 1, PITCH = 240, BLK = Q
 
 __device__ int g_error = 0;                  // sticky: a bounded wait ran out
 
+// Row-parallel (K-sharded) linear with the all-reduce inside the launch.  Every rank owns an
+// exchange buffer that all ranks have mapped (peer[r] = rank r's buffer as seen from here):
+//   +0     uint32 epoch (local), +4 uint32 finished-CTA counter (local)
+//   +256   uint32 flags[8 ranks][256 CTAs]: rank r's CTA c has delivered its rows for epoch >= value
+//   +8448  float  slots[2 sets][8 ranks][max_n]: the partial outputs, set = epoch parity
+struct TpArgs {
+    int world, rank, max_n;
+    uint8_t* peer[8];
+};
+constexpr int TP_FLAGS_OFF = 256, TP_SLOTS_OFF = 8448;
+
 struct Seg {
     const uint8_t* data;
     int64_t row_bytes;
@@ -86,6 +97,7 @@ struct Params {
     int gated;                               // seg[0] = gate, seg[1] = up, y = act(gate) * up
     int act;
     int depth;                               // ring slots per warp
+    TpArgs tp;                               // world == 0: plain linear
 };
 struct Maps {
     CUtensorMap m[MAX_SEG];                  // (row_bytes / 4, n_rows) uint32, box PITCH/4 x 16
@@ -505,6 +517,12 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
         xsrc = xs;
     }
 
+    // tensor-parallel exchange: this call's epoch and slot set
+    uint32_t tp_next = 0;
+    if (RT == 1 && P.tp.world) {
+        tp_next = *reinterpret_cast<volatile uint32_t*>(P.tp.peer[P.tp.rank]) + 1u;
+    }
+
     const ScaleSel ss = make_scale_sel(t);
     XF xc[CACHE ? SBS : 1];
     if (CACHE) {
@@ -576,6 +594,10 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
             if (RT == 2) {
                 const float a = (P.act == ALLOYB_ACT_SILU) ? act_silu(v) : act_gelu_tanh(v);
                 y[row] = __float2half_rn(a * u);
+            } else if (P.tp.world) {
+                // this rank's partial of output `row`, delivered to every rank's slot for this rank
+                const size_t off = TP_SLOTS_OFF + (static_cast<size_t>((tp_next & 1u) * 8 + P.tp.rank) * P.tp.max_n + row) * 4;
+                for (int p = 0; p < P.tp.world; ++p) *reinterpret_cast<float*>(P.tp.peer[p] + off) = v;
             } else {
                 __half r = __float2half_rn(v);
                 if (P.residual) r = __float2half_rn(__half2float(P.residual[row]) + __half2float(r));
@@ -611,6 +633,50 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
             }
         }
         cursor_next(cc, P, lo, hi, n_groups);
+    }
+    if (RT == 1 && P.tp.world) {
+        // ---- all-reduce of this CTA's rows: publish, wait for the same CTA of every rank, sum in
+        // rank order (identical on all ranks), add the residual, store.
+        __syncthreads();
+        uint8_t* mine = P.tp.peer[P.tp.rank];
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            for (int p = 0; p < P.tp.world; ++p) {
+                uint32_t* f = reinterpret_cast<uint32_t*>(P.tp.peer[p] + TP_FLAGS_OFF) + P.tp.rank * 256 + blockIdx.x;
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(tp_next) : "memory");
+            }
+        }
+        if (threadIdx.x < P.tp.world) {
+            const uint32_t* f = reinterpret_cast<const uint32_t*>(mine + TP_FLAGS_OFF) + threadIdx.x * 256 + blockIdx.x;
+            uint32_t v = 0, i = 0;
+            for (; i < SPIN_LIMIT; ++i) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                if (static_cast<int32_t>(v - tp_next) >= 0) break;
+                if (i > 64) __nanosleep(64);
+            }
+            if (i == SPIN_LIMIT) atomicExch(&g_error, 1);
+        }
+        __syncthreads();
+        const float* slots = reinterpret_cast<const float*>(mine + TP_SLOTS_OFF) +
+                             static_cast<size_t>(tp_next & 1u) * 8 * P.tp.max_n;
+        __half* y = static_cast<__half*>(P.seg[0].y);
+        for (int row = lo + threadIdx.x; row < hi; row += blockDim.x) {
+            float v = 0.f;
+            for (int r = 0; r < P.tp.world; ++r) v += __ldcg(slots + static_cast<size_t>(r) * P.tp.max_n + row);
+            __half o = __float2half_rn(v);
+            if (P.residual) o = __float2half_rn(__half2float(P.residual[row]) + __half2float(o));
+            y[row] = o;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t* ctr = reinterpret_cast<uint32_t*>(mine + 4);
+            __threadfence();
+            if (atomicAdd(ctr, 1u) == gridDim.x - 1) {
+                *ctr = 0u;
+                __threadfence();
+                *reinterpret_cast<volatile uint32_t*>(mine) = tp_next;      // the next call's epoch
+            }
+        }
     }
     if (!ok) {
         // a wait ran out (sticky error word set; this CTA's results are garbage): let copies in
@@ -681,8 +747,11 @@ static int env_int(const char* name, int dflt) {
 // One fp16 token against Q4_K or Q6_K matrices of one format (plain: up to MAX_SEGS row-stacked
 // outputs; gated: Q4_K gate/up pair with the activation fused).  NOT_TAKEN for anything else.
 int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg, int n_seg, bool gated, int act,
-                    const void* residual, const void* norm_w, float eps, cudaStream_t stream) {
+                    const void* residual, const void* norm_w, float eps, cudaStream_t stream, const alloyb_tp* tp) {
     using namespace st;
+    if (tp && (gated || n_seg != 1 || tp->world < 1 || tp->world > 8 || tp->rank < 0 || tp->rank >= tp->world ||
+               seg[0].N > tp->max_n))
+        return ALLOYB_NOT_TAKEN;
     if (M != 1 || dtype != ALLOYB_F16 || K % QK_K || n_seg < 1 || n_seg > MAX_SEG) return ALLOYB_NOT_TAKEN;
     if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(norm_w) % 16) return ALLOYB_NOT_TAKEN;
     if (norm_w && K > 16384) return ALLOYB_NOT_TAKEN;             // the normalised token lives in shared memory
@@ -712,6 +781,12 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
     P.residual = static_cast<const __half*>(residual);
     P.norm_w = static_cast<const __half*>(norm_w);
     P.eps = eps;
+    if (tp) {
+        P.tp.world = tp->world;
+        P.tp.rank = tp->rank;
+        P.tp.max_n = tp->max_n;
+        for (int r = 0; r < tp->world; ++r) P.tp.peer[r] = static_cast<uint8_t*>(tp->peer[r]);
+    }
     P.n_seg = gated ? 1 : n_seg;
     P.nsb = nsb;
     P.gated = gated ? 1 : 0;
@@ -767,7 +842,7 @@ int try_gemv_stream_mixed(const void* x, int M, int K, int dtype, const WeightSe
         grp[f][cnt[f]++] = seg[i];
     }
     if (cnt[0] == 0 || cnt[1] == 0)
-        return try_gemv_stream(x, M, K, dtype, seg, n_seg, false, 0, residual, norm_w, eps, stream);
+        return try_gemv_stream(x, M, K, dtype, seg, n_seg, false, 0, residual, norm_w, eps, stream, nullptr);
     if (residual) return ALLOYB_NOT_TAKEN;
     // both launches must be possible before the first one is made: probe with the cheap checks
     if (dtype != ALLOYB_F16 || K % QK_K || (K / QK_K) % 8) return ALLOYB_NOT_TAKEN;
@@ -776,7 +851,7 @@ int try_gemv_stream_mixed(const void* x, int M, int K, int dtype, const WeightSe
             seg[i].row_bytes < static_cast<int64_t>(K / QK_K) * (seg[i].format == ALLOYB_Q4_K ? Q4K_BYTES : Q6K_BYTES))
             return ALLOYB_NOT_TAKEN;
     for (int f = 0; f < 2; ++f) {
-        const int rc = try_gemv_stream(x, M, K, dtype, grp[f], cnt[f], false, 0, nullptr, norm_w, eps, stream);
+        const int rc = try_gemv_stream(x, M, K, dtype, grp[f], cnt[f], false, 0, nullptr, norm_w, eps, stream, nullptr);
         if (rc != ALLOYB_OK) return rc == ALLOYB_NOT_TAKEN ? ALLOYB_E_SHAPE : rc;
     }
     return ALLOYB_OK;

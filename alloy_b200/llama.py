@@ -63,7 +63,8 @@ class QuantLlamaDecoder:
 
     def __init__(self, shape: LlamaShape, batch: int, context: int, *, device="cuda", seed: int = 0,
                  kv: str = "f16", tp_rank: int = 0, tp_size: int = 1, process_group=None,
-                 dtype: torch.dtype = torch.float16, d_scale: float = 1.0) -> None:
+                 dtype: torch.dtype = torch.float16, d_scale: float = 1.0, peer_allreduce: bool = True,
+                 tp_dry: bool = False) -> None:
         if kv not in ("f16", "q8_paged"):
             raise ValueError(f"kv must be 'f16' or 'q8_paged', got {kv!r}")
         if shape.heads % tp_size or shape.kv_heads % tp_size or shape.ffn % (256 * tp_size) \
@@ -72,6 +73,17 @@ class QuantLlamaDecoder:
         self.shape, self.batch, self.context = shape, int(batch), int(context)
         self.device, self.dtype, self.kv_kind = torch.device(device), dtype, kv
         self.tp_rank, self.tp_size, self.pg = tp_rank, tp_size, process_group
+        # row-parallel outputs are summed inside the GEMV launch over peer memory (NCCL only sets
+        # it up and serves the shapes the fused kernel does not cover)
+        # tp_dry: this rank's share of the step with nobody to exchange with (sums are the local
+        # partials): what one rank of a TP-N step computes, for profiling under tools that cannot
+        # wrap a multi-rank run
+        self.exchange = None
+        self.tp_dry = bool(tp_dry)
+        if tp_dry:
+            self.exchange = tp.PeerExchange(shape.hidden)
+        elif tp_size > 1 and peer_allreduce and self.device.type == "cuda" and dtype == torch.float16:
+            self.exchange = tp.PeerExchange(shape.hidden, tp_rank, tp_size, process_group, self.device)
         s = shape
         self.heads_l = s.heads // tp_size
         self.kv_heads_l = s.kv_heads // tp_size
@@ -155,11 +167,28 @@ class QuantLlamaDecoder:
                 blocks[:, 0:2] = sc.view(torch.uint8).view(-1, 2)
                 self.pools.append(pool)
 
+    def _row_parallel(self, x, fmt, w, h):
+        """h + sum over ranks of x_r W_r^T: inside the GEMV launch over peer memory when the
+        fused kernel covers the shape, else the plain linear + NCCL all-reduce."""
+        if self.exchange is not None:
+            y = ops.linear_allreduce(x, fmt, w, h, self.exchange)
+            if y is not None:
+                self.fused_allreduce_calls += 1
+                return y
+        mm = torch.ops.alloy.gguf_q4_k_mm if fmt == "q4_k" else torch.ops.alloy.gguf_q6_k_mm
+        return h + tp.row_parallel(x, lambda t: mm(t, w), self.pg)
+
     # ------------------------------------------------------------------ one decode step
+
+    def step_eager_logits(self) -> torch.Tensor:
+        """One eager (uncaptured) step; returns the logits."""
+        self._step()
+        return self.logits
 
     def _step(self) -> None:
         s, b = self.shape, self.batch
         n0 = ops.launch_count()
+        self.fused_allreduce_calls = 0
         h = ops._embedding(self.ids, 0, self.embed, None, out_dtype=self.dtype)
         scale = 1.0 / (s.head_dim ** 0.5)
         for li, lw in enumerate(self.layers):
@@ -185,14 +214,14 @@ class QuantLlamaDecoder:
             if self.tp_size == 1:
                 h = torch.ops.alloy.linear_residual(a2, lw.wo, None, h, "q4_k")
             else:
-                h = h + tp.row_parallel(a2, lambda t: torch.ops.alloy.gguf_q4_k_mm(t, lw.wo), self.pg)
+                h = self._row_parallel(a2, "q4_k", lw.wo, h)
             act = ops.gated_normed(h, lw.norm_post, s.eps, lw.wg, lw.wu)
             if self.tp_size == 1:
                 h = torch.ops.alloy.linear_residual(act, lw.wd, None, h, "q6_k")
             else:
-                h = h + tp.row_parallel(act, lambda t: torch.ops.alloy.gguf_q6_k_mm(t, lw.wd), self.pg)
+                h = self._row_parallel(act, "q6_k", lw.wd, h)
         logits = ops.linear_multi(h, [("q6_k", self.head, None)], norm=(self.norm_final, s.eps))[0]
-        if self.tp_size > 1:
+        if self.tp_size > 1 and not self.tp_dry:
             logits = tp.gather_columns(logits, self.pg)
         self.logits = logits
         self.next_ids.copy_(ops.argmax(logits))

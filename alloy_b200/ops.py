@@ -195,6 +195,31 @@ def linear_multi(x: torch.Tensor, specs: Sequence[tuple[str, torch.Tensor, torch
     return outs
 
 
+def linear_allreduce(x: torch.Tensor, fmt_name: str, weight: torch.Tensor, residual: torch.Tensor | None,
+                     exchange) -> torch.Tensor | None:
+    """Row-parallel linear with the all-reduce inside the launch (``alloyb_linear_allreduce``).
+
+    ``x`` is this rank's K slice of the activations, ``weight`` its K slice of the packed matrix,
+    ``exchange`` a ``tp.PeerExchange``.  Returns ``residual + sum over ranks`` or ``None`` when the
+    fused kernel does not cover the shape (nothing was launched).
+    """
+    fmt = _FORMATS[fmt_name]
+    k = _k_of(fmt, weight)
+    x = _check_acts(x, k)
+    m = x.shape[0]
+    y = torch.empty((m, weight.shape[0]), dtype=x.dtype, device=x.device)
+    desc = (Weight * 1)(Weight(fmt, weight.shape[0], weight.data_ptr(), None, 0, y.data_ptr(), 0))
+    L = _lib.load()
+    import ctypes as C
+    rc = L.alloyb_linear_allreduce(x.data_ptr(), m, k, _dtype_code(x), desc,
+                                   residual.data_ptr() if residual is not None else None,
+                                   C.byref(exchange.desc), _stream())
+    if rc == 1:
+        return None
+    check(rc, "alloyb_linear_allreduce")
+    return y
+
+
 def gated_normed(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, gate: torch.Tensor, up: torch.Tensor,
                  act: str = "silu") -> torch.Tensor:
     """act(RMSNorm(x) G^T) * (RMSNorm(x) U^T) for Q4_K gate/up (``alloyb_gated_linear_normed``)."""

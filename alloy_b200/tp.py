@@ -64,3 +64,52 @@ def gather_columns(y_shard: torch.Tensor, group=None) -> torch.Tensor:
     parts = [torch.empty_like(y_shard) for _ in range(world)]
     dist.all_gather(parts, y_shard.contiguous(), group=group)
     return torch.cat(parts, dim=1)
+
+
+class PeerExchange:
+    """This rank's exchange buffer plus the mapped buffers of the other ranks of ``group``.
+
+    Set-up for ``ops.linear_allreduce`` (the row-parallel linear whose all-reduce runs inside
+    the GEMV launch over NVLink peer memory).  Every rank allocates one buffer through the C
+    library, the 64-byte CUDA IPC handles travel through one ``all_gather`` of the group, and
+    each rank maps the others' buffers.  ``world == 1`` needs no group.
+    """
+
+    def __init__(self, max_n: int, rank: int = 0, world: int = 1, group=None, device=None) -> None:
+        import ctypes as C
+
+        from . import _lib
+
+        if not 1 <= world <= 8:
+            raise ValueError("1..8 ranks")
+        self.rank, self.world, self.max_n = rank, world, int(max_n)
+        self._L = L = _lib.load()
+        self._own = C.c_void_p()
+        _lib.check(L.alloyb_tp_alloc(L.alloyb_tp_buffer_bytes(self.max_n), C.byref(self._own)), "alloyb_tp_alloc")
+        self._imported: list = []
+        ptrs = [None] * world
+        ptrs[rank] = self._own.value
+        if world > 1:
+            handle = (C.c_ubyte * 64)()
+            _lib.check(L.alloyb_tp_ipc_export(self._own, handle), "alloyb_tp_ipc_export")
+            mine = torch.tensor(list(handle), dtype=torch.uint8, device=device)
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine, group=group)
+            for r in range(world):
+                if r == rank:
+                    continue
+                raw = (C.c_ubyte * 64)(*parts[r].cpu().tolist())
+                p = C.c_void_p()
+                _lib.check(L.alloyb_tp_ipc_import(raw, C.byref(p)), "alloyb_tp_ipc_import")
+                self._imported.append(p)
+                ptrs[r] = p.value
+            dist.barrier(group=group)
+        self.desc = _lib.TP(world, rank, self.max_n, (C.c_void_p * 8)(*ptrs, *([None] * (8 - world))))
+
+    def close(self) -> None:
+        for p in self._imported:
+            self._L.alloyb_tp_ipc_close(p)
+        self._imported = []
+        if self._own:
+            self._L.alloyb_tp_free(self._own)
+            self._own = None

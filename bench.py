@@ -217,6 +217,7 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    dry = args.tp_dry if world == 1 else 0
     if args.gpus != world:
         raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (torchrun); WORLD_SIZE={world}")
     torch.cuda.set_device(local)
@@ -236,7 +237,7 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
     def build(batch):
         note(f"building decoder batch={batch}")
         d = llama.QuantLlamaDecoder(shape, batch, wl["context"], device=dev, seed=0, kv=wl["kv"],
-                                    tp_rank=rank, tp_size=world, process_group=pg)
+                                    tp_rank=rank, tp_size=dry or world, process_group=pg, tp_dry=bool(dry))
         torch.cuda.synchronize()
         note("weights ready; capturing")
         d.capture()
@@ -288,7 +289,29 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
     e2e_val = args.batch * args.steps / (e2e_ms * 1e-3)
     w_bytes = shape.weight_bytes()
     peak, peak_kind = _measured_peaks()
-    roof = gemv_roofline(dec) if world == 1 else None
+    roof = gemv_roofline(dec)
+    tp_check = None
+    if world > 1 and args.check_tp:
+        # the same step with the all-reduce inside the GEMV launches (peer memory) and with NCCL
+        # (small weight magnitudes: the timing model's residual stream overflows fp16)
+        note("tp check: building the twins")
+        mk = lambda peer: llama.QuantLlamaDecoder(shape, args.batch, wl["context"], device=dev, seed=0, kv=wl["kv"],
+                                                  tp_rank=rank, tp_size=world, process_group=pg, d_scale=0.05,
+                                                  peer_allreduce=peer)
+        fused, twin = mk(True), mk(False)
+        for d in (fused, twin):
+            d.ids.fill_(11)
+        a = fused.step_eager_logits()
+        b = twin.step_eager_logits()
+        diff = (a.float() - b.float()).abs().max()
+        rms = b.float().pow(2).mean().sqrt()
+        both = torch.stack([diff, rms])
+        torch.distributed.all_reduce(both, op=torch.distributed.ReduceOp.MAX)
+        tp_check = {"max_abs_diff_over_rms_vs_nccl": float((both[0] / both[1]).item()),
+                    "fused_calls_per_step": fused.fused_allreduce_calls, "finite": bool(torch.isfinite(a.float()).all().item())}
+        torch.cuda.synchronize()
+        del fused, twin
+        torch.cuda.empty_cache()
     launches_step = dec.launches_per_step + shape.layers + 1   # + KV append per layer + id copy
     finite = bool(torch.isfinite(dec.logits.float()).all().item())
 
@@ -319,7 +342,7 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
         "config": {"workload": workload, "batch": args.batch, "context": wl["context"], "kv": wl["kv"],
-                   "parallelism": f"tp{world}", "weight_bytes_per_step": w_bytes // world,
+                   "parallelism": f"tp{world}" if not dry else f"rank 0 of tp{dry}, no peers (not a bench value)", "weight_bytes_per_step": w_bytes // world,
                    "l2": "each step streams its weights once (GBs, far above the 126 MB L2)",
                    "logits_finite": finite},
         "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -334,6 +357,11 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
                             "frac": roof["gbs"] / peak, "traffic": _ncu_traffic("gated_q4k"),
                             "kernel": roof["kernel"], "bytes_per_launch": roof["bytes_per_launch"],
                             "us_per_launch": roof["us_per_launch"], "peak_kind": peak_kind}
+    if tp_check is not None:
+        line["config"]["tp_check"] = tp_check
+    if world > 1:
+        line["config"]["allreduce"] = ("inside the o_proj/down GEMV launches over NVLink peer memory"
+                                       if dec.exchange is not None else "NCCL")
     if per_batch:
         line["per_batch"] = per_batch
     if cpu is not None:
@@ -363,6 +391,11 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--tp-dry", type=int, default=0,
+                    help="1 GPU: time rank 0's share of a TP-N step with nobody to exchange with (profiling aid; "
+                         "not a bench value)")
+    ap.add_argument("--check-tp", action="store_true",
+                    help="N > 1: also run one step with NCCL all-reduces and report the logits difference")
     ap.add_argument("--no-sweep", action="store_true", help="skip the batch 1/4/16/32 sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
     ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")

@@ -132,6 +132,34 @@ int alloyb_gated_linear_normed(const void* x, const void* norm_weight, float eps
                                const void* up_scales, void* y, int M, int N, int K, int format,
                                int act, int dtype, void* stream);
 
+/* ------------------------------------------------------------------ tensor parallel (new)
+ * The reference is single-GPU; these have no counterpart in it.  One process per GPU.  Every
+ * rank allocates one exchange buffer (alloyb_tp_buffer_bytes(max_n) bytes, zero-filled by
+ * alloyb_tp_alloc), exports its CUDA IPC handle (64 bytes), and imports the other ranks'
+ * handles; `peer[r]` is rank r's buffer as mapped in this process (the own pointer for r ==
+ * rank).  max_n = the largest output width that will be reduced. */
+typedef struct alloyb_tp {
+    int world;      /* 1..8 */
+    int rank;
+    int max_n;
+    void* peer[8];
+} alloyb_tp;
+size_t alloyb_tp_buffer_bytes(int max_n);
+int alloyb_tp_alloc(size_t bytes, void** out);
+int alloyb_tp_free(void* p);
+int alloyb_tp_ipc_export(void* p, void* handle64);
+int alloyb_tp_ipc_import(const void* handle64, void** out);
+int alloyb_tp_ipc_close(void* p);
+/* Row-parallel linear: y = residual + sum over ranks of x_r * W_r^T, where every rank holds a K
+ * slice of the weight (whole super-blocks) and the matching slice of the activations.  The
+ * partial outputs cross NVLink inside the GEMV launch (stores into the peers' exchange buffers,
+ * a flag per CTA, the sum taken in rank order on every rank): no separate collective.  All
+ * ranks must make the same sequence of calls.  Returns 1 (nothing launched) when the shape is
+ * outside the fused kernel (it covers one fp16 token, Q4_K / Q6_K, K a multiple of 2048 or
+ * N >= 2368); the caller then runs alloyb_linear and its own all-reduce. */
+int alloyb_linear_allreduce(const void* x, int M, int K, int dtype, const alloyb_weight* w,
+                            const void* residual, const alloyb_tp* tp, void* stream);
+
 /* ------------------------------------------------------------------ q8_0 KV cache
  * Quantise n_tokens rows per (batch, kv head) of fp16 `src` into the split
  * cache tensors at positions [start, start+n_tokens): codes int8 (B,KV_H,S_max,D),

@@ -179,6 +179,30 @@ def test_linear_normed_qkv_and_gate_up(m, dt):
     assert_close(to_np(y), ref, tdt, f"normed gate/up m={m} {dt}")
 
 
+# Row-parallel linear with the all-reduce inside the launch: with one rank the exchange
+# degenerates to "deliver to myself, wait for my own flag, add the residual", which runs the
+# whole device path (epochs, both slot sets, flags) on a single GPU.  The 2-GPU sum is checked
+# in the tensor-parallel bench run (logits against the NCCL path).
+@pytest.mark.parametrize("fmt,n,k", [("q4_k", 4096, 4096), ("q6_k", 4096, 14336), ("q4_k", 8192, 1024), ("q6_k", 1000, 2048)])
+def test_linear_allreduce_single_rank(fmt, n, k):
+    from alloy_b200 import tp
+    rng = np.random.default_rng([n, k, len(fmt), 23])
+    w_dev, w = _weights(fmt, rng, n, k)
+    ex = tp.PeerExchange(max_n=8192)
+    try:
+        for call in range(3):                       # epochs 1..3: both slot sets, flag reuse
+            x = synth.activations(rng, 1, k)
+            r = synth.activations(rng, 1, n)
+            y = ops.linear_allreduce(_dev(x), fmt, w_dev[0], _dev(r), ex)
+            assert y is not None
+            lin = torch.from_numpy(O.mm_ref_f64(x, w)).to(torch.float16).double().numpy()
+            assert_close(to_np(y), lin + r.astype(np.float64), torch.float16, f"allreduce w=1 {fmt} call {call}")
+        assert ops.linear_allreduce(_dev(synth.activations(rng, 3, k)), fmt, w_dev[0], None, ex) is None
+    finally:
+        torch.cuda.synchronize()
+        ex.close()
+
+
 def test_q4k_mm_golden(golden):
     g = golden["q4k"]
     y = torch.ops.alloy.gguf_q4_k_mm(_dev(g["x"]), _dev(g["blocks"]))
