@@ -3,31 +3,80 @@
 
 namespace alloyb {
 
-template <typename T>
-__global__ void __launch_bounds__(256) rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ w,
-                                                       T* __restrict__ y, int K, float eps) {
+// One CTA per row.  fp32 sum of squares; x * r is narrowed to T before the weight multiplies it
+// (the reference's rounding points, metal/std/norm.py:58-73).  VEC: 16-byte loads of a row that
+// is 16-byte aligned with K a multiple of 8 (2-byte types), the row kept in registers between
+// the two passes when it fits (K <= 8 * blockDim).
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(1024) rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                                        T* __restrict__ y, int K, float eps) {
     pdl_launch_dependents();
-    __shared__ float red[8];
+    __shared__ float red[32];
     const int row = blockIdx.x;
     const T* xr = x + static_cast<int64_t>(row) * K;
+    T* yr = y + static_cast<int64_t>(row) * K;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     pdl_wait();
     float ss = 0.f;
-    for (int i = threadIdx.x; i < K; i += 256) {
-        const float v = to_f32<T>(xr[i]);
-        ss = fmaf(v, v, ss);
+    uint4 keep = make_uint4(0u, 0u, 0u, 0u);
+    if (VEC) {
+        for (int i = threadIdx.x * 8; i < K; i += blockDim.x * 8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+            if (i == static_cast<int>(threadIdx.x) * 8) keep = v;
+            const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float f = to_f32<T>(e[j]);
+                ss = fmaf(f, f, ss);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < K; i += blockDim.x) {
+            const float v = to_f32<T>(xr[i]);
+            ss = fmaf(v, v, ss);
+        }
     }
     ss = warp_sum(ss);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    if (lane == 0) red[warp] = ss;
     __syncthreads();
     float tot = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) tot += red[i];
+    for (int i = 0; i < nw; ++i) tot += red[i];
     const float r = rsqrtf(tot / static_cast<float>(K) + eps);
-    T* yr = y + static_cast<int64_t>(row) * K;
-    for (int i = threadIdx.x; i < K; i += 256) {
-        const T normed = from_f32<T>(to_f32<T>(xr[i]) * r);          // narrow before the weight
-        yr[i] = from_f32<T>(to_f32<T>(w[i]) * to_f32<T>(normed));
+    if (VEC) {
+        for (int i = threadIdx.x * 8; i < K; i += blockDim.x * 8) {
+            const uint4 v = (i == static_cast<int>(threadIdx.x) * 8) ? keep : *reinterpret_cast<const uint4*>(xr + i);
+            const uint4 wv = *reinterpret_cast<const uint4*>(w + i);
+            const T* e = reinterpret_cast<const T*>(&v);
+            const T* we = reinterpret_cast<const T*>(&wv);
+            uint4 o;
+            T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const T normed = from_f32<T>(to_f32<T>(e[j]) * r);      // narrow before the weight
+                oe[j] = from_f32<T>(to_f32<T>(we[j]) * to_f32<T>(normed));
+            }
+            *reinterpret_cast<uint4*>(yr + i) = o;
+        }
+    } else {
+        for (int i = threadIdx.x; i < K; i += blockDim.x) {
+            const T normed = from_f32<T>(to_f32<T>(xr[i]) * r);          // narrow before the weight
+            yr[i] = from_f32<T>(to_f32<T>(w[i]) * to_f32<T>(normed));
+        }
     }
+}
+
+template <typename T>
+static cudaError_t launch_rms_norm(const void* x, const void* w, void* y, int M, int K, float eps, cudaStream_t st) {
+    const bool vec = sizeof(T) == 2 && K % 8 == 0 &&
+                     (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) % 16 == 0;
+    if (vec) {
+        int threads = (K / 8 + 31) / 32 * 32;
+        if (threads > 1024) threads = 1024;
+        return launch_pdl(rms_norm_kernel<T, true>, dim3(M), dim3(threads), 0, st, static_cast<const T*>(x),
+                          static_cast<const T*>(w), static_cast<T*>(y), K, eps);
+    }
+    return launch_pdl(rms_norm_kernel<T, false>, dim3(M), dim3(256), 0, st, static_cast<const T*>(x),
+                      static_cast<const T*>(w), static_cast<T*>(y), K, eps);
 }
 
 // One thread per (row, j < D/2): rows = B*H of q then B*KV_H of k.
@@ -176,24 +225,14 @@ extern "C" int alloyb_rms_norm(const void* x, const void* weight, void* y, int M
     if (M < 0 || K <= 0) return ALLOYB_E_SHAPE;
     if (M == 0) return ALLOYB_OK;
     cudaStream_t st = as_stream(stream);
+    cudaError_t e;
     switch (dtype) {
-        case ALLOYB_F16:
-            launch_pdl(rms_norm_kernel<__half>, dim3(M), dim3(256), 0, st, static_cast<const __half*>(x),
-                                                       static_cast<const __half*>(weight),
-                                                       static_cast<__half*>(y), K, eps);
-            break;
-        case ALLOYB_BF16:
-            launch_pdl(rms_norm_kernel<__nv_bfloat16>, dim3(M), dim3(256), 0, st, 
-                static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight),
-                static_cast<__nv_bfloat16*>(y), K, eps);
-            break;
-        case ALLOYB_F32:
-            launch_pdl(rms_norm_kernel<float>, dim3(M), dim3(256), 0, st, static_cast<const float*>(x),
-                                                      static_cast<const float*>(weight),
-                                                      static_cast<float*>(y), K, eps);
-            break;
+        case ALLOYB_F16: e = launch_rms_norm<__half>(x, weight, y, M, K, eps, st); break;
+        case ALLOYB_BF16: e = launch_rms_norm<__nv_bfloat16>(x, weight, y, M, K, eps, st); break;
+        case ALLOYB_F32: e = launch_rms_norm<float>(x, weight, y, M, K, eps, st); break;
         default: return ALLOYB_E_DTYPE;
     }
+    if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
     return check_launch();
 }
 

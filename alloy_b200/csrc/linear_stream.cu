@@ -418,8 +418,10 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     // this CTA's rows, this group's tiles (every n_groups-th), this warp's K slice
     const int lo = static_cast<int>(static_cast<int64_t>(P.total_rows) * blockIdx.x / gridDim.x);
     const int hi = static_cast<int>(static_cast<int64_t>(P.total_rows) * (blockIdx.x + 1) / gridDim.x);
-    const int slice = P.nsb / GW;                                    // super-blocks per warp per tile
-    const int sb_lo = wg * slice;
+    // super-blocks [sb_lo, sb_lo + slice) of every tile; slices differ by at most one super-block
+    // when GW does not divide the count (one-super-block slots only)
+    const int sb_lo = (wg * P.nsb) / GW;
+    const int slice = ((wg + 1) * P.nsb) / GW - sb_lo;
     const int spt = (slice / SBS) * RT;                              // stages per tile
     int my_tiles = 0;
     {
@@ -761,17 +763,14 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
     if (fmt != ALLOYB_Q4_K && !(fmt == ALLOYB_Q6_K && !gated)) return ALLOYB_NOT_TAKEN;
     int64_t all_rows = 0;
     for (int i = 0; i < (gated ? 1 : n_seg); ++i) all_rows += seg[i].N;
-    // whole tiles per warp once every SM owns at least two tiles per warp, else an 8-way K split
-    static const int force_gw = env_int("ALLOYB_ST_GW", 0);
-    int gw = (all_rows / 16 >= static_cast<int64_t>(2) * WARPS * 148) ? 1 : 8;
-    if (force_gw == 1 || force_gw == 8) gw = force_gw;
-    if (nsb % gw) {
-        if (nsb % 8 == 0) gw = 8;
-        else if (all_rows / 16 >= 148) gw = 1;
-        else return ALLOYB_NOT_TAKEN;
-    }
-    const int slice = nsb / gw;
-    const int kind = fmt == ALLOYB_Q6_K ? Q6 : ((slice % 2 == 0) ? Q4x2 : Q4x1);
+    // whole tiles per warp once every SM owns at least two tiles per warp, else the K dimension of
+    // a tile is split over 8 warps (4 when a row has only 4-7 super-blocks)
+    static const int force_gw = env_int("ALLOYB_ST_GW", 0);       // tuning aid
+    int gw = (all_rows / 16 >= static_cast<int64_t>(2) * WARPS * 148) ? 1 : (nsb >= 8 ? 8 : (nsb >= 4 ? 4 : 0));
+    if ((force_gw == 1 || force_gw == 4 || force_gw == 8) && nsb >= force_gw) gw = force_gw;
+    if (gw == 0) return ALLOYB_NOT_TAKEN;
+    // two super-blocks per slot only when every warp's slice is a whole number of pairs
+    const int kind = fmt == ALLOYB_Q6_K ? Q6 : ((nsb % (2 * gw) == 0) ? Q4x2 : Q4x1);
     const int sbs = kind == Q4x2 ? 2 : 1;
     const int blk = fmt == ALLOYB_Q6_K ? Q6K_BYTES : Q4K_BYTES;
     const int pitch = kind == Q6 ? Geom<Q6>::PITCH : (kind == Q4x2 ? Geom<Q4x2>::PITCH : Geom<Q4x1>::PITCH);
@@ -811,7 +810,7 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
     if (!encode) { set_cuda_error(cudaErrorNotSupported); return ALLOYB_E_CUDA; }
     for (int i = 0; i < n_seg; ++i) {
         // the packed matrix as rows of 32-bit words; a box is one slot: pitch/4 words x 16 rows
-        const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(nsb) * blk / 4, static_cast<cuuint64_t>(seg[i].N)};
+        const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(seg[i].row_bytes) / 4, static_cast<cuuint64_t>(seg[i].N)};
         const cuuint64_t gstr[1] = {static_cast<cuuint64_t>(seg[i].row_bytes)};
         const cuuint32_t box[2] = {static_cast<cuuint32_t>(pitch / 4), 16};
         const cuuint32_t estr[2] = {1, 1};
@@ -821,10 +820,11 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
         if (cr != CUDA_SUCCESS) { set_cuda_error(cudaErrorInvalidValue); return ALLOYB_E_CUDA; }
     }
     for (int i = n_seg; i < MAX_SEG; ++i) maps.m[i] = maps.m[0];
-    const bool cache = slice == sbs;
+    const bool cache = gw > 1 && nsb == sbs * gw;        // every warp's slice is exactly one slot
 #define ALLOYB_ST_LAUNCH(KIND, RT)                                                                              \
     (gw == 1 ? launch<KIND, RT, false, 1>(maps, P, stream)                                                     \
-             : (cache ? launch<KIND, RT, true, 8>(maps, P, stream) : launch<KIND, RT, false, 8>(maps, P, stream)))
+     : gw == 4 ? (cache ? launch<KIND, RT, true, 4>(maps, P, stream) : launch<KIND, RT, false, 4>(maps, P, stream)) \
+               : (cache ? launch<KIND, RT, true, 8>(maps, P, stream) : launch<KIND, RT, false, 8>(maps, P, stream)))
     if (kind == Q6) return ALLOYB_ST_LAUNCH(Q6, 1);
     if (gated) return kind == Q4x2 ? ALLOYB_ST_LAUNCH(Q4x2, 2) : ALLOYB_ST_LAUNCH(Q4x1, 2);
     return kind == Q4x2 ? ALLOYB_ST_LAUNCH(Q4x2, 1) : ALLOYB_ST_LAUNCH(Q4x1, 1);

@@ -109,6 +109,15 @@ def _k_of(fmt: int, w: torch.Tensor) -> int:
     return w.shape[1] // bb * 256
 
 
+def _pitched(w: torch.Tensor) -> tuple[torch.Tensor, int]:
+    """A packed weight as (tensor, row pitch in bytes; 0 = dense).  Rows may be padded (a column
+    shard whose row length is not a multiple of 16 bytes keeps a 16-byte pitch so that the
+    tensor-core kernels can copy it); anything else is made contiguous."""
+    if w.ndim == 2 and w.stride(1) == 1 and w.stride(0) >= w.shape[1] and w.element_size() == 1:
+        return w, (0 if w.stride(0) == w.shape[1] else w.stride(0))
+    return w.contiguous(), 0
+
+
 def _check_acts(x: torch.Tensor, k: int) -> torch.Tensor:
     if x.ndim != 2:
         raise ValueError(f"activations must be (M, K), got {tuple(x.shape)}")
@@ -133,7 +142,7 @@ def _linear(x: torch.Tensor, fmt: int, weights: Sequence[torch.Tensor],
     for i, w in enumerate(weights):
         if _k_of(fmt, w) != k:
             raise ValueError("batched matrices must share K")
-        w = w.contiguous()
+        w, pitch = _pitched(w)
         y = torch.empty((m, w.shape[0]), dtype=x.dtype, device=x.device)
         s_ptr = None
         if fmt == _lib.Q8_0:
@@ -145,7 +154,7 @@ def _linear(x: torch.Tensor, fmt: int, weights: Sequence[torch.Tensor],
             keep.append(s)
             s_ptr = s.data_ptr()
         keep.append(w)
-        descs[i] = Weight(fmt, w.shape[0], w.data_ptr(), s_ptr, 0, y.data_ptr(), 0)
+        descs[i] = Weight(fmt, w.shape[0], w.data_ptr(), s_ptr, pitch, y.data_ptr(), 0)
         outs.append(y)
     r_ptr = None
     if residual is not None:
@@ -180,7 +189,8 @@ def linear_multi(x: torch.Tensor, specs: Sequence[tuple[str, torch.Tensor, torch
         if _k_of(fmt, w) != k:
             raise ValueError("matrices must share K")
         y = torch.empty((m, w.shape[0]), dtype=x.dtype, device=x.device)
-        descs[i] = Weight(fmt, w.shape[0], w.data_ptr(), s.data_ptr() if s is not None else None, 0,
+        w, pitch = _pitched(w)
+        descs[i] = Weight(fmt, w.shape[0], w.data_ptr(), s.data_ptr() if s is not None else None, pitch,
                           y.data_ptr(), 0)
         outs.append(y)
     L = _lib.load()
@@ -208,7 +218,8 @@ def linear_allreduce(x: torch.Tensor, fmt_name: str, weight: torch.Tensor, resid
     x = _check_acts(x, k)
     m = x.shape[0]
     y = torch.empty((m, weight.shape[0]), dtype=x.dtype, device=x.device)
-    desc = (Weight * 1)(Weight(fmt, weight.shape[0], weight.data_ptr(), None, 0, y.data_ptr(), 0))
+    weight, pitch = _pitched(weight)
+    desc = (Weight * 1)(Weight(fmt, weight.shape[0], weight.data_ptr(), None, pitch, y.data_ptr(), 0))
     L = _lib.load()
     import ctypes as C
     rc = L.alloyb_linear_allreduce(x.data_ptr(), m, k, _dtype_code(x), desc,

@@ -36,7 +36,14 @@ def shard_cols(blocks: torch.Tensor, fmt: str, rank: int, world: int) -> torch.T
     if nb % world:
         raise ValueError(f"{nb} super-blocks per row do not split {world} ways")
     per = nb // world
-    return blocks.view(n, nb, bb)[:, rank * per:(rank + 1) * per].reshape(n, per * bb).contiguous()
+    shard = blocks.view(n, nb, bb)[:, rank * per:(rank + 1) * per].reshape(n, per * bb)
+    if (per * bb) % 16 == 0:
+        return shard.contiguous()
+    # keep a 16-byte row pitch (bulk / TMA copies need it): a strided view of a padded buffer
+    pitch = (per * bb + 15) // 16 * 16
+    buf = torch.zeros((n, pitch), dtype=blocks.dtype, device=blocks.device)
+    buf[:, :per * bb] = shard
+    return buf[:, :per * bb]
 
 
 def k_slice(k: int, rank: int, world: int) -> slice:

@@ -115,7 +115,8 @@ def test_mm_matches_oracle(fmt, m, n, k, dt):
 # (K = 2048 / 4096), slices longer than one slot (K = 6144, 14336), stacked matrices, residual.
 @pytest.mark.parametrize("fmt", ["q4_k", "q6_k"])
 @pytest.mark.parametrize("n,k", [(4096, 4096), (1000, 2048), (77, 4096), (4096, 14336), (50, 14336),
-                                 (2100, 6144), (5, 2048), (2367, 4096)])
+                                 (2100, 6144), (5, 2048), (2367, 4096), (4096, 1024), (2000, 3584), (512, 3072),
+                                 (8192, 1280)])
 def test_one_token_stream(fmt, n, k):
     rng = np.random.default_rng([n, k, len(fmt), 7])
     w_dev, w = _weights(fmt, rng, n, k)
@@ -201,6 +202,28 @@ def test_linear_allreduce_single_rank(fmt, n, k):
     finally:
         torch.cuda.synchronize()
         ex.close()
+
+
+# A K shard whose rows are not a multiple of 16 bytes long (Q6_K, 14 super-blocks = 2940 bytes)
+# keeps a 16-byte pitch: the op takes the strided view as it is.
+@pytest.mark.parametrize("world", [2, 4])
+def test_column_shard_padded_pitch(world):
+    from alloy_b200 import tp
+    rng = np.random.default_rng(world)
+    n, k = 600, 3584 * world
+    full = synth.q6k_blocks(rng, n, k)
+    x = synth.activations(rng, 1, k)
+    wf = O.dequant_q6_k(full)
+    acc = np.zeros((1, n))
+    for r in range(world):
+        shard = tp.shard_cols(_dev(full), "q6_k", r, world)
+        assert shard.stride(0) % 16 == 0 and shard.shape[1] == 14 * 210
+        ks = tp.k_slice(k, r, world)
+        y = torch.ops.alloy.gguf_q6_k_mm(_dev(np.ascontiguousarray(x[:, ks])), shard)
+        part = O.mm_ref_f64(x[:, ks], wf[:, ks])
+        assert_close(to_np(y), part, torch.float16, f"padded shard {r}/{world}")
+        acc += part
+    assert np.allclose(acc, O.mm_ref_f64(x, wf), rtol=1e-9, atol=1e-9)
 
 
 def test_q4k_mm_golden(golden):
