@@ -169,20 +169,33 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
     // ---- Q fragments (rows = heads of this group; rows >= G are zero) and per-block sums of q
     uint32_t qa[NKP][2][2];
     float qsum[NKP];
+    const bool q_vec = P.q_dtype == ALLOYB_F16 && ((reinterpret_cast<uintptr_t>(P.q) | (P.q_bs * 2) | (P.q_hs * 2)) & 15) == 0;
 #pragma unroll
     for (int kp = 0; kp < NKP; ++kp) {
         float s = 0.f;
+        const int64_t base = b * P.q_bs + static_cast<int64_t>(kvh * G + g) * P.q_hs + 32 * kp + 8 * t;
+        if (q_vec) {
+            // eight consecutive fp16 of head g: one 16-byte load
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (g < G) v = __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(P.q) + base));
+            qa[kp][0][0] = v.x;
+            qa[kp][0][1] = v.y;
+            qa[kp][1][0] = v.z;
+            qa[kp][1][1] = v.w;
+            const float2 a = unpack_h2(v.x), b2 = unpack_h2(v.y), c = unpack_h2(v.z), d2 = unpack_h2(v.w);
+            s = ((a.x + a.y) + (b2.x + b2.y)) + ((c.x + c.y) + (d2.x + d2.y));
+        } else {
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            float v[4] = {0.f, 0.f, 0.f, 0.f};
-            if (g < G) {
-                const int64_t base = b * P.q_bs + static_cast<int64_t>(kvh * G + g) * P.q_hs + 32 * kp + 8 * t + 4 * j;
+            for (int j = 0; j < 2; ++j) {
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
+                if (g < G) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) v[e] = q_elem(P.q, P.q_dtype, base + e);
+                    for (int e = 0; e < 4; ++e) v[e] = q_elem(P.q, P.q_dtype, base + 4 * j + e);
+                }
+                qa[kp][j][0] = pack_h2(v[0], v[1]);
+                qa[kp][j][1] = pack_h2(v[2], v[3]);
+                s += (v[0] + v[1]) + (v[2] + v[3]);
             }
-            qa[kp][j][0] = pack_h2(v[0], v[1]);
-            qa[kp][j][1] = pack_h2(v[2], v[3]);
-            s += (v[0] + v[1]) + (v[2] + v[3]);
         }
         s += __shfl_xor_sync(0xffffffffu, s, 1);
         s += __shfl_xor_sync(0xffffffffu, s, 2);
@@ -421,22 +434,39 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
     __syncthreads();
 
     // ---- merge the four warps, write the split's partial, let the last CTA combine the splits
-    for (int i = threadIdx.x; i < G * D; i += WARPS * 32) {
-        const int hg = i / D, d = i - hg * D;
+    // per (warp, head) rescale factor once: exp2(m_w - max) / sum_w l_w exp2(m_w - max)
+    if (threadIdx.x < G) {
+        const int hg = threadIdx.x;
         float mx = NEG_BIG;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) mx = fmaxf(mx, sm_m[w][hg]);
-        float lt = 0.f, ot = 0.f;
+        float sc[WARPS], lt = 0.f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
-            const float sc = exp2f(sm_m[w][hg] - mx);
-            lt = fmaf(sm_l[w][hg], sc, lt);
-            ot = fmaf(sm_o[w][hg][d], sc, ot);
+            sc[w] = exp2f(sm_m[w][hg] - mx);
+            lt = fmaf(sm_l[w][hg], sc[w], lt);
         }
-        const int h = kvh * G + hg;
-        const int64_t pi = (static_cast<int64_t>(b) * P.H + h) * P.splits + split;
-        P.part_o[pi * D + d] = lt > 0.f ? ot / lt : 0.f;
-        if (d == 0) P.part_lse[pi] = lt > 0.f ? mx + log2f(lt) : NEG_BIG;
+        const float inv = lt > 0.f ? 1.0f / lt : 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) sm_l[w][hg] = sc[w] * inv;       // sm_l now holds the factors
+        const int64_t pi = (static_cast<int64_t>(b) * P.H + kvh * G + hg) * P.splits + split;
+        P.part_lse[pi] = lt > 0.f ? mx + log2f(lt) : NEG_BIG;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * (D / 4); i += WARPS * 32) {
+        const int hg = i / (D / 4), d = (i - hg * (D / 4)) * 4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const float f = sm_l[w][hg];
+            const float4 v = *reinterpret_cast<const float4*>(&sm_o[w][hg][d]);
+            acc.x = fmaf(v.x, f, acc.x);
+            acc.y = fmaf(v.y, f, acc.y);
+            acc.z = fmaf(v.z, f, acc.z);
+            acc.w = fmaf(v.w, f, acc.w);
+        }
+        const int64_t pi = (static_cast<int64_t>(b) * P.H + kvh * G + hg) * P.splits + split;
+        *reinterpret_cast<float4*>(P.part_o + pi * D + d) = acc;
     }
     __threadfence();
     __syncthreads();
@@ -448,43 +478,53 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // split weights once per head (into the now-free per-warp rows), then the weighted sums with
-    // eight independent loads in flight per thread
+    // split weights: one warp per head (lanes over the splits), then 16-byte loads of the partials
     float* wgt = reinterpret_cast<float*>(sm_buf);            // [G][splits], splits <= 64
     __syncthreads();
-    for (int i = threadIdx.x; i < G * P.splits; i += WARPS * 32)
-        wgt[i] = __ldcg(P.part_lse + (static_cast<int64_t>(b) * P.H + kvh * G + i / P.splits) * P.splits + i % P.splits);
-    __syncthreads();
-    if (threadIdx.x < G) {
-        float* w = wgt + threadIdx.x * P.splits;
-        float mx = NEG_BIG;
-        for (int s2 = 0; s2 < P.splits; ++s2) mx = fmaxf(mx, w[s2]);
-        float sum = 0.f;
-        for (int s2 = 0; s2 < P.splits; ++s2) {
-            const float e = w[s2] > 0.5f * NEG_BIG ? exp2f(w[s2] - mx) : 0.f;
-            w[s2] = e;
-            sum += e;
-        }
+    for (int hg = warp; hg < G; hg += WARPS) {
+        const float* lse = P.part_lse + (static_cast<int64_t>(b) * P.H + kvh * G + hg) * P.splits;
+        const float l0 = lane < P.splits ? __ldcg(lse + lane) : NEG_BIG;
+        const float l1 = lane + 32 < P.splits ? __ldcg(lse + lane + 32) : NEG_BIG;
+        const float mx = warp_max(fmaxf(l0, l1));
+        const float e0 = l0 > 0.5f * NEG_BIG ? exp2f(l0 - mx) : 0.f;
+        const float e1 = l1 > 0.5f * NEG_BIG ? exp2f(l1 - mx) : 0.f;
+        const float sum = warp_sum(e0 + e1);
         const float inv = sum > 0.f ? 1.0f / sum : 0.f;
-        for (int s2 = 0; s2 < P.splits; ++s2) w[s2] *= inv;
+        if (lane < P.splits) wgt[hg * P.splits + lane] = e0 * inv;
+        if (lane + 32 < P.splits) wgt[hg * P.splits + lane + 32] = e1 * inv;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < G * D; i += WARPS * 32) {
-        const int hg = i / D, d = i - hg * D;
+    for (int i = threadIdx.x; i < G * (D / 4); i += WARPS * 32) {
+        const int hg = i / (D / 4), d = (i - hg * (D / 4)) * 4;
         const int h = kvh * G + hg;
-        const float* po = P.part_o + (static_cast<int64_t>(b) * P.H + h) * P.splits * D + d;
+        const float4* po = reinterpret_cast<const float4*>(P.part_o + (static_cast<int64_t>(b) * P.H + h) * P.splits * D + d);
         const float* w = wgt + hg * P.splits;
-        float acc = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         int s2 = 0;
         for (; s2 + 8 <= P.splits; s2 += 8) {
-            float v[8];
+            float4 v[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = __ldcg(po + static_cast<int64_t>(s2 + u) * D);
+            for (int u = 0; u < 8; ++u) v[u] = __ldcg(po + static_cast<int64_t>(s2 + u) * (D / 4));
 #pragma unroll
-            for (int u = 0; u < 8; ++u) acc = fmaf(w[s2 + u], v[u], acc);
+            for (int u = 0; u < 8; ++u) {
+                acc.x = fmaf(w[s2 + u], v[u].x, acc.x);
+                acc.y = fmaf(w[s2 + u], v[u].y, acc.y);
+                acc.z = fmaf(w[s2 + u], v[u].z, acc.z);
+                acc.w = fmaf(w[s2 + u], v[u].w, acc.w);
+            }
         }
-        for (; s2 < P.splits; ++s2) acc = fmaf(w[s2], __ldcg(po + static_cast<int64_t>(s2) * D), acc);
-        out_elem(P.out, P.q_dtype, (static_cast<int64_t>(b) * P.H + h) * D + d, acc);
+        for (; s2 < P.splits; ++s2) {
+            const float4 v = __ldcg(po + static_cast<int64_t>(s2) * (D / 4));
+            acc.x = fmaf(w[s2], v.x, acc.x);
+            acc.y = fmaf(w[s2], v.y, acc.y);
+            acc.z = fmaf(w[s2], v.z, acc.z);
+            acc.w = fmaf(w[s2], v.w, acc.w);
+        }
+        const int64_t o = (static_cast<int64_t>(b) * P.H + h) * D + d;
+        out_elem(P.out, P.q_dtype, o, acc.x);
+        out_elem(P.out, P.q_dtype, o + 1, acc.y);
+        out_elem(P.out, P.q_dtype, o + 2, acc.z);
+        out_elem(P.out, P.q_dtype, o + 3, acc.w);
     }
 }
 
