@@ -83,7 +83,19 @@ class QuantLlamaDecoder:
         if tp_dry:
             self.exchange = tp.PeerExchange(shape.hidden)
         elif tp_size > 1 and peer_allreduce and self.device.type == "cuda" and dtype == torch.float16:
-            self.exchange = tp.PeerExchange(shape.hidden, tp_rank, tp_size, process_group, self.device)
+            # every rank must end up on the same path: if mapping the peers' buffers fails anywhere
+            # (no peer access between two of the GPUs, IPC not permitted), all ranks use NCCL
+            try:
+                ex = tp.PeerExchange(shape.hidden, tp_rank, tp_size, process_group, self.device)
+            except Exception as e:  # noqa: BLE001 - any set-up failure means "no peer path"
+                ex = None
+                self.exchange_error = repr(e)
+            ok = torch.tensor([1 if ex is not None else 0], device=self.device)
+            torch.distributed.all_reduce(ok, op=torch.distributed.ReduceOp.MIN, group=process_group)
+            if int(ok.item()) == 1:
+                self.exchange = ex
+            elif ex is not None:
+                ex.close()
         s = shape
         self.heads_l = s.heads // tp_size
         self.kv_heads_l = s.kv_heads // tp_size

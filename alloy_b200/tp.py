@@ -110,7 +110,6 @@ class PeerExchange:
                 _lib.check(L.alloyb_tp_ipc_import(raw, C.byref(p)), "alloyb_tp_ipc_import")
                 self._imported.append(p)
                 ptrs[r] = p.value
-            dist.barrier(group=group)
         self.desc = _lib.TP(world, rank, self.max_n, (C.c_void_p * 8)(*ptrs, *([None] * (8 - world))))
 
     def close(self) -> None:
