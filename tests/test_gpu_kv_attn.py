@@ -207,6 +207,66 @@ def test_attention_paged_q8(b, kv_h, group, d, lo, hi):
     assert_close(to_np(out)[:, :, 0], ref, torch.float16, "paged q8")
 
 
+def test_attention_paged_q8_full_size_properties():
+    """Batch 64, contexts 4096..32768 (2.4 GB of q8_0 KV): properties that need no CPU reference.
+
+    1. Physical page placement does not matter: the same sequences stored under another page
+       permutation give bit-identical outputs.
+    2. With every V row of a head equal to one vector, the output is that vector for every query
+       (the softmax weights sum to one), whatever K holds.
+    """
+    from alloy_b200.kv import PagedKVPool
+    b, kv_h, group, d = 64, 8, 4, 128
+    cpu = torch.Generator().manual_seed(5)
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    lens = torch.randint(4096, 32768 + 1, (b,), generator=cpu)
+    pages_per = [(int(n) + 16) // 16 for n in lens]
+    total = sum(pages_per)
+    order = torch.randperm(total, generator=cpu).tolist()
+    store = PagedKVPool(total, kv_h, d, b, max(pages_per), DEV, free_order=order)
+    for i in range(b):
+        store.reserve(i, int(lens[i]) + 1)
+    store.pool.copy_(torch.randint(0, 256, store.pool.shape, dtype=torch.uint8, device=DEV, generator=gen))
+    blocks = store.pool.view(-1, 34)
+    sc = torch.empty(blocks.shape[0], device=DEV).uniform_(0.015, 0.03, generator=gen).half()
+    blocks[:, 0:2] = sc.view(torch.uint8).view(-1, 2)
+    h = kv_h * group
+    q = torch.randn((b, h, 1, d), device=DEV, generator=gen).half()
+    nk = torch.randn((b, kv_h, 1, d), device=DEV, generator=gen).half()
+    nv = torch.randn((b, kv_h, 1, d), device=DEV, generator=gen).half()
+    pos = lens.to(torch.int32).to(DEV)
+    base_pool = store.pool.clone()
+    out1 = torch.ops.alloy.attention_cache_q8_paged(q, nk, nv, pos, store.page_table, store.pool).clone()
+    assert torch.isfinite(out1.float()).all()
+
+    # 1. another physical placement of the same pages
+    perm = torch.randperm(total, generator=cpu).to(DEV)
+    pool2 = torch.empty_like(base_pool)
+    pool2[perm] = base_pool
+    table2 = store.page_table.clone()
+    valid = table2 >= 0
+    table2[valid] = perm[table2[valid].long()].to(table2.dtype)
+    out2 = torch.ops.alloy.attention_cache_q8_paged(q, nk, nv, pos, table2, pool2)
+    assert torch.equal(out1, out2)
+    del pool2
+
+    # 2. constant V rows per head: one q8_0 row (4 blocks of 34 bytes) repeated over all tokens
+    store.pool.copy_(base_pool)
+    row = store.pool[0, 1, :, 0].clone()                                  # (kv_h, 136) of page 0, V slab
+    store.pool[:, 1] = row[None, :, None, :]
+    nv_const = torch.empty((kv_h, d), device=DEV)
+    rb = row.view(kv_h, 4, 34)
+    scale = rb[:, :, 0:2].contiguous().view(torch.float16).float()        # (kv_h, 4, 1)
+    codes = rb[:, :, 2:].contiguous().view(torch.int8).float()            # (kv_h, 4, 32)
+    vconst = (codes * scale).reshape(kv_h, d)                             # dequantised V row per head
+    # the appended token's V must be that vector too: pass the dequantised row (it re-quantises to itself)
+    nv2 = vconst.half()[None, :, None, :].expand(b, kv_h, 1, d).contiguous()
+    out3 = torch.ops.alloy.attention_cache_q8_paged(q, nk, nv2, pos, store.page_table, store.pool)
+    want = vconst[:, None, :].expand(kv_h, group, d).reshape(1, h, 1, d).expand(b, h, 1, d)
+    err = (out3.float() - want).abs().max() / want.abs().max()
+    assert float(err) < 2e-3, float(err)
+
+
 def test_paged_append_entry_and_bad_page_is_skipped():
     rng = np.random.default_rng(5)
     b, kv_h, d = 2, 2, 128
