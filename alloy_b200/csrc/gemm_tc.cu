@@ -38,7 +38,8 @@ constexpr int PACK_ROW = 240;           // packed super-block per row: 144 (Q4_K
                                         // 15 x 16 bytes keeps 128-bit reads of 8 rows conflict-free
 constexpr int PACK_STAGE = BN * PACK_ROW;   // 28 KB
 constexpr int PACK_STAGES = 2;
-constexpr int THREADS = 192;            // warp 0 copies, warp 1 MMA, warps 2-5 decode + epilogue
+constexpr int DEC_THREADS = 256;        // two decode threads per weight row (half a k-step each)
+constexpr int THREADS = 64 + DEC_THREADS;   // warp 0 copies, warp 1 MMA, warps 2-9 decode + epilogue
 constexpr int TMEM_COLS = 256;
 constexpr uint32_t SPIN = 1u << 22;
 
@@ -179,7 +180,7 @@ __device__ __forceinline__ uint8_t* swz(uint8_t* tile, int r, int chunk) {
 
 // Decode k-step `ks` (0..3) of one Q4_K super-block of this thread's row: 64 weights.
 template <bool BF16>
-__device__ __forceinline__ void decode_q4k(const uint8_t* blk, int ks, uint8_t* tile, int r) {
+__device__ __forceinline__ void decode_q4k(const uint8_t* blk, int ks, uint8_t* tile, int r, int hsel) {
     const uint4 hdr = lds_u128(blk);
     const float d = half_bits_to_f32(hdr.x & 0xffffu), dmin = half_bits_to_f32(hdr.x >> 16);
     int sc0, m0, sc1, m1;
@@ -187,15 +188,17 @@ __device__ __forceinline__ void decode_q4k(const uint8_t* blk, int ks, uint8_t* 
     q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * ks + 1, sc1, m1);
     const float dl = d * static_cast<float>(sc0), ml = dmin * static_cast<float>(m0);
     const float dh = d * static_cast<float>(sc1), mh = dmin * static_cast<float>(m1);
-    const uint4 q0 = lds_u128(blk + 16 + ks * 32), q1 = lds_u128(blk + 32 + ks * 32);
-    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    // this thread's half of the 32 quant bytes: bytes 16*hsel .. +15 -> chunks 2*hsel, 2*hsel+1
+    const uint4 q0 = lds_u128(blk + 16 + ks * 32 + 16 * hsel);
+    const uint32_t qw[4] = {q0.x, q0.y, q0.z, q0.w};
     // low nibbles -> k 0..31 (chunks 0-3), high nibbles -> k 32..63 (chunks 4-7)
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int cc = 0; cc < 2; ++cc) {
+        const int c = 2 * hsel + cc;
         uint32_t lo[4], hi[4];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const uint32_t w = qw[c * 2 + h];
+            const uint32_t w = qw[cc * 2 + h];
             float fl[4], fh[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -216,11 +219,11 @@ __device__ __forceinline__ void decode_q4k(const uint8_t* blk, int ks, uint8_t* 
 
 // Q6_K: the block sits at `blk` (2-byte aligned).  k-step ks: elements 64*ks .. +63.
 template <bool BF16>
-__device__ __forceinline__ void decode_q6k(const uint8_t* blk, int ks, uint8_t* tile, int r) {
+__device__ __forceinline__ void decode_q6k(const uint8_t* blk, int ks, uint8_t* tile, int r, int hsel) {
     const int h = ks >> 1, jb = (ks & 1) * 2;            // sub-blocks j = jb, jb+1 of half h
     const float d = half_bits_to_f32(lds_u16(blk + 208));
-#pragma unroll
-    for (int jj = 0; jj < 2; ++jj) {
+    {
+        const int jj = hsel;                             // this thread's sub-block pair of the k-step
         const int j = jb + jj;
         const uint8_t* ql = blk + h * 64 + (j & 1) * 32;
         const uint8_t* qh = blk + 128 + h * 32;
@@ -268,12 +271,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             bar_init(&bars->a_full[s], 1);
-            bar_init(&bars->b_full[s], 128);
+            bar_init(&bars->b_full[s], DEC_THREADS);
             bar_init(&bars->empty[s], 1);
         }
         for (int s = 0; s < PACK_STAGES; ++s) {
             bar_init(&bars->p_full[s], 1);
-            bar_init(&bars->p_empty[s], 128);
+            bar_init(&bars->p_empty[s], DEC_THREADS);
         }
         bar_init(&bars->acc_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -348,8 +351,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
             __syncwarp();
         }
     } else {
-        // ------------------------------------------------ decode (one weight row per thread)
-        const int r = threadIdx.x - 64;
+        // ------------------------------------------------ decode (two threads per weight row)
+        const int r = (threadIdx.x - 64) & (BN - 1), hsel = (threadIdx.x - 64) >> 7;
         const bool live = n0 + r < P.N;
         bool ok = true;
         for (int ks = 0; ks < ksteps; ++ks) {
@@ -362,11 +365,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
                                      (P.format == ALLOYB_Q4_K ? 0 : ((sb * Q6K_BYTES) & 15));
                 if (!live) {
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) sts_u128(swz(tile, r, c), make_uint4(0u, 0u, 0u, 0u));
+                    for (int c = 0; c < 4; ++c) sts_u128(swz(tile, r, 4 * hsel + c), make_uint4(0u, 0u, 0u, 0u));
                 } else if (P.format == ALLOYB_Q4_K) {
-                    decode_q4k<BF16>(blk, ks & 3, tile, r);
+                    decode_q4k<BF16>(blk, ks & 3, tile, r, hsel);
                 } else {
-                    decode_q6k<BF16>(blk, ks & 3, tile, r);
+                    decode_q6k<BF16>(blk, ks & 3, tile, r, hsel);
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores -> MMA reads
             }
@@ -378,8 +381,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
             const int quarter = warp & 3;                   // TMEM lanes this warp may read
-#pragma unroll 1
-            for (int half = 0; half < 2; ++half) {
+            const int half = (warp - 2) >> 2;               // warps 2-5: tokens 0..127, warps 6-9: 128..255
+            {
                 const int tok = m0 + half * 128 + quarter * 32 + lane;
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 16) {

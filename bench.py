@@ -174,7 +174,8 @@ def run_reference(args, shape, workload: str) -> None:
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
         "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload, "batch": args.batch},
+        "config": {"workload": workload, "batch": args.batch, "context": WORKLOADS[workload]["context"],
+                   "kv": WORKLOADS[workload]["kv"], "parallelism": "host cores (attention and norms left out)"},
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": last["cores"], "kind": "port",
                          "sample": last["sample"]},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

@@ -26,6 +26,7 @@ cannot be imported on Linux.
 from __future__ import annotations
 
 import argparse
+import os
 import ast
 import pathlib
 import sys
@@ -51,7 +52,8 @@ def _extract(path: pathlib.Path, names: list[str]) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("ALLOY_REFERENCE"), required="ALLOY_REFERENCE" not in os.environ,
+                    help="path of the rayanht/alloy checkout (or set ALLOY_REFERENCE)")
     args = ap.parse_args()
     ref = pathlib.Path(args.reference)
 

@@ -2,6 +2,7 @@
 symbol the header declares, the op schemas equal the reference's, and host-side
 validation behaves like the reference's."""
 
+import os
 import pathlib
 import re
 
@@ -47,7 +48,9 @@ HOT_OPS = ["gguf_q4_k_mm", "batched_gguf_q4_k_mm", "gguf_q4_k_silu", "gguf_q4_k_
 
 
 def test_op_schemas_match_reference_source():
-    src = pathlib.Path("/root/reference/packages/alloy-torch/src/alloy_torch/custom_ops.py")
+    # the reference checkout: ALLOY_REFERENCE, else a sibling "reference" directory of the repo
+    root = os.environ.get("ALLOY_REFERENCE") or str(pathlib.Path(__file__).resolve().parents[2] / "reference")
+    src = pathlib.Path(root) / "packages/alloy-torch/src/alloy_torch/custom_ops.py"
     if not src.exists():
         pytest.skip("reference checkout not present")
     text = src.read_text()
