@@ -54,17 +54,22 @@ LLAMA3_70B = LlamaShape(layers=80, hidden=8192, ffn=28672, heads=64, kv_heads=8,
 
 
 class LayerWeights:
-    __slots__ = ("wq", "wk", "wv", "wo", "wg", "wu", "wd", "norm_in", "norm_post")
+    __slots__ = ("wq", "wk", "wv", "wo", "wg", "wu", "wd", "norm_in", "norm_post", "fmt")
+
+    def __init__(self) -> None:
+        # format name of every matrix (Q4_K_M: Q4_K for q/k/o/gate/up, Q6_K for v/down)
+        self.fmt = {"wq": "q4_k", "wk": "q4_k", "wv": "q6_k", "wo": "q4_k", "wg": "q4_k", "wu": "q4_k", "wd": "q6_k"}
 
 
 
 class QuantLlamaDecoder:
-    """Random-init (seeded) Q4_K_M Llama-shape decoder for one decode step per call."""
+    """Q4_K_M Llama-shape decoder for one decode step per call: random-init (seeded) weights, or
+    the tensors of a GGUF checkpoint (``weights``: ``gguf_loader.LlamaWeights``, unsharded)."""
 
     def __init__(self, shape: LlamaShape, batch: int, context: int, *, device="cuda", seed: int = 0,
                  kv: str = "f16", tp_rank: int = 0, tp_size: int = 1, process_group=None,
                  dtype: torch.dtype = torch.float16, d_scale: float = 1.0, peer_allreduce: bool = True,
-                 tp_dry: bool = False) -> None:
+                 tp_dry: bool = False, weights=None) -> None:
         if kv not in ("f16", "q8_paged"):
             raise ValueError(f"kv must be 'f16' or 'q8_paged', got {kv!r}")
         if shape.heads % tp_size or shape.kv_heads % tp_size or shape.ffn % (256 * tp_size) \
@@ -112,22 +117,38 @@ class QuantLlamaDecoder:
         def rows(t, per):
             return tp.shard_rows(t, r, n)
 
-        self.embed = synth.q4k_blocks_device(s.vocab, s.hidden, gen, self.device, d_scale)
+        self.embed_fmt, self.head_fmt = "q4_k", "q6_k"
         self.layers: list[LayerWeights] = []
-        for _ in range(s.layers):
-            lw = LayerWeights()
-            lw.wq = rows(synth.q4k_blocks_device(s.heads * s.head_dim, s.hidden, gen, self.device, d_scale), hd_l)
-            lw.wk = rows(synth.q4k_blocks_device(s.kv_heads * s.head_dim, s.hidden, gen, self.device, d_scale), kvd_l)
-            lw.wv = rows(synth.q6k_blocks_device(s.kv_heads * s.head_dim, s.hidden, gen, self.device, d_scale), kvd_l)
-            lw.wo = tp.shard_cols(synth.q4k_blocks_device(s.hidden, s.heads * s.head_dim, gen, self.device, d_scale), "q4_k", r, n)
-            lw.wg = rows(synth.q4k_blocks_device(s.ffn, s.hidden, gen, self.device, d_scale), self.ffn_l)
-            lw.wu = rows(synth.q4k_blocks_device(s.ffn, s.hidden, gen, self.device, d_scale), self.ffn_l)
-            lw.wd = tp.shard_cols(synth.q6k_blocks_device(s.hidden, s.ffn, gen, self.device, d_scale), "q6_k", r, n)
-            lw.norm_in = self._norm_weight(gen)
-            lw.norm_post = self._norm_weight(gen)
-            self.layers.append(lw)
-        self.norm_final = self._norm_weight(gen)
-        self.head = rows(synth.q6k_blocks_device(s.vocab, s.hidden, gen, self.device, d_scale), self.vocab_l)
+        if weights is not None:
+            # checkpoint tensors: same sharding as the synthetic model
+            self.embed, self.embed_fmt = weights.embed.tensor, weights.embed.fmt
+            for lsrc in weights.layers:
+                lw = LayerWeights()
+                lw.fmt = {k: lsrc[k].fmt for k in lw.fmt}
+                lw.wq, lw.wk, lw.wv = (rows(lsrc[k].tensor, 0) for k in ("wq", "wk", "wv"))
+                lw.wg, lw.wu = rows(lsrc["wg"].tensor, 0), rows(lsrc["wu"].tensor, 0)
+                lw.wo = tp.shard_cols(lsrc["wo"].tensor, lw.fmt["wo"], r, n)
+                lw.wd = tp.shard_cols(lsrc["wd"].tensor, lw.fmt["wd"], r, n)
+                lw.norm_in, lw.norm_post = lsrc["norm_in"].tensor, lsrc["norm_post"].tensor
+                self.layers.append(lw)
+            self.norm_final = weights.norm_final.tensor
+            self.head, self.head_fmt = rows(weights.head.tensor, 0), weights.head.fmt
+        else:
+            self.embed = synth.q4k_blocks_device(s.vocab, s.hidden, gen, self.device, d_scale)
+            for _ in range(s.layers):
+                lw = LayerWeights()
+                lw.wq = rows(synth.q4k_blocks_device(s.heads * s.head_dim, s.hidden, gen, self.device, d_scale), hd_l)
+                lw.wk = rows(synth.q4k_blocks_device(s.kv_heads * s.head_dim, s.hidden, gen, self.device, d_scale), kvd_l)
+                lw.wv = rows(synth.q6k_blocks_device(s.kv_heads * s.head_dim, s.hidden, gen, self.device, d_scale), kvd_l)
+                lw.wo = tp.shard_cols(synth.q4k_blocks_device(s.hidden, s.heads * s.head_dim, gen, self.device, d_scale), "q4_k", r, n)
+                lw.wg = rows(synth.q4k_blocks_device(s.ffn, s.hidden, gen, self.device, d_scale), self.ffn_l)
+                lw.wu = rows(synth.q4k_blocks_device(s.ffn, s.hidden, gen, self.device, d_scale), self.ffn_l)
+                lw.wd = tp.shard_cols(synth.q6k_blocks_device(s.hidden, s.ffn, gen, self.device, d_scale), "q6_k", r, n)
+                lw.norm_in = self._norm_weight(gen)
+                lw.norm_post = self._norm_weight(gen)
+                self.layers.append(lw)
+            self.norm_final = self._norm_weight(gen)
+            self.head = rows(synth.q6k_blocks_device(s.vocab, s.hidden, gen, self.device, d_scale), self.vocab_l)
         self.inv_freq = (1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, dtype=torch.float32) /
                                                  s.head_dim))).to(self.device)
         self._init_kv(gen)
@@ -201,14 +222,14 @@ class QuantLlamaDecoder:
         s, b = self.shape, self.batch
         n0 = ops.launch_count()
         self.fused_allreduce_calls = 0
-        h = ops._embedding(self.ids, 0, self.embed, None, out_dtype=self.dtype)
+        h = ops._embedding(self.ids, ops._FORMATS[self.embed_fmt], self.embed, None, out_dtype=self.dtype)
         scale = 1.0 / (s.head_dim ** 0.5)
         for li, lw in enumerate(self.layers):
             # q/k are Q4_K and v is Q6_K: one launch for the three projections beats the norm fused
             # into one streaming launch per format (measured), so the norm stays its own kernel here
             xn = ops.rms_norm(h, lw.norm_in, s.eps)
-            q, k, v = ops.linear_multi(xn, [("q4_k", lw.wq, None), ("q4_k", lw.wk, None),
-                                            ("q6_k", lw.wv, None)])
+            q, k, v = ops.linear_multi(xn, [(lw.fmt["wq"], lw.wq, None), (lw.fmt["wk"], lw.wk, None),
+                                            (lw.fmt["wv"], lw.wv, None)])
             q3 = q.view(b, self.heads_l, s.head_dim)
             k3 = k.view(b, self.kv_heads_l, s.head_dim)
             ops.rope_inplace(q3, k3, self.pos, self.inv_freq)
@@ -224,15 +245,20 @@ class QuantLlamaDecoder:
                                                              pool.pool)
             a2 = a.transpose(1, 2).reshape(b, self.heads_l * s.head_dim)
             if self.tp_size == 1:
-                h = torch.ops.alloy.linear_residual(a2, lw.wo, None, h, "q4_k")
+                h = torch.ops.alloy.linear_residual(a2, lw.wo, None, h, lw.fmt["wo"])
             else:
-                h = self._row_parallel(a2, "q4_k", lw.wo, h)
-            act = ops.gated_normed(h, lw.norm_post, s.eps, lw.wg, lw.wu)
+                h = self._row_parallel(a2, lw.fmt["wo"], lw.wo, h)
+            if lw.fmt["wg"] == "q4_k" and lw.fmt["wu"] == "q4_k":
+                act = ops.gated_normed(h, lw.norm_post, s.eps, lw.wg, lw.wu)
+            else:
+                gate, up = ops.linear_multi(h, [(lw.fmt["wg"], lw.wg, None), (lw.fmt["wu"], lw.wu, None)],
+                                            norm=(lw.norm_post, s.eps))
+                act = ops.silu_mul(gate, up)
             if self.tp_size == 1:
-                h = torch.ops.alloy.linear_residual(act, lw.wd, None, h, "q6_k")
+                h = torch.ops.alloy.linear_residual(act, lw.wd, None, h, lw.fmt["wd"])
             else:
-                h = self._row_parallel(act, "q6_k", lw.wd, h)
-        logits = ops.linear_multi(h, [("q6_k", self.head, None)], norm=(self.norm_final, s.eps))[0]
+                h = self._row_parallel(act, lw.fmt["wd"], lw.wd, h)
+        logits = ops.linear_multi(h, [(self.head_fmt, self.head, None)], norm=(self.norm_final, s.eps))[0]
         if self.tp_size > 1 and not self.tp_dry:
             logits = tp.gather_columns(logits, self.pg)
         self.logits = logits

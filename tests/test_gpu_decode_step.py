@@ -63,3 +63,41 @@ def test_decode_step_matches_oracle(batch):
     torch.cuda.synchronize()
     assert torch.equal(dec.logits, torch.from_numpy(got).to(dec.logits))
     assert dec.launches_per_step > 0
+
+
+def test_decode_step_from_gguf_file(tmp_path):
+    """A Llama-architecture GGUF file (written with gguf.GGUFWriter: permuted q/k rows, Q6_K and Q4_K
+    v/down in alternating layers, tied head) served by the decoder equals the oracle's step on the
+    arrays the file was made from."""
+    from alloy_b200 import gguf_loader
+    from tests._gguf_fixture import TINY_META, write_tiny_llama
+
+    path = tmp_path / "tiny.gguf"
+    arrays = write_tiny_llama(path, seed=11, tied_head=True)
+    batch, ctx = 2, 80
+    dec = gguf_loader.load_llama_decoder(path, batch, ctx, seed=5)
+    assert dec.shape.layers == TINY_META["layers"] and dec.head_fmt == "q4_k"
+    deq = {"q4_k": O.dequant_q4_k, "q6_k": O.dequant_q6_k}
+    layers = []
+    for lay in arrays["layers"]:
+        d = {k: deq[lay[k][0]](lay[k][1]) for k in ("wq", "wk", "wv", "wo", "wg", "wu", "wd")}
+        d["norm_in"] = lay["norm_in"].astype(np.float16)
+        d["norm_post"] = lay["norm_post"].astype(np.float16)
+        layers.append(d)
+    rng = np.random.default_rng(1)
+    ids = rng.integers(0, TINY_META["vocab"], size=batch)
+    dec.ids.copy_(torch.from_numpy(ids))
+    kc = [k.float().cpu().numpy() for k in dec.k_cache]
+    vc = [v.float().cpu().numpy() for v in dec.v_cache]
+    table = deq["q4_k"](arrays["embed"][1])
+    ref_logits, _, _ = OD.decode_step(ids, ctx - 1, table, layers, arrays["norm_final"].astype(np.float16), table,
+                                      dec.inv_freq.cpu().numpy(), kc, vc, TINY_META["heads"], TINY_META["kv_heads"],
+                                      TINY_META["head_dim"], TINY_META["eps"])
+    assert np.isfinite(ref_logits.astype(np.float32)).all()
+    dec.step()
+    torch.cuda.synchronize()
+    got = to_np(dec.logits)
+    _, mean = rel_errors(got, ref_logits.astype(np.float64), torch.float16)
+    ref64 = ref_logits.astype(np.float64)
+    worst = np.abs(got - ref64).max() / np.sqrt((ref64 ** 2).mean())
+    assert worst <= 1e-2 and mean <= 2e-3, (worst, mean)
