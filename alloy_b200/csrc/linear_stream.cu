@@ -391,7 +391,9 @@ __device__ __forceinline__ void unit_q6k(uint32_t blk, const XFrag6& f, int g, i
 
 // KIND: slot geometry / weight format.  RT: matrices per tile (2 = gate/up pair).  CACHE: the warp's
 // slice is exactly one slot long and its B fragments stay in registers for the whole launch.
-template <int KIND, int RT, bool CACHE, int GW>
+// GU: gate/up pair with the two matrices dealt to the two groups (group 0 streams gate rows, group 1
+// the up rows of the SAME tiles, RT = 1 each), so both groups do the same work whatever the tile count.
+template <int KIND, int RT, bool CACHE, int GW, bool GU = false>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     constexpr int SBS = Geom<KIND>::SBS, PITCH = Geom<KIND>::PITCH, SLOT = 16 * PITCH, BLK = Geom<KIND>::BLK;
@@ -400,9 +402,12 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int grp = warp / GW, wg = warp % GW;
     constexpr int n_warps = WARPS, n_groups = WARPS / GW;
+    static_assert(!GU || (RT == 1 && GW == 8), "gate/up split: two groups of eight warps");
+    constexpr int tstep = GU ? 1 : n_groups;                        // tiles between two of this group's tiles
     const int D = P.depth;
     // [warps][D] slots | [groups][2][GW][RT][16] partials | [warps][MAX_D] barriers
-    float* red = reinterpret_cast<float*>(smem + n_warps * D * SLOT) + grp * (2 * GW * RT * 16);
+    float* red_all = reinterpret_cast<float*>(smem + n_warps * D * SLOT);
+    float* red = red_all + grp * (2 * GW * RT * 16);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + n_warps * D * SLOT + n_groups * 2 * GW * RT * 16 * 4);
     const uint32_t ring = smem_u32(smem + warp * D * SLOT);
     const uint32_t bar0 = smem_u32(bars + warp * MAX_D);
@@ -427,10 +432,10 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     {
         Cursor c = {0, 0, 0};
         cursor_enter(c, P, lo, hi);
-        cursor_next(c, P, lo, hi, grp);
+        cursor_next(c, P, lo, hi, GU ? 0 : grp);
         while (c.seg < P.n_seg) {
             ++my_tiles;
-            cursor_next(c, P, lo, hi, n_groups);
+            cursor_next(c, P, lo, hi, tstep);
         }
     }
     const int n_stage = my_tiles * spt;
@@ -438,11 +443,11 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     // producer side: stage sequence = for tile, for slot-sized step of the slice, for matrix
     Cursor pc = {0, 0, 0};
     cursor_enter(pc, P, lo, hi);
-    cursor_next(pc, P, lo, hi, grp);
+    cursor_next(pc, P, lo, hi, GU ? 0 : grp);
     int issued = 0, p_r = 0, p_slot = 0;
     auto issue = [&]() {
         const int sb = sb_lo + (p_r / RT) * SBS, mt = p_r % RT;
-        const int si = P.gated ? mt : pc.seg;
+        const int si = GU ? grp : (P.gated ? mt : pc.seg);
         const int nvalid = pc.lim - pc.row < 16 ? pc.lim - pc.row : 16;
         const uint32_t bar = bar0 + 8 * p_slot, dst = ring + p_slot * SLOT;
         const int win = (sb * BLK) & ~15;                            // 16-byte-aligned start of the stage in a row
@@ -468,7 +473,7 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
         if (++p_slot == D) p_slot = 0;
         if (++p_r == spt) {
             p_r = 0;
-            cursor_next(pc, P, lo, hi, n_groups);
+            cursor_next(pc, P, lo, hi, tstep);
         }
     };
     while (issued < n_stage && issued < D) issue();
@@ -521,7 +526,7 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
 
     // tensor-parallel exchange: this call's epoch and slot set
     uint32_t tp_next = 0;
-    if (RT == 1 && P.tp.world) {
+    if (RT == 1 && !GU && P.tp.world) {
         tp_next = *reinterpret_cast<volatile uint32_t*>(P.tp.peer[P.tp.rank]) + 1u;
     }
 
@@ -540,7 +545,7 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     uint32_t c_ph = 0;
     Cursor cc = {0, 0, 0};
     cursor_enter(cc, P, lo, hi);
-    cursor_next(cc, P, lo, hi, grp);
+    cursor_next(cc, P, lo, hi, GU ? 0 : grp);
     for (int it = 0; it < my_tiles; ++it) {
         float acc[RT][2];
 #pragma unroll
@@ -593,7 +598,7 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
             const Seg& sg = P.seg[cc.seg];
             const int row = cc.row + tl;
             __half* y = static_cast<__half*>(sg.y);
-            if (RT == 2) {
+            if (RT == 2 || GU) {
                 const float a = (P.act == ALLOYB_ACT_SILU) ? act_silu(v) : act_gelu_tanh(v);
                 y[row] = __float2half_rn(a * u);
             } else if (P.tp.world) {
@@ -611,6 +616,23 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
             if (t == 0) {
                 store(g, acc[0][0], RT == 2 ? acc[RT - 1][0] : 0.f);
                 store(g + 8, acc[0][1], RT == 2 ? acc[RT - 1][1] : 0.f);
+            }
+        } else if constexpr (GU) {
+            // ... then gate (warps 0-7) and up (warps 8-15) meet: double-buffered partials, one CTA barrier
+            float* rbuf = red_all + (it & 1) * (WARPS * 16);
+            if (t == 0) {
+                rbuf[warp * 16 + g] = acc[0][0];
+                rbuf[warp * 16 + g + 8] = acc[0][1];
+            }
+            __syncthreads();
+            if (threadIdx.x < 16) {
+                float v = 0.f, u = 0.f;
+#pragma unroll
+                for (int w = 0; w < GW; ++w) {
+                    v += rbuf[w * 16 + threadIdx.x];
+                    u += rbuf[(GW + w) * 16 + threadIdx.x];
+                }
+                store(threadIdx.x, v, u);
             }
         } else {
             // ... then the K slices of the group (double-buffered partials, one named barrier)
@@ -634,9 +656,9 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
                 store(tl, v, u);
             }
         }
-        cursor_next(cc, P, lo, hi, n_groups);
+        cursor_next(cc, P, lo, hi, tstep);
     }
-    if (RT == 1 && P.tp.world) {
+    if (RT == 1 && !GU && P.tp.world) {
         // ---- all-reduce of this CTA's rows: publish, wait for the same CTA of every rank, sum in
         // rank order (identical on all ranks), add the residual, store.
         __syncthreads();
@@ -687,10 +709,10 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     }
 }
 
-template <int KIND, int RT, bool CACHE, int GW>
+template <int KIND, int RT, bool CACHE, int GW, bool GU = false>
 static int launch(const Maps& maps, const Params& P, cudaStream_t stream) {
     static bool configured = false;
-    auto kern = gemv_stream_kernel<KIND, RT, CACHE, GW>;
+    auto kern = gemv_stream_kernel<KIND, RT, CACHE, GW, GU>;
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
@@ -826,6 +848,15 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
      : gw == 4 ? (cache ? launch<KIND, RT, true, 4>(maps, P, stream) : launch<KIND, RT, false, 4>(maps, P, stream)) \
                : (cache ? launch<KIND, RT, true, 8>(maps, P, stream) : launch<KIND, RT, false, 8>(maps, P, stream)))
     if (kind == Q6) return ALLOYB_ST_LAUNCH(Q6, 1);
+    if (gated && gw == 8) {
+        // the two matrices go to the two groups of eight warps
+        static const bool no_gu = env_int("ALLOYB_ST_NO_GU", 0) != 0;       // tuning aid
+        if (!no_gu) {
+            if (kind == Q4x2)
+                return cache ? launch<Q4x2, 1, true, 8, true>(maps, P, stream) : launch<Q4x2, 1, false, 8, true>(maps, P, stream);
+            return cache ? launch<Q4x1, 1, true, 8, true>(maps, P, stream) : launch<Q4x1, 1, false, 8, true>(maps, P, stream);
+        }
+    }
     if (gated) return kind == Q4x2 ? ALLOYB_ST_LAUNCH(Q4x2, 2) : ALLOYB_ST_LAUNCH(Q4x1, 2);
     return kind == Q4x2 ? ALLOYB_ST_LAUNCH(Q4x2, 1) : ALLOYB_ST_LAUNCH(Q4x1, 1);
 #undef ALLOYB_ST_LAUNCH
