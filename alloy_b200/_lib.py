@@ -66,6 +66,8 @@ SIGNATURES = {
     "alloyb_gated_linear": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "alloyb_linear_normed": (_i, [_p, _p, _f, _p, _i, _i, _i, C.POINTER(Weight), _i, _p]),
     "alloyb_gated_linear_normed": (_i, [_p, _p, _f, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "alloyb_rope_kv_append": (_i, [_i, _p, _p, _p, _i64, _i64, _p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i64,
+                                   _p, _p]),
     "alloyb_tp_buffer_bytes": (_sz, [_i]),
     "alloyb_tp_alloc": (_i, [_sz, C.POINTER(_p)]),
     "alloyb_tp_free": (_i, [_p]),

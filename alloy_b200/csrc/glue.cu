@@ -101,8 +101,10 @@ __global__ void rope_kernel(T* __restrict__ q, T* __restrict__ k, const int32_t*
     sincosf(angle, &s, &c);
     const float x1 = to_f32<T>(base[j]);
     const float x2 = to_f32<T>(base[j + half]);
-    base[j] = from_f32<T>(x1 * c - x2 * s);
-    base[j + half] = from_f32<T>(x2 * c + x1 * s);
+    // two rounded products and one rounded sum, never a fused multiply-add: the same fp32 sequence
+    // as the element-wise reference (and as the fused RoPE + append kernel)
+    base[j] = from_f32<T>(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s)));
+    base[j + half] = from_f32<T>(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s)));
 }
 
 template <typename T>

@@ -50,6 +50,36 @@ __global__ void kv_quantize_range_kernel(const __half* __restrict__ src, int64_t
     if (lane == 0) scales[row * nblk + blk] = qb.scale;
 }
 
+// One 32-element block of a new K (which = 0) or V (1) row at position p, one element per lane, into
+// the cache of any layout (q8 layouts quantise it).
+template <int LAYOUT>
+__device__ __forceinline__ void store_kv_block(const KVPtrs& kv, int which, int b, int h, int p, int blk, int lane,
+                                               __half xin, int KV_H, int D, int* status) {
+    const int nblk = D / 32;
+    if (LAYOUT == ALLOYB_KV_F16) {
+        __half* cache = static_cast<__half*>(which ? kv.v0 : kv.k0);
+        cache[((static_cast<int64_t>(b) * KV_H + h) * kv.S_max + p) * D + blk * 32 + lane] = xin;
+        return;
+    }
+    const Q8Block qb = quantize_block_q8(__half2float(xin));
+    if (LAYOUT == ALLOYB_KV_Q8_SPLIT) {
+        const int64_t row = (static_cast<int64_t>(b) * KV_H + h) * kv.S_max + p;
+        static_cast<int8_t*>(which ? kv.v0 : kv.k0)[row * D + blk * 32 + lane] = static_cast<int8_t>(qb.code);
+        if (lane == 0) static_cast<__half*>(which ? kv.v1 : kv.k1)[row * nblk + blk] = qb.scale;
+    } else {
+        const int32_t* table = static_cast<const int32_t*>(kv.k1);
+        const int64_t page = table[static_cast<int64_t>(b) * kv.max_pages + p / PAGE_TOKENS];
+        if (page < 0 || page >= kv.num_pages) {
+            if (lane == 0 && status) atomicOr(status, KV_STATUS_PAGE_RANGE);
+            return;
+        }
+        uint8_t* dst = static_cast<uint8_t*>(kv.k0) + paged_row_offset(page, which, h, p % PAGE_TOKENS, KV_H, D) +
+                       blk * KV_BLOCK_BYTES;
+        if (lane == 0) *reinterpret_cast<__half*>(dst) = qb.scale;
+        reinterpret_cast<int8_t*>(dst + 2)[lane] = static_cast<int8_t>(qb.code);
+    }
+}
+
 // One new token per sequence, any layout; one warp per (b, h, K|V, block).
 template <int LAYOUT>
 __global__ void kv_append_kernel(const __half* __restrict__ new_k, const __half* __restrict__ new_v,
@@ -73,30 +103,7 @@ __global__ void kv_append_kernel(const __half* __restrict__ new_k, const __half*
         return;
     }
     const __half xin = (which ? new_v : new_k)[b * sb + h * sh + blk * 32 + lane];
-    if (LAYOUT == ALLOYB_KV_F16) {
-        __half* cache = static_cast<__half*>(which ? kv.v0 : kv.k0);
-        cache[((static_cast<int64_t>(b) * KV_H + h) * kv.S_max + p) * D + blk * 32 + lane] = xin;
-        return;
-    }
-    const Q8Block qb = quantize_block_q8(__half2float(xin));
-    if (LAYOUT == ALLOYB_KV_Q8_SPLIT) {
-        const int64_t row = (static_cast<int64_t>(b) * KV_H + h) * kv.S_max + p;
-        static_cast<int8_t*>(which ? kv.v0 : kv.k0)[row * D + blk * 32 + lane] =
-            static_cast<int8_t>(qb.code);
-        if (lane == 0) static_cast<__half*>(which ? kv.v1 : kv.k1)[row * nblk + blk] = qb.scale;
-    } else {
-        const int32_t* table = static_cast<const int32_t*>(kv.k1);
-        const int64_t page = table[static_cast<int64_t>(b) * kv.max_pages + p / PAGE_TOKENS];
-        if (page < 0 || page >= kv.num_pages) {
-            if (lane == 0 && status) atomicOr(status, KV_STATUS_PAGE_RANGE);
-            return;
-        }
-        uint8_t* dst = static_cast<uint8_t*>(kv.k0) +
-                       paged_row_offset(page, which, h, p % PAGE_TOKENS, KV_H, D) +
-                       blk * KV_BLOCK_BYTES;
-        if (lane == 0) *reinterpret_cast<__half*>(dst) = qb.scale;
-        reinterpret_cast<int8_t*>(dst + 2)[lane] = static_cast<int8_t>(qb.code);
-    }
+    store_kv_block<LAYOUT>(kv, which, b, h, p, blk, lane, xin, KV_H, D, status);
 }
 
 __global__ void kv_dequant_kernel(const int8_t* __restrict__ codes, const __half* __restrict__ scales,
@@ -113,6 +120,64 @@ __global__ void kv_dequant_kernel(const int8_t* __restrict__ codes, const __half
         const float s = __half2float(scales[row * (D / 32) + c / 32]);
         out[i] = __float2half_rn(__fmul_rn(static_cast<float>(codes[i]), s));
     }
+}
+
+// RoPE (rotate-half) of the new token's q (in place) and k, and the append of k / v to the cache, in
+// one launch.  A warp owns 32 rotation pairs (j, j + D/2) of one head, i.e. two whole 32-element
+// blocks, so the rotated K row is quantised without leaving the warp.  Same arithmetic and
+// rounding points as rope_inplace followed by the append: fp32 rotation, fp16 result, q8 of that.
+template <int LAYOUT>
+__global__ void rope_kv_append_kernel(__half* __restrict__ q, const __half* __restrict__ new_k,
+                                      const __half* __restrict__ new_v, int64_t sb, int64_t sh, KVPtrs kv,
+                                      const int32_t* __restrict__ pos, int pos_count,
+                                      const float* __restrict__ inv_freq, int B, int H, int KV_H, int D,
+                                      int* __restrict__ status) {
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int npair = D / 64, nblk = D / 32;          // pair-warps per head, blocks per row
+    const int64_t wq = static_cast<int64_t>(B) * H * npair, wk = static_cast<int64_t>(B) * KV_H * npair,
+                  wv = static_cast<int64_t>(B) * KV_H * nblk;
+    int64_t wid = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+    if (wid >= wq + wk + wv) return;
+    pdl_wait();
+    if (wid < wq + wk) {
+        const bool is_q = wid < wq;
+        if (!is_q) wid -= wq;
+        const int heads = is_q ? H : KV_H;
+        const int ph = static_cast<int>(wid % npair);
+        const int hh = static_cast<int>((wid / npair) % heads);
+        const int b = static_cast<int>(wid / npair / heads);
+        const int p = pos[pos_count == 1 ? 0 : b];
+        const int j = 32 * ph + lane, half = D / 2;
+        const float angle = static_cast<float>(p) * inv_freq[j];
+        float sn, cs;
+        sincosf(angle, &sn, &cs);
+        if (is_q) {
+            __half* base = q + (static_cast<int64_t>(b) * H + hh) * D;
+            const float x1 = __half2float(base[j]), x2 = __half2float(base[j + half]);
+            base[j] = __float2half_rn(__fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn)));
+            base[j + half] = __float2half_rn(__fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn)));
+            return;
+        }
+        if (p < 0 || p >= kv.S_max) {
+            if (lane == 0 && status) atomicOr(status, KV_STATUS_POS_RANGE);
+            return;
+        }
+        const __half* base = new_k + b * sb + hh * sh;
+        const float x1 = __half2float(base[j]), x2 = __half2float(base[j + half]);
+        store_kv_block<LAYOUT>(kv, 0, b, hh, p, ph, lane,
+                               __float2half_rn(__fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn))), KV_H, D, status);
+        store_kv_block<LAYOUT>(kv, 0, b, hh, p, ph + npair, lane,
+                               __float2half_rn(__fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn))), KV_H, D, status);
+        return;
+    }
+    wid -= wq + wk;
+    const int blk = static_cast<int>(wid % nblk);
+    const int h = static_cast<int>((wid / nblk) % KV_H);
+    const int b = static_cast<int>(wid / nblk / KV_H);
+    const int p = pos[pos_count == 1 ? 0 : b];
+    if (p < 0 || p >= kv.S_max) return;                // reported by the K warps
+    store_kv_block<LAYOUT>(kv, 1, b, h, p, blk, lane, new_v[b * sb + h * sh + blk * 32 + lane], KV_H, D, status);
 }
 
 int launch_kv_append(int layout, const void* new_k, const void* new_v, int64_t sb, int64_t sh,
@@ -193,4 +258,47 @@ extern "C" int alloyb_kv_append_q8_paged(const void* new_k, const void* new_v, i
     kv.num_pages = num_pages;
     return launch_kv_append(ALLOYB_KV_Q8_PAGED, new_k, new_v, batch_stride, head_stride, kv, seq_pos,
                             B, B, KV_H, D, status, as_stream(stream));
+}
+
+extern "C" int alloyb_rope_kv_append(int layout, void* q, const void* new_k, const void* new_v,
+                                     int64_t new_batch_stride, int64_t new_head_stride, void* k0, void* k1,
+                                     void* v0, void* v1, const int32_t* pos, int pos_count, const float* inv_freq,
+                                     int B, int H, int KV_H, int D, int S_max, int64_t num_pages, int32_t* status,
+                                     void* stream) {
+    if (!q || !new_k || !new_v || !k0 || !pos || !inv_freq) return ALLOYB_E_NULL;
+    if (B <= 0 || H <= 0 || KV_H <= 0 || D <= 0 || D % 64 || S_max <= 0) return ALLOYB_E_SHAPE;
+    if (pos_count != 1 && pos_count != B) return ALLOYB_E_SHAPE;
+    KVPtrs kv;
+    kv.k0 = k0; kv.k1 = k1; kv.v0 = v0; kv.v1 = v1;
+    kv.S_max = S_max;
+    kv.max_pages = S_max / PAGE_TOKENS;
+    kv.num_pages = num_pages;
+    if (layout == ALLOYB_KV_F16) { if (!v0) return ALLOYB_E_NULL; }
+    else if (layout == ALLOYB_KV_Q8_SPLIT) { if (!k1 || !v0 || !v1) return ALLOYB_E_NULL; }
+    else if (layout == ALLOYB_KV_Q8_PAGED) {
+        if (!k1) return ALLOYB_E_NULL;
+        if (S_max % PAGE_TOKENS || num_pages <= 0) return ALLOYB_E_SHAPE;
+    } else return ALLOYB_E_SHAPE;
+    const int64_t warps = static_cast<int64_t>(B) * (H + KV_H) * (D / 64) + static_cast<int64_t>(B) * KV_H * (D / 32);
+    const int blocks = static_cast<int>((warps * 32 + 255) / 256);
+    cudaStream_t st = as_stream(stream);
+    __half* qh = static_cast<__half*>(q);
+    const __half* nk = static_cast<const __half*>(new_k);
+    const __half* nv = static_cast<const __half*>(new_v);
+    int* stw = reinterpret_cast<int*>(status);
+    switch (layout) {
+        case ALLOYB_KV_F16:
+            launch_pdl(rope_kv_append_kernel<ALLOYB_KV_F16>, dim3(blocks), dim3(256), 0, st, qh, nk, nv, new_batch_stride,
+                       new_head_stride, kv, pos, pos_count, inv_freq, B, H, KV_H, D, stw);
+            break;
+        case ALLOYB_KV_Q8_SPLIT:
+            launch_pdl(rope_kv_append_kernel<ALLOYB_KV_Q8_SPLIT>, dim3(blocks), dim3(256), 0, st, qh, nk, nv,
+                       new_batch_stride, new_head_stride, kv, pos, pos_count, inv_freq, B, H, KV_H, D, stw);
+            break;
+        default:
+            launch_pdl(rope_kv_append_kernel<ALLOYB_KV_Q8_PAGED>, dim3(blocks), dim3(256), 0, st, qh, nk, nv,
+                       new_batch_stride, new_head_stride, kv, pos, pos_count, inv_freq, B, H, KV_H, D, stw);
+            break;
+    }
+    return check_launch();
 }

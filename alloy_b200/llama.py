@@ -232,17 +232,19 @@ class QuantLlamaDecoder:
                                             (lw.fmt["wv"], lw.wv, None)])
             q3 = q.view(b, self.heads_l, s.head_dim)
             k3 = k.view(b, self.kv_heads_l, s.head_dim)
-            ops.rope_inplace(q3, k3, self.pos, self.inv_freq)
-            q4 = q3.unsqueeze(2)
-            k4 = k3.unsqueeze(2)
-            v4 = v.view(b, self.kv_heads_l, 1, s.head_dim)
+            v3 = v.view(b, self.kv_heads_l, s.head_dim)
+            q4, k4, v4 = q3.unsqueeze(2), k3.unsqueeze(2), v3.unsqueeze(2)
+            # RoPE of q and k and the cache append in one launch; attention then only reads
             if self.kv_kind == "f16":
+                ops.rope_kv_append(q3, k3, v3, self.pos, self.inv_freq, k_cache=self.k_cache[li],
+                                   v_cache=self.v_cache[li])
                 a = torch.ops.alloy.attention_cache(q4, k4, v4, self.pos, self.k_cache[li],
-                                                    self.v_cache[li], scale)
+                                                    self.v_cache[li], scale, 0, False)
             else:
                 pool = self.pools[li]
+                ops.rope_kv_append(q3, k3, v3, self.seq_pos, self.inv_freq, paged=(pool.page_table, pool.pool))
                 a = torch.ops.alloy.attention_cache_q8_paged(q4, k4, v4, self.seq_pos, pool.page_table,
-                                                             pool.pool)
+                                                             pool.pool, -1.0, False)
             a2 = a.transpose(1, 2).reshape(b, self.heads_l * s.head_dim)
             if self.tp_size == 1:
                 h = torch.ops.alloy.linear_residual(a2, lw.wo, None, h, lw.fmt["wo"])

@@ -598,6 +598,43 @@ def rope_inplace(q: torch.Tensor, k: torch.Tensor, pos: torch.Tensor, inv_freq: 
           "alloyb_rope_inplace")
 
 
+def rope_kv_append(q: torch.Tensor, new_k: torch.Tensor, new_v: torch.Tensor, pos: torch.Tensor,
+                   inv_freq: torch.Tensor, *, k_cache: torch.Tensor | None = None, v_cache: torch.Tensor | None = None,
+                   q8_split: tuple | None = None, paged: tuple | None = None) -> None:
+    """Rotate-half RoPE of the decode token's q (contiguous fp16 (B, H, D), in place) and k, and the
+    append of the rotated k and of v at ``pos`` to ONE cache, in one launch
+    (``alloyb_rope_kv_append``); run the attention op with ``write_kv=False`` afterwards.
+
+    The cache is ``k_cache``/``v_cache`` (fp16 (B, KV_H, S, D)), ``q8_split`` = (k_codes, k_scales,
+    v_codes, v_scales), or ``paged`` = (page_table, kv_pool).  new_k/new_v: fp16 (B, KV_H, D).
+    """
+    b, h, d = q.shape
+    kv_h = new_k.shape[1]
+    if q.dtype != torch.float16 or not q.is_contiguous():
+        raise ValueError("q must be contiguous float16 (B, H, D)")
+    for name, t in (("new_k", new_k), ("new_v", new_v)):
+        if t.dtype != torch.float16 or tuple(t.shape) != (b, kv_h, d) or t.stride(2) != 1:
+            raise ValueError(f"{name} must be float16 {(b, kv_h, d)} with unit inner stride")
+    if new_k.stride() != new_v.stride():
+        new_k, new_v = new_k.contiguous(), new_v.contiguous()
+    pos = _pos_i32(pos.reshape(-1))
+    if k_cache is not None:
+        layout, ptrs, s_max, n_pages = _lib.KV_F16, (k_cache, None, v_cache, None), k_cache.shape[2], 0
+    elif q8_split is not None:
+        layout, ptrs, s_max, n_pages = _lib.KV_Q8_SPLIT, tuple(q8_split), q8_split[0].shape[2], 0
+    elif paged is not None:
+        table, pool = paged
+        layout, ptrs, s_max, n_pages = _lib.KV_Q8_PAGED, (pool, table, None, None), table.shape[1] * 16, pool.shape[0]
+    else:
+        raise ValueError("one cache must be given")
+    ws = attn_workspace(q.device, b, h, d)
+    L = _lib.load()
+    check(L.alloyb_rope_kv_append(layout, q.data_ptr(), new_k.data_ptr(), new_v.data_ptr(), new_k.stride(0),
+                                  new_k.stride(1), *[t.data_ptr() if t is not None else None for t in ptrs],
+                                  pos.data_ptr(), pos.numel(), inv_freq.data_ptr(), b, h, kv_h, d, s_max, n_pages,
+                                  ws.data_ptr(), _stream()), "alloyb_rope_kv_append")
+
+
 def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     y = torch.empty_like(gate)
     L = _lib.load()

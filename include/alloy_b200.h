@@ -132,6 +132,19 @@ int alloyb_gated_linear_normed(const void* x, const void* norm_weight, float eps
                                const void* up_scales, void* y, int M, int N, int K, int format,
                                int act, int dtype, void* stream);
 
+/* RoPE of the decode token's q (fp16, contiguous (B, H, D), rotated in place) and k, plus the
+ * append of the rotated k and of v to the cache at pos, in one launch (the reference runs
+ * rope_apply -- metal/std/rope.py:28-84 -- and the fused cache write of attention_cache[_q8] as
+ * separate steps; results are those of alloyb_rope_inplace followed by the append).  Cache
+ * pointers as in alloyb_attn_decode for the same layout; attention then runs with write_kv = 0.
+ * D must be a multiple of 64.  status (may be NULL): OR of the bits alloyb_attn_workspace_status
+ * reports. */
+int alloyb_rope_kv_append(int layout, void* q, const void* new_k, const void* new_v,
+                          int64_t new_batch_stride, int64_t new_head_stride, void* k0, void* k1,
+                          void* v0, void* v1, const int32_t* pos, int pos_count,
+                          const float* inv_freq, int B, int H, int KV_H, int D, int S_max,
+                          int64_t num_pages, int32_t* status, void* stream);
+
 /* ------------------------------------------------------------------ tensor parallel (new)
  * The reference is single-GPU; these have no counterpart in it.  One process per GPU.  Every
  * rank allocates one exchange buffer (alloyb_tp_buffer_bytes(max_n) bytes, zero-filled by

@@ -267,6 +267,69 @@ def test_attention_paged_q8_full_size_properties():
     assert float(err) < 2e-3, float(err)
 
 
+@pytest.mark.parametrize("layout", ["f16", "q8_split", "paged"])
+def test_rope_kv_append_equals_rope_then_append(layout):
+    """The fused RoPE + append launch leaves q and the cache exactly as rope_inplace followed by the
+    attention op's own append does (bit-identical), and attention with write_kv=False then matches."""
+    rng = np.random.default_rng(len(layout))
+    b, kv_h, group, d, s_max = 3, 2, 4, 128, 256
+    h = kv_h * group
+    lens = [17, 200, 64]
+    q = torch.from_numpy(synth.activations(rng, b * h, d).reshape(b, h, d)).to(DEV)
+    nk = torch.from_numpy(synth.kv_rows(rng, (b, kv_h, d))).to(DEV)
+    nv = torch.from_numpy(synth.kv_rows(rng, (b, kv_h, d))).to(DEV)
+    inv = (1.0 / (500000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(DEV)
+    pos = torch.tensor(lens, dtype=torch.int32, device=DEV)
+
+    def caches():
+        g = torch.Generator(device=DEV).manual_seed(7)
+        if layout == "f16":
+            return [torch.randn((b, kv_h, s_max, d), device=DEV, generator=g).half() for _ in range(2)]
+        if layout == "q8_split":
+            mk = lambda: (torch.randint(-127, 128, (b, kv_h, s_max, d), device=DEV, generator=g, dtype=torch.int8),
+                          torch.rand((b, kv_h, s_max, d // 32), device=DEV, generator=g).mul(0.02).half())
+            (kc, ks), (vc, vs) = mk(), mk()
+            return [kc, ks, vc, vs]
+        store = kv.PagedKVPool(b * (s_max // 16), kv_h, d, b, s_max // 16, DEV)
+        for i in range(b):
+            store.reserve(i, lens[i] + 1)
+        store.pool.copy_(torch.randint(0, 256, store.pool.shape, dtype=torch.uint8, device=DEV, generator=g))
+        blk = store.pool.view(-1, 34)
+        blk[:, 0:2] = torch.full((blk.shape[0],), 0.02, device=DEV).half().view(torch.uint8).view(-1, 2)
+        return [store]
+
+    def attend(qr, kr, c, write):
+        q4, k4, v4 = qr.unsqueeze(2), kr.unsqueeze(2), nv.unsqueeze(2)
+        if layout == "f16":                      # one shared position for the fp16 op: use sequence 0's
+            return torch.ops.alloy.attention_cache(q4, k4, v4, pos[:1], c[0], c[1], -1.0, 0, write)
+        if layout == "q8_split":
+            return torch.ops.alloy.attention_cache_q8(q4, k4, v4, pos[:1], c[0], c[1], c[2], c[3], -1.0, 0, write)
+        return torch.ops.alloy.attention_cache_q8_paged(q4, k4, v4, pos, c[0].page_table, c[0].pool, -1.0, write)
+
+    p_arg = pos if layout == "paged" else pos[:1]
+    # two steps: rope, then the op's own append
+    c1 = caches()
+    q1, k1 = q.clone(), nk.clone()
+    ops.rope_inplace(q1, k1, p_arg, inv)
+    out1 = attend(q1, k1, c1, True)
+    # fused
+    c2 = caches()
+    q2 = q.clone()
+    if layout == "f16":
+        ops.rope_kv_append(q2, nk, nv, p_arg, inv, k_cache=c2[0], v_cache=c2[1])
+    elif layout == "q8_split":
+        ops.rope_kv_append(q2, nk, nv, p_arg, inv, q8_split=tuple(c2))
+    else:
+        ops.rope_kv_append(q2, nk, nv, p_arg, inv, paged=(c2[0].page_table, c2[0].pool))
+    out2 = attend(q2, nk, c2, False)
+    assert torch.equal(q1, q2)
+    a = [t if isinstance(t, torch.Tensor) else t.pool for t in c1]
+    bb = [t if isinstance(t, torch.Tensor) else t.pool for t in c2]
+    for x, y in zip(a, bb):
+        assert torch.equal(x, y)
+    assert torch.equal(out1, out2)
+
+
 def test_paged_append_entry_and_bad_page_is_skipped():
     rng = np.random.default_rng(5)
     b, kv_h, d = 2, 2, 128
