@@ -1,4 +1,5 @@
-// Bandwidth-bound dequant-GEMV / skinny GEMM for decode (M <= 32 tokens per pass).
+// Dequant-GEMV / skinny GEMM for 2..128 tokens (32 per pass) and for the one-token shapes the
+// persistent streaming kernel (linear_stream.cu) does not take (bf16, K not a multiple of 1024).
 //
 // Why tensor cores on a memory-bound op: at HBM speed a B200 streams ~11.5e12
 // Q4_K weights per second but issues only ~1.1e12 warp instructions per second,
