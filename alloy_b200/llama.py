@@ -84,6 +84,7 @@ class QuantLlamaDecoder:
         # partials): what one rank of a TP-N step computes, for profiling under tools that cannot
         # wrap a multi-rank run
         self.exchange = None
+        self.exchange_error = None
         self.tp_dry = bool(tp_dry)
         if tp_dry:
             self.exchange = tp.PeerExchange(shape.hidden)
@@ -225,8 +226,8 @@ class QuantLlamaDecoder:
         h = ops._embedding(self.ids, ops._FORMATS[self.embed_fmt], self.embed, None, out_dtype=self.dtype)
         scale = 1.0 / (s.head_dim ** 0.5)
         for li, lw in enumerate(self.layers):
-            # q/k are Q4_K and v is Q6_K: one launch for the three projections beats the norm fused
-            # into one streaming launch per format (measured), so the norm stays its own kernel here
+            # q/k (Q4_K) and v (Q6_K) run as one streaming launch per format; the norm stays its own
+            # kernel here (folding it into both launches measured slower)
             xn = ops.rms_norm(h, lw.norm_in, s.eps)
             q, k, v = ops.linear_multi(xn, [(lw.fmt["wq"], lw.wq, None), (lw.fmt["wk"], lw.wk, None),
                                             (lw.fmt["wv"], lw.wv, None)])
@@ -269,8 +270,24 @@ class QuantLlamaDecoder:
 
     def capture(self) -> None:
         """Warm up once eagerly, then record the step into a CUDA graph."""
+        if self.tp_size > 1 and not self.tp_dry:
+            # the ranks enter their first exchange together (a rank still building its weights
+            # would let the others' bounded waits run out)
+            torch.cuda.synchronize()
+            torch.distributed.barrier(group=self.pg)
         self._step()
         torch.cuda.synchronize()
+        if self.tp_size > 1 and not self.tp_dry and self.exchange is not None:
+            # did any rank's wait on a peer run out?  Then nobody uses the peer path.
+            from . import _lib
+            bad = torch.tensor([1 if _lib.load().alloyb_device_error(1) != 0 else 0], device=self.device)
+            torch.distributed.all_reduce(bad, op=torch.distributed.ReduceOp.MAX, group=self.pg)
+            if int(bad.item()):
+                self.exchange_error = "a bounded wait on a peer ran out in the first step; using NCCL all-reduces"
+                self.exchange.close()
+                self.exchange = None
+                self._step()
+                torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             self._step()
