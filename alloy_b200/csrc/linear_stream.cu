@@ -413,6 +413,8 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     const uint32_t bar0 = smem_u32(bars + warp * MAX_D);
     const int xs_off = n_warps * D * SLOT + n_groups * 2 * GW * RT * 16 * 4 + n_warps * MAX_D * 8;      // 16-byte aligned
 
+    if (threadIdx.x < (P.gated ? 2 : P.n_seg))        // the TMA unit fetches the descriptors ahead of the first copy
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&maps.m[threadIdx.x])) : "memory");
     if (lane == 0) {
         for (int s = 0; s < D; ++s) mbar_init(bar0 + 8 * s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
