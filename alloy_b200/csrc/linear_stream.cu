@@ -44,8 +44,9 @@ namespace st {
 
 constexpr int WARPS = 16;                    // warps per CTA
 // Warps per group (= K slices per tile) is a kernel template parameter GW: 8 when an SM owns few
-// tiles (the K split is what keeps all its warps busy), 1 when it owns at least two tiles per warp
-// (every warp then runs whole tiles on its own, with no reduction and no barrier at all).
+// tiles (the K split is what keeps all its warps busy; 16 when it owns one or three, so that no
+// group is a tile short; 4 for rows of only 4-7 super-blocks), 1 when it owns at least two tiles
+// per warp (every warp then runs whole tiles on its own, with no reduction and no barrier at all).
 constexpr int MAX_D = 4;                     // ring slots per warp (upper bound)
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr int MAX_SEG = MAX_SEGS;
@@ -791,7 +792,12 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
     // a tile is split over 8 warps (4 when a row has only 4-7 super-blocks)
     static const int force_gw = env_int("ALLOYB_ST_GW", 0);       // tuning aid
     int gw = (all_rows / 16 >= static_cast<int64_t>(2) * WARPS * 148) ? 1 : (nsb >= 8 ? 8 : (nsb >= 4 ? 4 : 0));
-    if ((force_gw == 1 || force_gw == 4 || force_gw == 8) && nsb >= force_gw) gw = force_gw;
+    // an odd, small number of tiles per SM would leave one of the two groups a tile short: all
+    // sixteen warps then share every tile (one super-block wide slices)
+    const int tiles_per_cta = static_cast<int>((all_rows + 16 * 148 - 1) / (16 * 148));
+    if (gw == 8 && !gated && nsb >= 16 && nsb % 16 == 0 && (tiles_per_cta == 1 || tiles_per_cta == 3)) gw = 16;
+    if ((force_gw == 1 || force_gw == 4 || force_gw == 8 || force_gw == 16) && nsb >= force_gw && !(gated && force_gw == 16))
+        gw = force_gw;
     if (gw == 0) return ALLOYB_NOT_TAKEN;
     // two super-blocks per slot only when every warp's slice is a whole number of pairs
     const int kind = fmt == ALLOYB_Q6_K ? Q6 : ((nsb % (2 * gw) == 0) ? Q4x2 : Q4x1);
@@ -845,6 +851,11 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
     }
     for (int i = n_seg; i < MAX_SEG; ++i) maps.m[i] = maps.m[0];
     const bool cache = gw > 1 && nsb == sbs * gw;        // every warp's slice is exactly one slot
+    if (gw == 16) {
+        if (kind == Q6) return cache ? launch<Q6, 1, true, 16>(maps, P, stream) : launch<Q6, 1, false, 16>(maps, P, stream);
+        if (kind == Q4x2) return cache ? launch<Q4x2, 1, true, 16>(maps, P, stream) : launch<Q4x2, 1, false, 16>(maps, P, stream);
+        return cache ? launch<Q4x1, 1, true, 16>(maps, P, stream) : launch<Q4x1, 1, false, 16>(maps, P, stream);
+    }
 #define ALLOYB_ST_LAUNCH(KIND, RT)                                                                              \
     (gw == 1 ? launch<KIND, RT, false, 1>(maps, P, stream)                                                     \
      : gw == 4 ? (cache ? launch<KIND, RT, true, 4>(maps, P, stream) : launch<KIND, RT, false, 4>(maps, P, stream)) \
