@@ -666,12 +666,12 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
         // rank order (identical on all ranks), add the residual, store.
         __syncthreads();
         uint8_t* mine = P.tp.peer[P.tp.rank];
-        if (threadIdx.x == 0) {
-            __threadfence_system();
-            for (int p = 0; p < P.tp.world; ++p) {
-                uint32_t* f = reinterpret_cast<uint32_t*>(P.tp.peer[p] + TP_FLAGS_OFF) + P.tp.rank * 256 + blockIdx.x;
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(tp_next) : "memory");
-            }
+        // one lane per peer (second warp): each release waits for the CTA's stores to that side of
+        // the switch on its own, so the eight round trips overlap instead of queueing behind one lane
+        if (threadIdx.x >= 32 && threadIdx.x < 32 + P.tp.world) {
+            const int p = threadIdx.x - 32;
+            uint32_t* f = reinterpret_cast<uint32_t*>(P.tp.peer[p] + TP_FLAGS_OFF) + P.tp.rank * 256 + blockIdx.x;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(tp_next) : "memory");
         }
         if (threadIdx.x < P.tp.world) {
             const uint32_t* f = reinterpret_cast<const uint32_t*>(mine + TP_FLAGS_OFF) + threadIdx.x * 256 + blockIdx.x;

@@ -135,15 +135,16 @@ class QuantLlamaDecoder:
             self.norm_final = weights.norm_final.tensor
             self.head, self.head_fmt = rows(weights.head.tensor, 0), weights.head.fmt
         else:
-            self.embed = synth.q4k_blocks_device(s.vocab, s.hidden, gen, self.device, d_scale)
+            ctr = {"centered": True}     # zero-mean weights: the residual stream stays inside fp16
+            self.embed = synth.q4k_blocks_device(s.vocab, s.hidden, gen, self.device, d_scale, **ctr)
             for _ in range(s.layers):
                 lw = LayerWeights()
-                lw.wq = rows(synth.q4k_blocks_device(s.heads * s.head_dim, s.hidden, gen, self.device, d_scale), hd_l)
-                lw.wk = rows(synth.q4k_blocks_device(s.kv_heads * s.head_dim, s.hidden, gen, self.device, d_scale), kvd_l)
+                lw.wq = rows(synth.q4k_blocks_device(s.heads * s.head_dim, s.hidden, gen, self.device, d_scale, **ctr), hd_l)
+                lw.wk = rows(synth.q4k_blocks_device(s.kv_heads * s.head_dim, s.hidden, gen, self.device, d_scale, **ctr), kvd_l)
                 lw.wv = rows(synth.q6k_blocks_device(s.kv_heads * s.head_dim, s.hidden, gen, self.device, d_scale), kvd_l)
-                lw.wo = tp.shard_cols(synth.q4k_blocks_device(s.hidden, s.heads * s.head_dim, gen, self.device, d_scale), "q4_k", r, n)
-                lw.wg = rows(synth.q4k_blocks_device(s.ffn, s.hidden, gen, self.device, d_scale), self.ffn_l)
-                lw.wu = rows(synth.q4k_blocks_device(s.ffn, s.hidden, gen, self.device, d_scale), self.ffn_l)
+                lw.wo = tp.shard_cols(synth.q4k_blocks_device(s.hidden, s.heads * s.head_dim, gen, self.device, d_scale, **ctr), "q4_k", r, n)
+                lw.wg = rows(synth.q4k_blocks_device(s.ffn, s.hidden, gen, self.device, d_scale, **ctr), self.ffn_l)
+                lw.wu = rows(synth.q4k_blocks_device(s.ffn, s.hidden, gen, self.device, d_scale, **ctr), self.ffn_l)
                 lw.wd = tp.shard_cols(synth.q6k_blocks_device(s.hidden, s.ffn, gen, self.device, d_scale), "q6_k", r, n)
                 lw.norm_in = self._norm_weight(gen)
                 lw.norm_post = self._norm_weight(gen)

@@ -97,13 +97,25 @@ def _uniform_f16_bytes(shape, gen: torch.Generator, device, d_scale: float = 1.0
 
 
 def q4k_blocks_device(n: int, k: int, gen: torch.Generator, device="cuda",
-                      d_scale: float = 1.0) -> torch.Tensor:
-    """Device-side Q4_K blocks with the benchmark distribution (d, dmin times ``d_scale``)."""
+                      d_scale: float = 1.0, centered: bool = False) -> torch.Tensor:
+    """Device-side Q4_K blocks with the benchmark distribution (d, dmin times ``d_scale``).
+
+    ``centered``: every sub-block gets min == scale and the block dmin = 7.5 d, so that a weight is
+    d * sc * (q - 7.5): zero-mean like a quantised model's weights (a stack of random layers then
+    keeps its residual stream inside fp16).  Uncentered blocks have a large positive mean.
+    """
     nb = _check_k(k)
     blk = torch.randint(0, 256, (n, nb, Q4K_BLOCK_BYTES), dtype=torch.uint8, device=device,
                         generator=gen)
-    blk[:, :, 0:2] = _uniform_f16_bytes((n, nb), gen, device, d_scale).view(n, nb, 2)
-    blk[:, :, 2:4] = _uniform_f16_bytes((n, nb), gen, device, d_scale).view(n, nb, 2)
+    d = _uniform_f16_bytes((n, nb), gen, device, d_scale)
+    blk[:, :, 0:2] = d.view(n, nb, 2)
+    if centered:
+        blk[:, :, 2:4] = (d.view(torch.float16).float() * 7.5).to(torch.float16).view(torch.uint8).view(n, nb, 2)
+        blk[:, :, 8:12] = blk[:, :, 4:8]                      # mins 0-3 (and the high bits of 4-7) = scales
+        lo = blk[:, :, 12:16] & 0x0F
+        blk[:, :, 12:16] = lo | (lo << 4)                     # low bits of mins 4-7 = those of scales 4-7
+    else:
+        blk[:, :, 2:4] = _uniform_f16_bytes((n, nb), gen, device, d_scale).view(n, nb, 2)
     return blk.view(n, nb * Q4K_BLOCK_BYTES)
 
 
