@@ -68,7 +68,7 @@ class QuantLlamaDecoder:
 
     def __init__(self, shape: LlamaShape, batch: int, context: int, *, device="cuda", seed: int = 0,
                  kv: str = "f16", tp_rank: int = 0, tp_size: int = 1, process_group=None,
-                 dtype: torch.dtype = torch.float16, d_scale: float = 1.0, peer_allreduce: bool = True,
+                 dtype: torch.dtype = torch.float16, d_scale: float = 1.0, centered: bool = False, peer_allreduce: bool = True,
                  tp_dry: bool = False, weights=None) -> None:
         if kv not in ("f16", "q8_paged"):
             raise ValueError(f"kv must be 'f16' or 'q8_paged', got {kv!r}")
@@ -135,7 +135,7 @@ class QuantLlamaDecoder:
             self.norm_final = weights.norm_final.tensor
             self.head, self.head_fmt = rows(weights.head.tensor, 0), weights.head.fmt
         else:
-            ctr = {"centered": True}     # zero-mean weights: the residual stream stays inside fp16
+            ctr = {"centered": centered}   # zero-mean Q4_K weights keep a deep random stack inside fp16
             self.embed = synth.q4k_blocks_device(s.vocab, s.hidden, gen, self.device, d_scale, **ctr)
             for _ in range(s.layers):
                 lw = LayerWeights()

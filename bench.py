@@ -242,7 +242,7 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
         # range): the residual stream of 32 to 80 random layers stays inside fp16, the logits finite
         d = llama.QuantLlamaDecoder(shape, batch, wl["context"], device=dev, seed=0, kv=wl["kv"],
                                     tp_rank=rank, tp_size=dry or world, process_group=pg, tp_dry=bool(dry),
-                                    d_scale=WEIGHT_D_SCALE)
+                                    d_scale=WEIGHT_D_SCALE, centered=True)
         torch.cuda.synchronize()
         note("weights ready; capturing")
         d.capture()
@@ -290,6 +290,17 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
         note(f"timed: {ms / args.steps:.3f} ms/step")
         e2e_ms, h2d, d2h = timed_e2e(dec, args.steps, args.warmup)
         note("e2e timed")
+        # a short run can end before nvidia-smi has printed once: keep the same step running (untimed,
+        # the same count on every rank) until rank 0's sampler holds a reading taken under load
+        for _ in range(40):
+            done = torch.tensor([1 if (clocks.rows or clocks.proc is None) else 0], device=dev)
+            if world > 1:
+                torch.distributed.broadcast(done, 0)
+            if int(done.item()):
+                break
+            for _ in range(20):
+                dec.step()
+            torch.cuda.synchronize()
     value = args.batch * args.steps / (ms * 1e-3)
     e2e_val = args.batch * args.steps / (e2e_ms * 1e-3)
     w_bytes = shape.weight_bytes()
@@ -300,7 +311,7 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
         # the same step with the all-reduce inside the GEMV launches (peer memory) and with NCCL
         note("tp check: building the twins")
         mk = lambda peer: llama.QuantLlamaDecoder(shape, args.batch, wl["context"], device=dev, seed=0, kv=wl["kv"],
-                                                  tp_rank=rank, tp_size=world, process_group=pg, d_scale=WEIGHT_D_SCALE,
+                                                  tp_rank=rank, tp_size=world, process_group=pg, d_scale=WEIGHT_D_SCALE, centered=True,
                                                   peer_allreduce=peer)
         fused, twin = mk(True), mk(False)
         for d in (fused, twin):
@@ -364,8 +375,12 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
                           "peak_gbs": peak, "peak_kind": peak_kind},
     }
     if roof is not None:
+        # the committed ncu capture is of the 8B shape's launch: quoted only where this run's launch is that one
+        traffic = _ncu_traffic("gated_q4k")
+        if traffic is not None and abs(traffic / roof["bytes_per_launch"] - 1.0) > 0.1:
+            traffic = None
         line["roofline"] = {"bound": "hbm", "achieved": roof["gbs"], "peak": peak, "unit": "GB/s",
-                            "frac": roof["gbs"] / peak, "traffic": _ncu_traffic("gated_q4k"),
+                            "frac": roof["gbs"] / peak, "traffic": traffic,
                             "kernel": roof["kernel"], "bytes_per_launch": roof["bytes_per_launch"],
                             "us_per_launch": roof["us_per_launch"], "peak_kind": peak_kind}
     if tp_check is not None:
