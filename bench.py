@@ -310,22 +310,33 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
     if world > 1 and args.check_tp:
         # the same step with the all-reduce inside the GEMV launches (peer memory) and with NCCL
         note("tp check: building the twins")
-        mk = lambda peer: llama.QuantLlamaDecoder(shape, args.batch, wl["context"], device=dev, seed=0, kv=wl["kv"],
-                                                  tp_rank=rank, tp_size=world, process_group=pg, d_scale=WEIGHT_D_SCALE, centered=True,
-                                                  peer_allreduce=peer)
+        # fp16 KV here: its random contents are a slice of the unsharded cache's, so that the same
+        # step of the whole model on this one GPU (fp32 sums over the full K) can referee the two
+        mk = lambda peer, size=world: llama.QuantLlamaDecoder(
+            shape, args.batch, wl["context"], device=dev, seed=0, kv="f16", tp_rank=rank if size > 1 else 0,
+            tp_size=size, process_group=pg if size > 1 else None, d_scale=WEIGHT_D_SCALE, centered=True,
+            peer_allreduce=peer)
         fused, twin = mk(True), mk(False)
         for d in (fused, twin):
             d.ids.fill_(11)
-        a = fused.step_eager_logits()
-        b = twin.step_eager_logits()
-        diff = (a.float() - b.float()).abs().max()
-        rms = b.float().pow(2).mean().sqrt()
-        both = torch.stack([diff, rms])
-        torch.distributed.all_reduce(both, op=torch.distributed.ReduceOp.MAX)
-        tp_check = {"max_abs_diff_over_rms_vs_nccl": float((both[0] / both[1]).item()),
-                    "fused_calls_per_step": fused.fused_allreduce_calls, "finite": bool(torch.isfinite(a.float()).all().item())}
+        a = fused.step_eager_logits().float().clone()
+        b = twin.step_eager_logits().float().clone()
+        calls = fused.fused_allreduce_calls
         torch.cuda.synchronize()
         del fused, twin
+        torch.cuda.empty_cache()
+        whole = mk(False, 1)
+        whole.ids.fill_(11)
+        c = whole.step_eager_logits().float().clone()
+        rms = c.pow(2).mean().sqrt()
+        both = torch.stack([(a - b).abs().max() / rms, (a - c).abs().max() / rms, (b - c).abs().max() / rms])
+        torch.distributed.all_reduce(both, op=torch.distributed.ReduceOp.MAX)
+        tp_check = {"max_abs_diff_over_rms": {"fused_vs_nccl": float(both[0].item()),
+                                              "fused_vs_one_gpu": float(both[1].item()),
+                                              "nccl_vs_one_gpu": float(both[2].item())},
+                    "fused_calls_per_step": calls, "finite": bool(torch.isfinite(a).all().item())}
+        torch.cuda.synchronize()
+        del whole
         torch.cuda.empty_cache()
     launches_step = dec.launches_per_step + shape.layers + 1   # + KV append per layer + id copy
     finite = bool(torch.isfinite(dec.logits.float()).all().item())
