@@ -43,6 +43,7 @@ class TP(C.Structure):
         ("world", C.c_int),
         ("rank", C.c_int),
         ("max_n", C.c_int),
+        ("spin_limit", C.c_int),
         ("peer", C.c_void_p * 8),
     ]
 
@@ -85,6 +86,14 @@ SIGNATURES = {
                                 _p, _i, _i, _i, _i, _i, _i64, _f, _i, _p, _sz, _p]),
     "alloyb_attn_decode_static": (_i, [_i, _p, _i64, _i64, _i, _p, _p, _p, _p, _p, _p, _i64, _i64, _p, _i,
                                        _p, _i, _i, _i, _i, _i, _i64, _f, _i, _p]),
+    "alloyb_attn_static_status": (_i, [C.POINTER(C.c_int32), _p]),
+    "alloyb_dequant_q5_0": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i, _i, _p]),
+    "alloyb_q5_0_mm": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p]),
+    "alloyb_kv_write": (_i, [_i, _p, _p, _i64, _i64, _i64, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i64, _i, _p, _p]),
+    "alloyb_attn_chunk": (_i, [_i, _p, _i64, _i64, _i64, _i, _p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i,
+                               _i64, _f, _p, _p]),
+    "alloyb_moe_workspace_bytes": (_sz, [_i, _i, _i]),
+    "alloyb_moe_routed": (_i, [_p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _sz, _p]),
     "alloyb_rms_norm": (_i, [_p, _p, _p, _i, _i, _f, _i, _p]),
     "alloyb_rope_inplace": (_i, [_p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _p]),
     "alloyb_silu_mul": (_i, [_p, _p, _p, _i64, _i, _p]),

@@ -367,13 +367,12 @@ extern "C" size_t alloyb_attn_workspace_bytes(int B, int H, int D) {
            align_up(bh * ATTN_MAX_SPLITS * D * sizeof(float), 256);
 }
 
-extern "C" int alloyb_attn_decode(int layout, const void* q, int64_t q_batch_stride,
-                                  int64_t q_head_stride, int q_dtype, void* k0, void* k1, void* v0,
-                                  void* v1, const void* new_k, const void* new_v,
-                                  int64_t new_batch_stride, int64_t new_head_stride,
-                                  const int32_t* pos, int pos_count, void* out, int B, int H, int KV_H,
-                                  int D, int S_max, int64_t num_pages, float scale, int write_kv,
-                                  void* workspace, size_t workspace_bytes, void* stream) {
+// Argument checks shared by the two decode entries (nothing is launched or written before they pass).
+static int attn_decode_validate(int layout, const void* q, int q_dtype, const void* k0, const void* k1,
+                                const void* v0, const void* v1, const void* new_k, const void* new_v,
+                                const int32_t* pos, int pos_count, const void* out, int B, int H, int KV_H,
+                                int D, int S_max, int64_t num_pages, int write_kv, const void* workspace,
+                                size_t workspace_bytes) {
     if (!q || !k0 || !pos || !out || !workspace) return ALLOYB_E_NULL;
     if (B <= 0 || H <= 0 || KV_H <= 0 || H % KV_H || D <= 0 || D % 32 || S_max <= 0)
         return ALLOYB_E_SHAPE;
@@ -388,6 +387,19 @@ extern "C" int alloyb_attn_decode(int layout, const void* q, int64_t q_batch_str
     if (write_kv && (!new_k || !new_v)) return ALLOYB_E_NULL;
     if (reinterpret_cast<uintptr_t>(workspace) % 256) return ALLOYB_E_ALIGN;
     if (workspace_bytes < alloyb_attn_workspace_bytes(B, H, D)) return ALLOYB_E_WORKSPACE;
+    return ALLOYB_OK;
+}
+
+extern "C" int alloyb_attn_decode(int layout, const void* q, int64_t q_batch_stride,
+                                  int64_t q_head_stride, int q_dtype, void* k0, void* k1, void* v0,
+                                  void* v1, const void* new_k, const void* new_v,
+                                  int64_t new_batch_stride, int64_t new_head_stride,
+                                  const int32_t* pos, int pos_count, void* out, int B, int H, int KV_H,
+                                  int D, int S_max, int64_t num_pages, float scale, int write_kv,
+                                  void* workspace, size_t workspace_bytes, void* stream) {
+    const int vrc = attn_decode_validate(layout, q, q_dtype, k0, k1, v0, v1, new_k, new_v, pos, pos_count, out, B, H,
+                                         KV_H, D, S_max, num_pages, write_kv, workspace, workspace_bytes);
+    if (vrc != ALLOYB_OK) return vrc;
     cudaStream_t st = as_stream(stream);
 
     AttnParams P;
@@ -517,6 +529,10 @@ extern "C" int alloyb_attn_decode_static(int layout, const void* q, int64_t q_ba
         g_attn_static_ptr[dev] = p;
     }
     void* ws = g_attn_static_ptr[dev];
+    // every argument is checked before the shared array is touched
+    const int vrc = attn_decode_validate(layout, q, q_dtype, k0, k1, v0, v1, new_k, new_v, pos, pos_count, out, B, H,
+                                         KV_H, D, S_max, num_pages, write_kv, ws, ALLOYB_ATTN_STATIC_BYTES);
+    if (vrc != ALLOYB_OK) return vrc;
     // status word + completion counters start every call at zero
     const size_t head = 256 + static_cast<size_t>(B) * H * sizeof(unsigned int);
     e = cudaMemsetAsync(ws, 0, head, as_stream(stream));
@@ -524,4 +540,16 @@ extern "C" int alloyb_attn_decode_static(int layout, const void* q, int64_t q_ba
     return alloyb_attn_decode(layout, q, q_batch_stride, q_head_stride, q_dtype, k0, k1, v0, v1, new_k,
                               new_v, new_batch_stride, new_head_stride, pos, pos_count, out, B, H, KV_H,
                               D, S_max, num_pages, scale, write_kv, ws, ALLOYB_ATTN_STATIC_BYTES, stream);
+}
+
+// Status word of the most recent alloyb_attn_decode_static call on the current device (the same
+// bits alloyb_attn_workspace_status reports; every static call starts it at zero).  Synchronises
+// the stream.  ALLOYB_E_SHAPE before the first static call on this device.
+extern "C" int alloyb_attn_static_status(int32_t* status_out, void* stream) {
+    if (!status_out) return ALLOYB_E_NULL;
+    int dev = -1;
+    const cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
+    if (dev < 0 || dev >= MAX_DEVICES || g_attn_static_ptr[dev] == nullptr) return ALLOYB_E_SHAPE;
+    return alloyb_attn_workspace_status(g_attn_static_ptr[dev], status_out, stream);
 }

@@ -480,13 +480,15 @@ int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, cu
     P.K = K;
     P.is_bf16 = dtype == ALLOYB_BF16;
 
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {};          // per device ordinal
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
-        configured = true;
+        configured[dev] = true;
     }
     const dim3 grid((seg.N + BN - 1) / BN, (M + BM - 1) / BM);
     if (dtype == ALLOYB_BF16) gemm_tc_kernel<true><<<grid, THREADS, SMEM_BYTES, st>>>(map, P);

@@ -180,6 +180,63 @@ __global__ void rope_kv_append_kernel(__half* __restrict__ q, const __half* __re
     store_kv_block<LAYOUT>(kv, 1, b, h, p, blk, lane, new_v[b * sb + h * sh + blk * 32 + lane], KV_H, D, status);
 }
 
+// n_tokens new rows per (sequence, kv head) into the cache at [start_b, start_b + n_tokens), any
+// layout (the prefill / verify write; the q8 layouts quantise the rows exactly as the append does):
+// one warp per (b, h, token, K|V, 32-element block).
+template <int LAYOUT>
+__global__ void kv_write_range_kernel(const __half* __restrict__ new_k, const __half* __restrict__ new_v, int64_t sb,
+                                      int64_t sh, int64_t stok, KVPtrs kv, const int32_t* __restrict__ start,
+                                      int start_count, int B, int KV_H, int D, int n_tokens, int* __restrict__ status) {
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int nblk = D / 32;
+    const int64_t warps_total = static_cast<int64_t>(B) * KV_H * n_tokens * nblk * 2;
+    const int64_t wid = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+    if (wid >= warps_total) return;
+    pdl_wait();
+    int64_t r = wid;
+    const int which = static_cast<int>(r & 1); r >>= 1;
+    const int blk = static_cast<int>(r % nblk); r /= nblk;
+    const int t = static_cast<int>(r % n_tokens); r /= n_tokens;
+    const int h = static_cast<int>(r % KV_H); r /= KV_H;
+    const int b = static_cast<int>(r);
+    const int p = start[start_count == 1 ? 0 : b] + t;
+    if (p < 0 || p >= kv.S_max) {
+        if (lane == 0 && status) atomicOr(status, KV_STATUS_POS_RANGE);
+        return;
+    }
+    const __half xin = (which ? new_v : new_k)[b * sb + h * sh + t * stok + blk * 32 + lane];
+    store_kv_block<LAYOUT>(kv, which, b, h, p, blk, lane, xin, KV_H, D, status);
+}
+
+int launch_kv_write_range(int layout, const void* new_k, const void* new_v, int64_t sb, int64_t sh, int64_t stok,
+                          const KVPtrs& kv, const int32_t* start, int start_count, int B, int KV_H, int D,
+                          int n_tokens, int* status, cudaStream_t st) {
+    const __half* nk = static_cast<const __half*>(new_k);
+    const __half* nv = static_cast<const __half*>(new_v);
+    const int64_t warps = static_cast<int64_t>(B) * KV_H * n_tokens * (D / 32) * 2;
+    const int64_t blocks64 = (warps * 32 + 255) / 256;
+    if (blocks64 > 0x7fffffff) return ALLOYB_E_SHAPE;
+    const int blocks = static_cast<int>(blocks64);
+    switch (layout) {
+        case ALLOYB_KV_F16:
+            launch_pdl(kv_write_range_kernel<ALLOYB_KV_F16>, dim3(blocks), dim3(256), 0, st, nk, nv, sb, sh, stok, kv,
+                       start, start_count, B, KV_H, D, n_tokens, status);
+            break;
+        case ALLOYB_KV_Q8_SPLIT:
+            launch_pdl(kv_write_range_kernel<ALLOYB_KV_Q8_SPLIT>, dim3(blocks), dim3(256), 0, st, nk, nv, sb, sh, stok,
+                       kv, start, start_count, B, KV_H, D, n_tokens, status);
+            break;
+        case ALLOYB_KV_Q8_PAGED:
+            launch_pdl(kv_write_range_kernel<ALLOYB_KV_Q8_PAGED>, dim3(blocks), dim3(256), 0, st, nk, nv, sb, sh, stok,
+                       kv, start, start_count, B, KV_H, D, n_tokens, status);
+            break;
+        default:
+            return ALLOYB_E_SHAPE;
+    }
+    return check_launch();
+}
+
 int launch_kv_append(int layout, const void* new_k, const void* new_v, int64_t sb, int64_t sh,
                      const KVPtrs& kv, const int32_t* pos, int pos_count, int B, int KV_H, int D,
                      int* status, cudaStream_t st) {

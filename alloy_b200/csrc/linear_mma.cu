@@ -24,7 +24,6 @@
 // the previous kernel, so they are issued BEFORE griddepcontrol.wait: with
 // programmatic dependent launch the next layer's weights are already in flight
 // while the previous kernel drains.
-#include <cstdlib>
 #include <type_traits>
 
 #include "kv.cuh"
@@ -66,7 +65,6 @@ struct MmaParams {
     const void* residual;
     int gated;            // 1: seg[0] = gate, seg[1] = up, y = act(gate) * up into seg[0].y
     int act;
-    int magic_f16;        // 1: fp16 quants as (1024+q)-1024 instead of fp16 subnormals
     int stage_bytes;
     int n_stages;         // ring depth actually used (<= MMA_STAGES)
 };
@@ -592,7 +590,7 @@ __global__ void __launch_bounds__(MMA_THREADS) linear_mma_kernel(const MmaParams
             if (fmt == ALLOYB_Q4_K) {
                 if constexpr (SB)
                     q4k_superblock_sb<RT>(stage, sb, x, kbase, acc);
-                else if (P.magic_f16 || sizeof(XT) != 2 || !std::is_same<XT, __half>::value)
+                else if (!std::is_same<XT, __half>::value)
                     q4k_superblock<XT, RT, NT, false>(stage, sb, tbl, x, P.M, P.K, kbase, acc);
                 else
                     q4k_superblock<XT, RT, NT, true>(stage, sb, tbl, x, P.M, P.K, kbase, acc);
@@ -668,27 +666,16 @@ __global__ void __launch_bounds__(MMA_THREADS) linear_mma_kernel(const MmaParams
 
 // ------------------------------------------------------------------------------- host
 
-static int magic_f16_flag() {
-    static const int flag = [] {
-        const char* e = std::getenv("ALLOYB_F16_MAGIC");
-        return (e && e[0] == '1') ? 1 : 0;
-    }();
-    return flag;
-}
-
-static bool no_stream_flag() {
-    static const bool flag = [] { const char* e = std::getenv("ALLOYB_NO_STREAM"); return e && e[0] == '1'; }();
-    return flag;
-}
-
 template <typename XT, int RT, int NT, bool SB = false>
 static int launch_mma(const MmaParams& P, int grid, int smem_bytes, cudaStream_t st) {
-    static bool configured = false;   // per template instance
+    static bool configured[64] = {};   // per template instance and device ordinal
     auto kern = linear_mma_kernel<XT, RT, NT, SB>;
-    if (!configured) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
-        configured = true;
+        configured[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
@@ -716,8 +703,7 @@ static int launch_mma_nt(MmaParams& P, int grid, int stage_rows_bytes, cudaStrea
     P.n_stages = stages;
     const int smem = fixed + stages * stage_rows_bytes;
     if constexpr (std::is_same<XT, __half>::value) {
-        static const bool no_sb = [] { const char* e = std::getenv("ALLOYB_NO_SB"); return e && e[0] == '1'; }();
-        if (P.M == 1 && !P.magic_f16 && !no_sb) return launch_mma<XT, RT, 1, true>(P, grid, smem, st);
+        if (P.M == 1) return launch_mma<XT, RT, 1, true>(P, grid, smem, st);
     }
     switch (NTt) {
         case 1: return launch_mma<XT, RT, 1>(P, grid, smem, st);
@@ -743,7 +729,7 @@ int try_linear_fast(const void* x, int M, int K, int dtype, const WeightSeg* seg
     if (dtype != ALLOYB_F16 && dtype != ALLOYB_BF16) return ALLOYB_NOT_TAKEN;
     if (reinterpret_cast<uintptr_t>(x) % 16 || K % 8) return ALLOYB_NOT_TAKEN;
     if (M > 128) return ALLOYB_NOT_TAKEN;
-    if (!no_stream_flag()) {
+    {
         const int rc = try_gemv_stream_mixed(x, M, K, dtype, seg, n_seg, residual, nullptr, 0.f, st);
         if (rc != ALLOYB_NOT_TAKEN) return rc;
     }
@@ -761,7 +747,6 @@ int try_linear_fast(const void* x, int M, int K, int dtype, const WeightSeg* seg
         P.K = K;
         P.n_seg = n_seg;
         P.gated = 0;
-        P.magic_f16 = magic_f16_flag();
         P.stage_bytes = stage_bytes;
         int tiles = 0;
         for (int i = 0; i < n_seg; ++i) {
@@ -797,7 +782,7 @@ int try_gated_fast(const void* x, const void* gate, const void* gate_scales, con
     WeightSeg us = gs;
     us.data = up;
     if (!seg_ok(gs, K) || !seg_ok(us, K)) return ALLOYB_NOT_TAKEN;
-    if (!no_stream_flag()) {
+    {
         const WeightSeg pair[2] = {gs, us};
         const int rc = try_gemv_stream(x, M, K, dtype, pair, 2, true, act, nullptr, nullptr, 0.f, st, nullptr);
         if (rc != ALLOYB_NOT_TAKEN) return rc;
@@ -812,7 +797,6 @@ int try_gated_fast(const void* x, const void* gate, const void* gate_scales, con
         P.n_seg = 2;
         P.gated = 1;
         P.act = act;
-        P.magic_f16 = magic_f16_flag();
         P.stage_bytes = stage_bytes;
         for (int i = 0; i < 2; ++i) {
             MmaSeg& d = P.seg[i];

@@ -33,7 +33,6 @@
 // shared memory); 16 threads apply the activation / residual and store.
 #include <cuda.h>
 
-#include <cstdlib>
 #include <type_traits>
 
 #include "linear.cuh"
@@ -50,6 +49,7 @@ constexpr int WARPS = 16;                    // warps per CTA
 constexpr int MAX_D = 4;                     // ring slots per warp (upper bound)
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr int MAX_SEG = MAX_SEGS;
+constexpr int MAX_DEVICES = 64;
 
 // Slot geometries.  A slot holds 16 rows of one stage; its row pitch is chosen so that the lanes'
 // shared-memory reads fall on 32 different banks.
@@ -75,6 +75,7 @@ __device__ int g_error = 0;                  // sticky: a bounded wait ran out
 //   +8448  float  slots[2 sets][8 ranks][max_n]: the partial outputs, set = epoch parity
 struct TpArgs {
     int world, rank, max_n;
+    uint32_t spin;                           // polls of a peer's flag before the wait gives up
     uint8_t* peer[8];
 };
 constexpr int TP_FLAGS_OFF = 256, TP_SLOTS_OFF = 8448;
@@ -676,12 +677,12 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
         if (threadIdx.x < P.tp.world) {
             const uint32_t* f = reinterpret_cast<const uint32_t*>(mine + TP_FLAGS_OFF) + threadIdx.x * 256 + blockIdx.x;
             uint32_t v = 0, i = 0;
-            for (; i < SPIN_LIMIT; ++i) {
+            for (; i < P.tp.spin; ++i) {
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
                 if (static_cast<int32_t>(v - tp_next) >= 0) break;
                 if (i > 64) __nanosleep(64);
             }
-            if (i == SPIN_LIMIT) atomicExch(&g_error, 1);
+            if (i == P.tp.spin) atomicExch(&g_error, 1);
         }
         __syncthreads();
         const float* slots = reinterpret_cast<const float*>(mine + TP_SLOTS_OFF) +
@@ -714,19 +715,23 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
 
 template <int KIND, int RT, bool CACHE, int GW, bool GU = false>
 static int launch(const Maps& maps, const Params& P, cudaStream_t stream) {
-    static bool configured = false;
+    // the opt-in to large dynamic shared memory and the SM count belong to a device, not to the process
+    static bool configured[MAX_DEVICES] = {};
+    static int sm_count[MAX_DEVICES] = {};
     auto kern = gemv_stream_kernel<KIND, RT, CACHE, GW, GU>;
-    if (!configured) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) dev = 0;
+    if (!configured[dev]) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
-        configured = true;
+        configured[dev] = true;
     }
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    if (!sm_count[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        sm_count[dev] = n;
     }
+    const int sms = sm_count[dev];
     constexpr int n_warps = WARPS, n_groups = WARPS / GW;
     const int smem = n_warps * P.depth * 16 * Geom<KIND>::PITCH + n_groups * 2 * GW * RT * 16 * 4 + n_warps * MAX_D * 8 +
                      (P.norm_w ? P.nsb * QK_K * 2 + WARPS * 4 : 0);
@@ -766,11 +771,6 @@ static EncodeFn encoder() {
 
 }  // namespace st
 
-static int env_int(const char* name, int dflt) {
-    const char* e = std::getenv(name);
-    return e ? std::atoi(e) : dflt;
-}
-
 // One fp16 token against Q4_K or Q6_K matrices of one format (plain: up to MAX_SEGS row-stacked
 // outputs; gated: Q4_K gate/up pair with the activation fused).  NOT_TAKEN for anything else.
 int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg, int n_seg, bool gated, int act,
@@ -780,7 +780,11 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
                seg[0].N > tp->max_n))
         return ALLOYB_NOT_TAKEN;
     if (M != 1 || dtype != ALLOYB_F16 || K % QK_K || n_seg < 1 || n_seg > MAX_SEG) return ALLOYB_NOT_TAKEN;
-    if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(norm_w) % 16) return ALLOYB_NOT_TAKEN;
+    // With an exchange attached every rank must take the same path: "not taken" is kept for what all
+    // ranks see alike (shape, format); a pointer or pitch only this rank has wrong is a hard error,
+    // so that no rank falls back to another all-reduce on its own while its peers wait here.
+    const int misaligned = tp ? ALLOYB_E_ALIGN : ALLOYB_NOT_TAKEN;
+    if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(norm_w) % 16) return misaligned;
     if (norm_w && K > 16384) return ALLOYB_NOT_TAKEN;             // the normalised token lives in shared memory
     const int nsb = K / QK_K;
     if (gated && (n_seg != 2 || seg[0].N != seg[1].N)) return ALLOYB_NOT_TAKEN;
@@ -790,14 +794,11 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
     for (int i = 0; i < (gated ? 1 : n_seg); ++i) all_rows += seg[i].N;
     // whole tiles per warp once every SM owns at least two tiles per warp, else the K dimension of
     // a tile is split over 8 warps (4 when a row has only 4-7 super-blocks)
-    static const int force_gw = env_int("ALLOYB_ST_GW", 0);       // tuning aid
     int gw = (all_rows / 16 >= static_cast<int64_t>(2) * WARPS * 148) ? 1 : (nsb >= 8 ? 8 : (nsb >= 4 ? 4 : 0));
     // an odd, small number of tiles per SM would leave one of the two groups a tile short: all
     // sixteen warps then share every tile (one super-block wide slices)
     const int tiles_per_cta = static_cast<int>((all_rows + 16 * 148 - 1) / (16 * 148));
     if (gw == 8 && !gated && nsb >= 16 && nsb % 16 == 0 && (tiles_per_cta == 1 || tiles_per_cta == 3)) gw = 16;
-    if ((force_gw == 1 || force_gw == 4 || force_gw == 8 || force_gw == 16) && nsb >= force_gw && !(gated && force_gw == 16))
-        gw = force_gw;
     if (gw == 0) return ALLOYB_NOT_TAKEN;
     // two super-blocks per slot only when every warp's slice is a whole number of pairs
     const int kind = fmt == ALLOYB_Q6_K ? Q6 : ((nsb % (2 * gw) == 0) ? Q4x2 : Q4x1);
@@ -814,18 +815,18 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
         P.tp.world = tp->world;
         P.tp.rank = tp->rank;
         P.tp.max_n = tp->max_n;
+        P.tp.spin = tp->spin_limit > 0 ? static_cast<uint32_t>(tp->spin_limit) : SPIN_LIMIT;
         for (int r = 0; r < tp->world; ++r) P.tp.peer[r] = static_cast<uint8_t*>(tp->peer[r]);
     }
     P.n_seg = gated ? 1 : n_seg;
     P.nsb = nsb;
     P.gated = gated ? 1 : 0;
     P.act = act;
-    static const int depth = env_int("ALLOYB_ST_DEPTH", 0);     // tuning aid: ring slots per warp
-    P.depth = depth > 0 ? (depth > MAX_D ? MAX_D : depth) : (kind == Q4x1 ? 3 : 2);
+    P.depth = kind == Q4x1 ? 3 : 2;                               // ring slots per warp (measured best)
     int64_t rows = 0;
     for (int i = 0; i < n_seg; ++i) {
         if (seg[i].format != fmt || seg[i].N <= 0) return ALLOYB_NOT_TAKEN;
-        if (reinterpret_cast<uintptr_t>(seg[i].data) % 16 || seg[i].row_bytes % 16) return ALLOYB_NOT_TAKEN;
+        if (reinterpret_cast<uintptr_t>(seg[i].data) % 16 || seg[i].row_bytes % 16) return misaligned;
         if (seg[i].row_bytes < static_cast<int64_t>(nsb) * blk) return ALLOYB_NOT_TAKEN;
         P.seg[i].data = static_cast<const uint8_t*>(seg[i].data);
         P.seg[i].row_bytes = seg[i].row_bytes;
@@ -863,12 +864,9 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
     if (kind == Q6) return ALLOYB_ST_LAUNCH(Q6, 1);
     if (gated && gw == 8) {
         // the two matrices go to the two groups of eight warps
-        static const bool no_gu = env_int("ALLOYB_ST_NO_GU", 0) != 0;       // tuning aid
-        if (!no_gu) {
-            if (kind == Q4x2)
-                return cache ? launch<Q4x2, 1, true, 8, true>(maps, P, stream) : launch<Q4x2, 1, false, 8, true>(maps, P, stream);
-            return cache ? launch<Q4x1, 1, true, 8, true>(maps, P, stream) : launch<Q4x1, 1, false, 8, true>(maps, P, stream);
-        }
+        if (kind == Q4x2)
+            return cache ? launch<Q4x2, 1, true, 8, true>(maps, P, stream) : launch<Q4x2, 1, false, 8, true>(maps, P, stream);
+        return cache ? launch<Q4x1, 1, true, 8, true>(maps, P, stream) : launch<Q4x1, 1, false, 8, true>(maps, P, stream);
     }
     if (gated) return kind == Q4x2 ? ALLOYB_ST_LAUNCH(Q4x2, 2) : ALLOYB_ST_LAUNCH(Q4x1, 2);
     return kind == Q4x2 ? ALLOYB_ST_LAUNCH(Q4x2, 1) : ALLOYB_ST_LAUNCH(Q4x1, 1);

@@ -1,7 +1,8 @@
 """KV-cache formats and stores.
 
-``KVFormat`` / ``Q8_0`` / ``resolve_kv_format`` follow the reference's
-``packages/alloy-server/src/alloy_server/kv_format.py:14-63``; ``alloc_quantized_kv``
+``KVFormat`` / ``Q8_0`` / ``KV_FORMATS`` / ``resolve_kv_format`` are adapted from the reference's
+``packages/alloy-server/src/alloy_server/kv_format.py:14-63`` (a format descriptor whose field
+names, values and error text are the contract its callers rely on); ``alloc_quantized_kv``
 allocates the split codes+scales tensors of
 ``packages/alloy-server/src/alloy_server/cache.py:36-60``.
 

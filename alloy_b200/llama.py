@@ -96,9 +96,7 @@ class QuantLlamaDecoder:
             except Exception as e:  # noqa: BLE001 - any set-up failure means "no peer path"
                 ex = None
                 self.exchange_error = repr(e)
-            ok = torch.tensor([1 if ex is not None else 0], device=self.device)
-            torch.distributed.all_reduce(ok, op=torch.distributed.ReduceOp.MIN, group=process_group)
-            if int(ok.item()) == 1:
+            if tp.agree(ex is not None, process_group, self.device):
                 self.exchange = ex
             elif ex is not None:
                 ex.close()
@@ -217,8 +215,22 @@ class QuantLlamaDecoder:
 
     def step_eager_logits(self) -> torch.Tensor:
         """One eager (uncaptured) step; returns the logits."""
+        self._enter_together()
         self._step()
         return self.logits
+
+    def _enter_together(self) -> None:
+        """Tensor-parallel ranks start an eager step together: a rank still busy elsewhere would let
+        its peers' bounded waits in the fused exchange run out."""
+        if self.tp_size > 1 and not self.tp_dry:
+            torch.cuda.synchronize()
+            torch.distributed.barrier(group=self.pg)
+
+    def device_error(self, clear: bool = True) -> int:
+        """The library's sticky device error word (non-zero: a bounded wait ran out somewhere since
+        it was last cleared, results since then are not to be trusted).  Synchronises the device."""
+        from . import _lib
+        return int(_lib.load().alloyb_device_error(1 if clear else 0))
 
     def _step(self) -> None:
         s, b = self.shape, self.batch
@@ -271,22 +283,18 @@ class QuantLlamaDecoder:
 
     def capture(self) -> None:
         """Warm up once eagerly, then record the step into a CUDA graph."""
-        if self.tp_size > 1 and not self.tp_dry:
-            # the ranks enter their first exchange together (a rank still building its weights
-            # would let the others' bounded waits run out)
-            torch.cuda.synchronize()
-            torch.distributed.barrier(group=self.pg)
+        # the ranks enter their first exchange together (a rank still building its weights
+        # would let the others' bounded waits run out)
+        self._enter_together()
         self._step()
         torch.cuda.synchronize()
         if self.tp_size > 1 and not self.tp_dry and self.exchange is not None:
             # did any rank's wait on a peer run out?  Then nobody uses the peer path.
-            from . import _lib
-            bad = torch.tensor([1 if _lib.load().alloyb_device_error(1) != 0 else 0], device=self.device)
-            torch.distributed.all_reduce(bad, op=torch.distributed.ReduceOp.MAX, group=self.pg)
-            if int(bad.item()):
+            if not tp.agree(self.device_error() == 0, self.pg, self.device):
                 self.exchange_error = "a bounded wait on a peer ran out in the first step; using NCCL all-reduces"
                 self.exchange.close()
                 self.exchange = None
+                self._enter_together()
                 self._step()
                 torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()

@@ -59,6 +59,27 @@ lib.define(
     "float scale=-1.0, int sliding_window=0, bool write_kv=True, "
     "Tensor? last_real=None) -> Tensor"
 )
+lib.define(
+    "attention_kv_update(Tensor q, Tensor new_k, Tensor new_v, "
+    "Tensor cache_pos, Tensor k_cache, Tensor v_cache, "
+    "float scale=-1.0, int sliding_window=0) -> Tensor"
+)
+lib.define(
+    "attention_kv_update_multi(Tensor q, Tensor new_k, Tensor new_v, "
+    "Tensor cache_pos, Tensor k_cache, Tensor v_cache, "
+    "float scale=-1.0, int sliding_window=0) -> Tensor"
+)
+# Q5_0 (three normalised buffers: nibbles, fifth bits, fp16 block scales).
+lib.define("gguf_q5_0_mm(Tensor activations, Tensor qweight, Tensor qhigh, Tensor scales) -> Tensor")
+lib.define("gguf_q5_0_embedding(Tensor input_ids, Tensor qweight, Tensor qhigh, Tensor scales) -> Tensor")
+lib.define(
+    "batched_gguf_q5_0_mm(Tensor activations, Tensor[] qweights, "
+    "Tensor[] qhighs, Tensor[] scales) -> Tensor[]"
+)
+lib.define(
+    "gguf_moe_routed(Tensor hidden, Tensor router_logits, Tensor gate_up_blocks, "
+    "Tensor down_qweight, int num_experts, int top_k, int moe_intermediate) -> Tensor"
+)
 # New ops (no reference schema).
 lib.define(
     "attention_cache_q8_paged(Tensor q, Tensor new_k, Tensor new_v, Tensor seq_pos, "
@@ -333,6 +354,79 @@ def _q8_silu(activations, gate_qweight, gate_scales, up_qweight, up_scales):
                   up_scales.contiguous(), _lib.Q8_0, _lib.ACT_SILU)
 
 
+# ------------------------------------------------------------------------------- Q5_0, routed experts
+
+
+def _q5_check(qweight, qhigh, scales):
+    if qweight.dtype != torch.uint8 or qhigh.dtype != torch.uint8 or scales.dtype != torch.float16:
+        raise TypeError("q5_0 buffers are uint8 qweight, uint8 qhigh and float16 scales")
+    n, half = qweight.shape
+    if tuple(qhigh.shape) != (n, half) or tuple(scales.shape) != (n, half // 16) or half % 16:
+        raise ValueError(f"q5_0 buffers must be (N, K/2), (N, K/2), (N, K/32); got {tuple(qweight.shape)}, "
+                         f"{tuple(qhigh.shape)}, {tuple(scales.shape)}")
+    return n, half * 2
+
+
+@torch.library.impl(lib, "gguf_q5_0_mm", "CUDA")
+def _q5_mm(activations, qweight, qhigh, scales):
+    n, k = _q5_check(qweight, qhigh, scales)
+    x = _check_acts(activations, k)
+    y = torch.empty((x.shape[0], n), dtype=x.dtype, device=x.device)
+    if x.shape[0] == 0:
+        return y
+    qweight, qhigh, scales = qweight.contiguous(), qhigh.contiguous(), scales.contiguous()
+    check(_lib.load().alloyb_q5_0_mm(x.data_ptr(), qweight.data_ptr(), qhigh.data_ptr(), scales.data_ptr(),
+                                     y.data_ptr(), x.shape[0], n, k, _dtype_code(x), _stream()), "alloyb_q5_0_mm")
+    return y
+
+
+@torch.library.impl(lib, "batched_gguf_q5_0_mm", "CUDA")
+def _bq5_mm(activations, qweights, qhighs, scales):
+    return [_q5_mm(activations, w, h, s) for w, h, s in zip(qweights, qhighs, scales)]
+
+
+@torch.library.impl(lib, "gguf_q5_0_embedding", "CUDA")
+def _q5_emb(input_ids, qweight, qhigh, scales):
+    n, k = _q5_check(qweight, qhigh, scales)
+    flat = input_ids.reshape(-1).to(torch.int64).contiguous()
+    out = torch.empty((flat.numel(), k), dtype=torch.float32, device=qweight.device)
+    if flat.numel():
+        qweight, qhigh, scales = qweight.contiguous(), qhigh.contiguous(), scales.contiguous()
+        check(_lib.load().alloyb_dequant_q5_0(qweight.data_ptr(), qhigh.data_ptr(), scales.data_ptr(),
+                                              flat.data_ptr(), out.data_ptr(), flat.numel(), n, k, _lib.F32,
+                                              _stream()), "alloyb_dequant_q5_0")
+    return out.reshape(tuple(input_ids.shape) + (k,))
+
+
+@torch.library.impl(lib, "gguf_moe_routed", "CUDA")
+def _moe_routed(hidden, router_logits, gate_up_blocks, down_qweight, num_experts, top_k, moe_intermediate):
+    if hidden.ndim != 2 or router_logits.ndim != 2 or router_logits.shape != (hidden.shape[0], num_experts):
+        raise ValueError("hidden must be (T, H) and router_logits (T, num_experts)")
+    t, hdim = hidden.shape
+    i = int(moe_intermediate)
+    if hdim % 256 or i % 256:
+        raise ValueError("hidden size and moe_intermediate must be multiples of 256")
+    if gate_up_blocks.dtype != torch.uint8 or down_qweight.dtype != torch.uint8:
+        raise TypeError("expert weights are packed uint8 blocks")
+    if gate_up_blocks.numel() != num_experts * 2 * i * (hdim // 256) * 144:
+        raise ValueError("gate_up_blocks must hold (E, 2*I, H/256*144) Q4_K bytes")
+    if down_qweight.numel() != num_experts * hdim * (i // 256) * 210:
+        raise ValueError("down_qweight must hold (E, H, I/256*210) Q6_K bytes")
+    hidden = hidden.contiguous()
+    logits = router_logits.to(torch.float32).contiguous()
+    out = torch.empty((t, hdim), dtype=torch.float32, device=hidden.device)
+    if t == 0:
+        return out
+    L = _lib.load()
+    n = L.alloyb_moe_workspace_bytes(t, int(top_k), i)
+    ws = torch.empty(n, dtype=torch.uint8, device=hidden.device)
+    check(L.alloyb_moe_routed(hidden.data_ptr(), _dtype_code(hidden), logits.data_ptr(),
+                              gate_up_blocks.contiguous().data_ptr(), down_qweight.contiguous().data_ptr(),
+                              out.data_ptr(), t, hdim, int(num_experts), int(top_k), i, ws.data_ptr(), n, _stream()),
+          "alloyb_moe_routed")
+    return out
+
+
 # ------------------------------------------------------------------------------- embeddings
 
 
@@ -439,38 +533,75 @@ def _pos_i32(pos: torch.Tensor) -> torch.Tensor:
     return pos.contiguous()
 
 
-def _decode_attention(layout, q, new_k, new_v, pos, k0, k1, v0, v1, s_max, num_pages, scale,
-                      write_kv, workspace=None):
+def _check_cache(layout, b, kv_h, d, k0, k1, v0, v1):
+    """Cache tensors against (B, KV_H, D): a mismatch would make the kernels index out of bounds."""
+    if layout == _lib.KV_Q8_PAGED:
+        pool, table = k0, k1
+        if pool.shape[1] != 2 or pool.shape[2] != kv_h or pool.shape[3] != 16 or pool.shape[4] != d // 32 * 34:
+            raise ValueError(f"kv_pool must be (pages, 2, {kv_h}, 16, {d // 32 * 34}), got {tuple(pool.shape)}")
+        if table.shape[0] < b:
+            raise ValueError(f"page_table has {table.shape[0]} rows for batch {b}")
+        return
+    for name, t in (("k cache", k0), ("v cache", v0)):
+        if t.ndim != 4 or t.shape[0] < b or t.shape[1] != kv_h or t.shape[3] != d:
+            raise ValueError(f"{name} must be (>= {b}, {kv_h}, S, {d}), got {tuple(t.shape)}")
+    if k0.shape != v0.shape:
+        raise ValueError("K and V caches must have the same shape")
+    if layout == _lib.KV_Q8_SPLIT:
+        want = (k0.shape[0], kv_h, k0.shape[2], d // 32)
+        for name, t in (("k scales", k1), ("v scales", v1)):
+            if tuple(t.shape) != want:
+                raise ValueError(f"{name} must be {want}, got {tuple(t.shape)}")
+
+
+def _cache_attention(layout, q, new_k, new_v, pos, k0, k1, v0, v1, s_max, num_pages, scale,
+                     write_kv, workspace=None):
+    """Shared body of the cache-attention ops: one query token per sequence runs the split-K decode
+    kernels, a chunk of several (prefill, verify) the causal chunk kernel after the chunk's K/V rows
+    have been written to the cache (quantised for the q8 layouts) -- the routing of the reference's
+    ``_attention_cache_handler`` / ``_attention_cache_q8_handler``
+    (packages/alloy-torch/src/alloy_torch/ops/attention.py:886-934, ops/kv_quant.py:58-162)."""
     if q.ndim != 4:
         raise ValueError(f"attention expects 4D Q (B, H, S, D), got {q.ndim}D")
     b, h, s, d = q.shape
     if d % 32 != 0:
         raise ValueError(f"attention needs head_dim % 32 == 0, got {d}")
-    if s != 1:
-        raise NotImplementedError(
-            "only the decode step (one query token per sequence) is implemented; "
-            f"got seq_len={s}")
+    if new_k.ndim != 4 or new_v.ndim != 4:
+        raise ValueError("new_k / new_v must be 4D (B, KV_H, S, D)")
     kv_h = new_k.shape[1]
+    if kv_h <= 0 or h % kv_h:
+        raise ValueError(f"{h} query heads do not group over {kv_h} KV heads")
+    _check_cache(layout, b, kv_h, d, k0, k1, v0, v1)
     if q.stride(3) != 1:
         q = q.contiguous()
     for name, t in (("new_k", new_k), ("new_v", new_v)):
         if t.dtype != torch.float16:
             raise TypeError(f"{name} must be float16, got {t.dtype}")
-        if tuple(t.shape) != (b, kv_h, 1, d):
-            raise ValueError(f"{name} must be {(b, kv_h, 1, d)}, got {tuple(t.shape)}")
+        if tuple(t.shape) != (b, kv_h, s, d):
+            raise ValueError(f"{name} must be {(b, kv_h, s, d)}, got {tuple(t.shape)}")
     if new_k.stride(3) != 1 or new_v.stride(3) != 1 or new_k.stride() != new_v.stride():
         new_k, new_v = new_k.contiguous(), new_v.contiguous()
-    out = torch.empty((b, 1, h, d), dtype=q.dtype, device=q.device)
+    out = torch.empty((b, s, h, d), dtype=q.dtype, device=q.device)
     ws = workspace if workspace is not None else attn_workspace(q.device, b, h, d)
     L = _lib.load()
-    check(L.alloyb_attn_decode(
-        layout, q.data_ptr(), q.stride(0), q.stride(1), _dtype_code(q),
-        k0.data_ptr(), k1.data_ptr() if k1 is not None else None,
-        v0.data_ptr() if v0 is not None else None, v1.data_ptr() if v1 is not None else None,
-        new_k.data_ptr(), new_v.data_ptr(), new_k.stride(0), new_k.stride(1),
-        pos.data_ptr(), pos.numel(), out.data_ptr(), b, h, kv_h, d, s_max, num_pages,
-        float(scale) if scale is not None else -1.0, 1 if write_kv else 0,
-        ws.data_ptr(), ws.numel(), _stream()), "alloyb_attn_decode")
+    ptrs = [t.data_ptr() if t is not None else None for t in (k0, k1, v0, v1)]
+    sc = float(scale) if scale is not None else -1.0
+    if s == 1:
+        check(L.alloyb_attn_decode(
+            layout, q.data_ptr(), q.stride(0), q.stride(1), _dtype_code(q), *ptrs,
+            new_k.data_ptr(), new_v.data_ptr(), new_k.stride(0), new_k.stride(1),
+            pos.data_ptr(), pos.numel(), out.data_ptr(), b, h, kv_h, d, s_max, num_pages,
+            sc, 1 if write_kv else 0, ws.data_ptr(), ws.numel(), _stream()), "alloyb_attn_decode")
+        return out.transpose(1, 2)
+    if d not in (64, 128, 256):
+        raise NotImplementedError(f"chunk attention is built for head_dim 64, 128 and 256, got {d}")
+    if write_kv:
+        check(L.alloyb_kv_write(layout, new_k.data_ptr(), new_v.data_ptr(), new_k.stride(0), new_k.stride(1),
+                                new_k.stride(2), *ptrs, pos.data_ptr(), pos.numel(), b, kv_h, d, s_max, num_pages,
+                                s, ws.data_ptr(), _stream()), "alloyb_kv_write")
+    check(L.alloyb_attn_chunk(layout, q.data_ptr(), q.stride(0), q.stride(1), q.stride(2), _dtype_code(q), *ptrs,
+                              pos.data_ptr(), pos.numel(), out.data_ptr(), b, h, kv_h, d, s, s_max, num_pages, sc,
+                              ws.data_ptr(), _stream()), "alloyb_attn_chunk")
     return out.transpose(1, 2)
 
 
@@ -484,6 +615,11 @@ def _norm_scale(scale, d):
 def _no_window(sliding_window, last_real):
     if sliding_window:
         raise NotImplementedError("sliding-window ring caches are outside this build's scope")
+    if last_real is not None:
+        # the bound the reference applies to padded chunks of a ring cache
+        # (packages/alloy-torch/src/alloy_torch/ops/kv_quant.py:70, :110): not computed here, so refuse it
+        raise NotImplementedError("last_real (the padded-chunk bound of sliding-window caches) is outside "
+                                  "this build's scope")
 
 
 @torch.library.impl(lib, "attention_cache", "CUDA")
@@ -495,8 +631,20 @@ def _attention_cache(q, new_k, new_v, cache_pos, k_cache, v_cache, scale, slidin
     if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
         raise ValueError("K/V caches must be contiguous (B, KV_H, S, D)")
     pos = _pos_i32(cache_pos.reshape(-1)[:1])
-    return _decode_attention(_lib.KV_F16, q, new_k, new_v, pos, k_cache, None, v_cache, None,
+    return _cache_attention(_lib.KV_F16, q, new_k, new_v, pos, k_cache, None, v_cache, None,
                              k_cache.shape[2], 0, _norm_scale(scale, q.shape[-1]), write_kv)
+
+
+@torch.library.impl(lib, "attention_kv_update", "CUDA")
+def _attention_kv_update(q, new_k, new_v, cache_pos, k_cache, v_cache, scale=-1.0, sliding_window=0):
+    return _attention_cache(q, new_k, new_v, cache_pos, k_cache, v_cache, scale, sliding_window, True, None)
+
+
+@torch.library.impl(lib, "attention_kv_update_multi", "CUDA")
+def _attention_kv_update_multi(q, new_k, new_v, cache_pos, k_cache, v_cache, scale=-1.0, sliding_window=0):
+    """Speculative-decode verify: 2..16 new tokens written at cache_pos.., each attending causally
+    (packages/alloy-torch/src/alloy_torch/ops/attention.py:1255-1275)."""
+    return _attention_cache(q, new_k, new_v, cache_pos, k_cache, v_cache, scale, sliding_window, True, None)
 
 
 @torch.library.impl(lib, "attention_cache_q8", "CUDA")
@@ -508,7 +656,7 @@ def _attention_cache_q8(q, new_k, new_v, cache_pos, k_codes, k_scales, v_codes, 
         if t.dtype != dt or not t.is_contiguous():
             raise TypeError("q8 cache tensors must be contiguous int8 codes / float16 scales")
     pos = _pos_i32(cache_pos.reshape(-1)[:1])
-    return _decode_attention(_lib.KV_Q8_SPLIT, q, new_k, new_v, pos, k_codes, k_scales, v_codes,
+    return _cache_attention(_lib.KV_Q8_SPLIT, q, new_k, new_v, pos, k_codes, k_scales, v_codes,
                              v_scales, k_codes.shape[2], 0, _norm_scale(scale, q.shape[-1]), write_kv)
 
 
@@ -522,7 +670,7 @@ def _attention_cache_q8_paged(q, new_k, new_v, seq_pos, page_table, kv_pool, sca
     if page_table.shape[0] != q.shape[0]:
         raise ValueError("page_table needs one row per sequence")
     pos = _pos_i32(seq_pos.reshape(-1))
-    return _decode_attention(_lib.KV_Q8_PAGED, q, new_k, new_v, pos, kv_pool, page_table, None, None,
+    return _cache_attention(_lib.KV_Q8_PAGED, q, new_k, new_v, pos, kv_pool, page_table, None, None,
                              page_table.shape[1] * 16, kv_pool.shape[0],
                              _norm_scale(scale, q.shape[-1]), write_kv)
 
@@ -566,6 +714,23 @@ torch.library.impl(lib, "gguf_q6_k_embedding", "Meta")(
 torch.library.impl(lib, "gguf_q8_0_embedding", "Meta")(
     lambda input_ids, qweight, scales: torch.empty(input_ids.shape + (qweight.shape[1],),
                                                    dtype=torch.float32, device=input_ids.device))
+torch.library.impl(lib, "gguf_q5_0_mm", "Meta")(
+    lambda activations, qweight, qhigh, scales:
+    torch.empty((activations.shape[0], scales.shape[0]), dtype=activations.dtype, device=activations.device))
+torch.library.impl(lib, "batched_gguf_q5_0_mm", "Meta")(
+    lambda activations, qweights, qhighs, scales:
+    [torch.empty((activations.shape[0], s.shape[0]), dtype=activations.dtype, device=activations.device)
+     for s in scales])
+torch.library.impl(lib, "gguf_q5_0_embedding", "Meta")(
+    lambda input_ids, qweight, qhigh, scales: torch.empty(input_ids.shape + (qweight.shape[1] * 2,),
+                                                          dtype=torch.float32, device=input_ids.device))
+torch.library.impl(lib, "gguf_moe_routed", "Meta")(
+    lambda hidden, router_logits, gate_up_blocks, down_qweight, num_experts, top_k, moe_intermediate:
+    torch.empty((hidden.shape[0], hidden.shape[1]), dtype=torch.float32, device=hidden.device))
+torch.library.impl(lib, "attention_kv_update", "Meta")(
+    lambda q, new_k, new_v, cache_pos, k_cache, v_cache, scale=-1.0, sliding_window=0: torch.empty_like(q))
+torch.library.impl(lib, "attention_kv_update_multi", "Meta")(
+    lambda q, new_k, new_v, cache_pos, k_cache, v_cache, scale=-1.0, sliding_window=0: torch.empty_like(q))
 torch.library.impl(lib, "attention_cache", "Meta")(
     lambda q, new_k, new_v, cache_pos, k_cache, v_cache, scale, sliding_window=0, write_kv=True,
     last_real=None: torch.empty_like(q))

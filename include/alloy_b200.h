@@ -72,6 +72,14 @@ int alloyb_dequant_q6k(const void* blocks, const int64_t* ids, void* out, int64_
 int alloyb_dequant_q8_0(const void* qweight, const void* scales, const int64_t* ids, void* out,
                         int64_t n_rows, int64_t table_rows, int K, int out_dtype, void* stream);
 
+/* Q5_0 in the reference's normalised three-buffer form (server/gguf/quant.py:414-490
+ * split_q5_0_weight): qweight (rows, K/2) u8 packs element k in the low and k+1 in the high nibble
+ * of byte k/2, qhigh (rows, K/2) u8 holds their fifth bits in bit 0 / bit 4 of the same byte,
+ * scales (rows, K/32) fp16; w = scale * ((nibble | fifth << 4) - 16).  Stands in for
+ * embedding_q5_0 (metal/std/quant.py:887-940) behind torch/custom_ops.py:89-91. */
+int alloyb_dequant_q5_0(const void* qweight, const void* qhigh, const void* scales, const int64_t* ids,
+                        void* out, int64_t n_rows, int64_t table_rows, int K, int out_dtype, void* stream);
+
 /* ------------------------------------------------------------------ quantised linear
  * y[m,n] = sum_k x[m,k] * deq(W)[n,k], fp32 accumulate, y in the activation
  * dtype.  One descriptor per weight matrix lets several sibling projections
@@ -110,6 +118,12 @@ int alloyb_q6k_mm(const void* x, const void* blocks, void* y, int M, int N, int 
                   void* stream);
 int alloyb_q8_0_mm(const void* x, const void* qweight, const void* scales, void* y, int M, int N,
                    int K, int dtype, void* stream);
+
+/* Q5_0 linear (torch/custom_ops.py:86-88 gguf_q5_0_mm; kernels metal/std/quant.py:941-1197):
+ * y (M, N) = x (M, K) * deq(W)^T, fp32 accumulate, y in the activation dtype.  A CUDA-core
+ * warp-per-row kernel for every M (the format is outside the Q4_K_M mixes). */
+int alloyb_q5_0_mm(const void* x, const void* qweight, const void* qhigh, const void* scales, void* y,
+                   int M, int N, int K, int dtype, void* stream);
 
 /* y = act(x*G^T) * (x*U^T), one launch sharing the activation load
  * (torch/custom_ops.py:53-58 gguf_q4_k_silu/_gelu, :109-111 gguf_q8_0_silu;
@@ -155,6 +169,9 @@ typedef struct alloyb_tp {
     int world;      /* 1..8 */
     int rank;
     int max_n;
+    int spin_limit; /* polls of a peer's flag before a wait gives up; 0 = the default (about 4 million,
+                       a few hundred ms).  A wait that gives up sets the sticky word alloyb_device_error
+                       reports; the call still returns, its output is then undefined. */
     void* peer[8];
 } alloyb_tp;
 size_t alloyb_tp_buffer_bytes(int max_n);
@@ -168,8 +185,11 @@ int alloyb_tp_ipc_close(void* p);
  * partial outputs cross NVLink inside the GEMV launch (stores into the peers' exchange buffers,
  * a flag per CTA, the sum taken in rank order on every rank): no separate collective.  All
  * ranks must make the same sequence of calls.  Returns 1 (nothing launched) when the shape is
- * outside the fused kernel (it covers one fp16 token, Q4_K / Q6_K, K a multiple of 2048 or
- * N >= 2368); the caller then runs alloyb_linear and its own all-reduce. */
+ * outside the fused kernel -- it covers one fp16 token on a Q4_K / Q6_K matrix whose rows hold at
+ * least four super-blocks (K >= 1024 on this rank) -- and the caller then runs alloyb_linear and
+ * its own all-reduce; that answer depends on shape and format only, so every rank gets the same
+ * one.  A pointer or row pitch that misses 16-byte alignment is ALLOYB_E_ALIGN here, never a
+ * quiet per-rank fallback. */
 int alloyb_linear_allreduce(const void* x, int M, int K, int dtype, const alloyb_weight* w,
                             const void* residual, const alloyb_tp* tp, void* stream);
 
@@ -199,6 +219,35 @@ int alloyb_kv_append_q8_paged(const void* new_k, const void* new_v, int64_t batc
                               int64_t head_stride, void* pool, const int32_t* page_table,
                               int max_pages, int64_t num_pages, const int32_t* seq_pos, int B,
                               int KV_H, int D, int32_t* status, void* stream);
+
+/* Write n_tokens new rows per (sequence, kv head) at positions [start_b, start_b + n_tokens) of a
+ * cache in any layout (k0..v1, S_max, num_pages as in alloyb_attn_decode); the q8 layouts quantise
+ * each row exactly as the one-token append does.  new_k / new_v: fp16 (B, KV_H, n_tokens, D) with
+ * the given strides in elements.  start: int32 device (start_count,), 1 = shared by every
+ * sequence.  The chunk write of the reference's prefill branch: kv_quantize_q8_range
+ * (metal/std/kv_quant.py:24-70) launched from torch/ops/kv_quant.py:101-119, and the fp16 row
+ * write of attention_prefill_warm (torch/ops/attention.py:96-100).  status as in
+ * alloyb_kv_append_q8_paged. */
+int alloyb_kv_write(int layout, const void* new_k, const void* new_v, int64_t batch_stride,
+                    int64_t head_stride, int64_t tok_stride, void* k0, void* k1, void* v0, void* v1,
+                    const int32_t* start, int start_count, int B, int KV_H, int D, int S_max,
+                    int64_t num_pages, int n_tokens, int32_t* status, void* stream);
+
+/* Causal attention of a chunk of n_tokens query tokens per sequence over a cache that already
+ * holds the chunk's rows: query i sits at position start_b + i and attends to [0, start_b + i].
+ * Covers the seq_len > 1 branches of attention_cache / attention_cache_q8 (prefill:
+ * torch/ops/kv_quant.py:121-162, where the reference dequantises history + chunk to an fp16
+ * scratch, metal/std/kv_quant.py:73-108, and runs fp16 prefill attention; here the codes are read
+ * directly and dequantised per tile in shared memory to the same fp16 values) and the 2..16-token
+ * verify step attention_kv_update_multi (torch/ops/attention.py:1255-1275).  q: (B, H, n_tokens,
+ * D) with strides in elements, f16 / bf16 / f32 (computed as fp16); out: (B, n_tokens, H, D)
+ * dense in q's dtype.  D is 64, 128 or 256.  No workspace.  status (may be NULL) receives the
+ * same bits as alloyb_attn_workspace_status. */
+int alloyb_attn_chunk(int layout, const void* q, int64_t q_batch_stride, int64_t q_head_stride,
+                      int64_t q_tok_stride, int q_dtype, void* k0, void* k1, void* v0, void* v1,
+                      const int32_t* start, int start_count, void* out, int B, int H, int KV_H, int D,
+                      int n_tokens, int S_max, int64_t num_pages, float scale, int32_t* status,
+                      void* stream);
 
 /* ------------------------------------------------------------------ decode attention
  * One query token per sequence, GQA (head h reads kv head h / (H/KV_H)),
@@ -257,6 +306,24 @@ int alloyb_attn_decode_static(int layout, const void* q, int64_t q_batch_stride,
                               int64_t new_batch_stride, int64_t new_head_stride, const int32_t* pos,
                               int pos_count, void* out, int B, int H, int KV_H, int D, int S_max,
                               int64_t num_pages, float scale, int write_kv, void* stream);
+/* Status word of the latest alloyb_attn_decode_static call on the current device (bit 0: a
+ * position, bit 1: a page id was out of range and skipped); each static call starts it at zero.
+ * Synchronises the stream.  No counterpart in the reference. */
+int alloyb_attn_static_status(int32_t* status_out, void* stream);
+
+/* ------------------------------------------------------------------ routed experts
+ * gguf_moe_routed (torch/custom_ops.py:59-66; kernels metal/std/moe.py:31-228): per token the
+ * top_k largest router logits (descending, lowest index on ties) with a softmax over just those;
+ * h = silu(x * gate_e^T) * (x * up_e^T) per slot from the fused Q4_K tensor gate_up_blocks
+ * (E, 2*I, H/256*144) (gate rows then up rows of each expert); out (T, H) fp32 =
+ * sum over slots of w_slot * (h_slot * down_e^T) with down_qweight Q6_K (E, H, I/256*210).
+ * hidden (T, H) f16 / bf16 / f32; router_logits (T, E) fp32.  workspace: at least
+ * alloyb_moe_workspace_bytes bytes, 256-aligned (routing, weights, per-slot activations). */
+size_t alloyb_moe_workspace_bytes(int T, int top_k, int moe_intermediate);
+int alloyb_moe_routed(const void* hidden, int hidden_dtype, const float* router_logits,
+                      const void* gate_up_blocks, const void* down_qweight, float* out, int T, int H,
+                      int num_experts, int top_k, int moe_intermediate, void* workspace,
+                      size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------ decode-step glue
  * Small fp16/bf16 ops of the decode step (not graded kernels):

@@ -19,6 +19,16 @@ Every function restates, in NumPy, arithmetic the reference defines:
 * decode attention: reference ``tests/kernels/test_kv_quant.py:225-239``
   (float64 softmax over the dequantised cache, GQA ``h // kv_group``,
   causal over positions [0, pos]).
+* chunk (prefill / verify) attention: the same per query row, query i of the
+  chunk at position start + i (reference ``tests/kernels/test_kv_quant.py:466-479``).
+* Q5_0: split of the 22-byte wire block into the three normalised buffers,
+  reference ``packages/alloy-server/src/alloy_server/gguf/quant.py:414-490``;
+  ``w = scale * ((nibble | fifth << 4) - 16)``.
+* routed experts: top-k over raw logits + softmax of the winners, SiLU-gated
+  Q4_K gate/up, Q6_K down, routing-weighted sum
+  (``packages/alloy-metal/src/alloy/std/moe.py:31-228``; the router identity
+  ``renorm(topk(softmax)) == softmax(topk)`` is the one the reference checks in
+  ``tests/kernels/test_moe.py:148-175``).
 
 The weight dequantisers' arithmetic lives in the third-party package
 ``gguf`` 0.19.0 (pinned in the reference's ``uv.lock:809-810``), which is not
@@ -28,8 +38,11 @@ Parity pins: ``tests/test_oracle.py`` checks this module bit-for-bit against
 the committed fixtures in ``tests/golden/`` — produced by running the
 reference's own test decoders (Q4_K, q8_0 KV, attention) and ``gguf`` 0.19.0
 (Q4_K, Q6_K, Q8_0) in a container that holds both (``tests/golden/make_golden.py``).
-Q6_K and Q8_0 weights have no decoder in the reference's own tests; they are
-pinned at the ``gguf`` boundary only.
+Q6_K, Q8_0 and Q5_0 weights have no decoder in the reference's own tests; they
+are pinned at the ``gguf`` boundary only (Q5_0 additionally against the
+reference's own ``split_q5_0_weight``).  The routed-expert op has only
+device-side references in the reference's tests: its oracle here is the
+composition of the pinned decoders, "parity unpinned" as an op.
 """
 
 from __future__ import annotations
@@ -155,6 +168,66 @@ def dequant_q8_0(codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
     return (codes.astype(np.float32) * s).astype(np.float32)
 
 
+# --------------------------------------------------------------------------- Q5_0 weights
+
+Q5_0_BYTES = 22
+
+
+def split_q5_0(wire: np.ndarray) -> tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """(N, K/32*22) uint8 wire blocks ``{fp16 d; u8 qh[4]; u8 qs[16]}`` -> the three
+    K-sequential buffers: qweight (N, K/2) with element k in the low and k+1 in the high
+    nibble of byte k/2, qhigh (N, K/2) with their fifth bits in bit 0 / bit 4, fp16 scales
+    (N, K/32).  Wire element l < 16 is ``qs[l] & 15`` with fifth bit ``qh32 >> l``; element
+    l + 16 is ``qs[l] >> 4`` with fifth bit ``qh32 >> (l + 16)``."""
+    n = wire.shape[0]
+    g = wire.shape[1] // Q5_0_BYTES
+    b = np.ascontiguousarray(wire).reshape(n, g, Q5_0_BYTES)
+    scales = np.ascontiguousarray(b[:, :, 0:2]).view(np.float16).reshape(n, g).copy()
+    qh32 = np.ascontiguousarray(b[:, :, 2:6]).view(np.uint32).reshape(n, g)
+    qs = b[:, :, 6:22]
+    nib = np.concatenate([qs & 15, qs >> 4], axis=2)                        # (n, g, 32) in K order
+    fifth = ((qh32[:, :, None] >> np.arange(32, dtype=np.uint32)) & 1).astype(np.uint8)
+    qweight = (nib[:, :, 0::2] | (nib[:, :, 1::2] << 4)).astype(np.uint8).reshape(n, g * 16)
+    qhigh = (fifth[:, :, 0::2] | (fifth[:, :, 1::2] << 4)).astype(np.uint8).reshape(n, g * 16)
+    return qweight, qhigh, scales
+
+
+def dequant_q5_0(qweight: np.ndarray, qhigh: np.ndarray, scales: np.ndarray) -> np.ndarray:
+    """The three normalised buffers -> (N, K) float32; ``w = scale * (q - 16)`` (exact)."""
+    n, half = qweight.shape
+    nib = np.stack([qweight & 15, qweight >> 4], axis=-1).reshape(n, half * 2).astype(np.int32)
+    fifth = np.stack([qhigh & 1, (qhigh >> 4) & 1], axis=-1).reshape(n, half * 2).astype(np.int32)
+    q = ((nib | (fifth << 4)) - 16).astype(np.float32)
+    return (q * np.repeat(scales.astype(np.float32), 32, axis=-1)).astype(np.float32)
+
+
+# --------------------------------------------------------------------------- routed experts
+
+
+def moe_routed_ref(x: np.ndarray, logits: np.ndarray, gate_up: np.ndarray, down: np.ndarray,
+                   top_k: int, inter: int) -> np.ndarray:
+    """float64 routed-expert output (T, H).  ``gate_up``: (E, 2*I, H/256*144) Q4_K bytes (gate
+    rows then up rows per expert); ``down``: (E, H, I/256*210) Q6_K bytes.  Router: softmax over
+    all experts, top-k, renormalise (ties: lowest index first)."""
+    t_n, hdim = x.shape
+    e_n = logits.shape[1]
+    out = np.zeros((t_n, hdim), np.float64)
+    lg = logits.astype(np.float64)
+    for t in range(t_n):
+        p = np.exp(lg[t] - lg[t].max())
+        p /= p.sum()
+        order = np.lexsort((np.arange(e_n), -lg[t]))[:top_k]
+        w = p[order] / p[order].sum()
+        for e, we in zip(order, w):
+            gu = dequant_q4_k(np.ascontiguousarray(gate_up[e]).reshape(2 * inter, -1)).astype(np.float64)
+            g = gu[:inter] @ x[t].astype(np.float64)
+            u = gu[inter:] @ x[t].astype(np.float64)
+            h = (silu(g) * u).astype(np.float32).astype(np.float64)          # the op keeps h in fp32
+            dw = dequant_q6_k(np.ascontiguousarray(down[e]).reshape(hdim, -1)).astype(np.float64)
+            out[t] += we * (dw @ h)
+    return out
+
+
 # --------------------------------------------------------------------------- matmul refs
 
 
@@ -245,6 +318,18 @@ def attention_decode_ref(k: np.ndarray, v: np.ndarray, q: np.ndarray, pos: int,
         p = np.exp(s - s.max())
         p /= p.sum()
         out[h] = p @ vh
+    return out
+
+
+def attention_chunk_ref(k: np.ndarray, v: np.ndarray, q: np.ndarray, start: int,
+                        scale: float | None = None) -> np.ndarray:
+    """float64 causal attention of a chunk for one sequence: ``q`` (H, S, D); query i sits at
+    position ``start + i`` and attends to cache positions [0, start + i] of ``k``/``v``
+    (KV_H, >= start + S, D), which already hold the chunk's rows.  Returns (H, S, D)."""
+    heads, s_n, dim = q.shape
+    out = np.empty((heads, s_n, dim), np.float64)
+    for i in range(s_n):
+        out[:, i] = attention_decode_ref(k, v, q[:, i], start + i, scale)
     return out
 
 

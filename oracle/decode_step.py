@@ -37,10 +37,11 @@ def _rope(x, pos, inv_freq):
 
 
 def decode_step(ids, pos, embed_w, layers, norm_final, head_w, inv_freq, k_caches, v_caches,
-                heads, kv_heads, head_dim, eps):
+                heads, kv_heads, head_dim, eps, kv_q8=False):
     """``layers``: dicts of dequantised fp32 matrices wq wk wv wo wg wu wd and fp16 norm_in
     norm_post.  ``k_caches``/``v_caches``: per layer fp32 (B, KV_H, S, D) arrays, updated in
-    place at ``pos``.  Returns (logits fp16 (B, vocab), next ids)."""
+    place at ``pos``.  ``kv_q8``: the new rows go through the q8_0 KV quantiser first (what a q8_0
+    cache stores and attention later reads).  Returns (logits fp16 (B, vocab), next ids, hidden)."""
     b = len(ids)
     h = _h(embed_w[np.asarray(ids)])
     for li, lw in enumerate(layers):
@@ -49,8 +50,12 @@ def decode_step(ids, pos, embed_w, layers, norm_final, head_w, inv_freq, k_cache
         k = _h(O.mm_ref_f64(xn, lw["wk"])).reshape(b, kv_heads, head_dim)
         v = _h(O.mm_ref_f64(xn, lw["wv"])).reshape(b, kv_heads, head_dim)
         q, k = _rope(q, pos, inv_freq), _rope(k, pos, inv_freq)
-        k_caches[li][:, :, pos] = k.astype(np.float32)
-        v_caches[li][:, :, pos] = v.astype(np.float32)
+        if kv_q8:
+            k_caches[li][:, :, pos] = O.kv_dequant_q8_0(*O.kv_quantize_q8_0(k))
+            v_caches[li][:, :, pos] = O.kv_dequant_q8_0(*O.kv_quantize_q8_0(v))
+        else:
+            k_caches[li][:, :, pos] = k.astype(np.float32)
+            v_caches[li][:, :, pos] = v.astype(np.float32)
         a = np.stack([O.attention_decode_ref(k_caches[li][i], v_caches[li][i], q[i], pos)
                       for i in range(b)])
         a = _h(a).reshape(b, heads * head_dim)

@@ -14,6 +14,12 @@ What produces each fixture:
   ``gguf.quants.dequantize``; the script asserts they agree bit-for-bit.
 * ``q6k.npz``, ``q8_0.npz``   ``gguf.quants.dequantize`` (the reference's tests
   hold no host decoder for these formats).
+* ``q5_0.npz``   the reference's ``split_q5_0_weight`` (the three normalised
+  buffers, from ``packages/alloy-server/src/alloy_server/gguf/quant.py``) on random
+  22-byte wire blocks, and ``gguf.quants.dequantize`` of the same blocks.
+* ``attn_chunk.npz``   causal chunk attention over a q8_0 cache: the reference's
+  ``_quantize_ref`` + ``_ref_attention`` applied per query row, as its prefill test
+  does inline (``tests/kernels/test_kv_quant.py:466-479``).
 * ``kv_q8.npz``   the reference's ``_quantize_ref`` from
   ``tests/kernels/test_kv_quant.py`` (codes + scales), its dequantisation, and
   its float64 ``_ref_attention``.
@@ -109,6 +115,37 @@ def main() -> None:
     out = kvt["_ref_attention"](dk, dv, q.astype(np.float32), pos, group)
     np.savez_compressed(HERE / "kv_q8.npz", k=k, v=v, k_codes=kc, k_scales=ks, v_codes=vc,
                         v_scales=vs, q=q, pos=np.int64(pos), group=np.int64(group), attn=out)
+    # ---- Q5_0: the reference's own wire -> three-buffer split, gguf's decode of the wire blocks
+    import torch
+
+    split_ns: dict = {"np": np, "torch": torch}
+    tree = ast.parse((ref / "packages/alloy-server/src/alloy_server/gguf/quant.py").read_text())
+    fn = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == "split_q5_0_weight"]
+    exec(compile(ast.Module(body=fn, type_ignores=[]), "quant.py", "exec"), split_ns)
+    rng = np.random.default_rng(6)
+    n5, k5 = 6, 256
+    wire5 = rng.integers(0, 256, size=(n5, k5 // 32, 22), dtype=np.uint8)
+    wire5[:, :, 0:2] = rng.uniform(1e-4, 2e-3, size=(n5, k5 // 32)).astype(np.float16).view(np.uint8).reshape(
+        n5, k5 // 32, 2)
+    wire5 = wire5.reshape(n5, -1)
+    qw5, qh5, sc5 = split_ns["split_q5_0_weight"](weights=wire5, in_features=k5, out_features=n5)
+    w5 = dequantize(wire5.reshape(-1, 22), T.Q5_0).reshape(n5, k5)
+    np.savez_compressed(HERE / "q5_0.npz", wire=wire5, qweight=qw5.numpy(), qhigh=qh5.numpy(), scales=sc5.numpy(),
+                        w=w5.astype(np.float32))
+
+    # ---- chunk attention over a q8_0 cache (history + chunk both read back from the codes)
+    rng = np.random.default_rng(8)
+    kv_heads, group, d, start, chunk = 2, 2, 64, 40, 24
+    kf = (rng.standard_normal((kv_heads, start + chunk, d)) * 2).astype(np.float16)
+    vf = (rng.standard_normal((kv_heads, start + chunk, d)) * 2).astype(np.float16)
+    kc, ks = kvt["_quantize_ref"](kf)
+    vc, vs = kvt["_quantize_ref"](vf)
+    dk = kc.astype(np.float32) * np.repeat(ks.astype(np.float32), 32, axis=-1)
+    dv = vc.astype(np.float32) * np.repeat(vs.astype(np.float32), 32, axis=-1)
+    qc = rng.standard_normal((kv_heads * group, chunk, d)).astype(np.float16)
+    rows = [kvt["_ref_attention"](dk, dv, qc[:, i].astype(np.float32), start + i, group) for i in range(chunk)]
+    np.savez_compressed(HERE / "attn_chunk.npz", k=kf, v=vf, q=qc, start=np.int64(start), group=np.int64(group),
+                        attn=np.stack(rows, axis=1))
     print("gguf", getattr(gguf, "__version__", "?"), "fixtures written to", HERE)
 
 

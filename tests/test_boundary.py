@@ -5,6 +5,7 @@ validation behaves like the reference's."""
 import os
 import pathlib
 import re
+import sys
 
 import numpy as np
 import pytest
@@ -80,14 +81,18 @@ def test_ops_have_no_cpu_kernel():
 def test_validate_quant_buffers_errors():
     blk = torch.zeros((8, 288), dtype=torch.uint8)
     quant.GGUFQ4_KLinear(in_features=512, out_features=8, blocks=blk)
-    with pytest.raises(ValueError, match="not divisible"):
+    with pytest.raises(ValueError, match="multiple of 256"):
         quant.GGUFQ4_KLinear(in_features=500, out_features=8, blocks=blk)
     with pytest.raises(ValueError, match="shape"):
         quant.GGUFQ4_KLinear(in_features=512, out_features=9, blocks=blk)
     with pytest.raises(TypeError):
         quant.GGUFQ6_KLinear(in_features=256, out_features=8, qweight=torch.zeros((8, 210), dtype=torch.int8))
-    with pytest.raises(ValueError, match="expects buffers"):
+    with pytest.raises(ValueError, match="missing"):
         quant.GGUFQ8_0Linear(in_features=64, out_features=8, qweight=torch.zeros((8, 64), dtype=torch.int8))
+    with pytest.raises(ValueError, match="unexpected"):
+        quant.GGUFQ4_KLinear(in_features=512, out_features=8, blocks=blk, scales=blk)
+    assert quant.QUANT_FORMATS["q5_0"].buffer_names == ("qweight", "qhigh", "scales")
+    assert quant.QUANT_FORMATS["q6_k"].shapes(8, 512) == {"qweight": (8, 420)}
 
 
 def test_split_q8_0_weight_matches_oracle():
@@ -100,6 +105,77 @@ def test_split_q8_0_weight_matches_oracle():
         quant.split_q8_0_weight(weights=wire, in_features=64, out_features=6)
     with pytest.raises(TypeError):
         quant.split_q8_0_weight(weights=wire.astype(np.int8), in_features=96, out_features=6)
+
+
+def test_split_q5_0_weight_matches_reference_fixture(golden):
+    """The Q5_0 wire split against the buffers the reference's own split_q5_0_weight produced."""
+    from oracle import blocks as O
+    g = golden["q5_0"]
+    n, k = g["w"].shape
+    qw, qh, sc = quant.split_q5_0_weight(weights=g["wire"], in_features=k, out_features=n)
+    assert np.array_equal(qw.numpy(), g["qweight"]) and np.array_equal(qh.numpy(), g["qhigh"])
+    assert np.array_equal(sc.numpy().view(np.uint16), g["scales"].view(np.uint16))
+    oq, oh, os_ = O.split_q5_0(g["wire"])
+    assert np.array_equal(oq, g["qweight"]) and np.array_equal(oh, g["qhigh"])
+    assert np.array_equal(os_.view(np.uint16), g["scales"].view(np.uint16))
+    with pytest.raises(ValueError):
+        quant.split_q5_0_weight(weights=g["wire"], in_features=k - 32, out_features=n)
+
+
+REFERENCE = pathlib.Path(os.environ.get("ALLOY_REFERENCE", "/root/reference"))
+
+
+@pytest.mark.skipif(not (REFERENCE / "packages/alloy-server/src/alloy_server/gguf/quant.py").exists(),
+                    reason="needs the rayanht/alloy checkout")
+def test_reference_modules_bind_and_run_on_this_op_library():
+    """The reference's OWN ``alloy_server/gguf/quant.py`` and ``kv_format.py``, loaded unchanged from the
+    checkout, bind every ``torch.ops.alloy.*`` symbol they name at import time and trace through the
+    Meta kernels registered here (the device forward of the same ops is what the GPU tests check)."""
+    import importlib.util
+
+    def load(rel, name):
+        spec = importlib.util.spec_from_file_location(name, REFERENCE / rel)
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[name] = mod           # dataclasses resolve string annotations through sys.modules
+        spec.loader.exec_module(mod)
+        return mod
+
+    try:
+        rq = load("packages/alloy-server/src/alloy_server/gguf/quant.py", "_ref_alloy_quant")
+    except ImportError as e:          # a dependency of the reference module that this image lacks
+        pytest.skip(f"reference module dependency missing: {e}")
+    rk = load("packages/alloy-server/src/alloy_server/kv_format.py", "_ref_alloy_kv_format")
+    assert rq.GGUF_Q5_0_MM is torch.ops.alloy.gguf_q5_0_mm.default
+    assert set(rq.QUANT_FORMATS) == set(quant.QUANT_FORMATS)
+    for name, fmt in rq.QUANT_FORMATS.items():
+        mine = quant.QUANT_FORMATS[name]
+        assert fmt.align == mine.align and fmt.buffer_names == mine.buffer_names
+        assert fmt.mm_op is mine.mm_op and fmt.embed_op is mine.embed_op
+        for a, b in zip(fmt.buffers, mine.buffers):
+            assert a.dtype is b.dtype and all(a.cols(k) == b.cols(k) for k in (256, 4096, 14336))
+    # the reference's modules, built on meta buffers, run through this library's schemas
+    lin4 = rq.GGUFQ4_KLinear(in_features=512, out_features=24,
+                             blocks=torch.zeros((24, 288), dtype=torch.uint8, device="meta"))
+    lin6 = rq.GGUFQ6_KLinear(in_features=512, out_features=24,
+                             qweight=torch.zeros((24, 420), dtype=torch.uint8, device="meta"))
+    lin8 = rq.GGUFQ8_0Linear(in_features=64, out_features=8,
+                             qweight=torch.zeros((8, 64), dtype=torch.int8, device="meta"),
+                             scales=torch.zeros((8, 2), dtype=torch.float16, device="meta"))
+    x = torch.zeros((2, 3, 512), dtype=torch.float16, device="meta")
+    assert lin4(x).shape == (2, 3, 24) and lin6(x).shape == (2, 3, 24) and lin4(x).dtype == torch.float16
+    assert lin8(torch.zeros((5, 64), dtype=torch.bfloat16, device="meta")).shape == (5, 8)
+    emb = rq.GGUFQ4_KEmbedding(num_embeddings=24, embedding_dim=512,
+                               blocks=torch.zeros((24, 288), dtype=torch.uint8, device="meta"))
+    ids = torch.zeros((2, 7), dtype=torch.int64, device="meta")
+    assert emb(ids).shape == (2, 7, 512) and emb(ids).dtype == torch.float32
+    # identical wire splits
+    wire = synth.q8_0_wire(np.random.default_rng(1), 4, 64)
+    a, b = rq.split_q8_0_weight(weights=wire, in_features=64, out_features=4)
+    c, d = quant.split_q8_0_weight(weights=wire, in_features=64, out_features=4)
+    assert torch.equal(a, c) and torch.equal(b.view(torch.int16), d.view(torch.int16))
+    assert rk.Q8_0 == rk.KV_FORMATS["q8_0"] and rk.Q8_0.name == kv.Q8_0.name
+    assert (rk.Q8_0.block_elems, rk.Q8_0.group_tokens, rk.Q8_0.bits_per_elem_k) == \
+        (kv.Q8_0.block_elems, kv.Q8_0.group_tokens, kv.Q8_0.bits_per_elem_k)
 
 
 def test_kv_format_and_page_pool_host_logic():

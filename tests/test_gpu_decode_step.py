@@ -65,6 +65,55 @@ def test_decode_step_matches_oracle(batch):
     assert dec.launches_per_step > 0
 
 
+MID = llama.LlamaShape(layers=2, hidden=1024, ffn=2048, heads=8, kv_heads=2, head_dim=128, vocab=1024,
+                       rope_theta=10000.0, eps=1e-5)
+
+
+def _paged_caches(dec, ctx):
+    """Per layer the dequantised (B, KV_H, ctx, D) K and V rows the paged pools hold."""
+    ks, vs = [], []
+    for pool in dec.pools:
+        host = pool.pool.cpu().numpy()
+        per_seq = [[], []]
+        for i in range(dec.batch):
+            pages = dec.pools[0].pages_of(i)              # one page table serves every layer
+            for which in (0, 1):
+                raw = O.gather_pages(host[:, which], pages, ctx)
+                per_seq[which].append(O.kv_dequant_q8_0(*O.kv_unpack_blocks(raw)))
+        ks.append(np.stack(per_seq[0]))
+        vs.append(np.stack(per_seq[1]))
+    return ks, vs
+
+
+@pytest.mark.parametrize("batch", [16, 32])
+@pytest.mark.parametrize("kv_kind", ["f16", "q8_paged"])
+def test_decode_step_big_batch_head_dim_128(batch, kv_kind):
+    """Batch 16 and 32 of the decode step on a head_dim-128 shape (the tensor-core attention kernel
+    and the 9..64-token linear path), with the fp16 cache and with the paged q8_0 pool."""
+    ctx = 96
+    dec = llama.QuantLlamaDecoder(MID, batch, ctx, seed=4, d_scale=0.05, kv=kv_kind)
+    rng = np.random.default_rng(batch)
+    ids = rng.integers(0, MID.vocab, size=batch)
+    dec.ids.copy_(torch.from_numpy(ids))
+    if kv_kind == "f16":
+        kc = [k.float().cpu().numpy() for k in dec.k_cache]
+        vc = [v.float().cpu().numpy() for v in dec.v_cache]
+    else:
+        kc, vc = _paged_caches(dec, ctx)
+    ref_logits, _, _ = OD.decode_step(
+        ids, ctx - 1, O.dequant_q4_k(dec.embed.cpu().numpy()), _oracle_inputs(dec), dec.norm_final.cpu().numpy(),
+        O.dequant_q6_k(dec.head.cpu().numpy()), dec.inv_freq.cpu().numpy(), kc, vc, MID.heads, MID.kv_heads,
+        MID.head_dim, MID.eps, kv_q8=(kv_kind == "q8_paged"))
+    assert np.isfinite(ref_logits.astype(np.float32)).all()
+    dec.step()
+    torch.cuda.synchronize()
+    got = to_np(dec.logits)
+    _, mean = rel_errors(got, ref_logits.astype(np.float64), torch.float16)
+    ref64 = ref_logits.astype(np.float64)
+    worst = np.abs(got - ref64).max() / np.sqrt((ref64 ** 2).mean())
+    assert worst <= 1e-2 and mean <= 2e-3, (worst, mean)
+
+
 def test_decode_step_from_gguf_file(tmp_path):
     """A Llama-architecture GGUF file (written with gguf.GGUFWriter: permuted q/k rows, Q6_K and Q4_K
     v/down in alternating layers, tied head) served by the decoder equals the oracle's step on the

@@ -239,6 +239,26 @@ def test_attention_paged_q8_full_size_properties():
     out1 = torch.ops.alloy.attention_cache_q8_paged(q, nk, nv, pos, store.page_table, store.pool).clone()
     assert torch.isfinite(out1.float()).all()
 
+    # 0. the float64 oracle on sampled (sequence, query head) pairs, the shortest and the longest
+    #    sequence among them: pages gathered from the pool as the call left it (new token appended)
+    order_by_len = torch.argsort(lens).tolist()
+    picks = [(order_by_len[0], 0), (order_by_len[0], h - 1), (order_by_len[-1], 5), (order_by_len[-1], 30),
+             (order_by_len[b // 2], 17), (7, 9), (40, 22)]
+    out_np = out1.float().cpu().numpy()
+    for seq, head in picks:
+        n_tok = int(lens[seq]) + 1
+        kvh = head // group
+        pages = torch.tensor(store.pages_of(seq), device=DEV)
+        slabs = store.pool[pages][:, :, kvh].cpu().numpy()                # (P, 2, 16, 136)
+        rows = []
+        for which in (0, 1):
+            raw = slabs[:, which].reshape(-1, slabs.shape[-1])[:n_tok]    # (tokens, 136)
+            c, sc_ = O.kv_unpack_blocks(raw)
+            rows.append(O.kv_dequant_q8_0(c, sc_)[None])                  # (1, tokens, D)
+        ref = O.attention_decode_ref(rows[0], rows[1], q[seq, head, 0].float().cpu().numpy()[None], n_tok - 1)
+        assert np.abs(out_np[seq, head, 0] - ref[0]).max() < 2e-3, (seq, head)
+        assert_close(out_np[seq, head, 0], ref[0], torch.float16, f"full-size paged, sequence {seq} head {head}")
+
     # 1. another physical placement of the same pages
     perm = torch.randperm(total, generator=cpu).to(DEV)
     pool2 = torch.empty_like(base_pool)

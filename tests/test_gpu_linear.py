@@ -204,6 +204,51 @@ def test_linear_allreduce_single_rank(fmt, n, k):
         ex.close()
 
 
+def test_peer_wait_runs_out_and_is_reported():
+    """A peer that never delivers: a two-rank descriptor on ONE GPU whose second buffer nobody writes,
+    with a short spin limit.  The kernel must come back, the sticky device error word must be set
+    (the host then drops the peer path), and the next call on a sound exchange must be clean."""
+    import ctypes as C
+
+    from alloy_b200 import _lib, tp
+    rng = np.random.default_rng(5)
+    n, k = 4096, 4096
+    w_dev, w = _weights("q4_k", rng, n, k)
+    L = _lib.load()
+    assert L.alloyb_device_error(1) == 0
+    mine, silent = tp.PeerExchange(max_n=n), tp.PeerExchange(max_n=n)
+    try:
+        peers = (C.c_void_p * 8)(mine.desc.peer[0], silent.desc.peer[0], *([None] * 6))
+        desc = _lib.TP(2, 0, n, 5000, peers)
+        x = _dev(synth.activations(rng, 1, k))
+        y = torch.empty((1, n), dtype=torch.float16, device=DEV)
+        wd = (_lib.Weight * 1)(_lib.Weight(_lib.Q4_K, n, w_dev[0].data_ptr(), None, 0, y.data_ptr(), 0))
+        rc = L.alloyb_linear_allreduce(x.data_ptr(), 1, k, _lib.F16, wd, None, C.byref(desc),
+                                       torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        torch.cuda.synchronize()                       # the launch returned: no hang
+        assert L.alloyb_device_error(1) != 0           # ... and said so
+        assert L.alloyb_device_error(0) == 0           # cleared by the read above
+        # a misaligned activation pointer under an exchange is a hard error, never "not taken"
+        xo = torch.zeros(k + 8, dtype=torch.float16, device=DEV)[1:k + 1]
+        rc = L.alloyb_linear_allreduce(xo.data_ptr(), 1, k, _lib.F16, wd, None, C.byref(desc),
+                                       torch.cuda.current_stream().cuda_stream)
+        assert rc == -2
+    finally:
+        torch.cuda.synchronize()
+        mine.close()
+        silent.close()
+    ex = tp.PeerExchange(max_n=n)
+    try:
+        x = synth.activations(rng, 1, k)
+        y = ops.linear_allreduce(_dev(x), "q4_k", w_dev[0], None, ex)
+        assert_close(to_np(y), O.mm_ref_f64(x, w), torch.float16, "after a timed-out call")
+        assert L.alloyb_device_error(1) == 0
+    finally:
+        torch.cuda.synchronize()
+        ex.close()
+
+
 # A K shard whose rows are not a multiple of 16 bytes long (Q6_K, 14 super-blocks = 2940 bytes)
 # keeps a 16-byte pitch: the op takes the strided view as it is.
 @pytest.mark.parametrize("world", [2, 4])

@@ -1,0 +1,85 @@
+"""Two-GPU parity of the row-parallel linear whose all-reduce runs inside the GEMV launch over peer
+memory: two child processes (one per GPU, NCCL for set-up only) against the float64 oracle and
+against the unsharded single-GPU kernel.  Skipped on a box with fewer than two GPUs."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    import alloy_b200  # noqa: F401
+    from alloy_b200 import _lib, ops, synth, tp
+    from oracle import blocks as O
+    from tests._util import rel_errors
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    out = {}
+    try:
+        ex = tp.PeerExchange(8192, rank, world, None, dev)
+        assert tp.agree(True, None, dev)
+        # 1. small shapes against the float64 oracle of the UNSHARDED product, three epochs each
+        rng = np.random.default_rng(77)                       # same draws on both ranks
+        worst = [0.0, 0.0]
+        for fmt, n, k in (("q4_k", 1024, 2048 * world), ("q6_k", 1000, 2048 * world)):
+            blk = synth.q4k_blocks(rng, n, k) if fmt == "q4_k" else synth.q6k_blocks(rng, n, k)
+            w = O.dequant_q4_k(blk) if fmt == "q4_k" else O.dequant_q6_k(blk)
+            shard = tp.shard_cols(torch.from_numpy(blk).to(dev), fmt, rank, world)
+            for _ in range(3):
+                x = synth.activations(rng, 1, k)
+                r = synth.activations(rng, 1, n)
+                xs = torch.from_numpy(np.ascontiguousarray(x[:, tp.k_slice(k, rank, world)])).to(dev)
+                torch.cuda.synchronize()
+                dist.barrier()
+                y = ops.linear_allreduce(xs, fmt, shard, torch.from_numpy(r).to(dev), ex)
+                assert y is not None
+                lin = torch.from_numpy(O.mm_ref_f64(x, w)).to(torch.float16).double().numpy()
+                mx, mean = rel_errors(y.float().cpu().numpy(), lin + r.astype(np.float64), torch.float16)
+                worst = [max(worst[0], mx), max(worst[1], mean)]
+        out["oracle"] = worst
+        # 2. the 70B o_proj / down shard shapes against the unsharded single-GPU kernel
+        torch.cuda.synchronize()
+        dist.barrier()
+        out["per_op"] = tp.check_row_parallel(ex, rank, world, None, dev)
+        torch.cuda.synchronize()
+        out["device_error"] = int(_lib.load().alloyb_device_error(1))
+        dist.barrier()
+        ex.close()
+        q.put((rank, out))
+    except Exception as e:  # noqa: BLE001 - reported to the parent
+        q.put((rank, repr(e)))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:  # noqa: BLE001
+            pass
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_allreduce_two_gpus():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 33500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=600) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+    for rank in range(world):
+        res = results[rank]
+        assert isinstance(res, dict), res
+        assert res["oracle"][0] <= 1e-2 and res["oracle"][1] <= 1e-3, res
+        assert res["per_op"]["pass"] and res["per_op"]["fused"]["calls"] == 6, res
+        assert res["device_error"] == 0, res

@@ -99,3 +99,53 @@ def test_against_gguf_package(fmt):
         ref = dequantize(b.reshape(-1, 34), T.Q8_0).reshape(32, 1024)
         got = O.dequant_q8_0(*O.split_q8_0(b))
     assert _same_bits(got, ref.astype(np.float32))
+
+
+def test_q5_0_golden(golden):
+    """Q5_0: the oracle's wire split equals the reference's own split_q5_0_weight, and its decode of
+    the three buffers equals gguf's decode of the wire blocks, bit for bit."""
+    g = golden["q5_0"]
+    qw, qh, sc = O.split_q5_0(g["wire"])
+    assert np.array_equal(qw, g["qweight"]) and np.array_equal(qh, g["qhigh"])
+    assert np.array_equal(sc.view(np.uint16), g["scales"].view(np.uint16))
+    w = O.dequant_q5_0(qw, qh, sc)
+    assert w.dtype == np.float32 and np.array_equal(w.view(np.uint32), g["w"].view(np.uint32))
+
+
+def test_attention_chunk_golden(golden):
+    """Causal chunk attention: the oracle against the reference's _ref_attention applied per query row."""
+    g = golden["attn_chunk"]
+    kc, ks = O.kv_quantize_q8_0(g["k"])
+    vc, vs = O.kv_quantize_q8_0(g["v"])
+    out = O.attention_chunk_ref(O.kv_dequant_q8_0(kc, ks), O.kv_dequant_q8_0(vc, vs),
+                                g["q"].astype(np.float32), int(g["start"]))
+    assert out.shape == g["attn"].shape
+    assert np.abs(out - g["attn"]).max() < 1e-12
+
+
+def test_moe_router_identity_and_composition():
+    """softmax over the top-k raw logits == renormalised top-k of the full softmax (the identity the
+    reference's router relies on), and a one-expert, top-1 routed op equals the plain gated MLP."""
+    import torch
+
+    rng = np.random.default_rng(11)
+    t_n, e_n, k = 5, 16, 4
+    logits = rng.standard_normal((t_n, e_n)).astype(np.float32)
+    p = torch.softmax(torch.from_numpy(logits).double(), -1)
+    top, idx = torch.topk(p, k, dim=-1)
+    w_hf = (top / top.sum(-1, keepdim=True)).numpy()
+    for t in range(t_n):
+        order = np.lexsort((np.arange(e_n), -logits[t].astype(np.float64)))[:k]
+        assert order.tolist() == idx[t].tolist()
+        sel = logits[t, order].astype(np.float64)
+        w = np.exp(sel - sel[0])
+        assert np.allclose(w / w.sum(), w_hf[t], rtol=1e-12, atol=0)
+    hdim, inter = 256, 256
+    gu = synth.q4k_blocks(rng, 2 * inter, hdim)[None]
+    dn = synth.q6k_blocks(rng, hdim, inter)[None]
+    x = rng.standard_normal((2, hdim)).astype(np.float32)
+    y = O.moe_routed_ref(x, np.zeros((2, 1), np.float32), gu, dn, 1, inter)
+    wgu = O.dequant_q4_k(gu[0]).astype(np.float64)
+    h = (O.silu(wgu[:inter] @ x.T.astype(np.float64)) * (wgu[inter:] @ x.T.astype(np.float64))).astype(np.float32)
+    ref = (O.dequant_q6_k(dn[0]).astype(np.float64) @ h.astype(np.float64)).T
+    assert np.allclose(y, ref, rtol=1e-12, atol=1e-12)

@@ -69,6 +69,36 @@ def test_tp_sharding_world2_gloo():
     assert sorted(results) == [(0, "ok"), (1, "ok")], results
 
 
+def _agree_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # rank 1 reports a failed peer set-up / a wait that ran out: BOTH ranks must leave the peer path
+        got = [tp.agree(True), tp.agree(rank != 1), tp.agree(rank != 0), tp.agree(False)]
+        q.put((rank, got))
+    except Exception as e:
+        q.put((rank, repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_fallback_decision_is_collective_world2_gloo():
+    """The choice between the fused peer-memory exchange and NCCL is one MIN all-reduce: a failure
+    seen by one rank only (its IPC mapping failed, its wait on a peer ran out) moves every rank."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_agree_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=180) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    assert results == {0: [True, False, False, False], 1: [True, False, False, False]}, results
+    assert tp.agree(True) and not tp.agree(False)          # no process group: the local answer
+
+
 def test_shard_helpers_single_process():
     w = torch.arange(4 * 2 * 144, dtype=torch.int64).remainder(251).to(torch.uint8).reshape(4, 288)
     a, b = tp.shard_cols(w, "q4_k", 0, 2), tp.shard_cols(w, "q4_k", 1, 2)
