@@ -13,7 +13,7 @@
 // (Gp = heads per CTA rounded up to a power of two), i.e. 64 (token, head) rows, 16 per warp; the
 // K/V tile in shared memory is shared by every row.  S = Q K^T and O += P V run on
 // mma.sync.m16n8k16 (fp16 operands, fp32 accumulation) with ldmatrix fragment loads; the softmax
-// is the usual online one in the exp2 frame; P enters the second product as fp16.
+// is the usual online one in the exp2 frame; P enters the second product as fp16 hi + lo halves.
 #include "kv.cuh"
 
 namespace alloyb {
@@ -23,6 +23,7 @@ constexpr int ROWS = 64;          // (token, head) rows per CTA
 constexpr int KT = 64;            // KV tokens per tile
 constexpr int WARPS = 4;
 constexpr float NEG_BIG = -1.0e30f;
+constexpr float P_BIAS = 64.0f;   // keeps small probabilities out of fp16's subnormal range in the P * V product
 
 struct Params {
     const void* q;
@@ -254,31 +255,6 @@ __global__ void __launch_bounds__(WARPS * 32) attn_chunk_kernel(const Params P) 
             alpha[rr] = exp2f(m_run[rr] - m_new);
             m_run[rr] = m_new;
         }
-        float ls[2] = {0.f, 0.f};
-        uint32_t pa[KT / 16][4];
-#pragma unroll
-        for (int n = 0; n < KT / 8; ++n) {
-            float p[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int rr = e >> 1;
-                p[e] = s[n][e] > 0.5f * NEG_BIG ? exp2f(s[n][e] - m_run[rr]) : 0.f;
-            }
-            // the row sum is taken over the fp16 values that enter the product
-            const uint32_t p01 = pack_h2(p[0], p[1]), p23 = pack_h2(p[2], p[3]);
-            const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&p01));
-            const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&p23));
-            ls[0] += f01.x + f01.y;
-            ls[1] += f23.x + f23.y;
-            pa[n >> 1][(n & 1) * 2] = p01;
-            pa[n >> 1][(n & 1) * 2 + 1] = p23;
-        }
-#pragma unroll
-        for (int rr = 0; rr < 2; ++rr) {
-            ls[rr] += __shfl_xor_sync(0xffffffffu, ls[rr], 1);
-            ls[rr] += __shfl_xor_sync(0xffffffffu, ls[rr], 2);
-            l_run[rr] = l_run[rr] * alpha[rr] + ls[rr];
-        }
 #pragma unroll
         for (int i = 0; i < D / 8; ++i) {
             o[i][0] *= alpha[0];
@@ -286,16 +262,49 @@ __global__ void __launch_bounds__(WARPS * 32) attn_chunk_kernel(const Params P) 
             o[i][2] *= alpha[1];
             o[i][3] *= alpha[1];
         }
-        // ---- O += P V
+        // ---- O += P V, sixteen tokens at a time.  P enters the tensor core as fp16 hi + lo halves (two
+        // products), which keeps ~22 bits of it: a single fp16 rounding of P alone would cost ~1e-3 of
+        // the output's rms, more than the parity tolerance allows on outputs that cancel to near zero.
+        float ls[2] = {0.f, 0.f};
 #pragma unroll
         for (int k2 = 0; k2 < KT / 16; ++k2) {
+            uint32_t ph[4], pl[4];
+#pragma unroll
+            for (int nn = 0; nn < 2; ++nn) {
+                const int n = 2 * k2 + nn;
+                float pv[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int rr = e >> 1;
+                    pv[e] = s[n][e] > 0.5f * NEG_BIG ? exp2f(s[n][e] - m_run[rr]) : 0.f;
+                }
+                ls[0] += pv[0] + pv[1];
+                ls[1] += pv[2] + pv[3];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) pv[e] *= P_BIAS;
+                const uint32_t h01 = pack_h2(pv[0], pv[1]), h23 = pack_h2(pv[2], pv[3]);
+                const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&h01));
+                const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&h23));
+                ph[nn * 2] = h01;
+                ph[nn * 2 + 1] = h23;
+                pl[nn * 2] = pack_h2(pv[0] - f01.x, pv[1] - f01.y);
+                pl[nn * 2 + 1] = pack_h2(pv[2] - f23.x, pv[3] - f23.y);
+            }
 #pragma unroll
             for (int n2 = 0; n2 < D / 16; ++n2) {
                 uint32_t bv[4];
                 ldsm_x4_t(v_addr + (k2 * 16 * PITCH) * 2 + n2 * 32, bv);
-                mma16816(o[2 * n2], pa[k2], bv[0], bv[1]);
-                mma16816(o[2 * n2 + 1], pa[k2], bv[2], bv[3]);
+                mma16816(o[2 * n2], ph, bv[0], bv[1]);
+                mma16816(o[2 * n2], pl, bv[0], bv[1]);
+                mma16816(o[2 * n2 + 1], ph, bv[2], bv[3]);
+                mma16816(o[2 * n2 + 1], pl, bv[2], bv[3]);
             }
+        }
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            ls[rr] += __shfl_xor_sync(0xffffffffu, ls[rr], 1);
+            ls[rr] += __shfl_xor_sync(0xffffffffu, ls[rr], 2);
+            l_run[rr] = l_run[rr] * alpha[rr] + ls[rr];
         }
     }
 
@@ -305,7 +314,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_chunk_kernel(const Params P) 
         if (!row_live[rr]) continue;
         const int r = warp * 16 + g + 8 * rr;
         const int tl = r >> gp_shift, hg = r & (P.Gp - 1);
-        const float inv = l_run[rr] > 0.f ? 1.0f / l_run[rr] : 0.f;
+        const float inv = l_run[rr] > 0.f ? 1.0f / (P_BIAS * l_run[rr]) : 0.f;
         const int64_t base = ((static_cast<int64_t>(b) * P.S + tok0 + tl) * P.H + kvh * P.G + hgrp * 8 + hg) * D;
 #pragma unroll
         for (int i = 0; i < D / 8; ++i)

@@ -25,6 +25,11 @@ constexpr int D = 128;
 constexpr int NKP = D / 32;
 constexpr int WARPS = 4;
 constexpr float NEG_BIG = -1.0e30f;
+// Probabilities enter the P * V product as fp16 (hi + lo halves).  At long contexts a typical
+// p * (block scale) is ~1e-5, inside fp16's subnormal range, where the two halves together keep
+// only ~10 bits.  The A operand is therefore biased by 2^6 (taken out again in the epilogue):
+// the largest possible value, 64 * 1 * 516 (the q8_0 scale of a block holding 65504), still fits.
+constexpr float P_BIAS = 64.0f;
 constexpr int SLAB = PAGE_TOKENS * NKP * KV_BLOCK_BYTES;     // 2176 bytes: one page of K (or V) of one head
 constexpr uint32_t SPIN = 1u << 22;
 
@@ -338,12 +343,13 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) vtok[i] = min(tok0 + (i >> 1) * 8 + 2 * t + (i & 1), t1 - 1);
         // P enters the tensor core as fp16 hi + lo halves (two products), which keeps ~22 bits of it
-        uint32_t pa0 = pack_h2(p[0][0], p[0][1]), pa2 = pack_h2(p[1][0], p[1][1]);
+        const float pb[4] = {p[0][0] * P_BIAS, p[0][1] * P_BIAS, p[1][0] * P_BIAS, p[1][1] * P_BIAS};
+        uint32_t pa0 = pack_h2(pb[0], pb[1]), pa2 = pack_h2(pb[2], pb[3]);
         uint32_t pl0, pl2;
         {
             const float2 r0 = unpack_h2(pa0), r2 = unpack_h2(pa2);
-            pl0 = pack_h2(p[0][0] - r0.x, p[0][1] - r0.y);
-            pl2 = pack_h2(p[1][0] - r2.x, p[1][1] - r2.y);
+            pl0 = pack_h2(pb[0] - r0.x, pb[1] - r0.y);
+            pl2 = pack_h2(pb[2] - r2.x, pb[3] - r2.y);
         }
 #pragma unroll
         for (int kp = 0; kp < NKP; ++kp) {
@@ -384,7 +390,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                     b1[e] = prmt(T[e], 0u, 0x4342u);
                 }
                 // P' = p * (block scale of the token) as fp16 hi + lo; keep its sum for the +128
-                const float f0 = p[0][0] * vs[0], f1 = p[0][1] * vs[1], f2 = p[1][0] * vs[2], f3 = p[1][1] * vs[3];
+                const float f0 = pb[0] * vs[0], f1 = pb[1] * vs[1], f2 = pb[2] * vs[2], f3 = pb[3] * vs[3];
                 pa0 = pack_h2(f0, f1);
                 pa2 = pack_h2(f2, f3);
                 const float2 r0 = unpack_h2(pa0), r2 = unpack_h2(pa2);
@@ -395,13 +401,28 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
             }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                float c[4] = {o[kp * 4 + e][0], o[kp * 4 + e][1], zz2, zz3};
-                mma(c, pa0, pa2, b0[e], b1[e]);
-                mma(c, pl0, pl2, b0[e], b1[e]);
-                o[kp * 4 + e][0] = c[0];
-                o[kp * 4 + e][1] = c[1];
-                zz2 = c[2];
-                zz3 = c[3];
+                if (Q8) {
+                    // Codes carry a +128 offset, so the accumulator would grow ~100x faster than the
+                    // signal it holds; the tensor core's accumulate step truncates, and over thousands
+                    // of tiles that bias reached 1e-3 of the output.  Each tile's product therefore
+                    // starts from zero and is added to the running sum on the CUDA cores (round to
+                    // nearest), where the offset is later taken out through ocorr.
+                    float c[4] = {0.f, 0.f, zz2, zz3};
+                    mma(c, pa0, pa2, b0[e], b1[e]);
+                    mma(c, pl0, pl2, b0[e], b1[e]);
+                    o[kp * 4 + e][0] += c[0];
+                    o[kp * 4 + e][1] += c[1];
+                    zz2 = c[2];
+                    zz3 = c[3];
+                } else {
+                    float c[4] = {o[kp * 4 + e][0], o[kp * 4 + e][1], zz2, zz3};
+                    mma(c, pa0, pa2, b0[e], b1[e]);
+                    mma(c, pl0, pl2, b0[e], b1[e]);
+                    o[kp * 4 + e][0] = c[0];
+                    o[kp * 4 + e][1] = c[1];
+                    zz2 = c[2];
+                    zz3 = c[3];
+                }
             }
         }
         __syncwarp();
@@ -420,7 +441,14 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
 #pragma unroll
             for (int e = 0; e < 4; ++e)
 #pragma unroll
-                for (int c = 0; c < 2; ++c) o[kp * 4 + e][c] = fmaf(o[kp * 4 + e][c], 16777216.0f, -128.0f * cs);
+                for (int c = 0; c < 2; ++c)
+                    o[kp * 4 + e][c] = fmaf(o[kp * 4 + e][c], 16777216.0f / P_BIAS, (-128.0f / P_BIAS) * cs);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < NKP * 4; ++i) {
+            o[i][0] *= 1.0f / P_BIAS;
+            o[i][1] *= 1.0f / P_BIAS;
         }
     }
     __syncthreads();                                   // every warp is done with the page stages

@@ -17,6 +17,12 @@ def _dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
 
 
+def _deq16(codes, scales):
+    """What a chunk reads from a q8_0 cache: fp16(code * scale), the rounding of the reference's
+    dequantise-to-scratch step (packages/alloy-metal/src/alloy/std/kv_quant.py:73-108)."""
+    return O.kv_dequant_q8_0(codes, scales).astype(np.float16).astype(np.float32)
+
+
 def test_attention_cache_q8_prefill_branch_reference_case():
     """The reference's own prefill case (tests/kernels/test_kv_quant.py:389-480): KV_H 2, group 2,
     D 64, S_MAX 512, 200 cached tokens, a 64-token chunk, cache_pos an arange, fp32 q.  The chunk
@@ -45,10 +51,15 @@ def test_attention_cache_q8_prefill_branch_reference_case():
     assert not caches[0][0, :, start + chunk:].any()
     k_full = O.kv_dequant_q8_0(np.concatenate([hc_k, nc_k], 1), np.concatenate([hs_k, ns_k], 1))
     v_full = O.kv_dequant_q8_0(np.concatenate([hc_v, nc_v], 1), np.concatenate([hs_v, ns_v], 1))
-    ref = O.attention_chunk_ref(k_full, v_full, q.astype(np.float16).astype(np.float64), start)
+    q16 = q.astype(np.float16).astype(np.float64)
     got = out[0].cpu().numpy()
-    assert np.abs(got - ref).max() < 2e-2            # the reference test's bound
-    assert_close(got, ref, torch.float32, "q8 prefill branch")
+    # the reference test's own yardstick and bound: unrounded code * scale, max abs < 2e-2
+    assert np.abs(got - O.attention_chunk_ref(k_full, v_full, q16, start)).max() < 2e-2
+    # the path's semantics (K/V rounded to fp16 as the reference's scratch holds them): parity tolerance
+    kc, ksc = np.concatenate([hc_k, nc_k], 1), np.concatenate([hs_k, ns_k], 1)
+    vc, vsc = np.concatenate([hc_v, nc_v], 1), np.concatenate([hs_v, ns_v], 1)
+    assert_close(got, O.attention_chunk_ref(_deq16(kc, ksc), _deq16(vc, vsc), q16, start), torch.float32,
+                 "q8 prefill branch")
 
 
 def test_attention_chunk_golden_fixture(golden):
@@ -65,7 +76,9 @@ def test_attention_chunk_golden_fixture(golden):
                                              torch.tensor([start], device=DEV), *caches, -1.0, 0, False)
     assert np.array_equal(caches[0][0].cpu().numpy(), kc)                 # write_kv=False: untouched
     assert np.abs(to_np(out)[0] - g["attn"]).max() < 2e-2
-    assert_close(to_np(out)[0], g["attn"], torch.float16, "chunk golden")
+    ref16 = O.attention_chunk_ref(_deq16(kc, ks), _deq16(vc, vs), g["q"].astype(np.float64), start)
+    assert np.abs(ref16 - g["attn"]).max() < 5e-3          # the fp16 rounding of K/V is all that separates them
+    assert_close(to_np(out)[0], ref16, torch.float16, "chunk golden")
 
 
 @pytest.mark.parametrize("b,kv_h,group,d,start,chunk,dtype", [
@@ -145,8 +158,7 @@ def test_attention_paged_q8_chunk_per_sequence_starts():
         kraw, vraw = O.kv_pack_blocks(kc, ks), O.kv_pack_blocks(vc, vs)
         for i, pg in enumerate(store.pages_of(s)):
             host[pg, 0], host[pg, 1] = kraw[:, i * 16:(i + 1) * 16], vraw[:, i * 16:(i + 1) * 16]
-        refs.append(O.attention_chunk_ref(O.kv_dequant_q8_0(kc, ks), O.kv_dequant_q8_0(vc, vs),
-                                          q[s].astype(np.float64), starts[s]))
+        refs.append(O.attention_chunk_ref(_deq16(kc, ks), _deq16(vc, vs), q[s].astype(np.float64), starts[s]))
     assert np.array_equal(store.pool.cpu().numpy(), host)
     assert np.abs(to_np(out) - np.stack(refs)).max() < 2e-2
     assert_close(to_np(out), np.stack(refs), torch.float16, "paged chunk")
