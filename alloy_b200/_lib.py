@@ -48,6 +48,30 @@ class TP(C.Structure):
     ]
 
 
+class Matrix(C.Structure):
+    """Mirror of ``alloyb_matrix``."""
+
+    _fields_ = [("format", C.c_int), ("N", C.c_int), ("data", C.c_void_p), ("row_bytes", C.c_int64)]
+
+
+class DecoderLayer(C.Structure):
+    """Mirror of ``alloyb_decoder_layer``."""
+
+    _fields_ = [("wq", Matrix), ("wk", Matrix), ("wv", Matrix), ("wo", Matrix), ("wg", Matrix), ("wu", Matrix),
+                ("wd", Matrix), ("norm_in", C.c_void_p), ("norm_post", C.c_void_p), ("k0", C.c_void_p),
+                ("k1", C.c_void_p), ("v0", C.c_void_p), ("v1", C.c_void_p)]
+
+
+class DecoderDesc(C.Structure):
+    """Mirror of ``alloyb_decoder_desc``."""
+
+    _fields_ = [("n_layers", C.c_int), ("hidden", C.c_int), ("ffn", C.c_int), ("heads", C.c_int),
+                ("kv_heads", C.c_int), ("head_dim", C.c_int), ("eps", C.c_float), ("kv_layout", C.c_int),
+                ("S_max", C.c_int), ("num_pages", C.c_int64), ("layers", C.POINTER(DecoderLayer)),
+                ("norm_final", C.c_void_p), ("head", Matrix), ("inv_freq", C.c_void_p), ("pos", C.c_void_p),
+                ("hidden_io", C.c_void_p), ("logits", C.c_void_p), ("tp", C.POINTER(TP))]
+
+
 _p, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 
 # name -> (restype, argtypes); must list every symbol the header declares.
@@ -94,6 +118,11 @@ SIGNATURES = {
                                _i64, _f, _p, _p]),
     "alloyb_moe_workspace_bytes": (_sz, [_i, _i, _i]),
     "alloyb_moe_routed": (_i, [_p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _sz, _p]),
+    "alloyb_decoder_create": (_i, [C.POINTER(DecoderDesc), C.POINTER(_p)]),
+    "alloyb_decoder_step": (_i, [_p, _p]),
+    "alloyb_decoder_phases": (_i, [_p]),
+    "alloyb_decoder_status": (_i, [_p, C.POINTER(C.c_int32), _p]),
+    "alloyb_decoder_destroy": (_i, [_p]),
     "alloyb_rms_norm": (_i, [_p, _p, _p, _i, _i, _f, _i, _p]),
     "alloyb_rope_inplace": (_i, [_p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _p]),
     "alloyb_silu_mul": (_i, [_p, _p, _p, _i64, _i, _p]),

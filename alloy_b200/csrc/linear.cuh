@@ -35,6 +35,7 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
 int try_gemv_stream_mixed(const void* x, int M, int K, int dtype, const WeightSeg* seg, int n_seg, const void* residual,
                           const void* norm_w, float eps, cudaStream_t stream);
 int gemv_stream_device_error(int clear);
+int decode_layer_device_error(int clear);
 
 // tcgen05 dequant-GEMM for prefill-sized M (one matrix).
 int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, cudaStream_t st);

@@ -824,7 +824,7 @@ extern "C" int alloyb_device_error(int clear) {
     cudaError_t e = cudaMemcpyFromSymbol(&v, alloyb::g_device_error, sizeof(int));
     if (e != cudaSuccess) { alloyb::set_cuda_error(e); return ALLOYB_E_CUDA; }
     const int v_tc = alloyb::gemm_tc_device_error(clear) | alloyb::attn_mma_device_error(clear) |
-                     alloyb::gemv_stream_device_error(clear);
+                     alloyb::gemv_stream_device_error(clear) | alloyb::decode_layer_device_error(clear);
     if (clear && v) {
         const int z = 0;
         e = cudaMemcpyToSymbol(alloyb::g_device_error, &z, sizeof(int));

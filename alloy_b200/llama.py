@@ -62,6 +62,69 @@ class LayerWeights:
 
 
 
+_FMT_CODE = {"q4_k": 0, "q6_k": 1}
+
+
+class _FusedStep:
+    """The decoder's layers handed to ``alloyb_decoder_create``: one persistent launch per step."""
+
+    def __init__(self, dec: "QuantLlamaDecoder") -> None:
+        import ctypes as C
+
+        from . import _lib
+        from ._lib import DecoderDesc, DecoderLayer, Matrix
+
+        s = dec.shape
+        self._L = L = _lib.load()
+        dev = dec.device
+        self.hidden = torch.zeros(s.hidden, dtype=torch.float16, device=dev)
+        self.logits = torch.zeros(dec.vocab_l, dtype=torch.float16, device=dev)
+
+        def mat(w: torch.Tensor, fmt: str) -> Matrix:
+            if fmt not in _FMT_CODE:
+                raise ValueError(f"format {fmt} is outside the one-launch step")
+            if w.stride(1) != 1:
+                raise ValueError("packed rows must have unit inner stride")
+            pitch = 0 if w.stride(0) == w.shape[1] else w.stride(0)
+            return Matrix(_FMT_CODE[fmt], w.shape[0], w.data_ptr(), pitch)
+
+        layers = (DecoderLayer * len(dec.layers))()
+        paged = dec.kv_kind == "q8_paged"
+        for li, lw in enumerate(dec.layers):
+            if paged:
+                pool = dec.pools[li]
+                k0, k1, v0, v1 = pool.pool.data_ptr(), pool.page_table.data_ptr(), None, None
+            else:
+                k0, k1, v0, v1 = dec.k_cache[li].data_ptr(), None, dec.v_cache[li].data_ptr(), None
+            layers[li] = DecoderLayer(mat(lw.wq, lw.fmt["wq"]), mat(lw.wk, lw.fmt["wk"]), mat(lw.wv, lw.fmt["wv"]),
+                                      mat(lw.wo, lw.fmt["wo"]), mat(lw.wg, lw.fmt["wg"]), mat(lw.wu, lw.fmt["wu"]),
+                                      mat(lw.wd, lw.fmt["wd"]), lw.norm_in.data_ptr(), lw.norm_post.data_ptr(),
+                                      k0, k1, v0, v1)
+        self._layers = layers
+        if paged:
+            s_max, n_pages = dec.pools[0].page_table.shape[1] * 16, dec.pools[0].pool.shape[0]
+        else:
+            s_max, n_pages = dec.k_cache[0].shape[2], 0
+        ex = dec.exchange
+        desc = DecoderDesc(len(dec.layers), s.hidden, dec.ffn_l, dec.heads_l, dec.kv_heads_l, s.head_dim, s.eps,
+                           _lib.KV_Q8_PAGED if paged else _lib.KV_F16, s_max, n_pages, layers,
+                           dec.norm_final.data_ptr(), mat(dec.head, dec.head_fmt), dec.inv_freq.data_ptr(),
+                           dec.pos.data_ptr(), self.hidden.data_ptr(), self.logits.data_ptr(),
+                           C.pointer(ex.desc) if ex is not None and ex.world > 1 else None)
+        self._handle = C.c_void_p()
+        _lib.check(L.alloyb_decoder_create(C.byref(desc), C.byref(self._handle)), "alloyb_decoder_create")
+        self.phases = int(L.alloyb_decoder_phases(self._handle))
+
+    def step(self) -> None:
+        from . import _lib
+        _lib.check(self._L.alloyb_decoder_step(self._handle, ops._stream()), "alloyb_decoder_step")
+
+    def close(self) -> None:
+        if self._handle:
+            self._L.alloyb_decoder_destroy(self._handle)
+            self._handle = None
+
+
 class QuantLlamaDecoder:
     """Q4_K_M Llama-shape decoder for one decode step per call: random-init (seeded) weights, or
     the tensors of a GGUF checkpoint (``weights``: ``gguf_loader.LlamaWeights``, unsharded)."""
@@ -69,7 +132,7 @@ class QuantLlamaDecoder:
     def __init__(self, shape: LlamaShape, batch: int, context: int, *, device="cuda", seed: int = 0,
                  kv: str = "f16", tp_rank: int = 0, tp_size: int = 1, process_group=None,
                  dtype: torch.dtype = torch.float16, d_scale: float = 1.0, centered: bool = False, peer_allreduce: bool = True,
-                 tp_dry: bool = False, weights=None) -> None:
+                 tp_dry: bool = False, weights=None, one_launch: bool | None = None) -> None:
         if kv not in ("f16", "q8_paged"):
             raise ValueError(f"kv must be 'f16' or 'q8_paged', got {kv!r}")
         if shape.heads % tp_size or shape.kv_heads % tp_size or shape.ffn % (256 * tp_size) \
@@ -160,6 +223,24 @@ class QuantLlamaDecoder:
         self.logits: torch.Tensor | None = None
         self._graph: torch.cuda.CUDAGraph | None = None
         self.launches_per_step = 0
+        # One sequence: the whole step runs as one persistent launch (``alloyb_decoder_step``) when the
+        # shape is inside what that kernel is built for; ``one_launch=False`` keeps the op-by-op step.
+        self._fused = None
+        self.one_launch_error = None
+        want = one_launch if one_launch is not None else True
+        if want and self.batch == 1 and self.device.type == "cuda" and dtype == torch.float16 and \
+                (tp_size == 1 or tp_dry or self.exchange is not None):
+            try:
+                self._fused = _FusedStep(self)
+            except Exception as e:  # noqa: BLE001 - outside the kernel's shapes: the op-by-op step serves it
+                self.one_launch_error = repr(e)
+                if one_launch:
+                    raise
+        if tp_size > 1 and not tp_dry:
+            # every rank runs the same kind of step
+            if not tp.agree(self._fused is not None, process_group, self.device) and self._fused is not None:
+                self._fused.close()
+                self._fused = None
 
     def _norm_weight(self, gen) -> torch.Tensor:
         w = torch.empty(self.shape.hidden, dtype=torch.float32, device=self.device)
@@ -236,6 +317,17 @@ class QuantLlamaDecoder:
         s, b = self.shape, self.batch
         n0 = ops.launch_count()
         self.fused_allreduce_calls = 0
+        if self._fused is not None:
+            fs = self._fused
+            ops._embedding(self.ids, ops._FORMATS[self.embed_fmt], self.embed, None, out=fs.hidden)
+            fs.step()
+            logits = fs.logits.view(1, -1)
+            if self.tp_size > 1 and not self.tp_dry:
+                logits = tp.gather_columns(logits, self.pg)
+            self.logits = logits
+            self.next_ids.copy_(ops.argmax(logits))
+            self.launches_per_step = ops.launch_count() - n0
+            return
         h = ops._embedding(self.ids, ops._FORMATS[self.embed_fmt], self.embed, None, out_dtype=self.dtype)
         scale = 1.0 / (s.head_dim ** 0.5)
         for li, lw in enumerate(self.layers):

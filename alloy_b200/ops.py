@@ -431,11 +431,16 @@ def _moe_routed(hidden, router_logits, gate_up_blocks, down_qweight, num_experts
 
 
 def _embedding(ids: torch.Tensor, fmt: int, w: torch.Tensor, scales: torch.Tensor | None,
-               out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+               out_dtype: torch.dtype = torch.float32, out: torch.Tensor | None = None) -> torch.Tensor:
     k = _k_of(fmt, w)
     w = w.contiguous()
     flat = ids.reshape(-1).to(torch.int64).contiguous()
-    out = torch.empty((flat.numel(), k), dtype=out_dtype, device=w.device)
+    if out is None:
+        out = torch.empty((flat.numel(), k), dtype=out_dtype, device=w.device)
+    elif out.numel() != flat.numel() * k or not out.is_contiguous():
+        raise ValueError("out must be a contiguous tensor of ids.numel() * K elements")
+    else:
+        out_dtype = out.dtype
     if flat.numel() == 0:
         return out.reshape(tuple(ids.shape) + (k,))
     L = _lib.load()

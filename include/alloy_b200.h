@@ -311,6 +311,55 @@ int alloyb_attn_decode_static(int layout, const void* q, int64_t q_batch_stride,
  * Synchronises the stream.  No counterpart in the reference. */
 int alloyb_attn_static_status(int32_t* status_out, void* stream);
 
+/* ------------------------------------------------------------------ one-launch decode step
+ * The whole decode step of a Llama-shape model for ONE token (batch 1, fp16 activations, Q4_K /
+ * Q6_K weights, head_dim 128, at most 8 query heads per KV head) as a single persistent launch:
+ * per layer RMSNorm + q/k/v, RoPE + KV append + attention, o_proj + residual, RMSNorm + gate/up +
+ * SiLU, down + residual, then the final norm and the output head -- the per-step call stack of the
+ * reference's serving loop (server/models/attention.py:845-886 for the attention block,
+ * torch/ops/linalg.py:462-497 / :726-802 for the linears, metal/std/norm.py:40-73, rope.py:28-84),
+ * which the reference runs as one graph of separate dispatches.  Results are those of the
+ * separate entry points above (same arithmetic per op).
+ *
+ * All sizes are this rank's LOCAL sizes when tensor-parallel (heads, kv_heads, ffn and head.N are
+ * shards; hidden is whole).  alloyb_decoder_create allocates (cudaMalloc) the device-side phase
+ * list and scratch once; alloyb_decoder_step allocates nothing, launches on `stream` (one memset
+ * plus one cooperative launch) and can be captured in a CUDA graph.  The caller writes the token's
+ * embedding into hidden_io and the token position into *pos before each step; afterwards logits
+ * holds head.N fp16 values and the KV caches hold the token's row. */
+typedef struct alloyb_matrix {
+    int format;              /* ALLOYB_Q4_K or ALLOYB_Q6_K */
+    int N;                   /* output rows */
+    const void* data;        /* packed rows, 16-byte aligned */
+    int64_t row_bytes;       /* pitch, multiple of 16; 0 = dense */
+} alloyb_matrix;
+typedef struct alloyb_decoder_layer {
+    alloyb_matrix wq, wk, wv, wo, wg, wu, wd;
+    const void* norm_in;     /* fp16 (hidden) */
+    const void* norm_post;
+    void* k0; void* k1; void* v0; void* v1;   /* this layer's cache for ONE sequence, as in alloyb_attn_decode */
+} alloyb_decoder_layer;
+typedef struct alloyb_decoder_desc {
+    int n_layers, hidden, ffn, heads, kv_heads, head_dim;
+    float eps;
+    int kv_layout;           /* ALLOYB_KV_F16 or ALLOYB_KV_Q8_PAGED */
+    int S_max;
+    int64_t num_pages;
+    const alloyb_decoder_layer* layers;
+    const void* norm_final;
+    alloyb_matrix head;
+    const float* inv_freq;   /* fp32 (head_dim / 2) */
+    const int32_t* pos;      /* device: position of the token being decoded */
+    void* hidden_io;         /* fp16 (hidden) */
+    void* logits;            /* fp16 (head.N) */
+    const alloyb_tp* tp;     /* NULL, or the exchange the o_proj / down sums go through */
+} alloyb_decoder_desc;
+int alloyb_decoder_create(const alloyb_decoder_desc* desc, void** handle);
+int alloyb_decoder_step(void* handle, void* stream);
+int alloyb_decoder_phases(void* handle);     /* phases the step walks (diagnostic) */
+int alloyb_decoder_status(void* handle, int32_t* status_out, void* stream);   /* bits as alloyb_attn_workspace_status */
+int alloyb_decoder_destroy(void* handle);
+
 /* ------------------------------------------------------------------ routed experts
  * gguf_moe_routed (torch/custom_ops.py:59-66; kernels metal/std/moe.py:31-228): per token the
  * top_k largest router logits (descending, lowest index on ties) with a softmax over just those;

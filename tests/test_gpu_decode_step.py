@@ -119,6 +119,59 @@ def test_decode_step_big_batch_head_dim_128(batch, kv_kind):
     assert worst <= 1e-2 and mean <= 4e-3, (worst, mean)
 
 
+WIDE = llama.LlamaShape(layers=3, hidden=2048, ffn=4096, heads=16, kv_heads=4, head_dim=128, vocab=2048,
+                        rope_theta=10000.0, eps=1e-5)
+
+
+@pytest.mark.parametrize("kv_kind", ["f16", "q8_paged"])
+def test_one_launch_step_matches_op_by_op_and_oracle(kv_kind):
+    """Batch 1: the whole step as ONE persistent launch (alloyb_decoder_step) against the op-by-op step
+    of the same weights and against the oracle, over two consecutive positions, eager and replayed."""
+    ctx = 200
+    mk = lambda fused: llama.QuantLlamaDecoder(WIDE, 1, ctx, seed=9, d_scale=0.2, centered=True, kv=kv_kind,
+                                               one_launch=fused)
+    fused, plain = mk(True), mk(False)
+    assert fused._fused is not None and plain._fused is None
+    assert fused._fused.phases == WIDE.layers * 6 + 1
+    if kv_kind == "f16":
+        kc = [k.float().cpu().numpy() for k in plain.k_cache]
+        vc = [v.float().cpu().numpy() for v in plain.v_cache]
+    else:
+        kc, vc = _paged_caches(plain, ctx)
+    layers = _oracle_inputs(plain)
+    embed, head = O.dequant_q4_k(plain.embed.cpu().numpy()), O.dequant_q6_k(plain.head.cpu().numpy())
+    rng = np.random.default_rng(2)
+    for step, pos in enumerate((ctx - 2, ctx - 1)):
+        ids = rng.integers(0, WIDE.vocab, size=1)
+        for d in (fused, plain):
+            d.ids.copy_(torch.from_numpy(ids))
+            d.pos.fill_(pos)
+            d.seq_pos.fill_(pos)
+            d.step()
+        torch.cuda.synchronize()
+        ref_logits, _, _ = OD.decode_step(ids, pos, embed, layers, plain.norm_final.cpu().numpy(), head,
+                                          plain.inv_freq.cpu().numpy(), kc, vc, WIDE.heads, WIDE.kv_heads,
+                                          WIDE.head_dim, WIDE.eps, kv_q8=(kv_kind == "q8_paged"))
+        ref64 = ref_logits.astype(np.float64)
+        rms = np.sqrt((ref64 ** 2).mean())
+        for name, d in (("one launch", fused), ("op by op", plain)):
+            got = to_np(d.logits)
+            _, mean = rel_errors(got, ref64, torch.float16)
+            worst = np.abs(got - ref64).max() / rms
+            assert worst <= 1e-2 and mean <= 6e-3, (name, step, worst, mean)
+        assert (fused.logits.float() - plain.logits.float()).abs().max() <= 1e-2 * rms
+        # first layer: same q/k/v arithmetic, same rotation -> the appended rows are the same bits
+        if kv_kind == "f16":
+            assert torch.equal(fused.k_cache[0][:, :, pos], plain.k_cache[0][:, :, pos])
+            assert torch.equal(fused.v_cache[0][:, :, pos], plain.v_cache[0][:, :, pos])
+        else:
+            assert torch.equal(fused.pools[0].pool, plain.pools[0].pool)
+        if step == 0:
+            fused.capture()                               # the second position runs as a graph replay
+    from alloy_b200 import _lib
+    assert _lib.load().alloyb_device_error(1) == 0
+
+
 def test_decode_step_from_gguf_file(tmp_path):
     """A Llama-architecture GGUF file (written with gguf.GGUFWriter: permuted q/k rows, Q6_K and Q4_K
     v/down in alternating layers, tied head) served by the decoder equals the oracle's step on the
