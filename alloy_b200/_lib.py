@@ -122,6 +122,8 @@ SIGNATURES = {
     "alloyb_decoder_step": (_i, [_p, _p]),
     "alloyb_decoder_phases": (_i, [_p]),
     "alloyb_decoder_status": (_i, [_p, C.POINTER(C.c_int32), _p]),
+    "alloyb_decoder_trace": (_i, [_p, _i]),
+    "alloyb_decoder_trace_read": (_i, [_p, C.POINTER(C.c_uint64), _i]),
     "alloyb_decoder_destroy": (_i, [_p]),
     "alloyb_rms_norm": (_i, [_p, _p, _p, _i, _i, _f, _i, _p]),
     "alloyb_rope_inplace": (_i, [_p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _p]),

@@ -3,14 +3,17 @@
 // A decode step at batch 1 is ~190 small dependent operations (per layer: RMSNorm + q/k/v, RoPE +
 // cache append + attention, o_proj + residual, RMSNorm + gate/up + SiLU, down + residual; then the
 // final norm and the output head).  Launched one by one, each pays a few microseconds of launch,
-// prologue and pipeline fill against one to ten microseconds of HBM time, and the step runs at a
-// third of the weight-streaming bound.  Here one cooperative grid (one CTA of sixteen warps per SM)
-// walks a list of PHASES prepared once on the host:
+// prologue and pipeline fill against one to ten microseconds of HBM time.  Here one cooperative
+// grid (one CTA of sixteen warps per SM) walks a list of PHASES prepared once on the host:
 //
 //   * a GEMV phase is the streaming dequant-GEMV of linear_stream.cu (same slot geometries, same
-//     per-super-block arithmetic, same K split over the warps, hence the same bits): the token is
-//     staged (and normalised, when the phase carries an RMSNorm) into shared memory with loads that
-//     bypass L1, every warp streams its K slice of the CTA's rows through its private TMA ring;
+//     per-super-block tensor-core arithmetic, same K split over the warps): the token is staged
+//     (and normalised, when the phase carries an RMSNorm) into shared memory with loads that bypass
+//     L1, together with the sums of its 16-element chunks (the Q4_K min and Q6_K offset terms);
+//     every warp streams its K slice of the CTA's rows through its private TMA ring.  ONE routine
+//     serves every weight format and grouping (the format is a per-matrix run-time value, so q, k
+//     and v of different formats are one phase): a step touches ~200 phases and a routine per
+//     variant did not fit the instruction cache;
 //   * the attention phase rotates q (and the new k) in its prologue, appends the new K/V row to the
 //     cache, and runs the split-K tensor-core decode attention of attn_mma.cu with sixteen warps
 //     per CTA, (kv head, split) pairs dealt over the CTAs, the last CTA of a head merging the splits;
@@ -38,9 +41,14 @@ constexpr int RED_BYTES = 4096;                       // per-tile partials of th
 constexpr int BAR_BYTES = WARPS * MAX_D * 8;
 constexpr int XS_HALVES = 28672;                      // the staged token: the largest K of a phase
 constexpr int XS_BYTES = XS_HALVES * 2;
-constexpr int MISC_BYTES = 256;
-constexpr int SMEM_BYTES = RING_BYTES + RED_BYTES + BAR_BYTES + XS_BYTES + MISC_BYTES;
-constexpr uint32_t GRID_SPIN = 1u << 22;
+constexpr int SUMS_BYTES = XS_HALVES / 16 * 4;        // fp32 sum of every 16-element chunk of the token
+constexpr int DESC_SLOT = 384, DESC_SLOTS = 3;        // phase descriptors cached in shared memory
+constexpr int PLAN_SLOT = 64;
+constexpr int OFF_RED = RING_BYTES, OFF_BAR = OFF_RED + RED_BYTES, OFF_XS = OFF_BAR + BAR_BYTES,
+              OFF_SUMS = OFF_XS + XS_BYTES, OFF_NRED = OFF_SUMS + SUMS_BYTES, OFF_DESC = OFF_NRED + 128,
+              OFF_PLAN = OFF_DESC + DESC_SLOTS * DESC_SLOT, SMEM_BYTES = OFF_PLAN + WARPS * PLAN_SLOT;
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+constexpr uint32_t GRID_SPIN = 1u << 24;
 constexpr float NEG_BIG = -1.0e30f;
 constexpr float P_BIAS = 64.0f;                       // see attn_mma.cu
 constexpr int AD = 128;                               // head_dim of the attention phase
@@ -50,14 +58,33 @@ constexpr int MAX_SPLITS = 64;
 
 enum { PH_GEMV = 0, PH_ATTN = 1 };
 
+struct GSeg {
+    const uint8_t* data;
+    int64_t row_bytes;
+    void* y;
+    int n_rows;
+    int row_base;        // first row of this matrix in the phase's stacked row space
+    int kind;            // st::Kind: slot geometry / weight format of this matrix
+    int map;             // index of its tensor map in the step's map array
+};
 struct GemvDesc {
-    Params P;
-    int kind;            // st::Kind
-    int gu;              // gate/up pair: gate rows to warps 0-7, up rows to warps 8-15
-    int gw;              // warps per K-split group: 1, 4, 8 or 16
-    int map0;            // index of seg[0]'s tensor map in the step's map array
-    int stage_x;         // 1: stage P.x into shared memory; 0: the previous phase's token is still there
+    const __half* x;
+    const __half* residual;
+    const __half* norm_w;        // non-null: RMSNorm(x; norm_w, eps) on the way in
+    float eps;
+    int n_seg;                   // matrices walked row-wise (1 for a gate/up pair)
+    GSeg seg[MAX_SEG];
+    int total_rows;
+    int nsb;
+    int gu;                      // gate/up pair: seg[0] rows to warps 0-7, seg[1] rows to warps 8-15, y = act(g) * u
+    int act;
+    int depth;                   // ring slots per warp
+    int gw;                      // warps per K-split group: 1, 4, 8 or 16
+    int sbs;                     // super-blocks per slot (the same for every matrix of the phase)
+    int slot_bytes;              // ring slot stride
+    int stage_x;                 // 1: stage x into shared memory; 0: the previous phase's token is still there
     int K;
+    TpArgs tp;                   // world == 0: plain linear
 };
 struct AttnDesc {
     const __half* q;     // this step's projections, un-rotated: (H, 128), (KV_H, 128), (KV_H, 128)
@@ -78,14 +105,19 @@ struct AttnDesc {
 struct PhaseDesc {
     int type;
     int barrier_after;
-    GemvDesc g;
-    AttnDesc a;
+    union {
+        GemvDesc g;
+        AttnDesc a;
+    };
 };
+static_assert(sizeof(PhaseDesc) <= DESC_SLOT && sizeof(PhaseDesc) % 4 == 0, "descriptor slot");
 struct StepDesc {
     const PhaseDesc* phases;
     int n_phases;
     const CUtensorMap* maps;
     unsigned int* barrier;       // zeroed on the stream before every launch
+    unsigned long long* trace;   // optional: per (phase, CTA) four nanosecond clocks: token staged, phase done,
+                                 // next phase's copies issued, barrier passed
 };
 
 struct RingState {
@@ -95,12 +127,16 @@ struct RingState {
     bool ok;             // false once a bounded wait of this warp ran out
 };
 
+// A warp's share of a phase.  Warp-uniform, kept in shared memory (one slot per warp).
 struct Plan {
-    int lo, hi, sb_lo, slice, spt, my_tiles, n_stage, issued, p_r, p_slot, D, gw, grp, wg, n_groups, tstep;
-    Cursor pc;
+    int lo, hi, sb_lo, slice, spt, my_tiles, n_stage, issued, p_r, p_slot, tstep, grp, wg;
+    int seg, row, lim;   // producer cursor
 };
+static_assert(sizeof(Plan) <= PLAN_SLOT, "plan slot");
 
 __device__ __forceinline__ uint4 ldcg128(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ int kind_pitch(int kind) { return kind == Q6 ? 240 : (kind == Q4x2 ? 304 : 144); }
+__device__ __forceinline__ int kind_blk(int kind) { return kind == Q6 ? Q6K_BYTES : Q4K_BYTES; }
 
 // ------------------------------------------------------------------------------------ grid barrier
 
@@ -108,108 +144,141 @@ __device__ __forceinline__ void grid_sync(unsigned int* ctr, unsigned int& targe
     __syncthreads();
     if (threadIdx.x == 0) {
         target += gridDim.x;
-        __threadfence();
-        atomicAdd(ctr, 1u);
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
         if (*reinterpret_cast<volatile int*>(&g_error) == 0) {
             uint32_t i = 0;
             for (; i < GRID_SPIN; ++i) {
                 unsigned int v;
                 asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
                 if (v >= target) break;
-                if (i > 16) __nanosleep(20);
             }
             if (i == GRID_SPIN) atomicExch(&g_error, 2);
         }
-        __threadfence();
     }
     __syncthreads();
 }
 
 // ------------------------------------------------------------------------------------ GEMV phases
 
-template <int KIND, bool GU>
+// Row cursor over the phase's stacked matrices (as st::Cursor, on this file's descriptor).
+__device__ __forceinline__ void cur_enter(int& seg, int& row, int& lim, const GemvDesc& d, int lo, int hi) {
+    while (seg < d.n_seg) {
+        const int base = d.seg[seg].row_base, n = d.seg[seg].n_rows;
+        const int a = lo > base ? lo - base : 0;
+        const int b = hi - base < n ? hi - base : n;
+        if (a < b) {
+            row = a;
+            lim = b;
+            return;
+        }
+        ++seg;
+    }
+}
+__device__ __forceinline__ void cur_next(int& seg, int& row, int& lim, const GemvDesc& d, int lo, int hi, int steps) {
+    for (int i = 0; i < steps && seg < d.n_seg; ++i) {
+        row += 16;
+        if (row >= lim) {
+            ++seg;
+            cur_enter(seg, row, lim, d, lo, hi);
+        }
+    }
+}
+
+// One stage (16 rows x sbs super-blocks of the producer cursor's tile) into the next ring slot.
 __device__ __forceinline__ void gemv_issue(Plan& pl, const GemvDesc& d, const CUtensorMap* maps, const RingState& rs,
                                            int lane) {
-    constexpr int SBS = Geom<KIND>::SBS, PITCH = Geom<KIND>::PITCH, SLOT = 16 * PITCH, BLK = Geom<KIND>::BLK;
-    const Params& P = d.P;
-    const int sb = pl.sb_lo + pl.p_r * SBS;
-    const int si = GU ? pl.grp : pl.pc.seg;
-    const int nvalid = pl.pc.lim - pl.pc.row < 16 ? pl.pc.lim - pl.pc.row : 16;
-    const uint32_t bar = rs.bar0 + 8 * pl.p_slot, dst = rs.ring + pl.p_slot * SLOT;
-    const int win = (sb * BLK) & ~15;                                // 16-byte-aligned start of the stage in a row
+    const GSeg& sg = d.seg[d.gu ? pl.grp : pl.seg];
+    const int kind = sg.kind, pitch = kind_pitch(kind), blk = kind_blk(kind);
+    const int sb = pl.sb_lo + pl.p_r * d.sbs;
+    const int nvalid = pl.lim - pl.row < 16 ? pl.lim - pl.row : 16;
+    const uint32_t bar = rs.bar0 + 8 * pl.p_slot, dst = rs.ring + pl.p_slot * d.slot_bytes;
+    const int win = (sb * blk) & ~15;                                // 16-byte-aligned start of the stage in a row
     if (nvalid == 16) {
         if (lane == 0) {
-            mbar_expect_tx(bar, SLOT);
-            tma_2d(dst, maps + d.map0 + si, win / 4, pl.pc.row, bar);
+            mbar_expect_tx(bar, 16 * pitch);
+            tma_2d(dst, maps + sg.map, win / 4, pl.row, bar);
         }
     } else {
-        int bytes = SBS * BLK;
-        if (KIND == Q6) {
-            const int left = static_cast<int>(P.seg[si].row_bytes) - win;
-            bytes = left < PITCH ? left : PITCH;
+        int bytes = d.sbs * blk;
+        if (kind == Q6) {
+            const int left = static_cast<int>(sg.row_bytes) - win;
+            bytes = left < pitch ? left : pitch;
         }
         if (lane == 0) mbar_expect_tx(bar, nvalid * bytes);
         __syncwarp();
-        if (lane < nvalid)
-            bulk_g2s(dst + lane * PITCH, P.seg[si].data + (pl.pc.row + lane) * P.seg[si].row_bytes + win, bytes, bar);
+        if (lane < nvalid) bulk_g2s(dst + lane * pitch, sg.data + (pl.row + lane) * sg.row_bytes + win, bytes, bar);
     }
     ++pl.issued;
-    if (++pl.p_slot == pl.D) pl.p_slot = 0;
+    if (++pl.p_slot == d.depth) pl.p_slot = 0;
     if (++pl.p_r == pl.spt) {
         pl.p_r = 0;
-        cursor_next(pl.pc, P, pl.lo, pl.hi, pl.tstep);
+        cur_next(pl.seg, pl.row, pl.lim, d, pl.lo, pl.hi, pl.tstep);
     }
 }
 
 // Plan this warp's share of the phase and start its first weight copies (they depend on nothing
 // this step computes, so this runs BEFORE the barrier that guards the phase's input).
-template <int KIND, bool GU>
-__device__ __noinline__ void gemv_begin(Plan& pl, const GemvDesc& d, const CUtensorMap* maps, const RingState& rs,
-                                           int warp, int lane) {
-    constexpr int SBS = Geom<KIND>::SBS;
-    const Params& P = d.P;
-    pl.gw = d.gw;
-    pl.grp = warp / d.gw;
-    pl.wg = warp % d.gw;
-    pl.n_groups = WARPS / d.gw;
-    pl.tstep = GU ? 1 : pl.n_groups;
-    pl.D = P.depth;
-    pl.lo = static_cast<int>(static_cast<int64_t>(P.total_rows) * blockIdx.x / gridDim.x);
-    pl.hi = static_cast<int>(static_cast<int64_t>(P.total_rows) * (blockIdx.x + 1) / gridDim.x);
-    pl.sb_lo = (pl.wg * P.nsb) / d.gw;
-    pl.slice = ((pl.wg + 1) * P.nsb) / d.gw - pl.sb_lo;
-    pl.spt = pl.slice / SBS;
-    pl.my_tiles = 0;
+__device__ __noinline__ void gemv_begin(Plan& pl_out, const GemvDesc& d, const CUtensorMap* maps, const RingState& rs_in,
+                                        int warp, int lane) {
+    // everything is computed in registers and stored once: the plan and the descriptor are both in
+    // shared memory, and stores to one would make the compiler re-read the other
+    const RingState rs = rs_in;
+    const int gw = d.gw, nsb = d.nsb, total_rows = d.total_rows, gu = d.gu, depth = d.depth, sbs = d.sbs;
+    Plan pl;
+    pl.grp = warp / gw;
+    pl.wg = warp % gw;
+    pl.tstep = gu ? 1 : WARPS / gw;
+    pl.lo = static_cast<int>(static_cast<uint32_t>(total_rows) * blockIdx.x / gridDim.x);
+    pl.hi = static_cast<int>(static_cast<uint32_t>(total_rows) * (blockIdx.x + 1) / gridDim.x);
+    pl.sb_lo = (pl.wg * nsb) / gw;
+    pl.slice = ((pl.wg + 1) * nsb) / gw - pl.sb_lo;
+    pl.spt = pl.slice / sbs;
+    int tiles = 0;
     {
-        Cursor c = {0, 0, 0};
-        cursor_enter(c, P, pl.lo, pl.hi);
-        cursor_next(c, P, pl.lo, pl.hi, GU ? 0 : pl.grp);
-        while (c.seg < P.n_seg) {
-            ++pl.my_tiles;
-            cursor_next(c, P, pl.lo, pl.hi, pl.tstep);
+        int seg = 0, row = 0, lim = 0;
+        cur_enter(seg, row, lim, d, pl.lo, pl.hi);
+        cur_next(seg, row, lim, d, pl.lo, pl.hi, gu ? 0 : pl.grp);
+        while (seg < d.n_seg) {
+            ++tiles;
+            cur_next(seg, row, lim, d, pl.lo, pl.hi, pl.tstep);
         }
     }
-    pl.n_stage = pl.my_tiles * pl.spt;
-    pl.pc = {0, 0, 0};
-    cursor_enter(pl.pc, P, pl.lo, pl.hi);
-    cursor_next(pl.pc, P, pl.lo, pl.hi, GU ? 0 : pl.grp);
+    pl.my_tiles = tiles;
+    pl.n_stage = tiles * pl.spt;
+    pl.seg = pl.row = pl.lim = 0;
+    cur_enter(pl.seg, pl.row, pl.lim, d, pl.lo, pl.hi);
+    cur_next(pl.seg, pl.row, pl.lim, d, pl.lo, pl.hi, gu ? 0 : pl.grp);
     pl.issued = pl.p_r = pl.p_slot = 0;
     if (rs.ok)
-        while (pl.issued < pl.n_stage && pl.issued < pl.D) gemv_issue<KIND, GU>(pl, d, maps, rs, lane);
+        while (pl.issued < pl.n_stage && pl.issued < depth) gemv_issue(pl, d, maps, rs, lane);
+    pl_out = pl;
 }
 
-// The token of a phase -> shared memory, read past L1 (another SM wrote it earlier in this launch);
-// with an RMSNorm the arithmetic is that of the stand-alone kernels (fp32 sum of squares, x * r
-// narrowed to fp16, then times the fp16 weight).
-__device__ __noinline__ void stage_token(const GemvDesc& d, __half* xs, float* nred) {
-    const Params& P = d.P;
+// The token of a phase -> shared memory (fp16) plus the fp32 sum of each 16-element chunk, read past
+// L1 (another SM wrote it earlier in this launch) in ONE round trip: a thread keeps its chunks in
+// registers between the sum of squares and the scaling.  RMSNorm arithmetic as the stand-alone
+// kernels: fp32 sum of squares, x * r narrowed to fp16, then times the fp16 weight.
+constexpr int STAGE_CHUNKS = XS_HALVES / 8 / (WARPS * 32);          // 16-byte chunks per thread at the largest K
+__device__ __noinline__ void stage_token(const GemvDesc& d, __half* xs, float* sums, float* nred) {
     const int K = d.K, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    __syncthreads();                                   // nobody still reads the previous phase's token
-    if (P.norm_w) {
+    const __half* x = d.x;
+    const __half* norm_w = d.norm_w;
+    uint4 xv[STAGE_CHUNKS], wv[STAGE_CHUNKS];
+#pragma unroll
+    for (int c = 0; c < STAGE_CHUNKS; ++c) {
+        const int i = (c * WARPS * 32 + threadIdx.x) * 8;
+        xv[c] = make_uint4(0u, 0u, 0u, 0u);
+        wv[c] = xv[c];
+        if (i < K) {
+            xv[c] = ldcg128(x + i);
+            if (norm_w) wv[c] = __ldg(reinterpret_cast<const uint4*>(norm_w + i));
+        }
+    }
+    if (norm_w) {
         float ssq = 0.f;
-        for (int i = threadIdx.x * 8; i < K; i += WARPS * 32 * 8) {
-            const uint4 v = ldcg128(P.x + i);
-            const __half2* h2 = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int c = 0; c < STAGE_CHUNKS; ++c) {
+            const __half2* h2 = reinterpret_cast<const __half2*>(&xv[c]);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float2 f2 = __half22float2(h2[j]);
@@ -223,12 +292,11 @@ __device__ __noinline__ void stage_token(const GemvDesc& d, __half* xs, float* n
         float tot = 0.f;
 #pragma unroll
         for (int i = 0; i < WARPS; ++i) tot += nred[i];
-        const float r = rsqrtf(tot / static_cast<float>(K) + P.eps);
-        for (int i = threadIdx.x * 8; i < K; i += WARPS * 32 * 8) {
-            const uint4 v = ldcg128(P.x + i);
-            const uint4 w = __ldg(reinterpret_cast<const uint4*>(P.norm_w + i));
-            const __half* hv = reinterpret_cast<const __half*>(&v);
-            const __half* hw = reinterpret_cast<const __half*>(&w);
+        const float r = rsqrtf(tot / static_cast<float>(K) + d.eps);
+#pragma unroll
+        for (int c = 0; c < STAGE_CHUNKS; ++c) {
+            const __half* hv = reinterpret_cast<const __half*>(&xv[c]);
+            const __half* hw = reinterpret_cast<const __half*>(&wv[c]);
             uint4 o;
             __half* ho = reinterpret_cast<__half*>(&o);
 #pragma unroll
@@ -236,90 +304,165 @@ __device__ __noinline__ void stage_token(const GemvDesc& d, __half* xs, float* n
                 const __half normed = __float2half_rn(__half2float(hv[j]) * r);
                 ho[j] = __float2half_rn(__half2float(hw[j]) * __half2float(normed));
             }
-            *reinterpret_cast<uint4*>(xs + i) = o;
+            xv[c] = o;
         }
-    } else {
-        for (int i = threadIdx.x * 8; i < K; i += WARPS * 32 * 8) *reinterpret_cast<uint4*>(xs + i) = ldcg128(P.x + i);
+    }
+#pragma unroll
+    for (int c = 0; c < STAGE_CHUNKS; ++c) {
+        const int i = (c * WARPS * 32 + threadIdx.x) * 8;
+        const __half2* h2 = reinterpret_cast<const __half2*>(&xv[c]);
+        float s8 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f2 = __half22float2(h2[j]);
+            s8 += f2.x + f2.y;
+        }
+        s8 += __shfl_xor_sync(0xffffffffu, s8, 1);                   // lanes 2k, 2k+1 hold one 16-element chunk
+        if (i < K) {
+            *reinterpret_cast<uint4*>(xs + i) = xv[c];
+            if ((lane & 1) == 0) sums[i >> 4] = s8;
+        }
     }
     __syncthreads();
 }
 
-template <int KIND, bool GU>
-__device__ __noinline__ void gemv_run(Plan& pl, const GemvDesc& d, const CUtensorMap* maps, RingState& rs,
-                                         const __half* xs, float* red_all, int warp, int lane) {
-    constexpr int SBS = Geom<KIND>::SBS, PITCH = Geom<KIND>::PITCH, SLOT = 16 * PITCH, BLK = Geom<KIND>::BLK;
-    using XF = typename std::conditional<KIND == Q6, XFrag6, XFrag>::type;
-    const Params& P = d.P;
-    const int g = lane >> 2, t = lane & 3;
-    const int GW = pl.gw, grp = pl.grp, wg = pl.wg;
-    const int D = pl.D;
-    float* red = red_all + grp * (2 * GW * 16);
-
-    uint32_t tp_next = 0;
-    if (!GU && P.tp.world) tp_next = *reinterpret_cast<volatile uint32_t*>(P.tp.peer[P.tp.rank]) + 1u;
-
-    const ScaleSel ss = make_scale_sel(t);
-    const bool cache = GW > 1 && pl.slice == SBS;      // the warp's slice is one slot: fragments are loop invariants
-    XF xc[SBS];
-    if (cache) {
+// B fragments of one super-block of the staged token (see st::load_xfrag); the per-sub-block sums
+// come from the staged chunk sums instead of eight extra MMAs.
+__device__ __forceinline__ void load_xfrag_s(XFrag& f, const __half* xs, const float* sums, int sb, int g, int t) {
 #pragma unroll
-        for (int i = 0; i < SBS; ++i) {
-            if constexpr (KIND == Q6) load_xfrag6(xc[i], xs, pl.sb_lo + i, g, t);
-            else load_xfrag(xc[i], xs, pl.sb_lo + i, g, t);
+    for (int j = 0; j < 8; ++j) f.b[j][0] = f.b[j][1] = 0u;
+    if ((g >> 1) == t) {
+        const uint4* xp = reinterpret_cast<const uint4*>(xs + sb * QK_K + 32 * g);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint4 v = xp[q];
+            f.b[2 * q][0] = prmt(v.x, v.y, 0x5410u);
+            f.b[2 * q][1] = prmt(v.x, v.y, 0x7632u);
+            f.b[2 * q + 1][0] = prmt(v.z, v.w, 0x5410u);
+            f.b[2 * q + 1][1] = prmt(v.z, v.w, 0x7632u);
         }
     }
+    const float4 s4 = *reinterpret_cast<const float4*>(sums + sb * 16 + 4 * t);       // sub-blocks 2t, 2t+1
+    f.sx0 = s4.x + s4.y;
+    f.sx1 = s4.z + s4.w;
+}
+__device__ __forceinline__ void load_xfrag6_s(XFrag6& f, const __half* xs, const float* sums, int sb, int g, int t) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint2 v = *reinterpret_cast<const uint2*>(xs + sb * QK_K + 128 * h + 16 * g + 4 * t);
+        f.b[h][0] = prmt(v.x, v.y, 0x5410u);
+        f.b[h][1] = prmt(v.x, v.y, 0x7632u);
+        const float2 s2 = *reinterpret_cast<const float2*>(sums + sb * 16 + 8 * h + 2 * t);
+        f.sx[h][0] = s2.x;
+        f.sx[h][1] = s2.y;
+    }
+}
+
+// st::unit_q4k with the slot's row pitch as a run-time value (one routine for both Q4_K geometries).
+__device__ __forceinline__ void unit_q4k_rt(uint32_t blk, int pitch, const XFrag& f, const ScaleSel& ss, int g, int t,
+                                            float& a0, float& a1) {
+    const uint32_t rb = blk + g * pitch, rb8 = rb + 8 * pitch;
+    const uint4 p0 = lds128(rb + 16 + 32 * t), p1 = lds128(rb + 32 + 32 * t);
+    const uint4 r0 = lds128(rb8 + 16 + 32 * t), r1 = lds128(rb8 + 32 + 32 * t);
+    const uint4 h0 = lds128(rb), h1 = lds128(rb8);
+    const uint32_t wg[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+    const uint32_t wh[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+    float clo[4], chi[4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t ug = wg[j] >> 8, uh = wh[j] >> 8;
+        if (j == 0) {
+            mma_zero(clo, wg[j] & 0x000f000fu, wh[j] & 0x000f000fu, ug & 0x000f000fu, uh & 0x000f000fu, f.b[j][0], f.b[j][1]);
+            mma_zero(chi, wg[j] & 0x00f000f0u, wh[j] & 0x00f000f0u, ug & 0x00f000f0u, uh & 0x00f000f0u, f.b[j][0], f.b[j][1]);
+        } else {
+            mma_acc(clo, wg[j] & 0x000f000fu, wh[j] & 0x000f000fu, ug & 0x000f000fu, uh & 0x000f000fu, f.b[j][0], f.b[j][1]);
+            mma_acc(chi, wg[j] & 0x00f000f0u, wh[j] & 0x00f000f0u, ug & 0x00f000f0u, uh & 0x00f000f0u, f.b[j][0], f.b[j][1]);
+        }
+    }
+    const uint32_t Y = prmt(h0.y, h1.y, ss.sel), Z = prmt(h0.z, h1.z, ss.sel), Wd = prmt(h0.w, h1.w, ss.sel);
+    const uint32_t sc4 = ((ss.high ? Wd : Y) & ss.m_a) | ((Y >> 2) & ss.m_b);
+    const uint32_t mn4 = ((ss.high ? (Wd >> 4) : Z) & ss.m_a) | ((Z >> 2) & ss.m_b);
+    const float2 dm0 = __half22float2(*reinterpret_cast<const __half2*>(&h0.x));
+    const float2 dm1 = __half22float2(*reinterpret_cast<const __half2*>(&h1.x));
+    float a = static_cast<float>(sc4 & 0xffu) * clo[0];
+    a = fmaf(static_cast<float>((sc4 >> 8) & 0xffu) * 0.0625f, chi[1], a);
+    float m = static_cast<float>(mn4 & 0xffu) * f.sx0;
+    m = fmaf(static_cast<float>((mn4 >> 8) & 0xffu), f.sx1, m);
+    a0 = fmaf(dm0.x * 16777216.0f, a, fmaf(-dm0.y, m, a0));
+    float b = static_cast<float>((sc4 >> 16) & 0xffu) * clo[2];
+    b = fmaf(static_cast<float>(sc4 >> 24) * 0.0625f, chi[3], b);
+    float n = static_cast<float>((mn4 >> 16) & 0xffu) * f.sx0;
+    n = fmaf(static_cast<float>(mn4 >> 24), f.sx1, n);
+    a1 = fmaf(dm1.x * 16777216.0f, b, fmaf(-dm1.y, n, a1));
+}
+
+__device__ __noinline__ void gemv_run(const Plan& pl_in, const GemvDesc& d, const CUtensorMap* maps, RingState& rs_io,
+                                      const __half* xs, const float* sums, float* red_all, int warp, int lane) {
+    Plan pl = pl_in;                                   // registers: nothing below stores to the shared copy
+    RingState rs = rs_io;
+    const int g = lane >> 2, t = lane & 3;
+    const int GW = d.gw, grp = pl.grp, wg = pl.wg, D = d.depth, gu = d.gu, sbs = d.sbs, slot_bytes = d.slot_bytes;
+    float* red = red_all + grp * (2 * GW * 16);
+    const int tp_world = gu ? 0 : d.tp.world, tp_rank = d.tp.rank, tp_max_n = d.tp.max_n, act = d.act;
+    const __half* residual = d.residual;
+
+    uint32_t tp_next = 0;
+    if (tp_world) tp_next = *reinterpret_cast<volatile uint32_t*>(d.tp.peer[tp_rank]) + 1u;
+    const ScaleSel ss = make_scale_sel(t);
 
     int c_slot = 0;
-    Cursor cc = {0, 0, 0};
-    cursor_enter(cc, P, pl.lo, pl.hi);
-    cursor_next(cc, P, pl.lo, pl.hi, GU ? 0 : grp);
-    for (int it = 0; it < pl.my_tiles; ++it) {
+    int cseg = 0, crow = 0, clim = 0;
+    cur_enter(cseg, crow, clim, d, pl.lo, pl.hi);
+    cur_next(cseg, crow, clim, d, pl.lo, pl.hi, gu ? 0 : grp);
+    const int my_tiles = pl.my_tiles, sb_lo = pl.sb_lo, sb_hi = pl.sb_lo + pl.slice;
+    for (int it = 0; it < my_tiles; ++it) {
+        const int kind = d.seg[gu ? grp : cseg].kind, pitch = kind_pitch(kind);
         float acc0 = 0.f, acc1 = 0.f;
-        for (int sb = pl.sb_lo; sb < pl.sb_lo + pl.slice; sb += SBS) {
-            const uint32_t slot = rs.ring + c_slot * SLOT;
+        for (int sb = sb_lo; sb < sb_hi; sb += sbs) {
+            const uint32_t slot = rs.ring + c_slot * slot_bytes;
             if (rs.ok) rs.ok = mbar_wait(rs.bar0 + 8 * c_slot, (rs.parity >> c_slot) & 1u);
             rs.parity ^= 1u << c_slot;
             if (++c_slot == D) c_slot = 0;
             rs.ok = __all_sync(0xffffffffu, rs.ok);
             if (rs.ok) {
-#pragma unroll
-                for (int i = 0; i < SBS; ++i) {
-                    if constexpr (KIND == Q6) {
-                        if (!cache) load_xfrag6(xc[0], xs, sb, g, t);
-                        const uint32_t off = static_cast<uint32_t>(sb * BLK) & 15u;
-                        if (off & 2u) unit_q6k<false>(slot + off, xc[0], g, t, acc0, acc1);
-                        else unit_q6k<true>(slot + off, xc[0], g, t, acc0, acc1);
-                    } else {
-                        if (!cache) load_xfrag(xc[i], xs, sb + i, g, t);
-                        unit_q4k<PITCH>(slot + i * BLK, xc[i], ss, g, t, acc0, acc1);
+                if (kind == Q6) {
+                    XFrag6 f;
+                    load_xfrag6_s(f, xs, sums, sb, g, t);
+                    const uint32_t off = static_cast<uint32_t>(sb * Q6K_BYTES) & 15u;
+                    if (off & 2u) unit_q6k<false>(slot + off, f, g, t, acc0, acc1);
+                    else unit_q6k<true>(slot + off, f, g, t, acc0, acc1);
+                } else {
+                    for (int i = 0; i < sbs; ++i) {
+                        XFrag f;
+                        load_xfrag_s(f, xs, sums, sb + i, g, t);
+                        unit_q4k_rt(slot + i * Q4K_BYTES, pitch, f, ss, g, t, acc0, acc1);
                     }
                 }
             }
             __syncwarp();
-            if (rs.ok && pl.issued < pl.n_stage) gemv_issue<KIND, GU>(pl, d, maps, rs, lane);   // refills the slot just drained
+            if (rs.ok && pl.issued < pl.n_stage) gemv_issue(pl, d, maps, rs, lane);      // refills the slot just drained
         }
         acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
         acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
         acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
         acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
         auto store = [&](int tl, float v, float u) {
-            if (cc.row + tl >= cc.lim) return;
-            const Seg& sg = P.seg[cc.seg];
-            const int row = cc.row + tl;
-            __half* y = static_cast<__half*>(sg.y);
-            if (GU) {
-                const float a = (P.act == ALLOYB_ACT_SILU) ? act_silu(v) : act_gelu_tanh(v);
+            if (crow + tl >= clim) return;
+            const int row = crow + tl;
+            __half* y = static_cast<__half*>(d.seg[cseg].y);
+            if (gu) {
+                const float a = (act == ALLOYB_ACT_SILU) ? act_silu(v) : act_gelu_tanh(v);
                 y[row] = __float2half_rn(a * u);
-            } else if (P.tp.world) {
-                const size_t off = TP_SLOTS_OFF + (static_cast<size_t>((tp_next & 1u) * 8 + P.tp.rank) * P.tp.max_n + row) * 4;
-                for (int p = 0; p < P.tp.world; ++p) *reinterpret_cast<float*>(P.tp.peer[p] + off) = v;
+            } else if (tp_world) {
+                const size_t off = TP_SLOTS_OFF + (static_cast<size_t>((tp_next & 1u) * 8 + tp_rank) * tp_max_n + row) * 4;
+                for (int p = 0; p < tp_world; ++p) *reinterpret_cast<float*>(d.tp.peer[p] + off) = v;
             } else {
                 __half r = __float2half_rn(v);
-                if (P.residual) r = __float2half_rn(__half2float(__ldcg(P.residual + row)) + __half2float(r));
+                if (residual) r = __float2half_rn(__half2float(__ldcg(residual + row)) + __half2float(r));
                 y[row] = r;
             }
         };
-        if (GU) {
+        if (gu) {
             float* rbuf = red_all + (it & 1) * (WARPS * 16);
             if (t == 0) {
                 rbuf[warp * 16 + g] = acc0;
@@ -354,37 +497,38 @@ __device__ __noinline__ void gemv_run(Plan& pl, const GemvDesc& d, const CUtenso
                 store(tl, v, 0.f);
             }
         }
-        cursor_next(cc, P, pl.lo, pl.hi, pl.tstep);
+        cur_next(cseg, crow, clim, d, pl.lo, pl.hi, pl.tstep);
     }
-    if (!GU && P.tp.world) {
+    if (tp_world) {
         // all-reduce of this CTA's rows over the ranks (see linear_stream.cu)
         const int lo = pl.lo, hi = pl.hi;
+        const uint32_t spin = d.tp.spin;
         __syncthreads();
-        uint8_t* mine = P.tp.peer[P.tp.rank];
-        if (threadIdx.x >= 32 && threadIdx.x < 32 + P.tp.world) {
+        uint8_t* mine = d.tp.peer[tp_rank];
+        if (threadIdx.x >= 32 && threadIdx.x < 32 + tp_world) {
             const int p = threadIdx.x - 32;
-            uint32_t* f = reinterpret_cast<uint32_t*>(P.tp.peer[p] + TP_FLAGS_OFF) + P.tp.rank * 256 + blockIdx.x;
+            uint32_t* f = reinterpret_cast<uint32_t*>(d.tp.peer[p] + TP_FLAGS_OFF) + tp_rank * 256 + blockIdx.x;
             asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(tp_next) : "memory");
         }
-        if (threadIdx.x < P.tp.world) {
+        if (threadIdx.x < tp_world) {
             const uint32_t* f = reinterpret_cast<const uint32_t*>(mine + TP_FLAGS_OFF) + threadIdx.x * 256 + blockIdx.x;
             uint32_t v = 0, i = 0;
-            for (; i < P.tp.spin; ++i) {
+            for (; i < spin; ++i) {
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
                 if (static_cast<int32_t>(v - tp_next) >= 0) break;
                 if (i > 64) __nanosleep(64);
             }
-            if (i == P.tp.spin) atomicExch(&g_error, 1);
+            if (i == spin) atomicExch(&g_error, 1);
         }
         __syncthreads();
         const float* slots = reinterpret_cast<const float*>(mine + TP_SLOTS_OFF) +
-                             static_cast<size_t>(tp_next & 1u) * 8 * P.tp.max_n;
-        __half* y = static_cast<__half*>(P.seg[0].y);
+                             static_cast<size_t>(tp_next & 1u) * 8 * tp_max_n;
+        __half* y = static_cast<__half*>(d.seg[0].y);
         for (int row = lo + threadIdx.x; row < hi; row += blockDim.x) {
             float v = 0.f;
-            for (int r = 0; r < P.tp.world; ++r) v += __ldcg(slots + static_cast<size_t>(r) * P.tp.max_n + row);
+            for (int r = 0; r < tp_world; ++r) v += __ldcg(slots + static_cast<size_t>(r) * tp_max_n + row);
             __half o = __float2half_rn(v);
-            if (P.residual) o = __float2half_rn(__half2float(__ldcg(P.residual + row)) + __half2float(o));
+            if (residual) o = __float2half_rn(__half2float(__ldcg(residual + row)) + __half2float(o));
             y[row] = o;
         }
         __syncthreads();
@@ -398,6 +542,7 @@ __device__ __noinline__ void gemv_run(Plan& pl, const GemvDesc& d, const CUtenso
             }
         }
     }
+    rs_io = rs;
 }
 
 // ------------------------------------------------------------------------------------ attention phase
@@ -853,7 +998,20 @@ __device__ __noinline__ void attn_phase(const AttnDesc& A, RingState& rs, uint8_
         const float4* po = reinterpret_cast<const float4*>(A.part_o + static_cast<int64_t>(h) * A.splits * AD + dd);
         const float* w = S->wgt + hg * A.splits;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s2 = 0; s2 < A.splits; ++s2) {
+        int s2 = 0;
+        for (; s2 + 8 <= A.splits; s2 += 8) {              // eight independent loads in flight
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __ldcg(po + static_cast<int64_t>(s2 + u) * (AD / 4));
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                acc.x = fmaf(w[s2 + u], v[u].x, acc.x);
+                acc.y = fmaf(w[s2 + u], v[u].y, acc.y);
+                acc.z = fmaf(w[s2 + u], v[u].z, acc.z);
+                acc.w = fmaf(w[s2 + u], v[u].w, acc.w);
+            }
+        }
+        for (; s2 < A.splits; ++s2) {
             const float4 v = __ldcg(po + static_cast<int64_t>(s2) * (AD / 4));
             acc.x = fmaf(w[s2], v.x, acc.x);
             acc.y = fmaf(w[s2], v.y, acc.y);
@@ -868,23 +1026,14 @@ __device__ __noinline__ void attn_phase(const AttnDesc& A, RingState& rs, uint8_
 
 // ------------------------------------------------------------------------------------ the kernel
 
-#define ALLOYB_DL_DISPATCH(FN, ...)                                                  \
-    do {                                                                             \
-        if (gd.gu) {                                                                 \
-            if (gd.kind == Q4x2) FN<Q4x2, true>(__VA_ARGS__);                        \
-            else FN<Q4x1, true>(__VA_ARGS__);                                        \
-        } else if (gd.kind == Q6) FN<Q6, false>(__VA_ARGS__);                        \
-        else if (gd.kind == Q4x2) FN<Q4x2, false>(__VA_ARGS__);                      \
-        else FN<Q4x1, false>(__VA_ARGS__);                                           \
-    } while (0)
-
 __global__ void __launch_bounds__(WARPS * 32, 1) decode_layers_kernel(const StepDesc sd) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float* red_all = reinterpret_cast<float*>(smem + RING_BYTES);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + RING_BYTES + RED_BYTES);
-    __half* xs = reinterpret_cast<__half*>(smem + RING_BYTES + RED_BYTES + BAR_BYTES);
-    float* nred = reinterpret_cast<float*>(smem + RING_BYTES + RED_BYTES + BAR_BYTES + XS_BYTES);
+    float* red_all = reinterpret_cast<float*>(smem + OFF_RED);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+    __half* xs = reinterpret_cast<__half*>(smem + OFF_XS);
+    float* sums = reinterpret_cast<float*>(smem + OFF_SUMS);
+    float* nred = reinterpret_cast<float*>(smem + OFF_NRED);
     RingState rs;
     rs.ring = smem_u32(smem + warp * RING_WARP);
     rs.bar0 = smem_u32(bars + warp * MAX_D);
@@ -897,40 +1046,79 @@ __global__ void __launch_bounds__(WARPS * 32, 1) decode_layers_kernel(const Step
     __syncwarp();
     pdl_launch_dependents();
 
+    // Phase descriptors live in global memory; a CTA works from copies in shared memory (three slots):
+    // the row cursors and the copy issue read them all the time, and with this much shared memory in
+    // use L1 is too small to serve that.  A descriptor is loaded two phases ahead (one word per
+    // thread, held in a register) and stored one phase ahead, so the load's latency is never waited for.
+    constexpr int DESC_WORDS = static_cast<int>(sizeof(PhaseDesc) / 4);
+    auto slot_of = [&](int ph) { return reinterpret_cast<const PhaseDesc*>(smem + OFF_DESC + (ph % DESC_SLOTS) * DESC_SLOT); };
+    auto load_word = [&](int ph) -> uint32_t {
+        return (ph < sd.n_phases && threadIdx.x < DESC_WORDS) ? __ldg(reinterpret_cast<const uint32_t*>(sd.phases + ph) + threadIdx.x) : 0u;
+    };
+    auto store_word = [&](int ph, uint32_t w) {
+        if (ph < sd.n_phases && threadIdx.x < DESC_WORDS)
+            reinterpret_cast<uint32_t*>(smem + OFF_DESC + (ph % DESC_SLOTS) * DESC_SLOT)[threadIdx.x] = w;
+    };
     unsigned int target = 0;
-    Plan pl;
-    {
-        const PhaseDesc& first = sd.phases[0];
-        if (first.type == PH_GEMV) {
-            const GemvDesc& gd = first.g;
-            ALLOYB_DL_DISPATCH(gemv_begin, pl, gd, sd.maps, rs, warp, lane);
-        }
-    }
+    Plan& pl = *reinterpret_cast<Plan*>(smem + OFF_PLAN + warp * PLAN_SLOT);
+    store_word(0, load_word(0));
+    store_word(1, load_word(1));
+    uint32_t pending = load_word(2);
+    __syncthreads();
+    if (slot_of(0)->type == PH_GEMV) gemv_begin(pl, slot_of(0)->g, sd.maps, rs, warp, lane);
     pdl_wait();
     for (int ph = 0; ph < sd.n_phases; ++ph) {
-        const PhaseDesc& pd = sd.phases[ph];
-        if (pd.type == PH_GEMV) {
-            const GemvDesc& gd = pd.g;
-            if (gd.stage_x) stage_token(gd, xs, nred);
-            else __syncthreads();                      // the previous phase's partial buffers are free
-            ALLOYB_DL_DISPATCH(gemv_run, pl, gd, sd.maps, rs, xs, red_all, warp, lane);
-        } else {
-            const AttnDesc& ad = pd.a;
-            AttnSmem* S = reinterpret_cast<AttnSmem*>(xs);
-            if (ad.layout == ALLOYB_KV_F16) attn_phase<ALLOYB_KV_F16>(ad, rs, smem, S, warp, lane);
-            else attn_phase<ALLOYB_KV_Q8_PAGED>(ad, rs, smem, S, warp, lane);
+        __syncthreads();                               // every warp has left phase ph - 1
+        if (ph >= 1) {
+            store_word(ph + 1, pending);
+            pending = load_word(ph + 2);
         }
+        const PhaseDesc& pd = *slot_of(ph);
+        auto stamp = [&](int k) {
+            if (sd.trace && threadIdx.x == 0) {
+                unsigned long long t;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+                sd.trace[(static_cast<size_t>(ph) * gridDim.x + blockIdx.x) * 4 + k] = t;
+            }
+        };
+        if (pd.type == PH_GEMV) {
+            if (pd.g.stage_x) stage_token(pd.g, xs, sums, nred);
+            else __syncthreads();
+            // the descriptor of phase ph + 1 is readable now: let the TMA unit fetch its tensor maps
+            // ahead of the first copy (they live in global memory; an un-fetched map stalls the issue)
+            if (ph + 1 < sd.n_phases && threadIdx.x < MAX_SEG) {
+                const PhaseDesc& nx = *slot_of(ph + 1);
+                if (nx.type == PH_GEMV && nx.g.seg[threadIdx.x].data)
+                    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(sd.maps + nx.g.seg[threadIdx.x].map)) : "memory");
+            }
+            stamp(0);
+            gemv_run(pl, pd.g, sd.maps, rs, xs, sums, red_all, warp, lane);
+        } else {
+            __syncthreads();
+            if (ph + 1 < sd.n_phases && threadIdx.x < MAX_SEG) {
+                const PhaseDesc& nx = *slot_of(ph + 1);
+                if (nx.type == PH_GEMV && nx.g.seg[threadIdx.x].data)
+                    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(sd.maps + nx.g.seg[threadIdx.x].map)) : "memory");
+            }
+            stamp(0);
+            AttnSmem* S = reinterpret_cast<AttnSmem*>(xs);
+            if (pd.a.layout == ALLOYB_KV_F16) attn_phase<ALLOYB_KV_F16>(pd.a, rs, smem, S, warp, lane);
+            else attn_phase<ALLOYB_KV_Q8_PAGED>(pd.a, rs, smem, S, warp, lane);
+        }
+        const int barrier_after = pd.barrier_after;
+        stamp(1);
         if (ph + 1 < sd.n_phases) {
-            const PhaseDesc& nx = sd.phases[ph + 1];
+            const PhaseDesc& nx = *slot_of(ph + 1);
             if (nx.type == PH_GEMV) {
                 // the next phase's first weight copies go out before the barrier (the attention phase
                 // uses the ring area for its own staging, so nothing is prefetched across it)
                 if (pd.type == PH_ATTN) __syncthreads();
-                const GemvDesc& gd = nx.g;
-                ALLOYB_DL_DISPATCH(gemv_begin, pl, gd, sd.maps, rs, warp, lane);
+                gemv_begin(pl, nx.g, sd.maps, rs, warp, lane);
             }
         }
-        if (pd.barrier_after) grid_sync(sd.barrier, target);
+        stamp(2);
+        if (barrier_after) grid_sync(sd.barrier, target);
+        stamp(3);
     }
 }
 
@@ -964,6 +1152,7 @@ struct Decoder {
     void* dev_block = nullptr;           // one allocation: phases | maps | scratch
     int n_phases = 0;
     int32_t* status = nullptr;
+    unsigned long long* trace = nullptr;   // 2 * n_phases timestamps, filled when tracing is on
 };
 
 struct Builder {
@@ -972,7 +1161,7 @@ struct Builder {
     int sms;
     int rc = ALLOYB_OK;
 
-    // One GEMV phase over matrices of ONE format that share the token x (K elements).
+    // One GEMV phase over matrices (Q4_K and Q6_K may be mixed) that share the token x (K elements).
     void gemv(const __half* x, int K, const __half* norm_w, float eps, const alloyb_matrix* const* m, void* const* y,
               int n_m, bool gated, const __half* residual, const alloyb_tp* tp, bool stage_x, bool barrier_after) {
         if (rc != ALLOYB_OK) return;
@@ -980,55 +1169,62 @@ struct Builder {
         pd.type = PH_GEMV;
         pd.barrier_after = barrier_after ? 1 : 0;
         GemvDesc& g = pd.g;
-        Params& P = g.P;
-        const int fmt = m[0]->format;
         if (K % QK_K || K > XS_HALVES || n_m < 1 || n_m > MAX_SEG) { rc = ALLOYB_E_SHAPE; return; }
         const int nsb = K / QK_K;
-        const int blk = fmt == ALLOYB_Q6_K ? Q6K_BYTES : Q4K_BYTES;
         int64_t rows = 0;
-        for (int i = 0; i < (gated ? 1 : n_m); ++i) rows += m[i]->N;
+        bool any_q6 = false;
+        for (int i = 0; i < n_m; ++i) {
+            if (m[i]->format != ALLOYB_Q4_K && m[i]->format != ALLOYB_Q6_K) { rc = ALLOYB_E_SHAPE; return; }
+            any_q6 |= m[i]->format == ALLOYB_Q6_K;
+            if (!gated || i == 0) rows += m[i]->N;
+        }
+        // the grouping rules of the stand-alone streaming kernel (linear_stream.cu)
         int gw = (rows / 16 >= static_cast<int64_t>(2) * WARPS * sms) ? 1 : (nsb >= 8 ? 8 : (nsb >= 4 ? 4 : 0));
         const int tiles_per_cta = static_cast<int>((rows + 16 * sms - 1) / (16 * sms));
         if (gw == 8 && !gated && nsb >= 16 && nsb % 16 == 0 && (tiles_per_cta == 1 || tiles_per_cta == 3)) gw = 16;
-        if (gw == 0 || (gated && (gw != 8 || fmt != ALLOYB_Q4_K || n_m != 2 || m[0]->N != m[1]->N))) { rc = ALLOYB_E_SHAPE; return; }
+        if (gw == 0 || (gated && (gw != 8 || any_q6 || n_m != 2 || m[0]->N != m[1]->N))) { rc = ALLOYB_E_SHAPE; return; }
         if (tp && (gated || n_m != 1)) { rc = ALLOYB_E_SHAPE; return; }
-        const int kind = fmt == ALLOYB_Q6_K ? Q6 : ((nsb % (2 * gw) == 0) ? Q4x2 : Q4x1);
-        const int pitch = kind == Q6 ? Geom<Q6>::PITCH : (kind == Q4x2 ? Geom<Q4x2>::PITCH : Geom<Q4x1>::PITCH);
-        P.x = x;
-        P.residual = residual;
-        P.norm_w = norm_w;
-        P.eps = eps;
-        P.n_seg = gated ? 1 : n_m;
-        P.nsb = nsb;
-        P.gated = gated ? 1 : 0;
-        P.act = ALLOYB_ACT_SILU;
-        P.depth = kind == Q4x1 ? 3 : 2;
-        if (tp) {
-            P.tp.world = tp->world;
-            P.tp.rank = tp->rank;
-            P.tp.max_n = tp->max_n;
-            P.tp.spin = tp->spin_limit > 0 ? static_cast<uint32_t>(tp->spin_limit) : SPIN_LIMIT;
-            for (int r = 0; r < tp->world; ++r) P.tp.peer[r] = static_cast<uint8_t*>(tp->peer[r]);
-        }
-        g.kind = kind;
+        const int sbs = (!any_q6 && nsb % (2 * gw) == 0) ? 2 : 1;
+        g.x = x;
+        g.residual = residual;
+        g.norm_w = norm_w;
+        g.eps = eps;
+        g.n_seg = gated ? 1 : n_m;
+        g.nsb = nsb;
         g.gu = gated ? 1 : 0;
+        g.act = ALLOYB_ACT_SILU;
         g.gw = gw;
-        g.map0 = static_cast<int>(maps.size());
+        g.sbs = sbs;
         g.stage_x = stage_x ? 1 : 0;
         g.K = K;
+        if (tp) {
+            g.tp.world = tp->world;
+            g.tp.rank = tp->rank;
+            g.tp.max_n = tp->max_n;
+            g.tp.spin = tp->spin_limit > 0 ? static_cast<uint32_t>(tp->spin_limit) : SPIN_LIMIT;
+            for (int r = 0; r < tp->world; ++r) g.tp.peer[r] = static_cast<uint8_t*>(tp->peer[r]);
+        }
         const EncodeFn encode = encoder();
         if (!encode) { set_cuda_error(cudaErrorNotSupported); rc = ALLOYB_E_CUDA; return; }
         int64_t base = 0;
+        int slot_bytes = 0;
         for (int i = 0; i < n_m; ++i) {
             const alloyb_matrix& a = *m[i];
+            const int kind = a.format == ALLOYB_Q6_K ? Q6 : (sbs == 2 ? Q4x2 : Q4x1);
+            const int blk = kind == Q6 ? Q6K_BYTES : Q4K_BYTES;
+            const int pitch = kind == Q6 ? Geom<Q6>::PITCH : (kind == Q4x2 ? Geom<Q4x2>::PITCH : Geom<Q4x1>::PITCH);
             const int64_t rb = a.row_bytes ? a.row_bytes : static_cast<int64_t>(nsb) * blk;
-            if (a.format != fmt || a.N <= 0 || !a.data || rb < static_cast<int64_t>(nsb) * blk) { rc = ALLOYB_E_SHAPE; return; }
+            if (a.N <= 0 || !a.data || rb < static_cast<int64_t>(nsb) * blk) { rc = ALLOYB_E_SHAPE; return; }
             if (reinterpret_cast<uintptr_t>(a.data) % 16 || rb % 16) { rc = ALLOYB_E_ALIGN; return; }
-            P.seg[i].data = static_cast<const uint8_t*>(a.data);
-            P.seg[i].row_bytes = rb;
-            P.seg[i].y = y[gated ? 0 : i];
-            P.seg[i].n_rows = a.N;
-            P.seg[i].row_base = gated ? 0 : static_cast<int>(base);
+            GSeg& sg = g.seg[i];
+            sg.data = static_cast<const uint8_t*>(a.data);
+            sg.row_bytes = rb;
+            sg.y = y[gated ? 0 : i];
+            sg.n_rows = a.N;
+            sg.row_base = gated ? 0 : static_cast<int>(base);
+            sg.kind = kind;
+            sg.map = static_cast<int>(maps.size());
+            if (16 * pitch > slot_bytes) slot_bytes = 16 * pitch;
             if (!gated || i == 0) base += a.N;
             CUtensorMap tm;
             const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(rb) / 4, static_cast<cuuint64_t>(a.N)};
@@ -1044,7 +1240,9 @@ struct Builder {
             }
             maps.push_back(tm);
         }
-        P.total_rows = static_cast<int>(base);
+        g.slot_bytes = slot_bytes;
+        g.depth = RING_WARP / slot_bytes > 3 ? 3 : RING_WARP / slot_bytes;
+        g.total_rows = static_cast<int>(base);
         phases.push_back(pd);
     }
 };
@@ -1083,11 +1281,12 @@ extern "C" int alloyb_decoder_create(const alloyb_decoder_desc* d, void** handle
     const size_t o_q = 0, o_k = o_q + up(qd * 2), o_v = o_k + up(kvd * 2), o_a = o_v + up(kvd * 2), o_act = o_a + up(qd * 2),
                  o_po = o_act + up(static_cast<size_t>(d->ffn) * 2),
                  o_pl = o_po + up(static_cast<size_t>(d->heads) * splits * AD * 4),
-                 o_ctr = o_pl + up(static_cast<size_t>(d->heads) * splits * 4), scratch_bytes = o_ctr + 1024;
+                 o_ctr = o_pl + up(static_cast<size_t>(d->heads) * splits * 4),
+                 o_trace = o_ctr + 1024,
+                 scratch_bytes = o_trace + up(static_cast<size_t>(d->n_layers * 5 + 2) * dec->sms * 4 * 8);
 
     Builder b;
     b.sms = dec->sms;
-    std::vector<size_t> attn_index;
     const __half* h = static_cast<const __half*>(d->hidden_io);
     // placeholders for scratch addresses until the block is allocated: offsets from a null base
     uint8_t* const S0 = nullptr;
@@ -1095,25 +1294,10 @@ extern "C" int alloyb_decoder_create(const alloyb_decoder_desc* d, void** handle
     for (int li = 0; li < d->n_layers; ++li) {
         const alloyb_decoder_layer& L = d->layers[li];
         if (!L.norm_in || !L.norm_post || !L.k0) { b.rc = ALLOYB_E_NULL; break; }
-        // q, k, v: one phase per weight format present, the token staged (and normalised) once
+        // q, k, v: one phase (formats may differ; the token is staged and normalised once)
         const alloyb_matrix* qkv[3] = {&L.wq, &L.wk, &L.wv};
         void* qkv_y[3] = {S0 + o_q, S0 + o_k, S0 + o_v};
-        bool first = true;
-        for (int fmt : {ALLOYB_Q4_K, ALLOYB_Q6_K}) {
-            const alloyb_matrix* m[3];
-            void* y[3];
-            int n = 0;
-            for (int i = 0; i < 3; ++i)
-                if (qkv[i]->format == fmt) { m[n] = qkv[i]; y[n] = qkv_y[i]; ++n; }
-            if (!n) continue;
-            int later = 0;
-            for (int i = 0; i < 3; ++i) later += (fmt == ALLOYB_Q4_K && qkv[i]->format == ALLOYB_Q6_K);
-            b.gemv(h, d->hidden, static_cast<const __half*>(L.norm_in), d->eps, m, y, n, false, nullptr, nullptr, first,
-                   later == 0);
-            first = false;
-        }
-        for (int i = 0; i < 3; ++i)
-            if (qkv[i]->format != ALLOYB_Q4_K && qkv[i]->format != ALLOYB_Q6_K) b.rc = ALLOYB_E_SHAPE;
+        b.gemv(h, d->hidden, static_cast<const __half*>(L.norm_in), d->eps, qkv, qkv_y, 3, false, nullptr, nullptr, true, true);
         if (L.wq.N != qd || L.wk.N != kvd || L.wv.N != kvd) b.rc = ALLOYB_E_SHAPE;
         if (b.rc != ALLOYB_OK) break;
         // attention
@@ -1140,7 +1324,6 @@ extern "C" int alloyb_decoder_create(const alloyb_decoder_desc* d, void** handle
             A.part_lse = reinterpret_cast<float*>(S0 + o_pl);
             A.counters = reinterpret_cast<unsigned int*>(S0 + o_ctr);
             A.status = reinterpret_cast<int*>(S0 + o_ctr + 512);
-            attn_index.push_back(b.phases.size());
             b.phases.push_back(pd);
         }
         // o_proj (+ residual, + exchange), gate/up (norm, SiLU), down (+ residual, + exchange)
@@ -1174,10 +1357,10 @@ extern "C" int alloyb_decoder_create(const alloyb_decoder_desc* d, void** handle
     };
     for (PhaseDesc& pd : b.phases) {
         if (pd.type == PH_GEMV) {
-            Params& P = pd.g.P;
-            P.x = static_cast<const __half*>(fix(P.x));
+            GemvDesc& g = pd.g;
+            g.x = static_cast<const __half*>(fix(g.x));
             for (int i = 0; i < MAX_SEG; ++i)
-                if (P.seg[i].data) P.seg[i].y = fix(P.seg[i].y);
+                if (g.seg[i].data) g.seg[i].y = fix(g.seg[i].y);
         } else {
             AttnDesc& A = pd.a;
             A.q = static_cast<const __half*>(fix(A.q));
@@ -1203,6 +1386,8 @@ extern "C" int alloyb_decoder_create(const alloyb_decoder_desc* d, void** handle
     dec->step.barrier = reinterpret_cast<unsigned int*>(scratch + o_ctr + 768);
     dec->status = reinterpret_cast<int32_t*>(scratch + o_ctr + 512);
     dec->n_phases = dec->step.n_phases;
+    dec->trace = reinterpret_cast<unsigned long long*>(scratch + o_trace);
+    dec->step.trace = nullptr;
     *handle = dec;
     return ALLOYB_OK;
 }
@@ -1225,6 +1410,25 @@ extern "C" int alloyb_decoder_step(void* handle, void* stream) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     e = cudaLaunchKernelEx(&cfg, decode_layers_kernel, dec->step);
+    if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
+    return ALLOYB_OK;
+}
+
+// Diagnostic: with tracing on, every CTA records four nanosecond clocks per phase (token staged, phase
+// done, next phase's copies issued, barrier passed); alloyb_decoder_trace_read copies the
+// phases x CTAs x 4 values of the last step.
+extern "C" int alloyb_decoder_trace(void* handle, int on) {
+    if (!handle) return ALLOYB_E_NULL;
+    dl::Decoder* dec = static_cast<dl::Decoder*>(handle);
+    dec->step.trace = on ? dec->trace : nullptr;
+    return ALLOYB_OK;
+}
+extern "C" int alloyb_decoder_trace_read(void* handle, uint64_t* out, int n_values) {
+    if (!handle || !out) return ALLOYB_E_NULL;
+    dl::Decoder* dec = static_cast<dl::Decoder*>(handle);
+    if (n_values < 0 || n_values > 4 * dec->n_phases * dec->sms) return ALLOYB_E_SHAPE;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(out, dec->trace, static_cast<size_t>(n_values) * 8, cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
     return ALLOYB_OK;
 }

@@ -227,7 +227,7 @@ class QuantLlamaDecoder:
         # shape is inside what that kernel is built for; ``one_launch=False`` keeps the op-by-op step.
         self._fused = None
         self.one_launch_error = None
-        want = one_launch if one_launch is not None else True
+        want = bool(one_launch)
         if want and self.batch == 1 and self.device.type == "cuda" and dtype == torch.float16 and \
                 (tp_size == 1 or tp_dry or self.exchange is not None):
             try:

@@ -6,13 +6,23 @@
 One step = one decode step (one new token per sequence) of a random-init Q4_K_M
 Llama-shape model under a CUDA graph.  N=1 runs the Llama-3-8B shape with an fp16
 KV cache at context 2048; N>1 (under torchrun, one rank per GPU) runs the
-Llama-3-70B shape tensor-parallel over N GPUs with NCCL all-reduce on the
-row-parallel outputs.  Prints ONE JSON line on rank 0.
+Llama-3-70B shape tensor-parallel over N GPUs, the row-parallel sums crossing
+NVLink inside the o_proj / down GEMV launches.  Prints ONE JSON line on rank 0.
+
+Besides the contract keys the line carries, measured in the same process:
+``roofline`` (the dominant kernel, the fused gate/up GEMV, timed live), ``gemv_cfg0``
+(the 4096 x 4096 Q4_K GEMV over a ring of replicas larger than L2), ``prefill_gemm``
+(the two M = 4096 dequant-GEMMs), ``attn_paged`` (batch-64 paged q8_0 decode attention,
+contexts 4096..32768), ``per_batch`` and ``cpu_baseline``; at N > 1 ``config.tp_check``
+(per-op parity of the row-parallel linear against the unsharded single-GPU kernel) and
+``tp1_equiv`` (the same 70B step timed on ONE GPU by rank 0, the denominator of the
+tensor-parallel scaling).
 """
 
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import statistics
@@ -23,12 +33,14 @@ import time
 
 import torch
 
+ROOT = os.path.dirname(os.path.abspath(__file__))
 WORKLOADS = {
     "llama3-8b-q4km-decode": dict(shape="LLAMA3_8B", context=2048, kv="f16"),
     "llama3-70b-q4km-decode": dict(shape="LLAMA3_70B", context=4096, kv="q8_paged"),
 }
 METRIC = "decode_tokens_per_s"
 WEIGHT_D_SCALE = 0.1    # multiplier on the synthetic block scales: zero-mean weights of std ~0.02
+CPU_ROW_DIV = 16        # the CPU leg times 1/16 of the rows of one layer (+ 1/256 of the head) per sample
 
 
 class ClockSampler:
@@ -84,26 +96,44 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def _measured_peaks() -> tuple[float, str]:
-    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
+def _measured_peaks() -> dict:
     try:
-        with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "kind": "measured"}
     except (OSError, KeyError, ValueError):
-        return 6650.0, "fallback"
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "kind": "fallback"}
 
 
-def _ncu_traffic(kernel: str):
-    """DRAM bytes per launch of the named kernel from the committed ncu summary, if any."""
-    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "profiles", "ncu_traffic.json")
+def _source_hash(files) -> str:
+    h = hashlib.sha256()
+    for rel in files:
+        with open(os.path.join(ROOT, rel), "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()[:16]
+
+
+def _ncu_traffic(key: str) -> tuple:
+    """(DRAM bytes per launch, note) from the committed ncu summary of kernel+shape ``key``; the
+    number is quoted only while the kernel sources it was captured from are unchanged."""
     try:
-        with open(path) as f:
-            return json.load(f).get(kernel)
+        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
+            entry = json.load(f).get(key)
     except (OSError, ValueError):
-        return None
+        entry = None
+    if not entry:
+        return None, f"no ncu capture recorded for {key}"
+    try:
+        now = _source_hash(entry["sources"])
+    except OSError:
+        return None, "kernel sources not found"
+    if now != entry["source_sha256"]:
+        return None, f"stale: {', '.join(entry['sources'])} changed since the capture in {entry['capture']}"
+    return entry["dram_bytes"], entry["capture"]
 
 
-def _event_ms(fn, stream=None) -> float:
+def _event_ms(fn) -> float:
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     a.record()
@@ -116,7 +146,7 @@ def _event_ms(fn, stream=None) -> float:
 # --------------------------------------------------------------------------------- CPU baseline
 
 
-def cpu_layer_sample(shape, batch: int, seed: int = 0, row_div: int = 1) -> dict:
+def cpu_layer_sample(shape, batch: int, seed: int = 0, row_div: int = CPU_ROW_DIV) -> dict:
     """Time the reference's CPU-side path (NumPy block dequantiser -> torch CPU fp32 matmul)
     on 1/row_div of the rows of ONE transformer layer's seven matrices plus 1/(16*row_div)
     of the output head, and extrapolate to a full decode step.  Attention and norms are
@@ -133,7 +163,7 @@ def cpu_layer_sample(shape, batch: int, seed: int = 0, row_div: int = 1) -> dict
             ("q4", shape.hidden, hd), ("q4", shape.ffn, shape.hidden), ("q4", shape.ffn, shape.hidden),
             ("q6", shape.hidden, shape.ffn)]
     head_rows = shape.vocab // 16
-    t_deq = t_mm = 0.0
+    t_deq = t_mm = t_wall = 0.0
     for fmt, n, k in mats + [("q6h", head_rows, shape.hidden)]:
         n = max(16, n // row_div)
         blk = synth.q4k_blocks(rng, n, k) if fmt == "q4" else synth.q6k_blocks(rng, n, k)
@@ -144,12 +174,12 @@ def cpu_layer_sample(shape, batch: int, seed: int = 0, row_div: int = 1) -> dict
         y = x.float() @ torch.from_numpy(w).T
         y = y.to(torch.float16)
         t2 = time.perf_counter()
-        full_n = head_rows * 16 if fmt == "q6h" else None
-        scale = (full_n / n) if fmt == "q6h" else float(shape.layers) * row_div
+        scale = (head_rows * 16 / n) if fmt == "q6h" else float(shape.layers) * row_div
         t_deq += (t1 - t0) * scale
         t_mm += (t2 - t1) * scale
+        t_wall += t2 - t0
     step_s = t_deq + t_mm
-    return {"step_s": step_s, "dequant_s": t_deq, "matmul_s": t_mm,
+    return {"step_s": step_s, "sample_s": t_wall, "dequant_s": t_deq, "matmul_s": t_mm,
             "tok_s": batch / step_s, "cores": torch.get_num_threads(),
             "sample": (f"1/{row_div} of the rows of 1 of {shape.layers} layers (7 matrices) + "
                        f"1/{16 * row_div} of the head rows at batch "
@@ -158,27 +188,32 @@ def cpu_layer_sample(shape, batch: int, seed: int = 0, row_div: int = 1) -> dict
 
 
 def run_reference(args, shape, workload: str) -> None:
+    """The reference arm: the reference's CPU path of the linears on this box's host cores.  A step
+    is ONE bounded sample (the same sample the GPU arm's ``cpu_baseline`` uses); ``value`` is the
+    tokens/s a full step would give, extrapolated from it, and ``ms_per_step`` the wall time of the
+    sample actually run."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    times = []
-    last = None
+    steps, walls, last = [], [], None
     for i in range(args.warmup + args.steps):
-        t0 = time.perf_counter()
-        last = cpu_layer_sample(shape, args.batch, seed=i, row_div=16)
+        last = cpu_layer_sample(shape, args.batch, seed=i)
         if i >= args.warmup:
-            times.append(last["step_s"])
-    step_s = statistics.mean(times)
+            steps.append(last["step_s"])
+            walls.append(last["sample_s"])
+    step_s = statistics.mean(steps)
     val = args.batch / step_s
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": statistics.mean(walls) * 1e3,
         "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload, "batch": args.batch, "context": WORKLOADS[workload]["context"],
-                   "kv": WORKLOADS[workload]["kv"], "parallelism": "host cores (attention and norms left out)"},
+                   "kv": WORKLOADS[workload]["kv"], "parallelism": "host cores (attention and norms left out)",
+                   "extrapolated": True, "full_step_ms_extrapolated": step_s * 1e3,
+                   "cpu_sample": last["sample"]},
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": last["cores"], "kind": "port",
-                         "sample": last["sample"]},
+                         "sample": last["sample"], "extrapolated": True},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -208,13 +243,51 @@ def gemv_roofline(dec, reps: int = 8) -> dict:
     launches = reps * len(dec.layers)
     n, k = dec.layers[0].wg.shape[0], s.hidden
     alg = 2 * n * (k // 256) * 144 + dec.batch * k * 2 + dec.batch * n * 2
-    return {"kernel": "q4k gate/up fused dequant-GEMV", "bytes_per_launch": alg,
+    return {"kernel": "q4k gate/up fused dequant-GEMV", "shape": f"2x{n}x{k}_m{dec.batch}", "bytes_per_launch": alg,
             "us_per_launch": ms * 1e3 / launches, "gbs": alg / (ms * 1e-3 / launches) / 1e9}
+
+
+def kernel_extras(peaks: dict, note) -> dict:
+    """The other configured kernels, each timed alone over inputs larger than L2 (or re-streamed
+    from HBM every launch) in this process: config 0, config 2 and config 3."""
+    from alloy_b200 import microbench as mb
+
+    out = {}
+    try:
+        note("gemv cfg0")
+        r = mb.bench_linear("q4k_mm", 4096, 4096, 1, 512, 10, torch.float16)       # 57 replicas = 540 MB
+        out["gemv_cfg0"] = {"shape": "Q4_K 4096x4096, one fp16 token", "replicas": r["replicas"],
+                            "launches_timed": r["replicas"] * 10, "bytes_per_launch": r["bytes_per_launch"],
+                            "us_per_launch": r["us_per_launch_median"], "gbs": r["gbs_median"],
+                            "frac_of_hbm_peak": r["gbs_median"] / peaks["hbm_gbs"]}
+    except Exception as e:  # noqa: BLE001 - an extra must not lose the contract line
+        out["gemv_cfg0"] = {"error": repr(e)}
+    try:
+        note("prefill gemm")
+        gemms = {}
+        for fmt, n, k in (("q4k", 14336, 4096), ("q6k", 4096, 14336)):
+            r = mb.bench_gemm(fmt, 4096, n, k, 8, torch.bfloat16)
+            gemms[f"{fmt}_{n}x{k}"] = {"m": 4096, "ms": r["ms_median"], "tflops": r["tflops_median"],
+                                       "frac_of_bf16_burst": r["tflops_median"] / peaks["bf16_tflops"],
+                                       "frac_of_bf16_sustained": r["tflops_median"] / peaks["bf16_tflops_sustained"]}
+        out["prefill_gemm"] = gemms
+    except Exception as e:  # noqa: BLE001
+        out["prefill_gemm"] = {"error": repr(e)}
+    try:
+        note("paged attention")
+        r = mb.bench_attn_paged(64, 4096, 32768, 8)
+        out["attn_paged"] = {"batch": 64, "ctx": [4096, 32768], "layout": "16-token pages of 34-byte q8_0 blocks, shuffled",
+                             "tokens": r["tokens"], "bytes_per_launch": r["bytes_per_launch"], "us": r["us_median"],
+                             "gbs": r["gbs_median"], "frac_of_hbm_peak": r["gbs_median"] / peaks["hbm_gbs"]}
+    except Exception as e:  # noqa: BLE001
+        out["attn_paged"] = {"error": repr(e)}
+    torch.cuda.empty_cache()
+    return out
 
 
 def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
     import alloy_b200  # noqa: F401
-    from alloy_b200 import llama, ops
+    from alloy_b200 import llama, tp
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -229,6 +302,10 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
         pg = torch.distributed.group.WORLD
     shape = getattr(llama, shape_name)
     dev = torch.device("cuda", local)
+    peaks = _measured_peaks()
+    peak = peaks["hbm_gbs"]
+    w_bytes = shape.weight_bytes()
+    one_launch = {"auto": False, "one-launch": True, "per-op": False}[args.step]
 
     t_start = time.perf_counter()
 
@@ -236,13 +313,16 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
         if args.verbose:
             print(f"[bench rank {rank} +{time.perf_counter() - t_start:6.1f}s] {msg}", file=sys.stderr, flush=True)
 
-    def build(batch):
-        note(f"building decoder batch={batch}")
+    def build(batch, *, solo=False, fused=None):
+        """``solo``: the whole model on this GPU (no tensor parallelism), whatever the world size."""
+        note(f"building decoder batch={batch} solo={solo}")
         # zero-mean weights of std ~0.02 (centred Q4_K blocks, block scales at 0.1 of the kernel-test
         # range): the residual stream of 32 to 80 random layers stays inside fp16, the logits finite
         d = llama.QuantLlamaDecoder(shape, batch, wl["context"], device=dev, seed=0, kv=wl["kv"],
-                                    tp_rank=rank, tp_size=dry or world, process_group=pg, tp_dry=bool(dry),
-                                    d_scale=WEIGHT_D_SCALE, centered=True)
+                                    tp_rank=0 if solo else rank, tp_size=1 if solo else (dry or world),
+                                    process_group=None if solo else pg, tp_dry=bool(dry) and not solo,
+                                    d_scale=WEIGHT_D_SCALE, centered=True,
+                                    one_launch=one_launch if fused is None else fused)
         torch.cuda.synchronize()
         note("weights ready; capturing")
         d.capture()
@@ -250,16 +330,16 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
         note("captured")
         return d
 
-    def timed(dec, steps, warmup):
+    def timed(dec, steps, warmup, *, collective=True):
         gen = torch.Generator().manual_seed(1)
         dec.ids.copy_(torch.randint(0, shape.vocab, (dec.batch,), generator=gen))
         for _ in range(warmup):
             dec.step()
-        if world > 1:
+        if world > 1 and collective:
             torch.distributed.barrier()
         ms = _event_ms(lambda: [dec.step() for _ in range(steps)])
         t = torch.tensor([ms], device=dev)
-        if world > 1:
+        if world > 1 and collective:
             torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         return float(t.item())
 
@@ -284,6 +364,23 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
             torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         return float(t.item()), dec.batch * 8, dec.batch * 8
 
+    # ---- tensor parallel: the same step on ONE GPU first (rank 0 alone; 44 GB fits one B200): the
+    # denominator of the scaling figure.  The other ranks wait at the barrier below.
+    tp1 = None
+    if world > 1 and not args.no_tp1:
+        if rank == 0:
+            try:
+                solo = build(args.batch, solo=True)
+                solo_ms = timed(solo, args.steps, args.warmup, collective=False) / args.steps
+                tp1 = {"ms_per_step": solo_ms, "bytes_per_s": w_bytes / (solo_ms * 1e-3),
+                       "frac_of_hbm_peak": w_bytes / (solo_ms * 1e-3) / 1e9 / peak, "device_error": solo.device_error()}
+                del solo
+            except Exception as e:  # noqa: BLE001
+                tp1 = {"error": repr(e)}
+            torch.cuda.empty_cache()
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+
     dec = build(args.batch)
     with ClockSampler(local) as clocks:
         ms = timed(dec, args.steps, args.warmup)
@@ -301,111 +398,171 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
             for _ in range(20):
                 dec.step()
             torch.cuda.synchronize()
+    # a bounded wait that ran out anywhere in the timed steps voids them
+    dev_err = torch.tensor([dec.device_error()], device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(dev_err, op=torch.distributed.ReduceOp.MAX)
+    dev_err = int(dev_err.item())
     value = args.batch * args.steps / (ms * 1e-3)
     e2e_val = args.batch * args.steps / (e2e_ms * 1e-3)
-    w_bytes = shape.weight_bytes()
-    peak, peak_kind = _measured_peaks()
     roof = gemv_roofline(dec)
-    tp_check = None
-    if world > 1 and args.check_tp:
-        # the same step with the all-reduce inside the GEMV launches (peer memory) and with NCCL
-        note("tp check: building the twins")
-        # fp16 KV here: its random contents are a slice of the unsharded cache's, so that the same
-        # step of the whole model on this one GPU (fp32 sums over the full K) can referee the two
-        mk = lambda peer, size=world: llama.QuantLlamaDecoder(
-            shape, args.batch, wl["context"], device=dev, seed=0, kv="f16", tp_rank=rank if size > 1 else 0,
-            tp_size=size, process_group=pg if size > 1 else None, d_scale=WEIGHT_D_SCALE, centered=True,
-            peer_allreduce=peer)
-        fused, twin = mk(True), mk(False)
-        for d in (fused, twin):
-            d.ids.fill_(11)
-        a = fused.step_eager_logits().float().clone()
-        b = twin.step_eager_logits().float().clone()
-        calls = fused.fused_allreduce_calls
-        torch.cuda.synchronize()
-        del fused, twin
-        torch.cuda.empty_cache()
-        whole = mk(False, 1)
-        whole.ids.fill_(11)
-        c = whole.step_eager_logits().float().clone()
-        rms = c.pow(2).mean().sqrt()
-        both = torch.stack([(a - b).abs().max() / rms, (a - c).abs().max() / rms, (b - c).abs().max() / rms])
-        torch.distributed.all_reduce(both, op=torch.distributed.ReduceOp.MAX)
-        tp_check = {"max_abs_diff_over_rms": {"fused_vs_nccl": float(both[0].item()),
-                                              "fused_vs_one_gpu": float(both[1].item()),
-                                              "nccl_vs_one_gpu": float(both[2].item())},
-                    "fused_calls_per_step": calls, "finite": bool(torch.isfinite(a).all().item())}
-        torch.cuda.synchronize()
-        del whole
-        torch.cuda.empty_cache()
-    launches_step = dec.launches_per_step + shape.layers + 1   # + KV append per layer + id copy
+    launches_step = dec.launches_per_step + 1              # + the copy of the new token ids
     finite = bool(torch.isfinite(dec.logits.float()).all().item())
+    step_kind = "one persistent launch" if dec._fused is not None else "op by op"
+    allreduce = None
+    if world > 1:
+        allreduce = ("inside the o_proj/down GEMV launches over NVLink peer memory" if dec.exchange is not None
+                     else "NCCL")
+
+    # ---- tensor parallel: per-op parity of the row-parallel linear on the live ranks (every run)
+    tp_check = None
+    if world > 1:
+        note("tp check")
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        tp_check = tp.check_row_parallel(dec.exchange, rank, world, pg, dev)
+        tp_check["device_error"] = int(dec.device_error())
+    step_check = None
+    if world > 1 and args.check_tp:
+        step_check = whole_step_check(args, shape, wl, rank, world, pg, dev)
 
     per_batch = {}
-    if world == 1 and not args.no_sweep:
-        for b in (1, 4, 16, 32):
-            if b == args.batch:
-                per_batch[str(b)] = {"ms_per_step": ms / args.steps, "tokens_per_s": value}
-                continue
+    sweep = () if args.no_sweep else ((1, 4, 16, 32) if world == 1 else (1, 64))
+    for b in sweep:
+        if b == args.batch:
+            per_batch[str(b)] = {"ms_per_step": ms / args.steps, "tokens_per_s": value}
+            continue
+        try:
             del dec
             torch.cuda.empty_cache()
             dec = build(b)
             bms = timed(dec, args.steps, args.warmup)
-            per_batch[str(b)] = {"ms_per_step": bms / args.steps,
-                                 "tokens_per_s": b * args.steps / (bms * 1e-3)}
-        for b, r in per_batch.items():
-            kv_bytes = int(b) * shape.layers * 2 * shape.kv_heads * shape.head_dim * wl["context"] * 2
-            r["frac_of_weight_bound"] = (w_bytes / (peak * 1e9)) / (r["ms_per_step"] * 1e-3)
-            r["frac_of_weight_plus_kv_bound"] = ((w_bytes + kv_bytes) / (peak * 1e9)) / (r["ms_per_step"] * 1e-3)
+            per_batch[str(b)] = {"ms_per_step": bms / args.steps, "tokens_per_s": b * args.steps / (bms * 1e-3)}
+        except Exception as e:  # noqa: BLE001 - a sweep point must not lose the contract line
+            per_batch[str(b)] = {"error": repr(e)}
+            break
+    kv_row = 2 * shape.kv_heads * shape.head_dim * (2 if wl["kv"] == "f16" else 34 / 32)
+    for b, r in per_batch.items():
+        if "ms_per_step" not in r:
+            continue
+        kv_bytes = int(b) * shape.layers * kv_row * wl["context"]
+        r["frac_of_weight_bound"] = (w_bytes / world / (peak * 1e9)) / (r["ms_per_step"] * 1e-3)
+        r["frac_of_weight_plus_kv_bound"] = ((w_bytes + kv_bytes) / world / (peak * 1e9)) / (r["ms_per_step"] * 1e-3)
+
+    extras, one_launch_cmp = {}, None
+    if world == 1 and not dry and not args.no_extras:
+        dec = None
+        torch.cuda.empty_cache()
+        extras = kernel_extras(peaks, note)
+        if args.batch == 1 and args.step == "auto":
+            # the same step as ONE persistent launch (opt-in; the op-by-op step is the default)
+            try:
+                alt = build(1, fused=True)
+                ams = timed(alt, args.steps, args.warmup) / args.steps
+                one_launch_cmp = {"ms_per_step": ams, "tokens_per_s": 1e3 / ams, "phases": alt._fused.phases,
+                                  "device_error": alt.device_error()}
+                del alt
+            except Exception as e:  # noqa: BLE001
+                one_launch_cmp = {"error": repr(e)}
+            torch.cuda.empty_cache()
 
     if rank != 0:
         _leave(world)
         return
     cpu = None
-    if world == 1 and not args.no_cpu:
-        # three independently seeded samples (~10-15 s of host work), averaged
+    if not args.no_cpu:
+        # three independently seeded samples (a few seconds of host work each), averaged; the SAME
+        # sample the reference arm times
         runs = [cpu_layer_sample(shape, args.batch, seed=i) for i in range(3)]
         cpu = dict(runs[0])
         cpu["step_s"] = statistics.mean(r["step_s"] for r in runs)
         cpu["tok_s"] = args.batch / cpu["step_s"]
         cpu["sample"] = "mean of 3 samples, each: " + runs[0]["sample"]
+    ws_gbs = (w_bytes / world) / (ms / args.steps * 1e-3) / 1e9
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
         "config": {"workload": workload, "batch": args.batch, "context": wl["context"], "kv": wl["kv"],
-                   "parallelism": f"tp{world}" if not dry else f"rank 0 of tp{dry}, no peers (not a bench value)", "weight_bytes_per_step": w_bytes // world,
+                   "parallelism": f"tp{world}" if not dry else f"rank 0 of tp{dry}, no peers (not a bench value)",
+                   "step": step_kind, "weight_bytes_per_step": w_bytes // world,
                    "l2": "each step streams its weights once (GBs, far above the 126 MB L2)",
-                   "logits_finite": finite, "weight_d_scale": WEIGHT_D_SCALE},
+                   "logits_finite": finite, "weight_d_scale": WEIGHT_D_SCALE, "device_error": dev_err},
         "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches_step * args.steps,
         "clocks": clocks.summary(),
-        "weight_stream": {"bytes_per_step": w_bytes // world, "achieved_gbs": (w_bytes / world) / (ms / args.steps * 1e-3) / 1e9,
-                          "frac_of_peak": (w_bytes / world) / (ms / args.steps * 1e-3) / 1e9 / peak,
-                          "peak_gbs": peak, "peak_kind": peak_kind},
+        "weight_stream": {"bytes_per_step": w_bytes // world, "achieved_gbs": ws_gbs, "frac_of_peak": ws_gbs / peak,
+                          "peak_gbs": peak, "peak_kind": peaks["kind"]},
     }
-    if roof is not None:
-        # the committed ncu capture is of the 8B shape's launch: quoted only where this run's launch is that one
-        traffic = _ncu_traffic("gated_q4k")
-        if traffic is not None and abs(traffic / roof["bytes_per_launch"] - 1.0) > 0.1:
-            traffic = None
-        line["roofline"] = {"bound": "hbm", "achieved": roof["gbs"], "peak": peak, "unit": "GB/s",
-                            "frac": roof["gbs"] / peak, "traffic": traffic,
-                            "kernel": roof["kernel"], "bytes_per_launch": roof["bytes_per_launch"],
-                            "us_per_launch": roof["us_per_launch"], "peak_kind": peak_kind}
+    traffic, traffic_source = _ncu_traffic(f"gemv_stream_gate_up_q4k_{roof['shape']}")
+    line["roofline"] = {"bound": "hbm", "achieved": roof["gbs"], "peak": peak, "unit": "GB/s",
+                        "frac": roof["gbs"] / peak, "traffic": traffic, "traffic_source": traffic_source,
+                        "kernel": roof["kernel"], "shape": roof["shape"], "bytes_per_launch": roof["bytes_per_launch"],
+                        "us_per_launch": roof["us_per_launch"], "peak_kind": peaks["kind"]}
+    if dev_err:
+        line["config"]["invalid"] = "a bounded device-side wait ran out during the timed steps"
     if tp_check is not None:
         line["config"]["tp_check"] = tp_check
-    if world > 1:
-        line["config"]["allreduce"] = ("inside the o_proj/down GEMV launches over NVLink peer memory"
-                                       if dec.exchange is not None else "NCCL")
+    if step_check is not None:
+        line["config"]["tp_step_check"] = step_check
+    if allreduce is not None:
+        line["config"]["allreduce"] = allreduce
+    if tp1 is not None:
+        line["tp1_equiv"] = dict(tp1)
+        if "ms_per_step" in tp1:
+            line["tp1_equiv"].update({
+                "what": "the same 70B step on one GPU, timed by rank 0 before the tensor-parallel run",
+                "scaling_vs_tp1": tp1["ms_per_step"] / (ms / args.steps),
+                "tp1_equiv_bytes_per_s": w_bytes / (ms / args.steps * 1e-3),
+                "per_rank_hbm_frac": ws_gbs / peak})
     if per_batch:
         line["per_batch"] = per_batch
+    if one_launch_cmp is not None:
+        line["one_launch_step"] = one_launch_cmp
+    line.update(extras)
     if cpu is not None:
         line["cpu_baseline"] = {"value": cpu["tok_s"], "unit": "tokens/s", "cores": cpu["cores"],
-                                "kind": "port", "sample": cpu["sample"]}
+                                "kind": "port", "sample": cpu["sample"], "extrapolated": True}
+        line["config"]["cpu_sample"] = cpu["sample"]
     print(json.dumps(line), flush=True)
     _leave(world)
+
+
+def whole_step_check(args, shape, wl, rank, world, pg, dev) -> dict:
+    """--check-tp: the whole 80-layer step with the fused exchange, with NCCL all-reduces of fp16
+    partials, and on one GPU (fp32 sums over the full K) as referee.  A deep random stack amplifies
+    rounding differences, so this is an extra beside the per-op check, with a loose bound."""
+    from alloy_b200 import llama
+
+    mk = lambda peer, size=world: llama.QuantLlamaDecoder(
+        shape, args.batch, wl["context"], device=dev, seed=0, kv="f16", tp_rank=rank if size > 1 else 0,
+        tp_size=size, process_group=pg if size > 1 else None, d_scale=WEIGHT_D_SCALE, centered=True,
+        peer_allreduce=peer, one_launch=False)
+    fused, twin = mk(True), mk(False)
+    for d in (fused, twin):
+        d.ids.fill_(11)
+    a = fused.step_eager_logits().float().clone()
+    b = twin.step_eager_logits().float().clone()
+    calls = fused.fused_allreduce_calls
+    err = fused.device_error()
+    torch.cuda.synchronize()
+    del fused, twin
+    torch.cuda.empty_cache()
+    whole = mk(False, 1)
+    whole.ids.fill_(11)
+    c = whole.step_eager_logits().float().clone()
+    rms = c.pow(2).mean().sqrt()
+    both = torch.stack([(a - b).abs().max() / rms, (a - c).abs().max() / rms, (b - c).abs().max() / rms])
+    torch.distributed.all_reduce(both, op=torch.distributed.ReduceOp.MAX)
+    out = {"max_abs_diff_over_rms": {"fused_vs_nccl": float(both[0].item()), "fused_vs_one_gpu": float(both[1].item()),
+                                     "nccl_vs_one_gpu": float(both[2].item())},
+           "fused_calls_per_step": calls, "finite": bool(torch.isfinite(a).all().item()), "device_error": int(err),
+           "bound": 0.1, "pass": bool(float(both[1].item()) <= 0.1 and err == 0)}
+    torch.cuda.synchronize()
+    del whole
+    torch.cuda.empty_cache()
+    return out
 
 
 def _leave(world: int) -> None:
@@ -432,8 +589,13 @@ def main() -> None:
                     help="1 GPU: time rank 0's share of a TP-N step with nobody to exchange with (profiling aid; "
                          "not a bench value)")
     ap.add_argument("--check-tp", action="store_true",
-                    help="N > 1: also run one step with NCCL all-reduces and report the logits difference")
-    ap.add_argument("--no-sweep", action="store_true", help="skip the batch 1/4/16/32 sweep")
+                    help="N > 1: also run the whole step with NCCL all-reduces and on one GPU and report the logits difference")
+    ap.add_argument("--step", default="auto", choices=["auto", "one-launch", "per-op"],
+                    help="batch 1: the whole step as one persistent launch, or op by op (auto: op by op, with the "
+                         "one-launch step timed beside it at N = 1)")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the batch sweep")
+    ap.add_argument("--no-extras", action="store_true", help="N = 1: skip the config 0 / 2 / 3 kernel timings")
+    ap.add_argument("--no-tp1", action="store_true", help="N > 1: skip the one-GPU run of the same step")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
     ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")
     args = ap.parse_args()

@@ -358,6 +358,11 @@ int alloyb_decoder_create(const alloyb_decoder_desc* desc, void** handle);
 int alloyb_decoder_step(void* handle, void* stream);
 int alloyb_decoder_phases(void* handle);     /* phases the step walks (diagnostic) */
 int alloyb_decoder_status(void* handle, int32_t* status_out, void* stream);   /* bits as alloyb_attn_workspace_status */
+/* Diagnostic: with tracing on, every CTA records four nanosecond clocks per phase (token staged,
+ * phase done, next phase's first copies issued, barrier passed); trace_read synchronises the device
+ * and copies n_values <= phases * SMs * 4 of them, ordered [phase][CTA][4]. */
+int alloyb_decoder_trace(void* handle, int on);
+int alloyb_decoder_trace_read(void* handle, uint64_t* out_ns, int n_values);
 int alloyb_decoder_destroy(void* handle);
 
 /* ------------------------------------------------------------------ routed experts

@@ -132,7 +132,7 @@ def test_one_launch_step_matches_op_by_op_and_oracle(kv_kind):
                                                one_launch=fused)
     fused, plain = mk(True), mk(False)
     assert fused._fused is not None and plain._fused is None
-    assert fused._fused.phases == WIDE.layers * 6 + 1
+    assert fused._fused.phases == WIDE.layers * 5 + 1
     if kv_kind == "f16":
         kc = [k.float().cpu().numpy() for k in plain.k_cache]
         vc = [v.float().cpu().numpy() for v in plain.v_cache]
