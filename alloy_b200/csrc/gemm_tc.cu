@@ -7,7 +7,7 @@
 //     (128-byte swizzle) and, once per super-block, the 128 packed weight rows with bulk copies;
 //   * warps 2-5 (128 threads, one weight row each) decode 64 weights of their row to fp32
 //     exactly as the block format defines them (Q4_K: d*sc*nib - dmin*m with ONE rounding;
-//     Q6_K: d*sc*(q-32), exact), round ONCE to the activation type and store them into the
+//     Q6_K: d*sc*(q-32), exact; Q8_0: scale*code, exact), round ONCE to the activation type and store them into the
 //     K-major, 128-byte-swizzled layout the MMA reads;
 //   * warp 1 (one lane) issues two tcgen05.mma (M = 128 tokens each, N = 128, K = 16 x 4) whose
 //     accumulators live in tensor memory (256 columns), and releases the stage with
@@ -34,8 +34,9 @@ constexpr int BK = 64;                  // K step: 64 x 2 bytes = one 128-byte s
 constexpr int STAGES = 3;
 constexpr int A_STAGE = BM * BK * 2;    // 32 KB
 constexpr int B_STAGE = BN * BK * 2;    // 16 KB
-constexpr int PACK_ROW = 240;           // packed super-block per row: 144 (Q4_K) / <= 224-byte window (Q6_K);
-                                        // 15 x 16 bytes keeps 128-bit reads of 8 rows conflict-free
+constexpr int PACK_ROW = 272;           // packed super-block per row: 144 (Q4_K) / <= 224-byte window (Q6_K) /
+                                        // 256 codes + 8 fp16 scales (Q8_0); 17 x 16 bytes keeps 128-bit reads
+                                        // of 8 rows conflict-free
 constexpr int PACK_STAGE = BN * PACK_ROW;   // 28 KB
 constexpr int PACK_STAGES = 2;
 constexpr int DEC_THREADS = 256;        // two decode threads per weight row (half a k-step each)
@@ -57,9 +58,10 @@ struct Bars {
 constexpr int SMEM_BYTES = 1024 /*align slack*/ + STAGES * (A_STAGE + B_STAGE) + PACK_STAGES * PACK_STAGE + 256;
 
 struct Params {
-    const uint8_t* w;         // packed rows
+    const uint8_t* w;         // packed rows (Q8_0: int8 codes, K per row)
+    const __half* scales;     // Q8_0: fp16 (N, K/32)
     int64_t row_bytes;
-    int format;               // ALLOYB_Q4_K / ALLOYB_Q6_K
+    int format;               // ALLOYB_Q4_K / ALLOYB_Q6_K / ALLOYB_Q8_0
     void* y;
     int64_t ldy;
     int M, N, K;
@@ -253,6 +255,31 @@ __device__ __forceinline__ void decode_q6k(const uint8_t* blk, int ks, uint8_t* 
     }
 }
 
+// Q8_0: the stage row holds 256 codes then the super-block's eight fp16 scales.  k-step ks: elements
+// 64*ks .. +63 = two 32-element blocks, one per thread of the pair; w = scale * code (exact in fp32).
+template <bool BF16>
+__device__ __forceinline__ void decode_q8_0(const uint8_t* blk, int ks, uint8_t* tile, int r, int hsel) {
+    const float sc = half_bits_to_f32(lds_u16(blk + 256 + (2 * ks + hsel) * 2));
+    const uint8_t* q = blk + ks * 64 + hsel * 32;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {                        // 16 codes -> two 16-byte chunks
+        const uint4 v = lds_u128(q + 16 * c);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float f0 = sc * static_cast<float>(static_cast<int8_t>(w[j] & 0xffu));
+            const float f1 = sc * static_cast<float>(static_cast<int8_t>((w[j] >> 8) & 0xffu));
+            const float f2 = sc * static_cast<float>(static_cast<int8_t>((w[j] >> 16) & 0xffu));
+            const float f3 = sc * static_cast<float>(static_cast<int8_t>(w[j] >> 24));
+            o[2 * j] = pack2<BF16>(f0, f1);
+            o[2 * j + 1] = pack2<BF16>(f2, f3);
+        }
+        sts_u128(swz(tile, r, 4 * hsel + 2 * c), make_uint4(o[0], o[1], o[2], o[3]));
+        sts_u128(swz(tile, r, 4 * hsel + 2 * c + 1), make_uint4(o[4], o[5], o[6], o[7]));
+    }
+}
+
 template <bool BF16>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
@@ -266,7 +293,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
     const int nsb = P.K / QK_K, ksteps = nsb * 4;
-    const int blk_bytes = P.format == ALLOYB_Q4_K ? Q4K_BYTES : Q6K_BYTES;
+    const int blk_bytes = P.format == ALLOYB_Q4_K ? Q4K_BYTES : (P.format == ALLOYB_Q6_K ? Q6K_BYTES : 256);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -306,14 +333,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
                 // as the aligned 224-byte window around it
                 const int start = sb * blk_bytes;
                 const int ws = start & ~15;
-                const uint32_t bytes = P.format == ALLOYB_Q4_K ? Q4K_BYTES : static_cast<uint32_t>(((start & 15) + Q6K_BYTES + 15) & ~15);
-                if (lane == 0) bar_expect(&bars->p_full[ps], bytes * BN);
+                const uint32_t bytes = P.format == ALLOYB_Q6_K ? static_cast<uint32_t>(((start & 15) + Q6K_BYTES + 15) & ~15)
+                                                               : static_cast<uint32_t>(blk_bytes);
+                const bool q8 = P.format == ALLOYB_Q8_0;
+                if (lane == 0) bar_expect(&bars->p_full[ps], (bytes + (q8 ? 16u : 0u)) * BN);
                 __syncwarp();
                 for (int r = lane; r < BN; r += 32) {
                     int row = n0 + r;
                     if (row >= P.N) row = P.N - 1;
                     bulk_g2s(p_st + ps * PACK_STAGE + r * PACK_ROW, P.w + static_cast<int64_t>(row) * P.row_bytes + ws,
                              bytes, &bars->p_full[ps]);
+                    if (q8)      // the super-block's eight block scales behind its codes
+                        bulk_g2s(p_st + ps * PACK_STAGE + r * PACK_ROW + 256,
+                                 P.scales + static_cast<int64_t>(row) * (P.K / Q8_BLOCK) + sb * 8, 16, &bars->p_full[ps]);
                 }
             }
             const int s = ks % STAGES;
@@ -362,14 +394,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
             if (ok) {
                 uint8_t* tile = b_st + s * B_STAGE;
                 const uint8_t* blk = p_st + ps * PACK_STAGE + r * PACK_ROW +
-                                     (P.format == ALLOYB_Q4_K ? 0 : ((sb * Q6K_BYTES) & 15));
+                                     (P.format == ALLOYB_Q6_K ? ((sb * Q6K_BYTES) & 15) : 0);
                 if (!live) {
 #pragma unroll
                     for (int c = 0; c < 4; ++c) sts_u128(swz(tile, r, 4 * hsel + c), make_uint4(0u, 0u, 0u, 0u));
                 } else if (P.format == ALLOYB_Q4_K) {
                     decode_q4k<BF16>(blk, ks & 3, tile, r, hsel);
-                } else {
+                } else if (P.format == ALLOYB_Q6_K) {
                     decode_q6k<BF16>(blk, ks & 3, tile, r, hsel);
+                } else {
+                    decode_q8_0<BF16>(blk, ks & 3, tile, r, hsel);
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores -> MMA reads
             }
@@ -430,8 +464,10 @@ int gemm_tc_device_error(int clear) {
 int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, cudaStream_t st) {
     using namespace tc;
     if (dtype != ALLOYB_F16 && dtype != ALLOYB_BF16) return ALLOYB_NOT_TAKEN;
-    if (seg.format != ALLOYB_Q4_K && seg.format != ALLOYB_Q6_K) return ALLOYB_NOT_TAKEN;
+    if (seg.format != ALLOYB_Q4_K && seg.format != ALLOYB_Q6_K && seg.format != ALLOYB_Q8_0) return ALLOYB_NOT_TAKEN;
     if (M < 64 || K % QK_K) return ALLOYB_NOT_TAKEN;
+    if (seg.format == ALLOYB_Q8_0 && (!seg.scales || reinterpret_cast<uintptr_t>(seg.scales) % 16 || seg.row_bytes != K))
+        return ALLOYB_NOT_TAKEN;
     if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(seg.data) % 16 || seg.row_bytes % 16)
         return ALLOYB_NOT_TAKEN;
     if (seg.format == ALLOYB_Q6_K) {
@@ -471,6 +507,7 @@ int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, cu
     }
     Params P;
     P.w = static_cast<const uint8_t*>(seg.data);
+    P.scales = static_cast<const __half*>(seg.scales);
     P.row_bytes = seg.row_bytes;
     P.format = seg.format;
     P.y = seg.y;

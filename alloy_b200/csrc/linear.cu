@@ -179,6 +179,21 @@ extern "C" int alloyb_linear(const void* x, int M, int K, int dtype, const alloy
     }
     rc = try_linear_fast(x, M, K, dtype, segs.seg, segs.n_seg, residual, st);
     if (rc != ALLOYB_NOT_TAKEN) return rc;
+    {
+        // Q8_0 matrices: the streaming GEMV of linear_q8.cu, one launch per matrix and four tokens
+        bool all_q8 = true;
+        for (int i = 0; i < segs.n_seg; ++i) all_q8 &= segs.seg[i].format == ALLOYB_Q8_0 && segs.seg[i].row_bytes == K;
+        if (all_q8 && M < 64) {
+            bool taken = true;
+            for (int i = 0; i < segs.n_seg && taken; ++i) {
+                const WeightSeg& sg = segs.seg[i];
+                rc = try_q8_gemv(x, M, K, dtype, sg.data, sg.scales, nullptr, nullptr, sg.y, sg.N, sg.ldy, residual, false, 0, st);
+                if (rc == ALLOYB_NOT_TAKEN) taken = false;          // only possible for the first matrix (shape-wide reasons)
+                else if (rc != ALLOYB_OK) return rc;
+            }
+            if (taken) return ALLOYB_OK;
+        }
+    }
 
     switch (dtype) {
         case ALLOYB_F16: return launch_rows<__half>(x, M, K, segs, residual, st);
@@ -237,6 +252,10 @@ extern "C" int alloyb_gated_linear(const void* x, const void* gate, const void* 
 
     int rc = try_gated_fast(x, gate, gate_scales, up, up_scales, y, M, N, K, format, act, dtype, st);
     if (rc != ALLOYB_NOT_TAKEN) return rc;
+    if (format == ALLOYB_Q8_0) {
+        rc = try_q8_gemv(x, M, K, dtype, gate, gate_scales, up, up_scales, y, N, N, nullptr, true, act, st);
+        if (rc != ALLOYB_NOT_TAKEN) return rc;
+    }
 
     const int blocks = (N + ROWS_WARPS - 1) / ROWS_WARPS;
     const uint8_t* g8 = static_cast<const uint8_t*>(gate);

@@ -37,6 +37,10 @@ int try_gemv_stream_mixed(const void* x, int M, int K, int dtype, const WeightSe
 int gemv_stream_device_error(int clear);
 int decode_layer_device_error(int clear);
 
+// Q8_0 streaming GEMV (1..63 tokens, four per pass), plain (w1 == nullptr) or gate/up fused.
+int try_q8_gemv(const void* x, int M, int K, int dtype, const void* w0, const void* s0, const void* w1, const void* s1,
+                void* y, int N, int64_t ldy, const void* residual, bool gated, int act, cudaStream_t st);
+
 // tcgen05 dequant-GEMM for prefill-sized M (one matrix).
 int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, cudaStream_t st);
 int gemm_tc_device_error(int clear);

@@ -13,6 +13,7 @@ graph; the figure printed is the mean device time per launch and the algorithmic
     python -m alloy_b200.microbench --op q6k_mm --n 4096 --k 14336 --m 4
     python -m alloy_b200.microbench --op attn_paged --batch 64 --ctx-lo 4096 --ctx-hi 32768
     python -m alloy_b200.microbench --op gemm_q4k --m 4096 --n 14336 --k 4096 --dtype bf16
+    python -m alloy_b200.microbench --op q8_mm --n 4096 --k 4096 --m 1
 """
 
 from __future__ import annotations
@@ -56,6 +57,10 @@ def bench_linear(op: str, n: int, k: int, m: int, ring_mb: int, sweeps: int, dty
         per = n * (k // 256) * 144
         make = lambda: (synth.q4k_blocks_device(n, k, gen),)
         call = lambda x, w: torch.ops.alloy.gguf_q4_k_mm(x, w[0])
+    elif op == "q8_mm":
+        per = n * k + n * (k // 32) * 2
+        make = lambda: synth.q8_0_weight_device(n, k, gen)
+        call = lambda x, w: torch.ops.alloy.gguf_q8_0_mm(x, w[0], w[1])
     elif op == "gated":
         per = 2 * n * (k // 256) * 144
         make = lambda: (synth.q4k_blocks_device(n, k, gen), synth.q4k_blocks_device(n, k, gen))
@@ -82,7 +87,12 @@ def bench_linear(op: str, n: int, k: int, m: int, ring_mb: int, sweeps: int, dty
 def bench_gemm(fmt: str, m: int, n: int, k: int, sweeps: int, dtype) -> dict:
     """Prefill dequant-GEMM (tcgen05 path): M tokens against one packed matrix."""
     gen = torch.Generator(device="cuda").manual_seed(0)
-    if fmt == "q6k":
+    if fmt == "q8":
+        qw, qs = synth.q8_0_weight_device(n, k, gen)
+        blk = qw
+        op = lambda x, w: torch.ops.alloy.gguf_q8_0_mm(x, w, qs)
+        wbytes = n * k + n * (k // 32) * 2
+    elif fmt == "q6k":
         blk = synth.q6k_blocks_device(n, k, gen)
         op = torch.ops.alloy.gguf_q6_k_mm
         wbytes = n * (k // 256) * 210
@@ -137,7 +147,7 @@ def bench_attn_paged(batch: int, lo: int, hi: int, sweeps: int, kv_heads: int = 
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", required=True,
-                    choices=["q4k_mm", "q6k_mm", "gated", "attn_paged", "gemm_q4k", "gemm_q6k"])
+                    choices=["q4k_mm", "q6k_mm", "q8_mm", "gated", "attn_paged", "gemm_q4k", "gemm_q6k", "gemm_q8"])
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--m", type=int, default=1)

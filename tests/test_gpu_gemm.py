@@ -33,10 +33,20 @@ def _ref(x_t, w_f32, dt):
     ("q4_k", 256, 128, 256, "bf16"), ("q4_k", 64, 256, 512, "bf16"), ("q4_k", 300, 200, 1024, "bf16"),
     ("q4_k", 512, 384, 2048, "f16"), ("q4_k", 1000, 136, 4096, "bf16"),
     ("q6_k", 256, 128, 2048, "bf16"), ("q6_k", 64, 256, 2048, "bf16"), ("q6_k", 300, 200, 4096, "bf16"),
-    ("q6_k", 512, 384, 2048, "f16"), ("q6_k", 1000, 136, 6144, "bf16")])
+    ("q6_k", 512, 384, 2048, "f16"), ("q6_k", 1000, 136, 6144, "bf16"),
+    ("q8_0", 256, 128, 256, "bf16"), ("q8_0", 64, 200, 1024, "f16"), ("q8_0", 1000, 136, 4096, "bf16")])
 def test_gemm_matches_oracle(fmt, m, n, k, dt):
     rng = np.random.default_rng([m, n, k, len(fmt)])
     tdt = DT[dt]
+    if fmt == "q8_0":
+        codes, scales = O.split_q8_0(synth.q8_0_wire(rng, n, k))
+        w = O.dequant_q8_0(codes, scales)
+        x = torch.from_numpy(synth.activations(rng, m, k, np.float32)).to(tdt).to(DEV)
+        y = torch.ops.alloy.gguf_q8_0_mm(x, _dev(codes), _dev(scales))
+        assert y.shape == (m, n) and y.dtype == tdt
+        assert_close(to_np(y), _ref(x, w, tdt), tdt, f"gemm {fmt} {m}x{n}x{k} {dt}")
+        assert _lib.load().alloyb_device_error(0) == 0
+        return
     if fmt == "q4_k":
         blk = synth.q4k_blocks(rng, n, k)
         w = O.dequant_q4_k(blk)

@@ -101,10 +101,10 @@ def test_mm_matches_oracle(fmt, m, n, k, dt):
     x = torch.from_numpy(synth.activations(rng, m, k, np.float32)).to(tdt)
     y = _MM[fmt](x.to(DEV), w_dev)
     assert y.shape == (m, n) and y.dtype == tdt
-    if m >= 64 and fmt == "q4_k":
+    if m >= 64 and fmt in ("q4_k", "q8_0"):
         # 64 tokens and more take the tensor-core GEMM, whose definition rounds the decoded weight
-        # to the activation type once (Q6_K rows of this K are not 16-byte aligned and Q8_0 has no
-        # GEMM: both stay on the exact-weight row kernels)
+        # to the activation type once (Q6_K rows of this K are not 16-byte aligned: they stay on the
+        # exact-weight row kernels)
         w = torch.from_numpy(w).to(tdt).float().numpy()
     ref = O.mm_ref_f64(x.float().numpy(), w)
     assert_close(to_np(y), ref, tdt, f"{fmt} m={m} n={n} k={k} {dt}")
