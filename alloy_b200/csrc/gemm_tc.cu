@@ -4,11 +4,16 @@
 //
 // One CTA computes a 256-token x 128-row output tile.  Per 64-wide K step:
 //   * warp 0 (one lane) brings the 256 x 64 activation tile in with ONE TMA tensor copy
-//     (128-byte swizzle) and, once per super-block, the 128 packed weight rows with bulk copies;
-//   * warps 2-5 (128 threads, one weight row each) decode 64 weights of their row to fp32
+//     (128-byte swizzle);
+//   * warp 10 (one lane) brings the 128 packed weight rows of a super-block in with ONE tensor copy over
+//     a byte view of the weight matrix (Q8_0: two swizzled copies of codes and one of scales), issued as
+//     soon as the slot's previous super-block is decoded, i.e. a whole super-block ahead of its use;
+//   * warps 2-9 (256 threads, two per weight row) decode 64 weights of their row to fp32
 //     exactly as the block format defines them (Q4_K: d*sc*nib - dmin*m with ONE rounding;
 //     Q6_K: d*sc*(q-32), exact; Q8_0: scale*code, exact), round ONCE to the activation type and store them into the
-//     K-major, 128-byte-swizzled layout the MMA reads;
+//     K-major, 128-byte-swizzled layout the MMA reads.  Codes become floats without a conversion
+//     instruction (a byte permute drops the code into the mantissa of 2^23) and the arithmetic runs on
+//     the two-wide fp32 instructions (add/mul/fma .f32x2);
 //   * warp 1 (one lane) issues two tcgen05.mma (M = 128 tokens each, N = 128, K = 16 x 4) whose
 //     accumulators live in tensor memory (256 columns), and releases the stage with
 //     tcgen05.commit.
@@ -34,13 +39,17 @@ constexpr int BK = 64;                  // K step: 64 x 2 bytes = one 128-byte s
 constexpr int STAGES = 3;
 constexpr int A_STAGE = BM * BK * 2;    // 32 KB
 constexpr int B_STAGE = BN * BK * 2;    // 16 KB
-constexpr int PACK_ROW = 272;           // packed super-block per row: 144 (Q4_K) / <= 224-byte window (Q6_K) /
-                                        // 256 codes + 8 fp16 scales (Q8_0); 17 x 16 bytes keeps 128-bit reads
-                                        // of 8 rows conflict-free
-constexpr int PACK_STAGE = BN * PACK_ROW;   // 28 KB
+// One super-block of 128 packed rows in shared memory:
+//   Q4_K  144-byte rows (9 x 16 bytes: 128-bit reads of 8 consecutive rows hit distinct banks);
+//   Q6_K  240-byte rows: the 16-byte-aligned window around the 210-byte block (15 x 16 bytes);
+//   Q8_0  two [128 rows x 128 codes] tiles in the 128-byte swizzle, then 16 bytes of scales per row.
+constexpr int Q4_ROW = 144, Q6_ROW = 240;
+constexpr int Q8_HALF = BN * 128;           // 16 KB
+constexpr int PACK_STAGE = 2 * Q8_HALF + BN * 16;   // 34 KB, the largest of the three
 constexpr int PACK_STAGES = 2;
 constexpr int DEC_THREADS = 256;        // two decode threads per weight row (half a k-step each)
-constexpr int THREADS = 64 + DEC_THREADS;   // warp 0 copies, warp 1 MMA, warps 2-9 decode + epilogue
+constexpr int THREADS = 64 + DEC_THREADS + 32;   // warp 0 A copies, warp 1 MMA, warps 2-9 decode + epilogue,
+                                                 // warp 10 packed-row copies
 constexpr int TMEM_COLS = 256;
 constexpr uint32_t SPIN = 1u << 22;
 
@@ -48,8 +57,8 @@ struct Bars {
     uint64_t a_full[STAGES];      // TMA -> MMA
     uint64_t b_full[STAGES];      // decode -> MMA (128 arrivals)
     uint64_t empty[STAGES];       // MMA -> TMA + decode (tcgen05.commit)
-    uint64_t p_full[PACK_STAGES];     // bulk copies -> decode
-    uint64_t p_empty[PACK_STAGES];    // decode -> copies (128 arrivals)
+    uint64_t p_full[PACK_STAGES];     // packed-row copies -> decode
+    uint64_t p_empty[PACK_STAGES];    // decode -> copies (256 arrivals)
     uint64_t acc_full;            // MMA -> epilogue
     uint32_t tmem_base;
     uint32_t pad;
@@ -58,9 +67,6 @@ struct Bars {
 constexpr int SMEM_BYTES = 1024 /*align slack*/ + STAGES * (A_STAGE + B_STAGE) + PACK_STAGES * PACK_STAGE + 256;
 
 struct Params {
-    const uint8_t* w;         // packed rows (Q8_0: int8 codes, K per row)
-    const __half* scales;     // Q8_0: fp16 (N, K/32)
-    int64_t row_bytes;
     int format;               // ALLOYB_Q4_K / ALLOYB_Q6_K / ALLOYB_Q8_0
     void* y;
     int64_t ldy;
@@ -96,12 +102,6 @@ __device__ __forceinline__ bool bar_wait(uint64_t* b, uint32_t parity) {
     }
     atomicExch(&g_tc_error, 2);
     return false;
-}
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     s32(dst)),
-                 "l"(src), "r"(bytes), "r"(s32(bar))
-                 : "memory");
 }
 __device__ __forceinline__ void tma_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile(
@@ -175,12 +175,49 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     return r;
 }
 
+// Two fp32 values in one 64-bit register and the two-wide fp32 instructions on them.
+__device__ __forceinline__ uint64_t f2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(uint64_t v) {
+    float lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+    return pack2<BF16>(lo, hi);
+}
+// Bytes e and e+1 of `codes` as the floats 2^23 + code: the byte lands in the low mantissa bits of
+// 0x4B000000 (2^23), where one unit in the last place is exactly 1.
+template <int E>
+__device__ __forceinline__ uint64_t magic2(uint32_t codes) {
+    return f2(__uint_as_float(__byte_perm(codes, 0x4B000000u, 0x7540 | E)),
+              __uint_as_float(__byte_perm(codes, 0x4B000000u, 0x7540 | (E + 1))));
+}
+
 // Row `r` of a [rows x 64] 2-byte tile in the swizzled K-major layout: 8 chunks of 16 bytes.
 __device__ __forceinline__ uint8_t* swz(uint8_t* tile, int r, int chunk) {
     return tile + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4);
 }
 
-// Decode k-step `ks` (0..3) of one Q4_K super-block of this thread's row: 64 weights.
+// Decode k-step `ks` (0..3) of one Q4_K super-block of this thread's row: 64 weights, of which this
+// thread (hsel) owns quant bytes 16*hsel .. +15: their low nibbles are k 16*hsel .. +15 (chunks
+// 2*hsel, 2*hsel+1), their high nibbles k 32 + the same (chunks 4 + ...).
 template <bool BF16>
 __device__ __forceinline__ void decode_q4k(const uint8_t* blk, int ks, uint8_t* tile, int r, int hsel) {
     const uint4 hdr = lds_u128(blk);
@@ -190,90 +227,87 @@ __device__ __forceinline__ void decode_q4k(const uint8_t* blk, int ks, uint8_t* 
     q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * ks + 1, sc1, m1);
     const float dl = d * static_cast<float>(sc0), ml = dmin * static_cast<float>(m0);
     const float dh = d * static_cast<float>(sc1), mh = dmin * static_cast<float>(m1);
-    // this thread's half of the 32 quant bytes: bytes 16*hsel .. +15 -> chunks 2*hsel, 2*hsel+1
+    const uint64_t dl2 = f2(dl, dl), ml2 = f2(-ml, -ml), dh2 = f2(dh, dh), mh2 = f2(-mh, -mh);
+    const uint64_t unbias = f2(-8388608.0f, -8388608.0f);
     const uint4 q0 = lds_u128(blk + 16 + ks * 32 + 16 * hsel);
     const uint32_t qw[4] = {q0.x, q0.y, q0.z, q0.w};
-    // low nibbles -> k 0..31 (chunks 0-3), high nibbles -> k 32..63 (chunks 4-7)
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc) {
-        const int c = 2 * hsel + cc;
         uint32_t lo[4], hi[4];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const uint32_t w = qw[cc * 2 + h];
-            float fl[4], fh[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const uint32_t byte = (w >> (8 * e)) & 0xffu;
-                // exact products, one rounding at the subtract (FMA), then one rounding to 16 bits
-                fl[e] = fmaf(dl, static_cast<float>(byte & 15u), -ml);
-                fh[e] = fmaf(dh, static_cast<float>(byte >> 4), -mh);
-            }
-            lo[h * 2] = pack2<BF16>(fl[0], fl[1]);
-            lo[h * 2 + 1] = pack2<BF16>(fl[2], fl[3]);
-            hi[h * 2] = pack2<BF16>(fh[0], fh[1]);
-            hi[h * 2 + 1] = pack2<BF16>(fh[2], fh[3]);
+            const uint32_t l4 = w & 0x0f0f0f0fu, h4 = (w >> 4) & 0x0f0f0f0fu;
+            // (2^23 + nib) - 2^23 is exact; then exact product and ONE rounding at the subtract (FMA)
+            lo[h * 2] = pack2<BF16>(f2_fma(f2_add(magic2<0>(l4), unbias), dl2, ml2));
+            lo[h * 2 + 1] = pack2<BF16>(f2_fma(f2_add(magic2<2>(l4), unbias), dl2, ml2));
+            hi[h * 2] = pack2<BF16>(f2_fma(f2_add(magic2<0>(h4), unbias), dh2, mh2));
+            hi[h * 2 + 1] = pack2<BF16>(f2_fma(f2_add(magic2<2>(h4), unbias), dh2, mh2));
         }
+        const int c = 2 * hsel + cc;
         sts_u128(swz(tile, r, c), make_uint4(lo[0], lo[1], lo[2], lo[3]));
         sts_u128(swz(tile, r, c + 4), make_uint4(hi[0], hi[1], hi[2], hi[3]));
     }
 }
 
-// Q6_K: the block sits at `blk` (2-byte aligned).  k-step ks: elements 64*ks .. +63.
+// Q6_K: the block sits at `blk` (2-byte aligned inside its 16-byte-aligned window).  k-step ks covers
+// elements 64*ks .. +63 = sub-rows j = jb, jb+1 of half h; this thread owns sub-row jb + hsel: 32
+// elements whose low nibbles are 32 bytes of ql and whose top two bits are 32 bytes of qh.  Both runs
+// are read as nine 4-byte-aligned words and shifted into place.
 template <bool BF16>
 __device__ __forceinline__ void decode_q6k(const uint8_t* blk, int ks, uint8_t* tile, int r, int hsel) {
-    const int h = ks >> 1, jb = (ks & 1) * 2;            // sub-blocks j = jb, jb+1 of half h
+    const int h = ks >> 1, j = (ks & 1) * 2 + hsel;
     const float d = half_bits_to_f32(lds_u16(blk + 208));
-    {
-        const int jj = hsel;                             // this thread's sub-block pair of the k-step
-        const int j = jb + jj;
-        const uint8_t* ql = blk + h * 64 + (j & 1) * 32;
-        const uint8_t* qh = blk + 128 + h * 32;
-        const uint32_t sc2 = lds_u16(blk + 192 + h * 8 + 2 * j);
-        const float s0 = d * static_cast<float>(static_cast<int8_t>(sc2 & 0xffu));
-        const float s1 = d * static_cast<float>(static_cast<int8_t>(sc2 >> 8));
+    const uint32_t sc2 = lds_u16(blk + 192 + h * 8 + 2 * j);
+    const float s0 = d * static_cast<float>(static_cast<int8_t>(sc2 & 0xffu));
+    const float s1 = d * static_cast<float>(static_cast<int8_t>(sc2 >> 8));
+    const uint64_t s02 = f2(s0, s0), s12 = f2(s1, s1);
+    const uint64_t unbias = f2(-8388640.0f, -8388640.0f);          // -(2^23 + 32)
+    const uint32_t a_ql = s32(blk + h * 64 + (j & 1) * 32), a_qh = s32(blk + 128 + h * 32);
+    const uint32_t sh = (a_ql & 3u) * 8u;                          // 0 or 16: same for both runs
+    uint32_t wl[9], wh[9];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {                    // 8 elements per 16-byte chunk
-            uint32_t out[4];
+    for (int i = 0; i < 9; ++i) {
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(wl[i]) : "r"((a_ql & ~3u) + 4 * i));
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(wh[i]) : "r"((a_qh & ~3u) + 4 * i));
+    }
+    const uint32_t shq = j >= 2 ? 4u : 0u, shh = 2u * j;
 #pragma unroll
-            for (int p = 0; p < 4; ++p) {                // 2 elements per 16-bit load
-                const int l = c * 8 + p * 2;
-                const uint32_t a = lds_u16(ql + l), b = lds_u16(qh + l);
-                float f[2];
+    for (int c = 0; c < 4; ++c) {                    // 8 elements per 16-byte chunk
+        uint32_t out[4];
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const uint32_t byte = (a >> (8 * e)) & 0xffu;
-                    const uint32_t nib = (j >= 2) ? (byte >> 4) : (byte & 15u);
-                    const uint32_t hi = (b >> (8 * e + 2 * j)) & 3u;
-                    const float q = static_cast<float>(static_cast<int>(nib | (hi << 4)) - 32);
-                    f[e] = (l + e < 16 ? s0 : s1) * q;   // exact in fp32
-                }
-                out[p] = pack2<BF16>(f[0], f[1]);
-            }
-            sts_u128(swz(tile, r, jj * 4 + c), make_uint4(out[0], out[1], out[2], out[3]));
+        for (int p = 0; p < 2; ++p) {
+            const int i = 2 * c + p;
+            const uint32_t ql = __funnelshift_r(wl[i], wl[i + 1], sh), qh = __funnelshift_r(wh[i], wh[i + 1], sh);
+            // four 6-bit codes, one per byte: nibble | (two high bits << 4)
+            const uint32_t q = ((ql >> shq) & 0x0f0f0f0fu) + ((qh >> shh) & 0x03030303u) * 16u;
+            const uint64_t s = i < 4 ? s02 : s12;    // elements 0-15 / 16-31 of the sub-row
+            out[p * 2] = pack2<BF16>(f2_mul(f2_add(magic2<0>(q), unbias), s));       // exact in fp32
+            out[p * 2 + 1] = pack2<BF16>(f2_mul(f2_add(magic2<2>(q), unbias), s));
         }
+        sts_u128(swz(tile, r, hsel * 4 + c), make_uint4(out[0], out[1], out[2], out[3]));
     }
 }
 
-// Q8_0: the stage row holds 256 codes then the super-block's eight fp16 scales.  k-step ks: elements
-// 64*ks .. +63 = two 32-element blocks, one per thread of the pair; w = scale * code (exact in fp32).
+// Q8_0: `st` is the stage: two [128 rows x 128 codes] tiles in the 128-byte swizzle, then eight fp16 scales
+// per row.  k-step ks: elements 64*ks .. +63 = two 32-element blocks, one per thread of the pair;
+// w = scale * code (exact in fp32).
 template <bool BF16>
-__device__ __forceinline__ void decode_q8_0(const uint8_t* blk, int ks, uint8_t* tile, int r, int hsel) {
-    const float sc = half_bits_to_f32(lds_u16(blk + 256 + (2 * ks + hsel) * 2));
-    const uint8_t* q = blk + ks * 64 + hsel * 32;
+__device__ __forceinline__ void decode_q8_0(const uint8_t* st, int ks, uint8_t* tile, int r, int hsel) {
+    const float sc = half_bits_to_f32(lds_u16(st + 2 * Q8_HALF + r * 16 + (2 * ks + hsel) * 2));
+    const uint64_t sc2 = f2(sc, sc), unbias = f2(-8388736.0f, -8388736.0f);     // -(2^23 + 128)
+    const uint8_t* row = st + (ks >> 1) * Q8_HALF + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll
     for (int c = 0; c < 2; ++c) {                        // 16 codes -> two 16-byte chunks
-        const uint4 v = lds_u128(q + 16 * c);
+        const int chunk = (ks & 1) * 4 + hsel * 2 + c;
+        const uint4 v = lds_u128(row + ((chunk ^ (r & 7)) << 4));
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
         uint32_t o[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float f0 = sc * static_cast<float>(static_cast<int8_t>(w[j] & 0xffu));
-            const float f1 = sc * static_cast<float>(static_cast<int8_t>((w[j] >> 8) & 0xffu));
-            const float f2 = sc * static_cast<float>(static_cast<int8_t>((w[j] >> 16) & 0xffu));
-            const float f3 = sc * static_cast<float>(static_cast<int8_t>(w[j] >> 24));
-            o[2 * j] = pack2<BF16>(f0, f1);
-            o[2 * j + 1] = pack2<BF16>(f2, f3);
+        for (int jj = 0; jj < 4; ++jj) {
+            const uint32_t u = w[jj] ^ 0x80808080u;      // code + 128 as an unsigned byte
+            o[2 * jj] = pack2<BF16>(f2_mul(f2_add(magic2<0>(u), unbias), sc2));
+            o[2 * jj + 1] = pack2<BF16>(f2_mul(f2_add(magic2<2>(u), unbias), sc2));
         }
         sts_u128(swz(tile, r, 4 * hsel + 2 * c), make_uint4(o[0], o[1], o[2], o[3]));
         sts_u128(swz(tile, r, 4 * hsel + 2 * c + 1), make_uint4(o[4], o[5], o[6], o[7]));
@@ -282,18 +316,18 @@ __device__ __forceinline__ void decode_q8_0(const uint8_t* blk, int ks, uint8_t*
 
 template <bool BF16>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
+               const __grid_constant__ CUtensorMap smap, const Params P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* a_st = smem;                                   // STAGES x 32 KB
     uint8_t* b_st = smem + STAGES * A_STAGE;                // STAGES x 16 KB
-    uint8_t* p_st = b_st + STAGES * B_STAGE;                // 2 x 28 KB packed rows
+    uint8_t* p_st = b_st + STAGES * B_STAGE;                // 2 x 34 KB packed rows
     Bars* bars = reinterpret_cast<Bars*>(p_st + PACK_STAGES * PACK_STAGE);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
     const int nsb = P.K / QK_K, ksteps = nsb * 4;
-    const int blk_bytes = P.format == ALLOYB_Q4_K ? Q4K_BYTES : (P.format == ALLOYB_Q6_K ? Q6K_BYTES : 256);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -321,33 +355,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     pdl_wait();
 
     if (warp == 0) {
-        // ------------------------------------------------ copies: packed rows (per super-block) + A tiles
+        // ------------------------------------------------ A tiles
         bool ok = true;
         for (int ks = 0; ks < ksteps && ok; ++ks) {
-            if ((ks & 3) == 0) {
-                const int sb = ks >> 2, ps = sb % PACK_STAGES;
-                if (sb >= PACK_STAGES) ok = bar_wait(&bars->p_empty[ps], ((sb / PACK_STAGES) - 1) & 1);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                // Q4_K blocks are 16-byte aligned; a Q6_K block (210 bytes, 2-byte aligned) is copied
-                // as the aligned 224-byte window around it
-                const int start = sb * blk_bytes;
-                const int ws = start & ~15;
-                const uint32_t bytes = P.format == ALLOYB_Q6_K ? static_cast<uint32_t>(((start & 15) + Q6K_BYTES + 15) & ~15)
-                                                               : static_cast<uint32_t>(blk_bytes);
-                const bool q8 = P.format == ALLOYB_Q8_0;
-                if (lane == 0) bar_expect(&bars->p_full[ps], (bytes + (q8 ? 16u : 0u)) * BN);
-                __syncwarp();
-                for (int r = lane; r < BN; r += 32) {
-                    int row = n0 + r;
-                    if (row >= P.N) row = P.N - 1;
-                    bulk_g2s(p_st + ps * PACK_STAGE + r * PACK_ROW, P.w + static_cast<int64_t>(row) * P.row_bytes + ws,
-                             bytes, &bars->p_full[ps]);
-                    if (q8)      // the super-block's eight block scales behind its codes
-                        bulk_g2s(p_st + ps * PACK_STAGE + r * PACK_ROW + 256,
-                                 P.scales + static_cast<int64_t>(row) * (P.K / Q8_BLOCK) + sb * 8, 16, &bars->p_full[ps]);
-                }
-            }
             const int s = ks % STAGES;
             if (ks >= STAGES) ok = bar_wait(&bars->empty[s], ((ks / STAGES) - 1) & 1);
             ok = __all_sync(0xffffffffu, ok);
@@ -355,6 +365,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
             if (lane == 0) {
                 bar_expect(&bars->a_full[s], A_STAGE);
                 tma_2d(a_st + s * A_STAGE, &xmap, ks * BK, m0, &bars->a_full[s]);
+            }
+            __syncwarp();
+        }
+    } else if (warp == 10) {
+        // ------------------------------------------------ packed rows: one tensor copy per super-block
+        bool ok = true;
+        for (int sb = 0; sb < nsb && ok; ++sb) {
+            const int ps = sb % PACK_STAGES;
+            if (sb >= PACK_STAGES) ok = bar_wait(&bars->p_empty[ps], ((sb / PACK_STAGES) - 1) & 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (lane == 0) {
+                uint8_t* dst = p_st + ps * PACK_STAGE;
+                if (P.format == ALLOYB_Q4_K) {
+                    bar_expect(&bars->p_full[ps], BN * Q4_ROW);
+                    tma_2d(dst, &wmap, sb * Q4K_BYTES, n0, &bars->p_full[ps]);
+                } else if (P.format == ALLOYB_Q6_K) {
+                    // a block is 2-byte aligned: copy the aligned window around it (reads past the row's
+                    // end are filled with zeros)
+                    bar_expect(&bars->p_full[ps], BN * Q6_ROW);
+                    tma_2d(dst, &wmap, (sb * Q6K_BYTES) & ~15, n0, &bars->p_full[ps]);
+                } else {
+                    bar_expect(&bars->p_full[ps], 2 * Q8_HALF + BN * 16);
+                    tma_2d(dst, &wmap, sb * 256, n0, &bars->p_full[ps]);
+                    tma_2d(dst + Q8_HALF, &wmap, sb * 256 + 128, n0, &bars->p_full[ps]);
+                    tma_2d(dst + 2 * Q8_HALF, &smap, sb * 16, n0, &bars->p_full[ps]);
+                }
             }
             __syncwarp();
         }
@@ -382,10 +419,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
             }
             __syncwarp();
         }
-    } else {
+    } else if (warp < 10) {
         // ------------------------------------------------ decode (two threads per weight row)
         const int r = (threadIdx.x - 64) & (BN - 1), hsel = (threadIdx.x - 64) >> 7;
-        const bool live = n0 + r < P.N;
         bool ok = true;
         for (int ks = 0; ks < ksteps; ++ks) {
             const int sb = ks >> 2, ps = sb % PACK_STAGES, s = ks % STAGES;
@@ -393,17 +429,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
             if (ok && ks >= STAGES) ok = bar_wait(&bars->empty[s], ((ks / STAGES) - 1) & 1);
             if (ok) {
                 uint8_t* tile = b_st + s * B_STAGE;
-                const uint8_t* blk = p_st + ps * PACK_STAGE + r * PACK_ROW +
-                                     (P.format == ALLOYB_Q6_K ? ((sb * Q6K_BYTES) & 15) : 0);
-                if (!live) {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) sts_u128(swz(tile, r, 4 * hsel + c), make_uint4(0u, 0u, 0u, 0u));
-                } else if (P.format == ALLOYB_Q4_K) {
-                    decode_q4k<BF16>(blk, ks & 3, tile, r, hsel);
+                const uint8_t* stg = p_st + ps * PACK_STAGE;
+                // rows past N arrive as zeros from the tensor copy and decode to zeros
+                if (P.format == ALLOYB_Q4_K) {
+                    decode_q4k<BF16>(stg + r * Q4_ROW, ks & 3, tile, r, hsel);
                 } else if (P.format == ALLOYB_Q6_K) {
-                    decode_q6k<BF16>(blk, ks & 3, tile, r, hsel);
+                    decode_q6k<BF16>(stg + r * Q6_ROW + ((sb * Q6K_BYTES) & 15), ks & 3, tile, r, hsel);
                 } else {
-                    decode_q8_0<BF16>(blk, ks & 3, tile, r, hsel);
+                    decode_q8_0<BF16>(stg, ks & 3, tile, r, hsel);
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores -> MMA reads
             }
@@ -470,17 +503,6 @@ int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, cu
         return ALLOYB_NOT_TAKEN;
     if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(seg.data) % 16 || seg.row_bytes % 16)
         return ALLOYB_NOT_TAKEN;
-    if (seg.format == ALLOYB_Q6_K) {
-        // the aligned window of a row's last block must end inside the row pitch
-        const int64_t last = static_cast<int64_t>(K / QK_K - 1) * Q6K_BYTES;
-        if ((last & ~15LL) + (((last & 15) + Q6K_BYTES + 15) & ~15LL) > seg.row_bytes) return ALLOYB_NOT_TAKEN;
-    }
-
-    CUtensorMap map;
-    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
-    const cuuint64_t gstr[1] = {static_cast<cuuint64_t>(K) * 2};
-    const cuuint32_t box[2] = {BK, BM};
-    const cuuint32_t estr[2] = {1, 1};
     // The driver's tensor-map encoder is looked up through the runtime, so the library carries no
     // link-time dependency on the driver and still loads (for symbol checks) on a machine without one.
     using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -497,18 +519,35 @@ int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, cu
         }
         encode = reinterpret_cast<EncodeFn>(fn);
     }
-    const CUresult cr = encode(
-        &map, dtype == ALLOYB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
-        const_cast<void*>(x), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (cr != CUDA_SUCCESS) {
+    // 2-D map over a row-major matrix: `inner` elements per row, `rows` rows `pitch` bytes apart.
+    auto map2d = [&](CUtensorMap* m, CUtensorMapDataType type, const void* base, uint64_t inner, uint64_t rows,
+                     uint64_t pitch, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swizzle) {
+        const cuuint64_t gdim[2] = {inner, rows};
+        const cuuint64_t gstr[1] = {pitch};
+        const cuuint32_t box[2] = {box_inner, box_rows};
+        const cuuint32_t estr[2] = {1, 1};
+        return encode(m, type, 2, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    };
+    CUtensorMap map, wmap, smap;
+    bool ok = map2d(&map, dtype == ALLOYB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x,
+                    K, M, static_cast<uint64_t>(K) * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+    // the packed rows as bytes: one box = one super-block of 128 rows
+    if (seg.format == ALLOYB_Q8_0) {
+        ok = ok && map2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, seg.data, K, seg.N, seg.row_bytes, 128, BN,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
+        ok = ok && map2d(&smap, CU_TENSOR_MAP_DATA_TYPE_UINT8, seg.scales, static_cast<uint64_t>(K / Q8_BLOCK) * 2, seg.N,
+                         static_cast<uint64_t>(K / Q8_BLOCK) * 2, 16, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
+    } else {
+        ok = ok && map2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, seg.data, seg.row_bytes, seg.N, seg.row_bytes,
+                         seg.format == ALLOYB_Q4_K ? Q4_ROW : Q6_ROW, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
+        smap = wmap;
+    }
+    if (!ok) {
         set_cuda_error(cudaErrorInvalidValue);
         return ALLOYB_E_CUDA;
     }
     Params P;
-    P.w = static_cast<const uint8_t*>(seg.data);
-    P.scales = static_cast<const __half*>(seg.scales);
-    P.row_bytes = seg.row_bytes;
     P.format = seg.format;
     P.y = seg.y;
     P.ldy = seg.ldy;
@@ -528,8 +567,8 @@ int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, cu
         configured[dev] = true;
     }
     const dim3 grid((seg.N + BN - 1) / BN, (M + BM - 1) / BM);
-    if (dtype == ALLOYB_BF16) gemm_tc_kernel<true><<<grid, THREADS, SMEM_BYTES, st>>>(map, P);
-    else gemm_tc_kernel<false><<<grid, THREADS, SMEM_BYTES, st>>>(map, P);
+    if (dtype == ALLOYB_BF16) gemm_tc_kernel<true><<<grid, THREADS, SMEM_BYTES, st>>>(map, wmap, smap, P);
+    else gemm_tc_kernel<false><<<grid, THREADS, SMEM_BYTES, st>>>(map, wmap, smap, P);
     return check_launch();
 }
 
