@@ -14,13 +14,16 @@
 //     K-major, 128-byte-swizzled layout the MMA reads.  Codes become floats without a conversion
 //     instruction (a byte permute drops the code into the mantissa of 2^23) and the arithmetic runs on
 //     the two-wide fp32 instructions (add/mul/fma .f32x2);
-//   * warp 1 (one lane) issues two tcgen05.mma (M = 128 tokens each, N = 128, K = 16 x 4) whose
-//     accumulators live in tensor memory (256 columns), and releases the stage with
-//     tcgen05.commit.
+//   * warp 1 (one lane) issues four tcgen05.mma per step with the WEIGHT rows as the M = 128 operand
+//     and the 256 tokens as N (K = 16 each): one instruction reads each operand tile once, which
+//     matters because shared-memory bandwidth, shared with the copies and the decode stores, is
+//     what bounds the step.  The accumulator (128 lanes = weight rows, 256 columns = tokens) lives
+//     in tensor memory; tcgen05.commit releases the stage.  The wait for the next stage is issued
+//     while the last queued MMAs still run.
 // Decoding a weight tile once per 256 tokens (not per 128) halves the CUDA-core work per flop;
 // the decode of step k+1 overlaps the MMAs of step k through a 3-deep stage ring.
-// After the last K step the four decode warps read the accumulators back with tcgen05.ld and
-// store C.  Every wait is bounded: on a time-out the sticky device error word is set, the CTA
+// After the last K step the eight decode warps read the accumulators back with tcgen05.ld and
+// store C (each lane one weight row: a warp writes 64 contiguous bytes per token).  Every wait is bounded: on a time-out the sticky device error word is set, the CTA
 // still frees its tensor memory and returns.
 #include <cuda.h>
 
@@ -33,8 +36,8 @@ namespace tc {
 
 __device__ int g_tc_error = 0;          // sticky: a bounded wait of this file's kernel ran out
 
-constexpr int BM = 256;                 // tokens per CTA (two UMMA M = 128 halves)
-constexpr int BN = 128;                 // weight rows per CTA (UMMA N)
+constexpr int BM = 256;                 // tokens per CTA (UMMA N)
+constexpr int BN = 128;                 // weight rows per CTA (UMMA M)
 constexpr int BK = 64;                  // K step: 64 x 2 bytes = one 128-byte swizzle row
 constexpr int STAGES = 3;
 constexpr int A_STAGE = BM * BK * 2;    // 32 KB
@@ -54,8 +57,7 @@ constexpr int TMEM_COLS = 256;
 constexpr uint32_t SPIN = 1u << 22;
 
 struct Bars {
-    uint64_t a_full[STAGES];      // TMA -> MMA
-    uint64_t b_full[STAGES];      // decode -> MMA (128 arrivals)
+    uint64_t full[STAGES];        // token-tile copy (1 arrival + bytes) and decode (256 arrivals) -> MMA
     uint64_t empty[STAGES];       // MMA -> TMA + decode (tcgen05.commit)
     uint64_t p_full[PACK_STAGES];     // packed-row copies -> decode
     uint64_t p_empty[PACK_STAGES];    // decode -> copies (256 arrivals)
@@ -139,14 +141,14 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     d |= static_cast<uint64_t>(2) << 61;                             // SWIZZLE_128B
     return d;
 }
-// kind::f16: D fp32, A/B both bf16 (1) or fp16 (0), both K-major, M = 128, N = BN.
+// kind::f16: D fp32, A/B both bf16 (1) or fp16 (0), both K-major, M = BN weight rows, N = BM tokens.
 __device__ __forceinline__ uint32_t umma_idesc(int is_bf16) {
     uint32_t d = 0;
     d |= 1u << 4;                                   // D format F32
     d |= static_cast<uint32_t>(is_bf16 ? 1 : 0) << 7;    // A format
     d |= static_cast<uint32_t>(is_bf16 ? 1 : 0) << 10;   // B format
-    d |= static_cast<uint32_t>(BN >> 3) << 17;      // N
-    d |= static_cast<uint32_t>(128 >> 4) << 24;     // M
+    d |= static_cast<uint32_t>(BM >> 3) << 17;      // N
+    d |= static_cast<uint32_t>(BN >> 4) << 24;      // M
     return d;
 }
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
@@ -331,8 +333,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            bar_init(&bars->a_full[s], 1);
-            bar_init(&bars->b_full[s], DEC_THREADS);
+            bar_init(&bars->full[s], 1 + DEC_THREADS);
             bar_init(&bars->empty[s], 1);
         }
         for (int s = 0; s < PACK_STAGES; ++s) {
@@ -363,8 +364,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if (lane == 0) {
-                bar_expect(&bars->a_full[s], A_STAGE);
-                tma_2d(a_st + s * A_STAGE, &xmap, ks * BK, m0, &bars->a_full[s]);
+                bar_expect(&bars->full[s], A_STAGE);
+                tma_2d(a_st + s * A_STAGE, &xmap, ks * BK, m0, &bars->full[s]);
             }
             __syncwarp();
         }
@@ -398,26 +399,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issue (one lane)
         const uint32_t idesc = umma_idesc(BF16 ? 1 : 0);
-        bool ok = true;
+        bool ok = bar_wait(&bars->full[0], 0);
+        ok = __all_sync(0xffffffffu, ok);
         for (int ks = 0; ks < ksteps && ok; ++ks) {
             const int s = ks % STAGES;
-            ok = bar_wait(&bars->a_full[s], (ks / STAGES) & 1) && bar_wait(&bars->b_full[s], (ks / STAGES) & 1);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t x0 = s32(a_st + s * A_STAGE), w0 = s32(b_st + s * B_STAGE);
             if (lane == 0) {
-                const uint32_t a0 = s32(a_st + s * A_STAGE), b0 = s32(b_st + s * B_STAGE);
 #pragma unroll
-                for (int kk = 0; kk < BK / 16; ++kk) {
-                    const uint64_t db = umma_desc(b0 + kk * 32);
-                    const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
-                    umma(tmem, umma_desc(a0 + kk * 32), db, idesc, acc);                    // tokens 0..127
-                    umma(tmem + BN, umma_desc(a0 + 128 * 128 + kk * 32), db, idesc, acc);   // tokens 128..255
-                }
+                for (int kk = 0; kk < BK / 16 - 1; ++kk)
+                    umma(tmem, umma_desc(w0 + kk * 32), umma_desc(x0 + kk * 32), idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+            }
+            // the next stage's wait overlaps the MMAs queued above
+            if (ks + 1 < ksteps) ok = bar_wait(&bars->full[(ks + 1) % STAGES], ((ks + 1) / STAGES) & 1);
+            if (lane == 0) {
+                umma(tmem, umma_desc(w0 + 96), umma_desc(x0 + 96), idesc, 1u);
                 umma_commit(&bars->empty[s]);
                 if (ks == ksteps - 1) umma_commit(&bars->acc_full);
             }
-            __syncwarp();
+            ok = __all_sync(0xffffffffu, ok);
         }
     } else if (warp < 10) {
         // ------------------------------------------------ decode (two threads per weight row)
@@ -440,7 +440,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores -> MMA reads
             }
-            bar_arrive(&bars->b_full[s]);
+            bar_arrive(&bars->full[s]);
             if ((ks & 3) == 3) bar_arrive(&bars->p_empty[ps]);
         }
         // ------------------------------------------------ epilogue: TMEM -> registers -> C
@@ -449,27 +449,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         if (ok) {
             const int quarter = warp & 3;                   // TMEM lanes this warp may read
             const int half = (warp - 2) >> 2;               // warps 2-5: tokens 0..127, warps 6-9: 128..255
-            {
-                const int tok = m0 + half * 128 + quarter * 32 + lane;
+            const int n = n0 + quarter * 32 + lane;         // this lane's weight row = output column
+            uint16_t* col = static_cast<uint16_t*>(P.y) + n;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + half * BN + c0, v);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (tok < P.M) {
-                        uint32_t o[8];
+            for (int c0 = 0; c0 < BM / 2; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + half * (BM / 2) + c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int tok = m0 + half * (BM / 2) + c0;
+                if (n < P.N) {
 #pragma unroll
-                        for (int e = 0; e < 8; ++e)
-                            o[e] = pack2<BF16>(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
-                        uint16_t* dst = static_cast<uint16_t*>(P.y) + static_cast<int64_t>(tok) * P.ldy + n0 + c0;
-                        if (n0 + c0 + 16 <= P.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-                            reinterpret_cast<uint4*>(dst)[0] = make_uint4(o[0], o[1], o[2], o[3]);
-                            reinterpret_cast<uint4*>(dst)[1] = make_uint4(o[4], o[5], o[6], o[7]);
-                        } else {
-                            for (int e = 0; e < 16; ++e)
-                                if (n0 + c0 + e < P.N) dst[e] = static_cast<uint16_t>(o[e >> 1] >> (16 * (e & 1)));
-                        }
-                    }
+                    for (int e = 0; e < 16; ++e)
+                        if (tok + e < P.M)
+                            col[static_cast<int64_t>(tok + e) * P.ldy] =
+                                static_cast<uint16_t>(pack2<BF16>(__uint_as_float(v[e]), 0.0f) & 0xffffu);
                 }
             }
         }
