@@ -178,6 +178,51 @@ __device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64
         ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// The same with the shared-memory descriptor given as its two halves (the low one carries the address)
+// and accumulation always on.
+__device__ __forceinline__ void umma_ts_acc(uint32_t tmem_d, uint32_t tmem_a, uint32_t db_lo, uint32_t db_hi,
+                                            uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 d;\n\tsetp.eq.u32 p, 0, 0;\n\tmov.b64 d, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], d, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "r"(db_lo), "r"(db_hi), "r"(idesc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_ts_first(uint32_t tmem_d, uint32_t tmem_a, uint32_t db_lo, uint32_t db_hi,
+                                              uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 d;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 d, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], d, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "r"(db_lo), "r"(db_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_a(uint32_t bar_addr) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
+}
+// Shared-address forms of the barrier test and the bounded wait behind it.
+__device__ __forceinline__ bool bar_test_a(uint32_t bar_addr, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar_addr), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __noinline__ bool bar_wait_slow(uint32_t bar_addr, uint32_t parity) {
+    for (uint32_t i = 0; i < SPIN; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar_addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (i > 32) __nanosleep(64);
+    }
+    atomicExch(&g_tc_error, 2);
+    return false;
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(bar)) : "memory");
 }
@@ -423,26 +468,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         // The tensor pipe queues about one instruction behind the running one, so nothing slow may sit
         // between two issues: the wait for the NEXT stage is placed before the last MMA of this one
         // (two MMAs are still in the pipe then) and the rest of the loop is a few instructions.
+        // This ONE thread's instruction stream paces the tensor pipe, so the loop is kept to a few dozen
+        // instructions per step: descriptors advance by adding to their low word, barriers are addressed
+        // by shared address, and the common already-complete wait is a single test.
         const uint32_t idesc = umma_idesc(BF16 ? 1 : 0);
         if (lane == 0) {
+            const uint64_t d0 = umma_desc(s32(x_st));
+            const uint32_t d_lo = static_cast<uint32_t>(d0), d_hi = static_cast<uint32_t>(d0 >> 32);
+            const uint32_t full0 = s32(&bars->full[0]), empty0 = s32(&bars->empty[0]), w_base = tmem + ACC_COLS;
             bool ok = true;
             uint32_t it = 0, tl = 0;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tl) {
                 // the epilogue must have read the previous tile's accumulator before it is overwritten
                 if (tl > 0) ok = bar_wait(&bars->acc_empty, (tl - 1) & 1);
                 if (ok) ok = bar_wait(&bars->full[it % STAGES], (it / STAGES) & 1);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
                     const uint32_t s = it % STAGES;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t x0 = s32(x_st + s * X_STAGE), w0 = tmem + ACC_COLS + s * W_COLS;
-#pragma unroll
-                    for (int kk = 0; kk < BK / 16 - 1; ++kk)
-                        umma_ts(tmem, w0 + kk * 8, umma_desc(x0 + kk * 32), idesc, (ks > 0 || kk > 0) ? 1u : 0u);
-                    if (ks + 1 < ksteps) ok = bar_wait(&bars->full[(it + 1) % STAGES], ((it + 1) / STAGES) & 1);
-                    umma_ts(tmem, w0 + 24, umma_desc(x0 + 96), idesc, 1u);
-                    umma_commit(&bars->empty[s]);
-                    if (ks == ksteps - 1) umma_commit(&bars->acc_full);
+                    const uint32_t lo = d_lo + s * (X_STAGE >> 4), w0 = w_base + s * W_COLS;
+                    umma_ts_first(tmem, w0, lo, d_hi, idesc, ks > 0 ? 1u : 0u);
+                    umma_ts_acc(tmem, w0 + 8, lo + 2, d_hi, idesc);
+                    umma_ts_acc(tmem, w0 + 16, lo + 4, d_hi, idesc);
+                    if (ks + 1 < ksteps) {
+                        const uint32_t nb = full0 + 8 * ((it + 1) % STAGES), np = ((it + 1) / STAGES) & 1;
+                        if (!bar_test_a(nb, np)) ok = bar_wait_slow(nb, np);
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    }
+                    umma_ts_acc(tmem, w0 + 24, lo + 6, d_hi, idesc);
+                    umma_commit_a(empty0 + 8 * s);
                 }
+                if (ok) umma_commit(&bars->acc_full);
             }
         }
         __syncwarp();
