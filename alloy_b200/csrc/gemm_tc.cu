@@ -11,8 +11,9 @@
 //   * warp 10 (one lane) brings the 128 packed weight rows of a super-block (four K steps) in with ONE
 //     tensor copy over a byte view of the weight matrix (Q8_0: two swizzled copies of codes and one of
 //     scales), issued as soon as the slot's previous super-block is decoded;
-//   * warps 2-9 (256 threads, two per weight row, each thread on the tensor-memory lane of its row)
-//     decode 64 weights of their row to fp32 exactly as the block format defines them (Q4_K:
+//   * warps 2-9 decode: two groups of four warps take alternate K steps, so each has two step times for
+//     its chain of waits, loads and stores; a thread sits on the tensor-memory lane of its weight row and
+//     decodes the row's 64 weights of the step to fp32 exactly as the block format defines them (Q4_K:
 //     d*sc*nib - dmin*m with ONE rounding; Q6_K: d*sc*(q-32), exact; Q8_0: scale*code, exact), round
 //     ONCE to the activation type and store 32 packed columns.  Codes become floats without a
 //     conversion instruction (a byte permute drops the code into the mantissa of 2^23) and the
@@ -21,9 +22,10 @@
 //     fp32 accumulator and releases the stage with tcgen05.commit; the wait for the next stage overlaps
 //     the MMAs just queued.
 // Four stages of tokens (shared memory) and decoded weights (tensor memory) and two or three of packed
-// rows run ahead across tile boundaries, so the copies and the decode of the next tile proceed while
-// warps 11-14 read the finished accumulator back with tcgen05.ld and store C (each lane one weight
-// row: a warp writes 64 contiguous bytes per token); only the first MMA of the next tile waits for them.
+// rows run ahead across tile boundaries.  Warps 11-18 drain the finished accumulator with tcgen05.ld into
+// REGISTERS (64 packed pairs per thread), hand tensor memory back to the MMA warp at once, and only then
+// store C (each lane one weight row: a warp writes 64 contiguous bytes per token) while the next tile's
+// MMAs already run.
 // Every wait is bounded: on a time-out the sticky device error word is set, the CTA still frees its
 // tensor memory and returns.
 #include <cuda.h>
@@ -55,19 +57,20 @@ constexpr int Q4_STAGE = BN * Q4_ROW, Q6_STAGE = BN * Q6_ROW, Q8_STAGE = 2 * Q8_
 constexpr int PACK_MAX_STAGES = 3;          // Q4_K and Q6_K run three deep, Q8_0 two
 constexpr int PACK_BYTES = 3 * Q6_STAGE;    // 90 KB: 3 x Q4_K, 3 x Q6_K or 2 x Q8_0 stages
 static_assert(2 * Q8_STAGE <= PACK_BYTES && 3 * Q4_STAGE <= PACK_BYTES, "packed-row region");
-constexpr int DEC_THREADS = 256;        // two decode threads per weight row (half a k-step each)
-constexpr int EPI_THREADS = 128;        // one per accumulator lane
-// warp 0 token copies, warp 1 MMA, warps 2-9 decode, warp 10 packed-row copies, warps 11-14 epilogue
+constexpr int DEC_THREADS = 256;        // two groups of 128 (one thread per weight row) on alternate k-steps
+constexpr int DEC_GROUP = 128;
+constexpr int EPI_THREADS = 256;        // two per accumulator lane (128 token columns each)
+// warp 0 token copies, warp 1 MMA, warps 2-9 decode, warp 10 packed-row copies, warps 11-18 epilogue
 constexpr int THREADS = 64 + DEC_THREADS + 32 + EPI_THREADS;
 constexpr uint32_t SPIN = 1u << 22;
 
 struct Bars {
-    uint64_t full[STAGES];        // token-tile copy (1 arrival + bytes) and decode (256 arrivals) -> MMA
+    uint64_t full[STAGES];        // token-tile copy (1 arrival + bytes) and decode (128 arrivals) -> MMA
     uint64_t empty[STAGES];       // MMA -> token copies + decode (tcgen05.commit)
     uint64_t p_full[PACK_MAX_STAGES];     // packed-row copies -> decode
     uint64_t p_empty[PACK_MAX_STAGES];    // decode -> copies (256 arrivals)
     uint64_t acc_full;            // MMA -> epilogue (tcgen05.commit)
-    uint64_t acc_empty;           // epilogue -> MMA (128 arrivals)
+    uint64_t acc_empty;           // epilogue -> MMA (256 arrivals)
     uint32_t tmem_base;
     uint32_t pad;
 };
@@ -233,6 +236,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
           "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(addr));
 }
+__device__ __forceinline__ void tmem_ld8(uint32_t addr, uint32_t (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(addr));
+}
 // Eight 32-bit columns of this thread's tensor-memory lane.
 __device__ __forceinline__ void tmem_st8(uint32_t addr, const uint32_t* v) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(addr), "r"(v[0]),
@@ -291,85 +299,101 @@ __device__ __forceinline__ uint64_t magic2_hi(uint32_t codes) {
 }
 
 // Decode k-step `ks` (0..3) of one Q4_K super-block of this thread's row: 64 weights = the low
-// nibbles (sub-block 2*ks, k 0..31) and the high nibbles (sub-block 2*ks + 1, k 32..63) of 32 quant
-// bytes.  Thread hsel takes nibble plane hsel: one scale, one minimum, columns 16*hsel .. +15.
+// nibbles (sub-block 2*ks, k 0..31 -> columns 0..15) and the high nibbles (sub-block 2*ks + 1,
+// k 32..63 -> columns 16..31) of 32 quant bytes.
 template <bool BF16>
-__device__ __forceinline__ void decode_q4k(const uint8_t* blk, int ks, int hsel, uint32_t (&out)[16]) {
+__device__ __forceinline__ void decode_q4k(const uint8_t* blk, int ks, uint32_t dst) {
     const uint4 hdr = lds_u128(blk);
-    const float d = half_bits_to_f32(hdr.x & 0xffffu), dmin = half_bits_to_f32(hdr.x >> 16);
-    int sc, mn;
-    q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * ks + hsel, sc, mn);
-    const float dl = d * static_cast<float>(sc), ml = dmin * static_cast<float>(mn);
-    const uint64_t dl2 = f2(dl, dl), ml2 = f2(-ml, -ml);
-    const uint64_t unbias = f2(-8388608.0f, -8388608.0f);
     const uint4 q0 = lds_u128(blk + 16 + ks * 32), q1 = lds_u128(blk + 32 + ks * 32);
+    const float d = half_bits_to_f32(hdr.x & 0xffffu), dmin = half_bits_to_f32(hdr.x >> 16);
+    const uint64_t unbias = f2(-8388608.0f, -8388608.0f);
     const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-    const uint32_t sh = 4u * hsel;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t n4 = (qw[i] >> sh) & 0x0f0f0f0fu;
-        // (2^23 + nib) - 2^23 is exact; then exact product and ONE rounding at the subtract (FMA)
-        out[2 * i] = pack2<BF16>(f2_fma(f2_add(magic2<0>(n4), unbias), dl2, ml2));
-        out[2 * i + 1] = pack2<BF16>(f2_fma(f2_add(magic2<2>(n4), unbias), dl2, ml2));
+    for (int pl = 0; pl < 2; ++pl) {                     // nibble plane = sub-block 2*ks + pl
+        int sc, mn;
+        q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * ks + pl, sc, mn);
+        const float dl = d * static_cast<float>(sc), ml = dmin * static_cast<float>(mn);
+        const uint64_t dl2 = f2(dl, dl), ml2 = f2(-ml, -ml);
+        uint32_t out[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t n4 = (qw[i] >> (4 * pl)) & 0x0f0f0f0fu;
+            // (2^23 + nib) - 2^23 is exact; then exact product and ONE rounding at the subtract (FMA)
+            out[2 * i] = pack2<BF16>(f2_fma(f2_add(magic2<0>(n4), unbias), dl2, ml2));
+            out[2 * i + 1] = pack2<BF16>(f2_fma(f2_add(magic2<2>(n4), unbias), dl2, ml2));
+        }
+        tmem_st8(dst + 16 * pl, out);
+        tmem_st8(dst + 16 * pl + 8, out + 8);
     }
 }
 
 // Q6_K: the block sits at `blk` (2-byte aligned inside its 16-byte-aligned window).  k-step ks covers
-// elements 64*ks .. +63 = sub-rows j = jb, jb+1 of half h; this thread owns sub-row jb + hsel: 32
-// elements (columns 16*hsel .. +15) whose low nibbles are 32 bytes of ql and whose top two bits are
-// 32 bytes of qh.  Both runs are read as nine 4-byte-aligned words and shifted into place.
+// elements 64*ks .. +63 = sub-rows j = jb, jb+1 of half h (32 elements = 16 columns each).  Sub-row j
+// takes the low (j < 2) or high nibbles of ql bytes 32*(j&1) .. +31 and bit pair j of qh bytes 0..31.
+// Each run is read as nine 4-byte-aligned words and shifted into place; the 16 columns of a sub-row
+// go to tensor memory at `dst` + 16*jj as soon as they are ready.
 template <bool BF16>
-__device__ __forceinline__ void decode_q6k(const uint8_t* blk, int ks, int hsel, uint32_t (&out)[16]) {
-    const int h = ks >> 1, j = (ks & 1) * 2 + hsel;
+__device__ __forceinline__ void decode_q6k(const uint8_t* blk, int ks, uint32_t dst) {
+    const int h = ks >> 1, jb = (ks & 1) * 2;
     const float d = half_bits_to_f32(lds_u16(blk + 208));
-    const uint32_t sc2 = lds_u16(blk + 192 + h * 8 + 2 * j);
-    const float s0 = d * static_cast<float>(static_cast<int8_t>(sc2 & 0xffu));
-    const float s1 = d * static_cast<float>(static_cast<int8_t>(sc2 >> 8));
-    // The code byte sits in mantissa bits 16-22 of 2^23: f = 2^16 * (128 + q).  With t = s * 2^-16,
-    // fma(t, f, -160 * s) = s * (q - 32): both constants and the result are exact in fp32.
-    const uint64_t t02 = f2(s0 * 0x1p-16f, s0 * 0x1p-16f), t12 = f2(s1 * 0x1p-16f, s1 * 0x1p-16f);
-    const uint64_t c02 = f2(-160.0f * s0, -160.0f * s0), c12 = f2(-160.0f * s1, -160.0f * s1);
-    const uint32_t a_ql = s32(blk + h * 64 + (j & 1) * 32), a_qh = s32(blk + 128 + h * 32);
-    const uint32_t sh = (a_ql & 3u) * 8u;                          // 0 or 16: same for both runs
-    uint32_t wl[9], wh[9];
+    const uint32_t sc4 = lds_u16(blk + 192 + h * 8 + 2 * jb) | (lds_u16(blk + 194 + h * 8 + 2 * jb) << 16);
+    const uint32_t a_ql = s32(blk + h * 64), a_qh = s32(blk + 128 + h * 32);
+    const uint32_t sh = (a_ql & 3u) * 8u;                          // 0 or 16: same for all runs
+    uint32_t wh[9];
 #pragma unroll
-    for (int i = 0; i < 9; ++i) {
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(wl[i]) : "r"((a_ql & ~3u) + 4 * i));
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(wh[i]) : "r"((a_qh & ~3u) + 4 * i));
-    }
-    // one funnel shift realigns the run AND brings the wanted nibble / bit pair down; what it drags in
-    // from the next word lands in masked bits
-    const uint32_t shq = sh + (j >= 2 ? 4u : 0u), shh = sh + 2u * j;
+    for (int i = 0; i < 9; ++i) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(wh[i]) : "r"((a_qh & ~3u) + 4 * i));
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t ql = __funnelshift_r(wl[i], wl[i + 1], shq), qh = __funnelshift_r(wh[i], wh[i + 1], shh);
-        // four 6-bit codes, one per byte: nibble | (two high bits << 4)
-        const uint32_t q = (ql & 0x0f0f0f0fu) + (qh & 0x03030303u) * 16u;
-        const bool first = i < 4;                    // elements 0-15 / 16-31 of the sub-row
-        out[2 * i] = pack2<BF16>(f2_fma(magic2_hi<0>(q), first ? t02 : t12, first ? c02 : c12));
-        out[2 * i + 1] = pack2<BF16>(f2_fma(magic2_hi<2>(q), first ? t02 : t12, first ? c02 : c12));
+    for (int jj = 0; jj < 2; ++jj) {
+        uint32_t wl[9];
+#pragma unroll
+        for (int i = 0; i < 9; ++i)
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(wl[i]) : "r"((a_ql & ~3u) + 32 * jj + 4 * i));
+        const float s0 = d * static_cast<float>(static_cast<int8_t>((sc4 >> (16 * jj)) & 0xffu));
+        const float s1 = d * static_cast<float>(static_cast<int8_t>((sc4 >> (16 * jj + 8)) & 0xffu));
+        // The code byte sits in mantissa bits 16-22 of 2^23: f = 2^16 * (128 + q).  With t = s * 2^-16,
+        // fma(t, f, -160 * s) = s * (q - 32): both constants and the result are exact in fp32.
+        const uint64_t t02 = f2(s0 * 0x1p-16f, s0 * 0x1p-16f), t12 = f2(s1 * 0x1p-16f, s1 * 0x1p-16f);
+        const uint64_t c02 = f2(-160.0f * s0, -160.0f * s0), c12 = f2(-160.0f * s1, -160.0f * s1);
+        // one funnel shift realigns the run AND brings the wanted nibble / bit pair down; what it drags
+        // in from the next word lands in masked bits
+        const uint32_t shq = sh + (jb >= 2 ? 4u : 0u), shh = sh + 2u * (jb + jj);
+        uint32_t out[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t ql = __funnelshift_r(wl[i], wl[i + 1], shq), qh = __funnelshift_r(wh[i], wh[i + 1], shh);
+            // four 6-bit codes, one per byte: nibble | (two high bits << 4)
+            const uint32_t q = (ql & 0x0f0f0f0fu) + (qh & 0x03030303u) * 16u;
+            const bool first = i < 4;                    // elements 0-15 / 16-31 of the sub-row
+            out[2 * i] = pack2<BF16>(f2_fma(magic2_hi<0>(q), first ? t02 : t12, first ? c02 : c12));
+            out[2 * i + 1] = pack2<BF16>(f2_fma(magic2_hi<2>(q), first ? t02 : t12, first ? c02 : c12));
+        }
+        tmem_st8(dst + 16 * jj, out);
+        tmem_st8(dst + 16 * jj + 8, out + 8);
     }
 }
 
 // Q8_0: `st` is the stage: two [128 rows x 128 codes] tiles in the 128-byte swizzle, then eight fp16 scales
-// per row.  k-step ks: elements 64*ks .. +63 = two 32-element blocks, one per thread of the pair
-// (columns 16*hsel .. +15); w = scale * code (exact in fp32).
+// per row.  k-step ks: elements 64*ks .. +63 = two 32-element blocks; w = scale * code (exact in fp32).
 template <bool BF16>
-__device__ __forceinline__ void decode_q8_0(const uint8_t* st, int ks, int r, int hsel, uint32_t (&out)[16]) {
-    const float sc = half_bits_to_f32(lds_u16(st + 2 * Q8_HALF + r * 16 + (2 * ks + hsel) * 2));
-    const uint64_t sc2 = f2(sc, sc), unbias = f2(-8388736.0f, -8388736.0f);     // -(2^23 + 128)
+__device__ __forceinline__ void decode_q8_0(const uint8_t* st, int ks, int r, uint32_t dst) {
+    const uint32_t scw = lds_u32(st + 2 * Q8_HALF + r * 16 + ks * 4);
     const uint8_t* row = st + (ks >> 1) * Q8_HALF + (r >> 3) * 1024 + (r & 7) * 128;
+    const uint64_t unbias = f2(-8388736.0f, -8388736.0f);     // -(2^23 + 128)
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {                        // 16 codes per 16-byte chunk
-        const int chunk = (ks & 1) * 4 + hsel * 2 + c;
+    for (int c = 0; c < 4; ++c) {                        // 16 codes per 16-byte chunk, two chunks per block
+        const float sc = half_bits_to_f32((scw >> (16 * (c >> 1))) & 0xffffu);
+        const uint64_t sc2 = f2(sc, sc);
+        const int chunk = (ks & 1) * 4 + c;
         const uint4 v = lds_u128(row + ((chunk ^ (r & 7)) << 4));
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t out[8];
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
             const uint32_t u = w[jj] ^ 0x80808080u;      // code + 128 as an unsigned byte
-            out[8 * c + 2 * jj] = pack2<BF16>(f2_mul(f2_add(magic2<0>(u), unbias), sc2));
-            out[8 * c + 2 * jj + 1] = pack2<BF16>(f2_mul(f2_add(magic2<2>(u), unbias), sc2));
+            out[2 * jj] = pack2<BF16>(f2_mul(f2_add(magic2<0>(u), unbias), sc2));
+            out[2 * jj + 1] = pack2<BF16>(f2_mul(f2_add(magic2<2>(u), unbias), sc2));
         }
+        tmem_st8(dst + 8 * c, out);
     }
 }
 
@@ -391,7 +415,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            bar_init(&bars->full[s], 1 + DEC_THREADS);
+            bar_init(&bars->full[s], 1 + DEC_GROUP);
             bar_init(&bars->empty[s], 1);
         }
         for (int s = 0; s < PACK_MAX_STAGES; ++s) {
@@ -502,74 +526,76 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         }
         __syncwarp();
     } else if (warp < 10) {
-        // ------------------------------------------------ decode: thread = (weight row, half of the k-step);
-        // the row is the tensor-memory lane this warp may access (its index modulo 4 picks the quarter)
-        const int r = (warp & 3) * 32 + lane, hsel = (warp - 2) >> 2;
+        // ------------------------------------------------ decode: thread = weight row = the tensor-memory
+        // lane this warp may access (its index modulo 4 picks the quarter); group g takes k-steps it = g mod 2
+        const int r = (warp & 3) * 32 + lane, g = (warp - 2) >> 2;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + ACC_COLS;
         bool ok = true;
         uint32_t it = 0, sbi = 0;
         for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
             for (int ks = 0; ks < ksteps; ++ks, ++it) {
                 const uint32_t ps = sbi % pstages, s = it % STAGES;
-                if (ok && (ks & 3) == 0) ok = bar_wait(&bars->p_full[ps], (sbi / pstages) & 1);
-                if (ok && it >= STAGES) ok = bar_wait(&bars->empty[s], ((it / STAGES) - 1) & 1);
-                if (ok) {
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint8_t* stg = p_st + ps * pstage_bytes;
-                    const uint32_t dst = lane_base + s * W_COLS;
-                    // rows past N arrive as zeros from the tensor copy and decode to zeros
-                    {
-                        uint32_t out[16];
+                if ((ks & 1) == g) {
+                    // first step of this group in the super-block: its packed rows must have landed
+                    if (ok && (ks & 3) == g) ok = bar_wait(&bars->p_full[ps], (sbi / pstages) & 1);
+                    if (ok && it >= STAGES) ok = bar_wait(&bars->empty[s], ((it / STAGES) - 1) & 1);
+                    if (ok) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint8_t* stg = p_st + ps * pstage_bytes;
+                        const uint32_t dst = lane_base + s * W_COLS;
+                        // rows past N arrive as zeros from the tensor copy and decode to zeros
                         if (P.format == ALLOYB_Q4_K)
-                            decode_q4k<BF16>(stg + r * Q4_ROW, ks & 3, hsel, out);
+                            decode_q4k<BF16>(stg + r * Q4_ROW, ks & 3, dst);
                         else if (P.format == ALLOYB_Q6_K)
-                            decode_q6k<BF16>(stg + r * Q6_ROW + ((static_cast<int>(sbi % nsb) * Q6K_BYTES) & 15), ks & 3, hsel, out);
+                            decode_q6k<BF16>(stg + r * Q6_ROW + ((static_cast<int>(sbi % nsb) * Q6K_BYTES) & 15), ks & 3, dst);
                         else
-                            decode_q8_0<BF16>(stg, ks & 3, r, hsel, out);
-                        tmem_st8(dst + 16 * hsel, out);
-                        tmem_st8(dst + 16 * hsel + 8, out + 8);
+                            decode_q8_0<BF16>(stg, ks & 3, r, dst);
+                        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     }
-                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    bar_arrive(&bars->full[s]);
+                    if ((ks & 3) == 2 + g) bar_arrive(&bars->p_empty[ps]);      // this group's last step of the super-block
                 }
-                bar_arrive(&bars->full[s]);
-                if ((ks & 3) == 3) {
-                    bar_arrive(&bars->p_empty[ps]);
-                    ++sbi;
-                }
+                if ((ks & 3) == 3) ++sbi;
             }
         }
     } else {
-        // ------------------------------------------------ epilogue: TMEM -> registers -> C
+        // ------------------------------------------------ epilogue: TMEM -> registers, release, -> C
         const int quarter = warp & 3;                       // TMEM lanes this warp may read
+        const int half = (warp - 11) >> 2;                  // token columns half*128 .. +127
         bool ok = true;
         uint32_t tl = 0;
         for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++tl) {
             const int n0 = (t % tiles_n) * BN, m0 = (t / tiles_n) * BM;
             if (ok) ok = bar_wait(&bars->acc_full, tl & 1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t acc[BM / 4];                           // 128 tokens of this lane's row, two per register
             if (ok) {
-                const int n = n0 + quarter * 32 + lane;     // this lane's weight row = output column
-                uint16_t* col = static_cast<uint16_t*>(P.y) + n;
-                const uint32_t src = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
-                uint32_t v[2][16];
-                tmem_ld16(src, v[0]);
+                const uint32_t src = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + half * (BM / 2);
 #pragma unroll
                 for (int c = 0; c < BM / 16; ++c) {
+                    uint32_t v[8];
+                    tmem_ld8(src + c * 8, v);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (c + 1 < BM / 16) tmem_ld16(src + (c + 1) * 16, v[(c + 1) & 1]);
-                    const int tok = m0 + c * 16;
-                    if (n < P.N) {
 #pragma unroll
-                        for (int e = 0; e < 16; ++e)
-                            if (tok + e < P.M)
-                                col[static_cast<int64_t>(tok + e) * P.ldy] =
-                                    static_cast<uint16_t>(pack2<BF16>(__uint_as_float(v[c & 1][e]), 0.0f) & 0xffffu);
-                    }
+                    for (int e = 0; e < 4; ++e)
+                        acc[c * 4 + e] = pack2<BF16>(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             }
-            bar_arrive(&bars->acc_empty);
+            bar_arrive(&bars->acc_empty);                   // the accumulator is free: the next tile may start
+            if (ok) {
+                const int n = n0 + quarter * 32 + lane;     // this lane's weight row = output column
+                const int tok0 = m0 + half * (BM / 2);
+                if (n < P.N) {
+                    uint16_t* col = static_cast<uint16_t*>(P.y) + static_cast<int64_t>(tok0) * P.ldy + n;
+#pragma unroll
+                    for (int e = 0; e < BM / 4; ++e) {
+                        if (tok0 + 2 * e < P.M) col[static_cast<int64_t>(2 * e) * P.ldy] = static_cast<uint16_t>(acc[e] & 0xffffu);
+                        if (tok0 + 2 * e + 1 < P.M) col[static_cast<int64_t>(2 * e + 1) * P.ldy] = static_cast<uint16_t>(acc[e] >> 16);
+                    }
+                }
+            }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
