@@ -298,11 +298,25 @@ __device__ __forceinline__ uint64_t magic2_hi(uint32_t codes) {
               __uint_as_float(__byte_perm(codes, 0x4B000000u, 0x7044 | ((E + 1) << 8))));
 }
 
+// Gate in front of a thread's first tensor-memory store of a k-step: the stage must have been released by
+// the MMAs that read it last.  `free_now` is the result of a test issued before the decode arithmetic.
+struct StageGate {
+    uint32_t bar, parity;
+    bool free_now, ok;
+    __device__ __forceinline__ void pass() {
+        if (!free_now) {
+            ok = bar_wait_slow(bar, parity);
+            free_now = true;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+};
+
 // Decode k-step `ks` (0..3) of one Q4_K super-block of this thread's row: 64 weights = the low
 // nibbles (sub-block 2*ks, k 0..31 -> columns 0..15) and the high nibbles (sub-block 2*ks + 1,
 // k 32..63 -> columns 16..31) of 32 quant bytes.
 template <bool BF16>
-__device__ __forceinline__ void decode_q4k(const uint8_t* blk, int ks, uint32_t dst) {
+__device__ __forceinline__ void decode_q4k(const uint8_t* blk, int ks, uint32_t dst, StageGate& gate) {
     const uint4 hdr = lds_u128(blk);
     const uint4 q0 = lds_u128(blk + 16 + ks * 32), q1 = lds_u128(blk + 32 + ks * 32);
     const float d = half_bits_to_f32(hdr.x & 0xffffu), dmin = half_bits_to_f32(hdr.x >> 16);
@@ -322,6 +336,7 @@ __device__ __forceinline__ void decode_q4k(const uint8_t* blk, int ks, uint32_t 
             out[2 * i] = pack2<BF16>(f2_fma(f2_add(magic2<0>(n4), unbias), dl2, ml2));
             out[2 * i + 1] = pack2<BF16>(f2_fma(f2_add(magic2<2>(n4), unbias), dl2, ml2));
         }
+        if (pl == 0) gate.pass();
         tmem_st8(dst + 16 * pl, out);
         tmem_st8(dst + 16 * pl + 8, out + 8);
     }
@@ -333,7 +348,7 @@ __device__ __forceinline__ void decode_q4k(const uint8_t* blk, int ks, uint32_t 
 // Each run is read as nine 4-byte-aligned words and shifted into place; the 16 columns of a sub-row
 // go to tensor memory at `dst` + 16*jj as soon as they are ready.
 template <bool BF16>
-__device__ __forceinline__ void decode_q6k(const uint8_t* blk, int ks, uint32_t dst) {
+__device__ __forceinline__ void decode_q6k(const uint8_t* blk, int ks, uint32_t dst, StageGate& gate) {
     const int h = ks >> 1, jb = (ks & 1) * 2;
     const float d = half_bits_to_f32(lds_u16(blk + 208));
     const uint32_t sc4 = lds_u16(blk + 192 + h * 8 + 2 * jb) | (lds_u16(blk + 194 + h * 8 + 2 * jb) << 16);
@@ -367,6 +382,7 @@ __device__ __forceinline__ void decode_q6k(const uint8_t* blk, int ks, uint32_t 
             out[2 * i] = pack2<BF16>(f2_fma(magic2_hi<0>(q), first ? t02 : t12, first ? c02 : c12));
             out[2 * i + 1] = pack2<BF16>(f2_fma(magic2_hi<2>(q), first ? t02 : t12, first ? c02 : c12));
         }
+        if (jj == 0) gate.pass();
         tmem_st8(dst + 16 * jj, out);
         tmem_st8(dst + 16 * jj + 8, out + 8);
     }
@@ -375,7 +391,7 @@ __device__ __forceinline__ void decode_q6k(const uint8_t* blk, int ks, uint32_t 
 // Q8_0: `st` is the stage: two [128 rows x 128 codes] tiles in the 128-byte swizzle, then eight fp16 scales
 // per row.  k-step ks: elements 64*ks .. +63 = two 32-element blocks; w = scale * code (exact in fp32).
 template <bool BF16>
-__device__ __forceinline__ void decode_q8_0(const uint8_t* st, int ks, int r, uint32_t dst) {
+__device__ __forceinline__ void decode_q8_0(const uint8_t* st, int ks, int r, uint32_t dst, StageGate& gate) {
     const uint32_t scw = lds_u32(st + 2 * Q8_HALF + r * 16 + ks * 4);
     const uint8_t* row = st + (ks >> 1) * Q8_HALF + (r >> 3) * 1024 + (r & 7) * 128;
     const uint64_t unbias = f2(-8388736.0f, -8388736.0f);     // -(2^23 + 128)
@@ -393,6 +409,7 @@ __device__ __forceinline__ void decode_q8_0(const uint8_t* st, int ks, int r, ui
             out[2 * jj] = pack2<BF16>(f2_mul(f2_add(magic2<0>(u), unbias), sc2));
             out[2 * jj + 1] = pack2<BF16>(f2_mul(f2_add(magic2<2>(u), unbias), sc2));
         }
+        if (c == 0) gate.pass();
         tmem_st8(dst + 8 * c, out);
     }
 }
@@ -538,18 +555,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 if ((ks & 1) == g) {
                     // first step of this group in the super-block: its packed rows must have landed
                     if (ok && (ks & 3) == g) ok = bar_wait(&bars->p_full[ps], (sbi / pstages) & 1);
-                    if (ok && it >= STAGES) ok = bar_wait(&bars->empty[s], ((it / STAGES) - 1) & 1);
+                    // the stage's previous use must be over before the first store to it, not before the
+                    // loads and the arithmetic: test now, and only wait (inside the decode, right before
+                    // its first tensor-memory store) if the test failed
+                    const uint32_t e_bar = s32(&bars->empty[s]), e_par = ((it / STAGES) - 1) & 1;
+                    const bool free_now = it < STAGES || bar_test_a(e_bar, e_par);
                     if (ok) {
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint8_t* stg = p_st + ps * pstage_bytes;
                         const uint32_t dst = lane_base + s * W_COLS;
+                        StageGate gate{e_bar, e_par, free_now, true};
                         // rows past N arrive as zeros from the tensor copy and decode to zeros
                         if (P.format == ALLOYB_Q4_K)
-                            decode_q4k<BF16>(stg + r * Q4_ROW, ks & 3, dst);
+                            decode_q4k<BF16>(stg + r * Q4_ROW, ks & 3, dst, gate);
                         else if (P.format == ALLOYB_Q6_K)
-                            decode_q6k<BF16>(stg + r * Q6_ROW + ((static_cast<int>(sbi % nsb) * Q6K_BYTES) & 15), ks & 3, dst);
+                            decode_q6k<BF16>(stg + r * Q6_ROW + ((static_cast<int>(sbi % nsb) * Q6K_BYTES) & 15), ks & 3, dst, gate);
                         else
-                            decode_q8_0<BF16>(stg, ks & 3, r, dst);
+                            decode_q8_0<BF16>(stg, ks & 3, r, dst, gate);
+                        ok = gate.ok;
                         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     }
