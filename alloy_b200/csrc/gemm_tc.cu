@@ -1,31 +1,38 @@
-// Prefill dequant-GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
+// Dequant-GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a: every linear of the path
+// with more than a handful of tokens (prefill, verification chunks, batched decode).
 //
-//   C[M tokens, N] = X[M, K] (bf16 | fp16)  *  deq(W)[N, K]^T      fp32 accumulate, C in X's type
+//   C[M tokens, N] = X[M, K] (bf16 | fp16)  *  deq(W)[N, K]^T  (+ residual)     fp32 accumulate, C in X's type
+//   C = act(X G^T) * (X U^T)  for a gate/up pair (up to 128 tokens)
 //
-// A persistent kernel: one CTA per SM walks output tiles of 128 weight rows x 256 tokens.  In the MMA
-// the WEIGHT rows are the M = 128 operand and the 256 tokens are N, and the decoded weights never touch
-// shared memory: the decode warps write them straight into TENSOR MEMORY (tcgen05.st), from where
-// tcgen05.mma reads its A operand, so the only shared-memory traffic of the tensor pipe is the token
-// tile -- shared-memory bandwidth is what bounds this kernel otherwise.  Per 64-wide K step:
-//   * warp 0 (one lane) brings the 256 x 64 token tile in with ONE TMA tensor copy (128-byte swizzle);
-//   * warp 10 (one lane) brings the 128 packed weight rows of a super-block (four K steps) in with ONE
-//     tensor copy over a byte view of the weight matrix (Q8_0: two swizzled copies of codes and one of
-//     scales), issued as soon as the slot's previous super-block is decoded;
-//   * warps 2-9 decode: two groups of four warps take alternate K steps, so each has two step times for
-//     its chain of waits, loads and stores; a thread sits on the tensor-memory lane of its weight row and
-//     decodes the row's 64 weights of the step to fp32 exactly as the block format defines them (Q4_K:
-//     d*sc*nib - dmin*m with ONE rounding; Q6_K: d*sc*(q-32), exact; Q8_0: scale*code, exact), round
-//     ONCE to the activation type and store 32 packed columns.  Codes become floats without a
-//     conversion instruction (a byte permute drops the code into the mantissa of 2^23) and the
-//     arithmetic runs on the two-wide fp32 instructions (add/mul/fma .f32x2);
-//   * warp 1 (one lane) issues four tcgen05.mma (M = 128, N = 256, K = 16) per step into a 256-column
-//     fp32 accumulator and releases the stage with tcgen05.commit; the wait for the next stage overlaps
-//     the MMAs just queued.
+// A persistent kernel: one CTA per SM walks work items = (tile of 128 weight rows x BM tokens, K range),
+// BM in {32, 64, 128, 256} chosen from M.  In the MMA the WEIGHT rows are the M = 128 operand and the
+// tokens are N, and the decoded weights never touch shared memory: the decode warps write them straight
+// into TENSOR MEMORY (tcgen05.st), from where tcgen05.mma reads its A operand, so the only shared-memory
+// traffic of the tensor pipe is the token tile -- shared-memory bandwidth is what bounds this kernel
+// otherwise.  Per 64-wide K step:
+//   * warp 0 (one lane) brings the BM x 64 token tile in with ONE TMA tensor copy (128-byte swizzle);
+//   * the packed-row warp (one lane) brings the 128 packed weight rows of a super-block (four K steps) in
+//     with ONE tensor copy over a byte view of the weight matrix (Q8_0: two swizzled copies of codes and
+//     one of scales), issued as soon as the slot's previous super-block is decoded;
+//   * the decode warps work in DG groups of four warps that take K steps round robin, so each group has
+//     DG step times for its chain of waits, loads and stores (DG = 2 under the 256-token tile, whose
+//     epilogue needs the registers; 4 otherwise, where decode alone bounds the kernel); a thread sits on the
+//     tensor-memory lane of its weight row and decodes the row's 64 weights of the step to fp32 exactly
+//     as the block format defines them (Q4_K: d*sc*nib - dmin*m with ONE rounding; Q6_K: d*sc*(q-32),
+//     exact; Q8_0: scale*code, exact), rounds ONCE to the activation type and stores 32 packed columns.
+//     Codes become floats without a conversion instruction (a byte permute drops the code into the
+//     mantissa of 2^23) and the arithmetic runs on the two-wide fp32 instructions (add/mul/fma .f32x2);
+//   * warp 1 (one lane) issues four tcgen05.mma (M = 128, N = BM, K = 16) per step into a BM-column fp32
+//     accumulator and releases the stage with tcgen05.commit; the wait for the next stage sits before the
+//     last MMA of the step.
 // Four stages of tokens (shared memory) and decoded weights (tensor memory) and two or three of packed
-// rows run ahead across tile boundaries.  Warps 11-18 drain the finished accumulator with tcgen05.ld into
-// REGISTERS (64 packed pairs per thread), hand tensor memory back to the MMA warp at once, and only then
-// store C (each lane one weight row: a warp writes 64 contiguous bytes per token) while the next tile's
-// MMAs already run.
+// rows run ahead across item boundaries.  Eight epilogue warps drain the finished accumulator with
+// tcgen05.ld into REGISTERS, hand tensor memory back to the MMA warp at once, and only then store C (each
+// lane one weight row: a warp writes 64 contiguous bytes per token) while the next item's MMAs run.
+// When a matrix has fewer row tiles than the GPU has SMs and all tokens fit one tile, K is split: every
+// item adds its partial tile to a zeroed fp32 buffer (red.global) and the LAST item of a tile to finish
+// (a per-tile counter) reads the sums back, applies residual / activation, stores C and re-zeroes both.
+// A gate/up pair runs as two K loops into two accumulators; the epilogue combines them.
 // Every wait is bounded: on a time-out the sticky device error word is set, the CTA still frees its
 // tensor memory and returns.
 #include <cuda.h>
@@ -39,14 +46,10 @@ namespace tc {
 
 __device__ int g_tc_error = 0;          // sticky: a bounded wait of this file's kernel ran out
 
-constexpr int BM = 256;                 // tokens per tile (UMMA N)
 constexpr int BN = 128;                 // weight rows per tile (UMMA M = tensor-memory lanes)
 constexpr int BK = 64;                  // K step: 64 x 2 bytes = one 128-byte swizzle row
-constexpr int STAGES = 4;
-constexpr int X_STAGE = BM * BK * 2;    // 32 KB of tokens
+constexpr int MAX_STAGES = 8;
 constexpr int W_COLS = BK / 2;          // tensor-memory columns of one decoded weight stage (two per column)
-constexpr int ACC_COLS = BM;            // fp32 accumulator: one column per token
-constexpr int TMEM_COLS = 512;          // 256 accumulator + 4 x 32 weights, rounded up to a power of two
 // One super-block of 128 packed rows in shared memory:
 //   Q4_K  144-byte rows (9 x 16 bytes: 128-bit reads of 8 consecutive rows hit distinct banks);
 //   Q6_K  240-byte rows: the 16-byte-aligned window around the 210-byte block (15 x 16 bytes);
@@ -54,36 +57,72 @@ constexpr int TMEM_COLS = 512;          // 256 accumulator + 4 x 32 weights, rou
 constexpr int Q4_ROW = 144, Q6_ROW = 240;
 constexpr int Q8_HALF = BN * 128;           // 16 KB
 constexpr int Q4_STAGE = BN * Q4_ROW, Q6_STAGE = BN * Q6_ROW, Q8_STAGE = 2 * Q8_HALF + BN * 16;
-constexpr int PACK_MAX_STAGES = 3;          // Q4_K and Q6_K run three deep, Q8_0 two
-constexpr int PACK_BYTES = 3 * Q6_STAGE;    // 90 KB: 3 x Q4_K, 3 x Q6_K or 2 x Q8_0 stages
-static_assert(2 * Q8_STAGE <= PACK_BYTES && 3 * Q4_STAGE <= PACK_BYTES, "packed-row region");
-constexpr int DEC_THREADS = 256;        // two groups of 128 (one thread per weight row) on alternate k-steps
-constexpr int DEC_GROUP = 128;
-constexpr int EPI_THREADS = 256;        // two per accumulator lane (128 token columns each)
-// warp 0 token copies, warp 1 MMA, warps 2-9 decode, warp 10 packed-row copies, warps 11-18 epilogue
-constexpr int THREADS = 64 + DEC_THREADS + 32 + EPI_THREADS;
+constexpr int PACK_MAX_STAGES = 5;          // Q4_K runs five deep, Q6_K three, Q8_0 two
+constexpr int PACK_BYTES = 3 * Q6_STAGE;    // 90 KB: 5 x Q4_K, 3 x Q6_K or 2 x Q8_0 stages
+static_assert(2 * Q8_STAGE <= PACK_BYTES && 5 * Q4_STAGE <= PACK_BYTES, "packed-row region");
+// A super-block of rows comes in as PACK_BOXES tensor copies of PACK_BOX_ROWS rows each: the copy unit
+// walks a box row by row, and several short boxes in flight finish sooner than one tall one.
+constexpr int PACK_BOXES = 4, PACK_BOX_ROWS = BN / PACK_BOXES;
+constexpr int DEC_GROUP = 128;          // one decode group: a thread per weight row
+constexpr int EPI_THREADS = 256;        // two per accumulator lane (half of the token columns each)
 constexpr uint32_t SPIN = 1u << 22;
+// Split-K scratch: fp32 sums [token][row] for up to SPLIT_MAX_ROWS rows (x 2 planes for a gate/up pair)
+// and SPLIT_MAX_BM tokens, and one counter per row tile.  Zero at load, re-zeroed by whoever finishes a
+// tile, so two GEMMs that split K must not overlap in time on one device.
+constexpr int SPLIT_MAX_TILES = 147, SPLIT_MAX_ROWS = SPLIT_MAX_TILES * BN, SPLIT_MAX_BM = 128;
+__device__ float g_split_sum[2 * SPLIT_MAX_BM * SPLIT_MAX_ROWS];
+__device__ unsigned int g_split_count[SPLIT_MAX_TILES];
+
+template <int BM, int DG>
+struct Cfg {
+    static constexpr int X_STAGE = BM * BK * 2;                 // one token tile
+    // Stages of tokens (shared memory) and decoded weights (tensor memory).  With DG decode groups on
+    // DG stages every group would wait for the MMAs of its own previous step before it may store the
+    // next one; twice as many stages let it run a step ahead.
+    static constexpr int STAGES = BM <= 128 ? 8 : 4;
+    static constexpr int DEC_WARPS = 4 * DG;
+    static constexpr int PACK_WARP = 2 + DEC_WARPS;             // warp 0 token copies, warp 1 MMA, then decode
+    static constexpr int EPI_WARP0 = PACK_WARP + 1;
+    // Issuing one tcgen05.mma costs its thread about as long as a 128-token MMA runs, so with a narrower
+    // token tile the issuing thread, not the tensor pipe, would set the pace: NI threads (warp 1 and NI - 1
+    // warps behind the epilogue's) then issue a quarter or a half of every step's MMAs each, into an
+    // accumulator of their own, and the epilogue adds the accumulators up.
+    static constexpr int NI = BM <= 32 ? 4 : (BM <= 64 ? 2 : 1);
+    static constexpr int MMA_WARP1 = EPI_WARP0 + EPI_THREADS / 32;      // issuers 1 .. NI-1
+    static constexpr int THREADS = (MMA_WARP1 + NI - 1) * 32;
+    // accumulators [gate/up][issuer] of BM columns each from column 0, decoded weights behind them
+    static constexpr int W_COL0 = 2 * NI * BM <= 256 ? 2 * NI * BM : BM;
+    static constexpr int TMEM_COLS = W_COL0 + STAGES * W_COLS <= 256 ? 256 : 512;
+    static constexpr int SMEM_BYTES = 1024 /*align slack*/ + STAGES * X_STAGE + PACK_BYTES + 256;
+    static_assert(W_COL0 + STAGES * W_COLS <= 512 && STAGES <= MAX_STAGES, "tensor memory");
+};
 
 struct Bars {
-    uint64_t full[STAGES];        // token-tile copy (1 arrival + bytes) and decode (128 arrivals) -> MMA
-    uint64_t empty[STAGES];       // MMA -> token copies + decode (tcgen05.commit)
+    uint64_t full[MAX_STAGES];    // token-tile copy (1 arrival + bytes) and decode (128 arrivals) -> MMA
+    uint64_t empty[MAX_STAGES];   // MMA -> token copies + decode (tcgen05.commit)
     uint64_t p_full[PACK_MAX_STAGES];     // packed-row copies -> decode
-    uint64_t p_empty[PACK_MAX_STAGES];    // decode -> copies (256 arrivals)
+    uint64_t p_empty[PACK_MAX_STAGES];    // decode -> copies (one arrival per decode thread)
     uint64_t acc_full;            // MMA -> epilogue (tcgen05.commit)
     uint64_t acc_empty;           // epilogue -> MMA (256 arrivals)
     uint32_t tmem_base;
-    uint32_t pad;
+    uint32_t last;                // split-K: this CTA finished a tile last
 };
-
-constexpr int SMEM_BYTES = 1024 /*align slack*/ + STAGES * X_STAGE + PACK_BYTES + 256;
 static_assert(sizeof(Bars) <= 256, "barrier block");
+
+struct Maps {
+    CUtensorMap x;                // tokens
+    CUtensorMap w[2];             // packed rows as bytes (gate/up: both matrices)
+    CUtensorMap s[2];             // Q8_0 scales
+};
 
 struct Params {
     int format;               // ALLOYB_Q4_K / ALLOYB_Q6_K / ALLOYB_Q8_0
     void* y;
+    const void* residual;     // same shape and pitch as y, or null
     int64_t ldy;
     int M, N, K;
-    int is_bf16;
+    int splits;               // K ranges per row tile (1: the item owns its output tile)
+    int gated, act;           // gate/up pair: y = act(gate) * up
 };
 
 __device__ __forceinline__ uint32_t s32(const void* p) {
@@ -161,13 +200,13 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     d |= static_cast<uint64_t>(2) << 61;                             // SWIZZLE_128B
     return d;
 }
-// kind::f16: D fp32, A/B both bf16 (1) or fp16 (0), both K-major, M = BN weight rows, N = BM tokens.
-__device__ __forceinline__ uint32_t umma_idesc(int is_bf16) {
+// kind::f16: D fp32, A/B both bf16 (1) or fp16 (0), both K-major, M = BN weight rows, N = `tokens`.
+__device__ __forceinline__ uint32_t umma_idesc(int is_bf16, int tokens) {
     uint32_t d = 0;
     d |= 1u << 4;                                   // D format F32
     d |= static_cast<uint32_t>(is_bf16 ? 1 : 0) << 7;    // A format
     d |= static_cast<uint32_t>(is_bf16 ? 1 : 0) << 10;   // B format
-    d |= static_cast<uint32_t>(BM >> 3) << 17;      // N
+    d |= static_cast<uint32_t>(tokens >> 3) << 17;  // N
     d |= static_cast<uint32_t>(BN >> 4) << 24;      // M
     return d;
 }
@@ -414,44 +453,91 @@ __device__ __forceinline__ void decode_q8_0(const uint8_t* st, int ks, int r, ui
     }
 }
 
+// One work item: a tile of 128 weight rows x BM tokens over super-blocks [sb0, sb1).
+struct Item {
+    int n0, tile_n, tile_m, sb0, sb1;
+};
+__device__ __forceinline__ Item item_of(int w, int tiles_n, int tiles_m, int nsb, int splits) {
+    Item it;
+    it.tile_n = w % tiles_n;
+    const int r = w / tiles_n, split = r / tiles_m;
+    it.n0 = it.tile_n * BN;
+    it.tile_m = r % tiles_m;
+    it.sb0 = static_cast<int>(static_cast<int64_t>(split) * nsb / splits);
+    it.sb1 = static_cast<int>(static_cast<int64_t>(split + 1) * nsb / splits);
+    return it;
+}
+
+__device__ __forceinline__ float apply_act(float g, int act) {
+    if (act == ALLOYB_ACT_SILU) return g / (1.0f + __expf(-g));
+    const float u = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (1.0f + tanhf(u));
+}
+
 template <bool BF16>
-__global__ void __launch_bounds__(THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
-               const __grid_constant__ CUtensorMap smap, const Params P) {
+__device__ __forceinline__ float to_f32(uint16_t v) {
+    return BF16 ? __uint_as_float(static_cast<uint32_t>(v) << 16) : half_bits_to_f32(v);
+}
+template <bool BF16>
+__device__ __forceinline__ uint16_t to_16(float v) {
+    return static_cast<uint16_t>(pack2<BF16>(v, 0.0f) & 0xffffu);
+}
+
+// Eight columns of this thread's lane, summed over the NI issuers' accumulators (BM columns apart).
+template <int NI, int BM>
+__device__ __forceinline__ void load_sum(uint32_t addr, uint32_t (&v)[8]) {
+    tmem_ld8(addr, v);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int a = 1; a < NI; ++a) {
+        uint32_t t[8];
+        tmem_ld8(addr + a * BM, t);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) + __uint_as_float(t[e]));
+    }
+}
+
+template <bool BF16, int BM, int DG>
+__global__ void __launch_bounds__(Cfg<BM, DG>::THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ Maps maps, const Params P) {
+    using C = Cfg<BM, DG>;
+    constexpr int X_STAGE = C::X_STAGE, STAGES = C::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* x_st = smem;                                   // STAGES x 32 KB token tiles
+    uint8_t* x_st = smem;                                   // STAGES token tiles
     uint8_t* p_st = smem + STAGES * X_STAGE;                // packed rows
     Bars* bars = reinterpret_cast<Bars*>(p_st + PACK_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nsb = P.K / QK_K, ksteps = nsb * 4;
-    const int tiles_n = (P.N + BN - 1) / BN, tiles_m = (P.M + BM - 1) / BM, n_tiles = tiles_n * tiles_m;
-    const int pstages = P.format == ALLOYB_Q8_0 ? 2 : 3;
+    const int nsb = P.K / QK_K;
+    const int tiles_n = (P.N + BN - 1) / BN, tiles_m = (P.M + BM - 1) / BM, n_items = tiles_n * tiles_m * P.splits;
+    const int n_sub = P.gated ? 2 : 1;                      // K loops (accumulators) per item
+    const int pstages = P.format == ALLOYB_Q4_K ? 5 : (P.format == ALLOYB_Q6_K ? 3 : 2);
     const int pstage_bytes = P.format == ALLOYB_Q4_K ? Q4_STAGE : (P.format == ALLOYB_Q6_K ? Q6_STAGE : Q8_STAGE);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             bar_init(&bars->full[s], 1 + DEC_GROUP);
-            bar_init(&bars->empty[s], 1);
+            bar_init(&bars->empty[s], C::NI);
         }
         for (int s = 0; s < PACK_MAX_STAGES; ++s) {
             bar_init(&bars->p_full[s], 1);
-            bar_init(&bars->p_empty[s], DEC_THREADS);
+            bar_init(&bars->p_empty[s], DG * DEC_GROUP);
         }
-        bar_init(&bars->acc_full, 1);
+        bar_init(&bars->acc_full, C::NI);
         bar_init(&bars->acc_empty, EPI_THREADS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {      // tensor memory: one warp allocates, the same warp frees
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&bars->tmem_base)),
-                     "r"(TMEM_COLS));
+                     "r"(C::TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = bars->tmem_base;          // accumulator: columns 0..255; weight stages behind it
+    const uint32_t tmem = bars->tmem_base;          // accumulator(s) from column 0; weight stages at W_COL0
     pdl_launch_dependents();
     pdl_wait();
 
@@ -459,171 +545,269 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         // ------------------------------------------------ token tiles
         bool ok = true;
         uint32_t it = 0;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-            const int m0 = (t / tiles_n) * BM;
-            for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
-                const uint32_t s = it % STAGES;
-                if (it >= STAGES) ok = bar_wait(&bars->empty[s], ((it / STAGES) - 1) & 1);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                if (lane == 0) {
-                    bar_expect(&bars->full[s], X_STAGE);
-                    tma_2d(x_st + s * X_STAGE, &xmap, ks * BK, m0, &bars->full[s]);
+        for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+            const Item im = item_of(w, tiles_n, tiles_m, nsb, P.splits);
+            for (int sub = 0; sub < n_sub && ok; ++sub) {
+                for (int ks = im.sb0 * 4; ks < im.sb1 * 4 && ok; ++ks, ++it) {
+                    const uint32_t s = it % STAGES;
+                    if (it >= STAGES) ok = bar_wait(&bars->empty[s], ((it / STAGES) - 1) & 1);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        bar_expect(&bars->full[s], X_STAGE);
+                        tma_2d(x_st + s * X_STAGE, &maps.x, ks * BK, im.tile_m * BM, &bars->full[s]);
+                    }
+                    __syncwarp();
                 }
-                __syncwarp();
             }
         }
-    } else if (warp == 10) {
+    } else if (warp == C::PACK_WARP) {
         // ------------------------------------------------ packed rows: one tensor copy per super-block
         bool ok = true;
         uint32_t sbi = 0;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-            const int n0 = (t % tiles_n) * BN;
-            for (int sb = 0; sb < nsb && ok; ++sb, ++sbi) {
-                const uint32_t ps = sbi % pstages;
-                if (sbi >= static_cast<uint32_t>(pstages)) ok = bar_wait(&bars->p_empty[ps], ((sbi / pstages) - 1) & 1);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                if (lane == 0) {
-                    uint8_t* dst = p_st + ps * pstage_bytes;
-                    if (P.format == ALLOYB_Q4_K) {
-                        bar_expect(&bars->p_full[ps], Q4_STAGE);
-                        tma_2d(dst, &wmap, sb * Q4K_BYTES, n0, &bars->p_full[ps]);
-                    } else if (P.format == ALLOYB_Q6_K) {
-                        // a block is 2-byte aligned: copy the aligned window around it (reads past the
-                        // row's end are filled with zeros)
-                        bar_expect(&bars->p_full[ps], Q6_STAGE);
-                        tma_2d(dst, &wmap, (sb * Q6K_BYTES) & ~15, n0, &bars->p_full[ps]);
-                    } else {
-                        bar_expect(&bars->p_full[ps], Q8_STAGE);
-                        tma_2d(dst, &wmap, sb * 256, n0, &bars->p_full[ps]);
-                        tma_2d(dst + Q8_HALF, &wmap, sb * 256 + 128, n0, &bars->p_full[ps]);
-                        tma_2d(dst + 2 * Q8_HALF, &smap, sb * 16, n0, &bars->p_full[ps]);
+        for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+            const Item im = item_of(w, tiles_n, tiles_m, nsb, P.splits);
+            for (int sub = 0; sub < n_sub && ok; ++sub) {
+                for (int sb = im.sb0; sb < im.sb1 && ok; ++sb, ++sbi) {
+                    const uint32_t ps = sbi % pstages;
+                    if (sbi >= static_cast<uint32_t>(pstages)) ok = bar_wait(&bars->p_empty[ps], ((sbi / pstages) - 1) & 1);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        uint8_t* dst = p_st + ps * pstage_bytes;
+                        if (P.format == ALLOYB_Q4_K) {
+                            bar_expect(&bars->p_full[ps], Q4_STAGE);
+#pragma unroll
+                            for (int b = 0; b < PACK_BOXES; ++b)
+                                tma_2d(dst + b * PACK_BOX_ROWS * Q4_ROW, &maps.w[sub], sb * Q4K_BYTES, im.n0 + b * PACK_BOX_ROWS,
+                                       &bars->p_full[ps]);
+                        } else if (P.format == ALLOYB_Q6_K) {
+                            // a block is 2-byte aligned: copy the aligned window around it (reads past the
+                            // row's end are filled with zeros)
+                            bar_expect(&bars->p_full[ps], Q6_STAGE);
+#pragma unroll
+                            for (int b = 0; b < PACK_BOXES; ++b)
+                                tma_2d(dst + b * PACK_BOX_ROWS * Q6_ROW, &maps.w[sub], (sb * Q6K_BYTES) & ~15,
+                                       im.n0 + b * PACK_BOX_ROWS, &bars->p_full[ps]);
+                        } else {
+                            bar_expect(&bars->p_full[ps], Q8_STAGE);
+#pragma unroll
+                            for (int b = 0; b < PACK_BOXES; ++b) {
+                                const int r0 = b * PACK_BOX_ROWS;
+                                tma_2d(dst + r0 * 128, &maps.w[sub], sb * 256, im.n0 + r0, &bars->p_full[ps]);
+                                tma_2d(dst + Q8_HALF + r0 * 128, &maps.w[sub], sb * 256 + 128, im.n0 + r0, &bars->p_full[ps]);
+                                tma_2d(dst + 2 * Q8_HALF + r0 * 16, &maps.s[sub], sb * 16, im.n0 + r0, &bars->p_full[ps]);
+                            }
+                        }
                     }
+                    __syncwarp();
                 }
-                __syncwarp();
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------ MMA issue (one lane)
-        // The tensor pipe queues about one instruction behind the running one, so nothing slow may sit
-        // between two issues: the wait for the NEXT stage is placed before the last MMA of this one
-        // (two MMAs are still in the pipe then) and the rest of the loop is a few instructions.
-        // This ONE thread's instruction stream paces the tensor pipe, so the loop is kept to a few dozen
-        // instructions per step: descriptors advance by adding to their low word, barriers are addressed
-        // by shared address, and the common already-complete wait is a single test.
-        const uint32_t idesc = umma_idesc(BF16 ? 1 : 0);
+    } else if (warp == 1 || warp >= C::MMA_WARP1) {
+        // ------------------------------------------------ MMA issue (one lane per issuer)
+        // This ONE thread's instruction stream paces the tensor pipe (which queues about one instruction
+        // behind the running one), so the loop is kept to a few dozen instructions per step: descriptors
+        // advance by adding to their low word, barriers are addressed by shared address, the common
+        // already-complete wait is a single test, and the wait for the NEXT stage sits before the last
+        // MMA of this one, while two MMAs are still in the pipe.
+        const uint32_t idesc = umma_idesc(BF16 ? 1 : 0, BM);
         if (lane == 0) {
             const uint64_t d0 = umma_desc(s32(x_st));
             const uint32_t d_lo = static_cast<uint32_t>(d0), d_hi = static_cast<uint32_t>(d0 >> 32);
-            const uint32_t full0 = s32(&bars->full[0]), empty0 = s32(&bars->empty[0]), w_base = tmem + ACC_COLS;
+            const uint32_t full0 = s32(&bars->full[0]), empty0 = s32(&bars->empty[0]), w_base = tmem + C::W_COL0;
+            constexpr int NI = C::NI, KK = 4 / NI;              // this issuer's MMAs per step: kk0 .. kk0 + KK - 1
+            const int issuer = warp == 1 ? 0 : warp - C::MMA_WARP1 + 1, kk0 = issuer * KK;
             bool ok = true;
             uint32_t it = 0, tl = 0;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tl) {
-                // the epilogue must have read the previous tile's accumulator before it is overwritten
+            for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++tl) {
+                const Item im = item_of(w, tiles_n, tiles_m, nsb, P.splits);
+                const int ksteps = (im.sb1 - im.sb0) * 4;
+                // the epilogue must have read the previous item's accumulators before they are overwritten
                 if (tl > 0) ok = bar_wait(&bars->acc_empty, (tl - 1) & 1);
-                if (ok) ok = bar_wait(&bars->full[it % STAGES], (it / STAGES) & 1);
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
-                    const uint32_t s = it % STAGES;
-                    const uint32_t lo = d_lo + s * (X_STAGE >> 4), w0 = w_base + s * W_COLS;
-                    umma_ts_first(tmem, w0, lo, d_hi, idesc, ks > 0 ? 1u : 0u);
-                    umma_ts_acc(tmem, w0 + 8, lo + 2, d_hi, idesc);
-                    umma_ts_acc(tmem, w0 + 16, lo + 4, d_hi, idesc);
-                    if (ks + 1 < ksteps) {
-                        const uint32_t nb = full0 + 8 * ((it + 1) % STAGES), np = ((it + 1) / STAGES) & 1;
-                        if (!bar_test_a(nb, np)) ok = bar_wait_slow(nb, np);
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int sub = 0; sub < n_sub && ok; ++sub) {
+                    const uint32_t acc = tmem + (sub * NI + issuer) * BM;
+                    ok = bar_wait(&bars->full[it % STAGES], (it / STAGES) & 1);
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
+                        const uint32_t s = it % STAGES;
+                        const uint32_t lo = d_lo + s * (X_STAGE >> 4) + 2 * kk0, w0 = w_base + s * W_COLS + 8 * kk0;
+                        umma_ts_first(acc, w0, lo, d_hi, idesc, ks > 0 ? 1u : 0u);
+                        if (KK == 4) {
+                            umma_ts_acc(acc, w0 + 8, lo + 2, d_hi, idesc);
+                            umma_ts_acc(acc, w0 + 16, lo + 4, d_hi, idesc);
+                        }
+                        if (ks + 1 < ksteps) {
+                            const uint32_t nb = full0 + 8 * ((it + 1) % STAGES), np = ((it + 1) / STAGES) & 1;
+                            if (!bar_test_a(nb, np)) ok = bar_wait_slow(nb, np);
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        }
+                        if (KK >= 2) umma_ts_acc(acc, w0 + 8 * (KK - 1), lo + 2 * (KK - 1), d_hi, idesc);
+                        umma_commit_a(empty0 + 8 * s);
                     }
-                    umma_ts_acc(tmem, w0 + 24, lo + 6, d_hi, idesc);
-                    umma_commit_a(empty0 + 8 * s);
                 }
                 if (ok) umma_commit(&bars->acc_full);
             }
         }
         __syncwarp();
-    } else if (warp < 10) {
+    } else if (warp < C::PACK_WARP) {
         // ------------------------------------------------ decode: thread = weight row = the tensor-memory
-        // lane this warp may access (its index modulo 4 picks the quarter); group g takes k-steps it = g mod 2
+        // lane this warp may access (its index modulo 4 picks the quarter); group g takes the k-steps whose
+        // running count is g modulo DG
         const int r = (warp & 3) * 32 + lane, g = (warp - 2) >> 2;
-        const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + ACC_COLS;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + C::W_COL0;
         bool ok = true;
         uint32_t it = 0, sbi = 0;
-        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-            for (int ks = 0; ks < ksteps; ++ks, ++it) {
-                const uint32_t ps = sbi % pstages, s = it % STAGES;
-                if ((ks & 1) == g) {
-                    // first step of this group in the super-block: its packed rows must have landed
-                    if (ok && (ks & 3) == g) ok = bar_wait(&bars->p_full[ps], (sbi / pstages) & 1);
-                    // the stage's previous use must be over before the first store to it, not before the
-                    // loads and the arithmetic: test now, and only wait (inside the decode, right before
-                    // its first tensor-memory store) if the test failed
-                    const uint32_t e_bar = s32(&bars->empty[s]), e_par = ((it / STAGES) - 1) & 1;
-                    const bool free_now = it < STAGES || bar_test_a(e_bar, e_par);
-                    if (ok) {
-                        const uint8_t* stg = p_st + ps * pstage_bytes;
-                        const uint32_t dst = lane_base + s * W_COLS;
-                        StageGate gate{e_bar, e_par, free_now, true};
-                        // rows past N arrive as zeros from the tensor copy and decode to zeros
-                        if (P.format == ALLOYB_Q4_K)
-                            decode_q4k<BF16>(stg + r * Q4_ROW, ks & 3, dst, gate);
-                        else if (P.format == ALLOYB_Q6_K)
-                            decode_q6k<BF16>(stg + r * Q6_ROW + ((static_cast<int>(sbi % nsb) * Q6K_BYTES) & 15), ks & 3, dst, gate);
-                        else
-                            decode_q8_0<BF16>(stg, ks & 3, r, dst, gate);
-                        ok = gate.ok;
-                        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        for (int w = blockIdx.x; w < n_items; w += gridDim.x) {
+            const Item im = item_of(w, tiles_n, tiles_m, nsb, P.splits);
+            for (int sub = 0; sub < n_sub; ++sub) {
+                for (int sb = im.sb0; sb < im.sb1; ++sb, ++sbi) {
+                    const uint32_t ps = sbi % pstages;
+                    bool have = false;                   // this thread waited for the super-block's rows
+#pragma unroll 1
+                    for (int k4 = 0; k4 < 4; ++k4, ++it) {
+                        if (static_cast<int>(it % DG) != g) continue;
+                        const uint32_t s = it % STAGES;
+                        if (ok && !have) ok = bar_wait(&bars->p_full[ps], (sbi / pstages) & 1);
+                        have = true;
+                        // the stage's previous use must be over before the first store to it, not before
+                        // the loads and the arithmetic: test now, and only wait (inside the decode, right
+                        // before its first tensor-memory store) if the test failed
+                        const uint32_t e_bar = s32(&bars->empty[s]), e_par = ((it / STAGES) - 1) & 1;
+                        const bool free_now = it < STAGES || bar_test_a(e_bar, e_par);
+                        if (ok) {
+                            const uint8_t* stg = p_st + ps * pstage_bytes;
+                            const uint32_t dst = lane_base + s * W_COLS;
+                            StageGate gate{e_bar, e_par, free_now, true};
+                            // rows past N arrive as zeros from the tensor copy and decode to zeros
+                            if (P.format == ALLOYB_Q4_K)
+                                decode_q4k<BF16>(stg + r * Q4_ROW, k4, dst, gate);
+                            else if (P.format == ALLOYB_Q6_K)
+                                decode_q6k<BF16>(stg + r * Q6_ROW + ((sb * Q6K_BYTES) & 15), k4, dst, gate);
+                            else
+                                decode_q8_0<BF16>(stg, k4, r, dst, gate);
+                            ok = gate.ok;
+                            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        }
+                        bar_arrive(&bars->full[s]);
                     }
-                    bar_arrive(&bars->full[s]);
-                    if ((ks & 3) == 2 + g) bar_arrive(&bars->p_empty[ps]);      // this group's last step of the super-block
+                    // every decode thread releases the super-block once, after its last step of it (a
+                    // group with no step in it -- DG = 4 always has one -- releases it at once)
+                    bar_arrive(&bars->p_empty[ps]);
                 }
-                if ((ks & 3) == 3) ++sbi;
             }
         }
     } else {
         // ------------------------------------------------ epilogue: TMEM -> registers, release, -> C
+        constexpr int HT = BM / 2;                          // tokens per thread
+        const int ew = warp - C::EPI_WARP0;
         const int quarter = warp & 3;                       // TMEM lanes this warp may read
-        const int half = (warp - 11) >> 2;                  // token columns half*128 .. +127
+        const int half = ew >> 2;                           // token columns half*HT .. +HT-1
+        const int et = threadIdx.x - C::EPI_WARP0 * 32;     // 0..255
         bool ok = true;
         uint32_t tl = 0;
-        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++tl) {
-            const int n0 = (t % tiles_n) * BN, m0 = (t / tiles_n) * BM;
+        for (int w = blockIdx.x; w < n_items; w += gridDim.x, ++tl) {
+            const Item im = item_of(w, tiles_n, tiles_m, nsb, P.splits);
+            const int n = im.n0 + quarter * 32 + lane;      // this lane's weight row = output column
+            const int tok0 = im.tile_m * BM + half * HT;
             if (ok) ok = bar_wait(&bars->acc_full, tl & 1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t acc[BM / 4];                           // 128 tokens of this lane's row, two per register
-            if (ok) {
-                const uint32_t src = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + half * (BM / 2);
+            const uint32_t src = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + half * HT;
+            if (P.splits == 1) {
+                uint32_t acc[HT / 2];                       // this lane's row, two tokens per register
+                if (ok) {
 #pragma unroll
-                for (int c = 0; c < BM / 16; ++c) {
-                    uint32_t v[8];
-                    tmem_ld8(src + c * 8, v);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    for (int c = 0; c < HT / 8; ++c) {
+                        uint32_t v[8];
+                        load_sum<C::NI, BM>(src + c * 8, v);
+                        if (P.gated) {
+                            uint32_t u[8];
+                            load_sum<C::NI, BM>(src + C::NI * BM + c * 8, u);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                        acc[c * 4 + e] = pack2<BF16>(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
+                            for (int e = 0; e < 8; ++e)
+                                v[e] = __float_as_uint(apply_act(__uint_as_float(v[e]), P.act) * __uint_as_float(u[e]));
+                        }
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            acc[c * 4 + e] = pack2<BF16>(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
+                    }
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 }
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            }
-            bar_arrive(&bars->acc_empty);                   // the accumulator is free: the next tile may start
-            if (ok) {
-                const int n = n0 + quarter * 32 + lane;     // this lane's weight row = output column
-                const int tok0 = m0 + half * (BM / 2);
-                if (n < P.N) {
+                bar_arrive(&bars->acc_empty);               // the accumulators are free: the next item may start
+                if (ok && n < P.N) {
                     uint16_t* col = static_cast<uint16_t*>(P.y) + static_cast<int64_t>(tok0) * P.ldy + n;
+                    const uint16_t* res =
+                        P.residual ? static_cast<const uint16_t*>(P.residual) + static_cast<int64_t>(tok0) * P.ldy + n : nullptr;
 #pragma unroll
-                    for (int e = 0; e < BM / 4; ++e) {
-                        if (tok0 + 2 * e < P.M) col[static_cast<int64_t>(2 * e) * P.ldy] = static_cast<uint16_t>(acc[e] & 0xffffu);
-                        if (tok0 + 2 * e + 1 < P.M) col[static_cast<int64_t>(2 * e + 1) * P.ldy] = static_cast<uint16_t>(acc[e] >> 16);
+                    for (int e = 0; e < HT; ++e) {
+                        if (tok0 + e < P.M) {
+                            uint16_t o = static_cast<uint16_t>(e & 1 ? acc[e >> 1] >> 16 : acc[e >> 1] & 0xffffu);
+                            // residual: dtype(residual + dtype(acc))
+                            if (res) o = to_16<BF16>(to_f32<BF16>(res[static_cast<int64_t>(e) * P.ldy]) + to_f32<BF16>(o));
+                            col[static_cast<int64_t>(e) * P.ldy] = o;
+                        }
                     }
                 }
+            } else {
+                // split K: add this item's partial tile to the fp32 sums, [plane][token][row]
+                const int pitch = tiles_n * BN;
+                float* sum = g_split_sum + static_cast<int64_t>(tok0) * pitch + n;
+                const int64_t plane = static_cast<int64_t>(SPLIT_MAX_BM) * pitch;
+                if (ok) {
+                    for (int sub = 0; sub < n_sub; ++sub) {
+#pragma unroll
+                        for (int c = 0; c < HT / 8; ++c) {
+                            uint32_t v[8];
+                            load_sum<C::NI, BM>(src + sub * C::NI * BM + c * 8, v);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                if (tok0 + c * 8 + e < P.M)
+                                    atomicAdd(sum + sub * plane + static_cast<int64_t>(c * 8 + e) * pitch, __uint_as_float(v[e]));
+                        }
+                    }
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                }
+                bar_arrive(&bars->acc_empty);
+                // the last item of the tile to get here finishes it
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+                if (et == 0) {
+                    const unsigned int old = atomicAdd(&g_split_count[im.tile_n], 1u);
+                    bars->last = old == static_cast<unsigned int>(P.splits - 1) ? 1u : 0u;
+                    if (bars->last) g_split_count[im.tile_n] = 0u;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+                if (bars->last && ok) {
+                    __threadfence();
+                    if (n < P.N) {
+                        uint16_t* col = static_cast<uint16_t*>(P.y) + static_cast<int64_t>(tok0) * P.ldy + n;
+                        const uint16_t* res = P.residual ? static_cast<const uint16_t*>(P.residual) +
+                                                               static_cast<int64_t>(tok0) * P.ldy + n
+                                                         : nullptr;
+                        for (int e = 0; e < HT; ++e) {
+                            if (tok0 + e >= P.M) break;
+                            float* a = sum + static_cast<int64_t>(e) * pitch;
+                            float v = __ldcg(a);
+                            __stcg(a, 0.0f);
+                            if (P.gated) {
+                                v = apply_act(v, P.act) * __ldcg(a + plane);
+                                __stcg(a + plane, 0.0f);
+                            }
+                            uint16_t o = to_16<BF16>(v);
+                            if (res) o = to_16<BF16>(to_f32<BF16>(res[static_cast<int64_t>(e) * P.ldy]) + to_f32<BF16>(o));
+                            col[static_cast<int64_t>(e) * P.ldy] = o;
+                        }
+                    }
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");     // bars->last may be rewritten
             }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::TMEM_COLS));
 }
 
 }  // namespace tc
@@ -639,21 +823,15 @@ int gemm_tc_device_error(int clear) {
     return v;
 }
 
-// C = X * deq(W)^T for one packed matrix.  NOT_TAKEN unless the shape is the prefill kind.
-int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, cudaStream_t st) {
-    using namespace tc;
-    if (dtype != ALLOYB_F16 && dtype != ALLOYB_BF16) return ALLOYB_NOT_TAKEN;
-    if (seg.format != ALLOYB_Q4_K && seg.format != ALLOYB_Q6_K && seg.format != ALLOYB_Q8_0) return ALLOYB_NOT_TAKEN;
-    if (M < 64 || K % QK_K) return ALLOYB_NOT_TAKEN;
-    if (seg.format == ALLOYB_Q8_0 && (!seg.scales || reinterpret_cast<uintptr_t>(seg.scales) % 16 || seg.row_bytes != K))
-        return ALLOYB_NOT_TAKEN;
-    if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(seg.data) % 16 || seg.row_bytes % 16)
-        return ALLOYB_NOT_TAKEN;
-    // The driver's tensor-map encoder is looked up through the runtime, so the library carries no
-    // link-time dependency on the driver and still loads (for symbol checks) on a machine without one.
-    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+namespace tc {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder is looked up through the runtime, so the library carries no link-time
+// dependency on the driver and still loads (for symbol checks) on a machine without one.
+static EncodeFn encoder() {
     static EncodeFn encode = nullptr;
     if (!encode) {
         void* fn = nullptr;
@@ -661,33 +839,111 @@ int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, cu
         const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr);
         if (e != cudaSuccess || qr != cudaDriverEntryPointSuccess || !fn) {
             set_cuda_error(e != cudaSuccess ? e : cudaErrorNotSupported);
-            return ALLOYB_E_CUDA;
+            return nullptr;
         }
         encode = reinterpret_cast<EncodeFn>(fn);
     }
-    // 2-D map over a row-major matrix: `inner` elements per row, `rows` rows `pitch` bytes apart.
-    auto map2d = [&](CUtensorMap* m, CUtensorMapDataType type, const void* base, uint64_t inner, uint64_t rows,
-                     uint64_t pitch, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swizzle) {
-        const cuuint64_t gdim[2] = {inner, rows};
-        const cuuint64_t gstr[1] = {pitch};
-        const cuuint32_t box[2] = {box_inner, box_rows};
-        const cuuint32_t estr[2] = {1, 1};
-        return encode(m, type, 2, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
-                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-    };
-    CUtensorMap map, wmap, smap;
-    bool ok = map2d(&map, dtype == ALLOYB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x,
-                    K, M, static_cast<uint64_t>(K) * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+    return encode;
+}
+
+// 2-D map over a row-major matrix: `inner` elements per row, `rows` rows `pitch` bytes apart.
+static bool map2d(EncodeFn encode, CUtensorMap* m, CUtensorMapDataType type, const void* base, uint64_t inner,
+                  uint64_t rows, uint64_t pitch, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swizzle) {
+    const cuuint64_t gdim[2] = {inner, rows};
+    const cuuint64_t gstr[1] = {pitch};
+    const cuuint32_t box[2] = {box_inner, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return encode(m, type, 2, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int sm_count_of_device(int& dev) {
+    static int sms[64] = {};
+    dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!sms[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 0;
+        sms[dev] = n;
+    }
+    return sms[dev];
+}
+
+template <bool BF16, int BM, int DG>
+static int launch(const Maps& maps, const Params& P, int grid, int dev, cudaStream_t st) {
+    static bool configured[64] = {};
+    using C = Cfg<BM, DG>;
+    if (!configured[dev]) {
+        const cudaError_t e =
+            cudaFuncSetAttribute(gemm_tc_kernel<BF16, BM, DG>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) { set_cuda_error(e); return ALLOYB_E_CUDA; }
+        configured[dev] = true;
+    }
+    gemm_tc_kernel<BF16, BM, DG><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(maps, P);
+    return check_launch();
+}
+
+template <bool BF16>
+static int launch_bm(int BM, const Maps& maps, const Params& P, int grid, int dev, cudaStream_t st) {
+    switch (BM) {
+        case 32: return launch<BF16, 32, 4>(maps, P, grid, dev, st);
+        case 64: return launch<BF16, 64, 4>(maps, P, grid, dev, st);
+        case 128: return launch<BF16, 128, 4>(maps, P, grid, dev, st);
+        default: return launch<BF16, 256, 2>(maps, P, grid, dev, st);
+    }
+}
+
+}  // namespace tc
+
+// C = X * deq(W)^T (+ residual) for one packed matrix, or act(X G^T) * (X U^T) for a gate/up pair
+// (`up` non-null; both matrices in seg's format and shape, M <= 128).  NOT_TAKEN unless the shape and
+// the alignment are the kind the kernel is built for.
+int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, const void* residual, const void* up,
+                const void* up_scales, int act, cudaStream_t st) {
+    using namespace tc;
+    if (dtype != ALLOYB_F16 && dtype != ALLOYB_BF16) return ALLOYB_NOT_TAKEN;
+    if (seg.format != ALLOYB_Q4_K && seg.format != ALLOYB_Q6_K && seg.format != ALLOYB_Q8_0) return ALLOYB_NOT_TAKEN;
+    if (M < GEMM_TC_MIN_M || K % QK_K) return ALLOYB_NOT_TAKEN;
+    if (up && M > SPLIT_MAX_BM) return ALLOYB_NOT_TAKEN;
+    const bool q8 = seg.format == ALLOYB_Q8_0;
+    if (q8 && (!seg.scales || reinterpret_cast<uintptr_t>(seg.scales) % 16 || seg.row_bytes != K)) return ALLOYB_NOT_TAKEN;
+    if (q8 && up && (!up_scales || reinterpret_cast<uintptr_t>(up_scales) % 16)) return ALLOYB_NOT_TAKEN;
+    if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(seg.data) % 16 || seg.row_bytes % 16 ||
+        reinterpret_cast<uintptr_t>(up) % 16)
+        return ALLOYB_NOT_TAKEN;
+
+    const EncodeFn encode = encoder();
+    if (!encode) return ALLOYB_E_CUDA;
+    int dev = 0;
+    const int sms = sm_count_of_device(dev);
+    if (!sms) { set_cuda_error(cudaErrorInvalidValue); return ALLOYB_E_CUDA; }
+
+    const int BM = M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
+    const int tiles_n = (seg.N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM, nsb = K / QK_K;
+    // too few row tiles for the SMs and one token tile: split K (the sums live in a fixed scratch)
+    int splits = 1;
+    if (tiles_m == 1 && BM <= SPLIT_MAX_BM && tiles_n <= SPLIT_MAX_TILES && 2 * tiles_n <= sms) {
+        splits = sms / tiles_n;
+        if (splits > nsb) splits = nsb;
+    }
+
+    Maps maps;
+    bool ok = map2d(encode, &maps.x, dtype == ALLOYB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                    x, K, M, static_cast<uint64_t>(K) * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
     // the packed rows as bytes: one box = one super-block of 128 rows
-    if (seg.format == ALLOYB_Q8_0) {
-        ok = ok && map2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, seg.data, K, seg.N, seg.row_bytes, 128, BN,
-                         CU_TENSOR_MAP_SWIZZLE_128B);
-        ok = ok && map2d(&smap, CU_TENSOR_MAP_DATA_TYPE_UINT8, seg.scales, static_cast<uint64_t>(K / Q8_BLOCK) * 2, seg.N,
-                         static_cast<uint64_t>(K / Q8_BLOCK) * 2, 16, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
-    } else {
-        ok = ok && map2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, seg.data, seg.row_bytes, seg.N, seg.row_bytes,
-                         seg.format == ALLOYB_Q4_K ? Q4_ROW : Q6_ROW, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
-        smap = wmap;
+    const void* mats[2] = {seg.data, up ? up : seg.data};
+    const void* scs[2] = {seg.scales, up ? up_scales : seg.scales};
+    for (int i = 0; i < 2 && ok; ++i) {
+        if (q8) {
+            ok = map2d(encode, &maps.w[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, mats[i], K, seg.N, seg.row_bytes, 128,
+                       PACK_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_128B) &&
+                 map2d(encode, &maps.s[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, scs[i], static_cast<uint64_t>(K / Q8_BLOCK) * 2,
+                       seg.N, static_cast<uint64_t>(K / Q8_BLOCK) * 2, 16, PACK_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+        } else {
+            ok = map2d(encode, &maps.w[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, mats[i], seg.row_bytes, seg.N, seg.row_bytes,
+                       seg.format == ALLOYB_Q4_K ? Q4_ROW : Q6_ROW, PACK_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+            maps.s[i] = maps.w[i];
+        }
     }
     if (!ok) {
         set_cuda_error(cudaErrorInvalidValue);
@@ -696,30 +952,19 @@ int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, cu
     Params P;
     P.format = seg.format;
     P.y = seg.y;
+    P.residual = residual;
     P.ldy = seg.ldy;
     P.M = M;
     P.N = seg.N;
     P.K = K;
-    P.is_bf16 = dtype == ALLOYB_BF16;
+    P.splits = splits;
+    P.gated = up ? 1 : 0;
+    P.act = act;
 
-    static int sm_count[64] = {};             // per device ordinal; 0 = kernel not configured yet
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
-    if (!sm_count[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        int sms = 0;
-        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (e != cudaSuccess || sms <= 0) { set_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidValue); return ALLOYB_E_CUDA; }
-        sm_count[dev] = sms;
-    }
-    // persistent: one CTA per SM walks the tiles (weight-row tile fastest, so neighbours share a token tile)
-    const int n_tiles = ((seg.N + BN - 1) / BN) * ((M + BM - 1) / BM);
-    const dim3 grid(n_tiles < sm_count[dev] ? n_tiles : sm_count[dev]);
-    if (dtype == ALLOYB_BF16) gemm_tc_kernel<true><<<grid, THREADS, SMEM_BYTES, st>>>(map, wmap, smap, P);
-    else gemm_tc_kernel<false><<<grid, THREADS, SMEM_BYTES, st>>>(map, wmap, smap, P);
-    return check_launch();
+    // persistent: one CTA per SM walks the items (weight-row tile fastest, so neighbours share a token tile)
+    const int n_items = tiles_n * tiles_m * splits;
+    const int grid = n_items < sms ? n_items : sms;
+    return dtype == ALLOYB_BF16 ? launch_bm<true>(BM, maps, P, grid, dev, st) : launch_bm<false>(BM, maps, P, grid, dev, st);
 }
 
 }  // namespace alloyb

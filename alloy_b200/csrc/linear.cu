@@ -156,27 +156,10 @@ static int launch_rows(const void* x, int M, int K, const RowSegs& segs, const v
 
 using namespace alloyb;
 
-extern "C" int alloyb_linear(const void* x, int M, int K, int dtype, const alloyb_weight* w, int n_w,
-                             const void* residual, void* stream) {
-    if (!x) return ALLOYB_E_NULL;
-    if (M < 0 || K <= 0) return ALLOYB_E_SHAPE;
-    RowSegs segs;
-    int rc = validate_segs(w, n_w, K, segs);
-    if (rc != ALLOYB_OK) return rc;
-    if (residual && n_w != 1) return ALLOYB_E_SHAPE;
-    if (M == 0) return ALLOYB_OK;
-    cudaStream_t st = as_stream(stream);
-
-    if (M >= 64 && !residual) {
-        // prefill-sized M: one tcgen05 GEMM per matrix
-        bool all = true;
-        for (int i = 0; i < segs.n_seg && all; ++i) {
-            rc = try_gemm_tc(x, M, K, dtype, segs.seg[i], st);
-            if (rc == ALLOYB_NOT_TAKEN) all = false;
-            else if (rc != ALLOYB_OK) return rc;
-        }
-        if (all) return ALLOYB_OK;
-    }
+// The GEMV family and, last, the exact-weight row kernels: any M, any alignment.
+static int linear_few_tokens(const void* x, int M, int K, int dtype, const RowSegs& segs, const void* residual,
+                             cudaStream_t st) {
+    int rc;
     rc = try_linear_fast(x, M, K, dtype, segs.seg, segs.n_seg, residual, st);
     if (rc != ALLOYB_NOT_TAKEN) return rc;
     {
@@ -201,6 +184,36 @@ extern "C" int alloyb_linear(const void* x, int M, int K, int dtype, const alloy
         case ALLOYB_F32: return launch_rows<float>(x, M, K, segs, residual, st);
         default: return ALLOYB_E_DTYPE;
     }
+}
+
+extern "C" int alloyb_linear(const void* x, int M, int K, int dtype, const alloyb_weight* w, int n_w,
+                             const void* residual, void* stream) {
+    if (!x) return ALLOYB_E_NULL;
+    if (M < 0 || K <= 0) return ALLOYB_E_SHAPE;
+    RowSegs segs;
+    int rc = validate_segs(w, n_w, K, segs);
+    if (rc != ALLOYB_OK) return rc;
+    if (residual && n_w != 1) return ALLOYB_E_SHAPE;
+    if (M == 0) return ALLOYB_OK;
+    cudaStream_t st = as_stream(stream);
+
+    if (M >= GEMM_TC_MIN_M) {
+        // more than a handful of tokens: one tcgen05 GEMM per matrix; a matrix it does not take (type,
+        // alignment) goes through the kernels below on its own
+        for (int i = 0; i < segs.n_seg; ++i) {
+            rc = try_gemm_tc(x, M, K, dtype, segs.seg[i], residual, nullptr, nullptr, 0, st);
+            if (rc == ALLOYB_NOT_TAKEN) {
+                RowSegs one;
+                one.n_seg = 1;
+                one.seg[0] = segs.seg[i];
+                one.total_rows = segs.seg[i].N;
+                rc = linear_few_tokens(x, M, K, dtype, one, residual, st);
+            }
+            if (rc != ALLOYB_OK) return rc;
+        }
+        return ALLOYB_OK;
+    }
+    return linear_few_tokens(x, M, K, dtype, segs, residual, st);
 }
 
 static int single(const void* x, int fmt, const void* data, const void* scales, void* y, int M,
@@ -250,7 +263,13 @@ extern "C" int alloyb_gated_linear(const void* x, const void* gate, const void* 
     if (M == 0) return ALLOYB_OK;
     cudaStream_t st = as_stream(stream);
 
-    int rc = try_gated_fast(x, gate, gate_scales, up, up_scales, y, M, N, K, format, act, dtype, st);
+    int rc = ALLOYB_NOT_TAKEN;
+    if (M >= GEMM_TC_MIN_M) {
+        const WeightSeg g = {format, N, gate, gate_scales, row_bytes, y, N};
+        rc = try_gemm_tc(x, M, K, dtype, g, nullptr, up, up_scales, act, st);
+        if (rc != ALLOYB_NOT_TAKEN) return rc;
+    }
+    rc = try_gated_fast(x, gate, gate_scales, up, up_scales, y, M, N, K, format, act, dtype, st);
     if (rc != ALLOYB_NOT_TAKEN) return rc;
     if (format == ALLOYB_Q8_0) {
         rc = try_q8_gemv(x, M, K, dtype, gate, gate_scales, up, up_scales, y, N, N, nullptr, true, act, st);

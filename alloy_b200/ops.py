@@ -325,9 +325,10 @@ def _gated(x, gate, gs, up, us, fmt, act):
     y = torch.empty((x.shape[0], gate.shape[0]), dtype=x.dtype, device=x.device)
     if x.shape[0] == 0:
         return y
-    if x.shape[0] >= 64 and fmt == _lib.Q4_K and act == _lib.ACT_SILU and x.dtype != torch.float32:
+    if x.shape[0] > 128 and fmt == _lib.Q4_K and act == _lib.ACT_SILU and x.dtype != torch.float32:
         # prefill: two single GEMMs + silu_mul, the split the reference measured faster than its
-        # fused dual-accumulator kernel (packages/alloy-torch/src/alloy_torch/ops/linalg.py:774-780)
+        # fused dual-accumulator kernel (packages/alloy-torch/src/alloy_torch/ops/linalg.py:774-780);
+        # up to 128 tokens the tensor-core GEMM keeps both accumulators in tensor memory
         g, u = _linear(x, fmt, [gate], None)[0], _linear(x, fmt, [up], None)[0]
         return silu_mul(g, u)
     L = _lib.load()

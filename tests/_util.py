@@ -32,3 +32,8 @@ def to_np(t: torch.Tensor) -> np.ndarray:
 
 def same_bits_f32(a: np.ndarray, b: np.ndarray) -> bool:
     return a.dtype == b.dtype == np.float32 and np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+# Token count from which linears take the tensor-core GEMM (GEMM_TC_MIN_M in csrc/linear.cuh), whose
+# definition rounds the decoded weight to the activation type once, as the reference's tiled GEMM does.
+GEMM_MIN_TOKENS = 28

@@ -7,7 +7,7 @@ import torch
 from alloy_b200 import llama
 from oracle import blocks as O
 from oracle import decode_step as OD
-from tests._util import rel_errors, to_np
+from tests._util import GEMM_MIN_TOKENS, rel_errors, to_np
 
 pytestmark = pytest.mark.gpu
 
@@ -15,15 +15,23 @@ TINY = llama.LlamaShape(layers=2, hidden=512, ffn=1024, heads=8, kv_heads=2, hea
                         rope_theta=10000.0, eps=1e-5)
 
 
-def _oracle_inputs(dec):
+def _r16(w, fmt, gemm):
+    """GEMM_MIN_TOKENS and more take the tensor-core GEMM, whose definition rounds the decoded weight to
+    fp16 once (Q6_K rows whose pitch is not a multiple of 16 bytes stay on the exact-weight kernels)."""
+    k = w.shape[1]
+    if gemm and (fmt == "q4_k" or (k // 256 * 210) % 16 == 0):
+        return w.astype(np.float16).astype(np.float32)
+    return w
+
+
+def _oracle_inputs(dec, gemm=False):
+    q4 = lambda t: _r16(O.dequant_q4_k(t.cpu().numpy()), "q4_k", gemm)
+    q6 = lambda t: _r16(O.dequant_q6_k(t.cpu().numpy()), "q6_k", gemm)
     layers = []
     for lw in dec.layers:
         layers.append({
-            "wq": O.dequant_q4_k(lw.wq.cpu().numpy()), "wk": O.dequant_q4_k(lw.wk.cpu().numpy()),
-            "wv": O.dequant_q6_k(lw.wv.cpu().numpy()), "wo": O.dequant_q4_k(lw.wo.cpu().numpy()),
-            "wg": O.dequant_q4_k(lw.wg.cpu().numpy()), "wu": O.dequant_q4_k(lw.wu.cpu().numpy()),
-            "wd": O.dequant_q6_k(lw.wd.cpu().numpy()),
-            "norm_in": lw.norm_in.cpu().numpy(), "norm_post": lw.norm_post.cpu().numpy()})
+            "wq": q4(lw.wq), "wk": q4(lw.wk), "wv": q6(lw.wv), "wo": q4(lw.wo), "wg": q4(lw.wg), "wu": q4(lw.wu),
+            "wd": q6(lw.wd), "norm_in": lw.norm_in.cpu().numpy(), "norm_post": lw.norm_post.cpu().numpy()})
     return layers
 
 
@@ -104,8 +112,9 @@ def test_decode_step_big_batch_head_dim_128(batch, kv_kind):
     else:
         kc, vc = _paged_caches(dec, ctx)
     ref_logits, _, _ = OD.decode_step(
-        ids, ctx - 1, O.dequant_q4_k(dec.embed.cpu().numpy()), _oracle_inputs(dec), dec.norm_final.cpu().numpy(),
-        O.dequant_q6_k(dec.head.cpu().numpy()), dec.inv_freq.cpu().numpy(), kc, vc, MID.heads, MID.kv_heads,
+        ids, ctx - 1, O.dequant_q4_k(dec.embed.cpu().numpy()), _oracle_inputs(dec, gemm=batch >= GEMM_MIN_TOKENS),
+        dec.norm_final.cpu().numpy(), _r16(O.dequant_q6_k(dec.head.cpu().numpy()), "q6_k", batch >= GEMM_MIN_TOKENS),
+        dec.inv_freq.cpu().numpy(), kc, vc, MID.heads, MID.kv_heads,
         MID.head_dim, MID.eps, kv_q8=(kv_kind == "q8_paged"))
     assert np.isfinite(ref_logits.astype(np.float32)).all()
     dec.step()

@@ -1,4 +1,4 @@
-"""GPU parity of the prefill dequant-GEMM (tcgen05 path, M >= 64) against the oracle.
+"""GPU parity of the dequant-GEMM (tcgen05 path, 28 tokens and more) against the oracle.
 
 The GEMM's definition includes ONE rounding of the exactly-decoded fp32 weight to the activation
 type (bf16 / fp16) before the tensor-core product, so the oracle here is
@@ -75,14 +75,19 @@ def test_gemm_rows_agree_with_gemv_path():
     assert np.abs(a - b).max() <= 1e-2 * np.sqrt((b * b).mean())
 
 
-def test_gated_prefill_two_gemms():
+@pytest.mark.parametrize("m", [128, 200])
+def test_gated_prefill(m):
+    """Up to 128 tokens gate and up stay fp32 accumulators of one launch; beyond, two GEMMs round each to
+    the activation type before the activation kernel multiplies them."""
     rng = np.random.default_rng(78)
-    m, n, k = 128, 256, 512
+    n, k = 256, 512
     g, u = synth.q4k_blocks(rng, n, k), synth.q4k_blocks(rng, n, k)
     x = torch.from_numpy(synth.activations(rng, m, k, np.float32)).to(torch.bfloat16).to(DEV)
     y = torch.ops.alloy.gguf_q4_k_silu(x, _dev(g), _dev(u))
-    gate = torch.from_numpy(_ref(x, O.dequant_q4_k(g), torch.bfloat16)).to(torch.bfloat16).double().numpy()
-    up = torch.from_numpy(_ref(x, O.dequant_q4_k(u), torch.bfloat16)).to(torch.bfloat16).double().numpy()
+    gate, up = _ref(x, O.dequant_q4_k(g), torch.bfloat16), _ref(x, O.dequant_q4_k(u), torch.bfloat16)
+    if m > 128:
+        gate = torch.from_numpy(gate).to(torch.bfloat16).double().numpy()
+        up = torch.from_numpy(up).to(torch.bfloat16).double().numpy()
     assert_close(to_np(y), O.silu(gate) * up, torch.bfloat16, "prefill gate/up")
 
 
@@ -101,4 +106,79 @@ def test_gemm_full_size_sampled_columns(fmt, n, k):
     w = O.dequant_q4_k(sub) if fmt == "q4_k" else O.dequant_q6_k(sub)
     assert_close(to_np(y[:, torch.from_numpy(cols).to(DEV)]), _ref(x, w, torch.bfloat16), torch.bfloat16,
                  f"full-size {fmt}")
+    assert _lib.load().alloyb_device_error(0) == 0
+
+
+def _weights(fmt, rng, n, k):
+    if fmt == "q8_0":
+        codes, scales = O.split_q8_0(synth.q8_0_wire(rng, n, k))
+        return (_dev(codes), _dev(scales)), O.dequant_q8_0(codes, scales)
+    blk = synth.q4k_blocks(rng, n, k) if fmt == "q4_k" else synth.q6k_blocks(rng, n, k)
+    return (_dev(blk), None), (O.dequant_q4_k(blk) if fmt == "q4_k" else O.dequant_q6_k(blk))
+
+
+# Batched-decode and chunk sizes: one token tile of 32 / 64 / 128 columns, ragged token and row
+# counts, matrices with fewer row tiles than SMs (K split over several CTAs whose partial tiles
+# meet in the fp32 scratch), with and without a residual.  Every case runs twice: the second call
+# finds the scratch and the tile counters as the first one left them.
+@pytest.mark.parametrize("fmt,m,n,k,dt", [
+    ("q4_k", 28, 4096, 4096, "f16"), ("q4_k", 31, 1024, 4096, "bf16"), ("q4_k", 32, 4096, 14336, "f16"),
+    ("q4_k", 64, 14336, 4096, "f16"), ("q4_k", 128, 200, 1024, "bf16"), ("q4_k", 129, 200, 1024, "bf16"),
+    ("q6_k", 50, 1024, 4096, "f16"), ("q6_k", 100, 4096, 14336, "bf16"), ("q6_k", 29, 130, 2048, "f16"),
+    ("q8_0", 33, 520, 2048, "f16"), ("q8_0", 30, 4096, 4096, "bf16")])
+def test_gemm_few_tokens_split_k_and_residual(fmt, m, n, k, dt):
+    rng = np.random.default_rng([m, n, k, len(fmt), 5])
+    tdt = DT[dt]
+    (wd, sd), w = _weights(fmt, rng, n, k)
+    x = torch.from_numpy(synth.activations(rng, m, k, np.float32)).to(tdt).to(DEV)
+    res = torch.from_numpy(synth.activations(rng, m, n, np.float32)).to(tdt).to(DEV)
+    ref = _ref(x, w, tdt)
+    name = {"q4_k": "q4_k", "q6_k": "q6_k", "q8_0": "q8_0"}[fmt]
+    for rep in range(2):
+        y = (torch.ops.alloy.gguf_q8_0_mm(x, wd, sd) if fmt == "q8_0" else
+             (torch.ops.alloy.gguf_q4_k_mm if fmt == "q4_k" else torch.ops.alloy.gguf_q6_k_mm)(x, wd))
+        assert y.shape == (m, n) and y.dtype == tdt
+        assert_close(to_np(y), ref, tdt, f"gemm {fmt} {m}x{n}x{k} {dt} call {rep}")
+        yr = torch.ops.alloy.linear_residual(x, wd, sd, res, name)
+        # residual: type(residual + type(acc)).  Two roundings, each relative to its own operand: where
+        # residual and product cancel the error is bounded by their magnitudes, not by the sum's
+        acc = torch.from_numpy(ref).to(tdt).double().numpy()
+        r64 = res.double().cpu().numpy()
+        err = np.abs(to_np(yr).astype(np.float64) - (r64 + acc))
+        ulp = 2.0 ** (-8 if tdt == torch.bfloat16 else -11)
+        bound = ulp * (2.0 * np.abs(acc) + np.abs(r64 + acc)) + 1e-3 * np.sqrt((ref ** 2).mean())
+        assert (err <= bound).all(), f"gemm+residual {fmt} {m}x{n}x{k} {dt} call {rep}: worst {np.max(err / bound):.2f} x bound"
+        assert err.mean() <= ulp * (np.abs(acc) + np.abs(r64 + acc)).mean()
+    assert _lib.load().alloyb_device_error(0) == 0
+
+
+# Gate/up pairs up to 128 tokens keep two accumulators in tensor memory; few row tiles split K over
+# two planes of the scratch.
+@pytest.mark.parametrize("m,n,k,dt", [(32, 14336, 4096, "f16"), (64, 1024, 4096, "bf16"), (128, 3584, 2048, "f16"),
+                                      (29, 200, 1024, "f16")])
+@pytest.mark.parametrize("act", ["silu", "gelu"])
+def test_gemm_gated_few_tokens(m, n, k, dt, act):
+    rng = np.random.default_rng([m, n, k, 7])
+    tdt = DT[dt]
+    g, u = synth.q4k_blocks(rng, n, k), synth.q4k_blocks(rng, n, k)
+    x = torch.from_numpy(synth.activations(rng, m, k, np.float32)).to(tdt).to(DEV)
+    op = torch.ops.alloy.gguf_q4_k_silu if act == "silu" else torch.ops.alloy.gguf_q4_k_gelu
+    gate, up = _ref(x, O.dequant_q4_k(g), tdt), _ref(x, O.dequant_q4_k(u), tdt)
+    ref = (O.silu(gate) if act == "silu" else O.gelu_tanh(gate)) * up
+    gd, ud = _dev(g), _dev(u)
+    for rep in range(2):
+        y = op(x, gd, ud)
+        assert y.shape == (m, n) and y.dtype == tdt
+        assert_close(to_np(y), ref, tdt, f"gated gemm {act} {m}x{n}x{k} {dt} call {rep}")
+    assert _lib.load().alloyb_device_error(0) == 0
+
+
+def test_gemm_gated_q8_few_tokens():
+    rng = np.random.default_rng(43)
+    m, n, k = 40, 640, 2048
+    (gc, gs), (uc, us) = (O.split_q8_0(synth.q8_0_wire(rng, n, k)) for _ in range(2))
+    x = torch.from_numpy(synth.activations(rng, m, k, np.float32)).half().to(DEV)
+    y = torch.ops.alloy.gguf_q8_0_silu(x, _dev(gc), _dev(gs), _dev(uc), _dev(us))
+    ref = O.silu(_ref(x, O.dequant_q8_0(gc, gs), torch.float16)) * _ref(x, O.dequant_q8_0(uc, us), torch.float16)
+    assert_close(to_np(y), ref, torch.float16, "q8 gated gemm")
     assert _lib.load().alloyb_device_error(0) == 0

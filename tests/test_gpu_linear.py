@@ -7,7 +7,7 @@ import torch
 
 from alloy_b200 import ops, quant, synth
 from oracle import blocks as O
-from tests._util import assert_close, same_bits_f32, to_np
+from tests._util import GEMM_MIN_TOKENS, assert_close, same_bits_f32, to_np
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -101,9 +101,9 @@ def test_mm_matches_oracle(fmt, m, n, k, dt):
     x = torch.from_numpy(synth.activations(rng, m, k, np.float32)).to(tdt)
     y = _MM[fmt](x.to(DEV), w_dev)
     assert y.shape == (m, n) and y.dtype == tdt
-    if m >= 64 and fmt in ("q4_k", "q8_0"):
-        # 64 tokens and more take the tensor-core GEMM, whose definition rounds the decoded weight
-        # to the activation type once (Q6_K rows of this K are not 16-byte aligned: they stay on the
+    if m >= GEMM_MIN_TOKENS and dt != "f32" and (fmt != "q6_k" or (k // 256 * 210) % 16 == 0):
+        # GEMM_MIN_TOKENS and more take the tensor-core GEMM, whose definition rounds the decoded weight
+        # to the activation type once (Q6_K rows whose pitch is not a multiple of 16 bytes stay on the
         # exact-weight row kernels)
         w = torch.from_numpy(w).to(tdt).float().numpy()
     ref = O.mm_ref_f64(x.float().numpy(), w)
@@ -309,8 +309,13 @@ def test_q4k_gated(m, n, k, act):
     x = synth.activations(rng, m, k)
     op = torch.ops.alloy.gguf_q4_k_silu if act == "silu" else torch.ops.alloy.gguf_q4_k_gelu
     y = op(_dev(x), _dev(g), _dev(u))
-    gate = O.mm_ref_f64(x, O.dequant_q4_k(g))
-    up = O.mm_ref_f64(x, O.dequant_q4_k(u))
+    wg, wu = O.dequant_q4_k(g), O.dequant_q4_k(u)
+    if m >= GEMM_MIN_TOKENS:
+        # that many tokens take the tensor-core GEMM, which rounds the decoded weight to the
+        # activation type once (as the reference's tiled GEMM does from five tokens up)
+        wg, wu = (w.astype(np.float16).astype(np.float32) for w in (wg, wu))
+    gate = O.mm_ref_f64(x, wg)
+    up = O.mm_ref_f64(x, wu)
     ref = (O.silu(gate) if act == "silu" else O.gelu_tanh(gate)) * up
     assert_close(to_np(y), ref, torch.float16, f"gated {act} m={m}")
 
