@@ -83,10 +83,10 @@ struct Cfg {
     static constexpr int DEC_WARPS = 4 * DG;
     static constexpr int PACK_WARP = 2 + DEC_WARPS;             // warp 0 token copies, warp 1 MMA, then decode
     static constexpr int EPI_WARP0 = PACK_WARP + 1;
-    // Issuing one tcgen05.mma costs its thread about as long as a 128-token MMA runs, so with a narrower
-    // token tile the issuing thread, not the tensor pipe, would set the pace: NI threads (warp 1 and NI - 1
-    // warps behind the epilogue's) then issue a quarter or a half of every step's MMAs each, into an
-    // accumulator of their own, and the epilogue adds the accumulators up.
+    // Under a narrow token tile an MMA is short and the issuing thread's own instruction stream (about a
+    // hundred cycles per tcgen05.mma) would pace the steps: NI threads (warp 1 and NI - 1 warps behind the
+    // epilogue's) then issue a quarter or a half of every step's MMAs each, into an accumulator of their
+    // own, and the epilogue adds the accumulators up.  (Worth 7 %: the decode warps bound these shapes.)
     static constexpr int NI = BM <= 32 ? 4 : (BM <= 64 ? 2 : 1);
     static constexpr int MMA_WARP1 = EPI_WARP0 + EPI_THREADS / 32;      // issuers 1 .. NI-1
     static constexpr int THREADS = (MMA_WARP1 + NI - 1) * 32;
