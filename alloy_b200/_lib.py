@@ -108,6 +108,8 @@ SIGNATURES = {
     "alloyb_attn_workspace_status": (_i, [_p, C.POINTER(C.c_int32), _p]),
     "alloyb_attn_decode": (_i, [_i, _p, _i64, _i64, _i, _p, _p, _p, _p, _p, _p, _i64, _i64, _p, _i,
                                 _p, _i, _i, _i, _i, _i, _i64, _f, _i, _p, _sz, _p]),
+    "alloyb_attn_decode_rope": (_i, [_i, _p, _i64, _i64, _p, _p, _p, _p, _p, _p, _i64, _i64, _p, _i, _p,
+                                     _p, _i, _i, _i, _i, _i, _i64, _f, _p, _sz, _p]),
     "alloyb_attn_decode_static": (_i, [_i, _p, _i64, _i64, _i, _p, _p, _p, _p, _p, _p, _i64, _i64, _p, _i,
                                        _p, _i, _i, _i, _i, _i, _i64, _f, _i, _p]),
     "alloyb_attn_static_status": (_i, [C.POINTER(C.c_int32), _p]),

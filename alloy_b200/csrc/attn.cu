@@ -390,16 +390,12 @@ static int attn_decode_validate(int layout, const void* q, int q_dtype, const vo
     return ALLOYB_OK;
 }
 
-extern "C" int alloyb_attn_decode(int layout, const void* q, int64_t q_batch_stride,
-                                  int64_t q_head_stride, int q_dtype, void* k0, void* k1, void* v0,
-                                  void* v1, const void* new_k, const void* new_v,
-                                  int64_t new_batch_stride, int64_t new_head_stride,
-                                  const int32_t* pos, int pos_count, void* out, int B, int H, int KV_H,
-                                  int D, int S_max, int64_t num_pages, float scale, int write_kv,
-                                  void* workspace, size_t workspace_bytes, void* stream) {
-    const int vrc = attn_decode_validate(layout, q, q_dtype, k0, k1, v0, v1, new_k, new_v, pos, pos_count, out, B, H,
-                                         KV_H, D, S_max, num_pages, write_kv, workspace, workspace_bytes);
-    if (vrc != ALLOYB_OK) return vrc;
+// Shared by the decode entries: workspace carve-up, split count, optional append, launch.
+static int attn_decode_run(int layout, const void* q, int64_t q_batch_stride, int64_t q_head_stride, int q_dtype,
+                           void* k0, void* k1, void* v0, void* v1, const void* new_k, const void* new_v,
+                           int64_t new_batch_stride, int64_t new_head_stride, const int32_t* pos, int pos_count,
+                           void* out, int B, int H, int KV_H, int D, int S_max, int64_t num_pages, float scale,
+                           int write_kv, void* workspace, void* stream, const AttnFuse* fuse) {
     cudaStream_t st = as_stream(stream);
 
     AttnParams P;
@@ -447,12 +443,61 @@ extern "C" int alloyb_attn_decode(int layout, const void* q, int64_t q_batch_str
     const int G = H / KV_H;
     if (D == 128 && G <= 8)
         return launch_attn_mma(layout, q, q_batch_stride, q_head_stride, q_dtype, P.kv, pos, pos_count, out, B, H,
-                               KV_H, P.scale_log2, P.splits, P.part_o, P.part_lse, P.counters, P.status, st);
+                               KV_H, P.scale_log2, P.splits, P.part_o, P.part_lse, P.counters, P.status, st, fuse);
+    if (fuse) return ALLOYB_NOT_TAKEN;
     switch (layout) {
         case ALLOYB_KV_F16: return launch_attn_d<ALLOYB_KV_F16>(P, D, G, st);
         case ALLOYB_KV_Q8_SPLIT: return launch_attn_d<ALLOYB_KV_Q8_SPLIT>(P, D, G, st);
         default: return launch_attn_d<ALLOYB_KV_Q8_PAGED>(P, D, G, st);
     }
+}
+
+
+extern "C" int alloyb_attn_decode(int layout, const void* q, int64_t q_batch_stride,
+                                  int64_t q_head_stride, int q_dtype, void* k0, void* k1, void* v0,
+                                  void* v1, const void* new_k, const void* new_v,
+                                  int64_t new_batch_stride, int64_t new_head_stride,
+                                  const int32_t* pos, int pos_count, void* out, int B, int H, int KV_H,
+                                  int D, int S_max, int64_t num_pages, float scale, int write_kv,
+                                  void* workspace, size_t workspace_bytes, void* stream) {
+    const int vrc = attn_decode_validate(layout, q, q_dtype, k0, k1, v0, v1, new_k, new_v, pos, pos_count, out, B, H,
+                                         KV_H, D, S_max, num_pages, write_kv, workspace, workspace_bytes);
+    if (vrc != ALLOYB_OK) return vrc;
+    return attn_decode_run(layout, q, q_batch_stride, q_head_stride, q_dtype, k0, k1, v0, v1, new_k, new_v,
+                           new_batch_stride, new_head_stride, pos, pos_count, out, B, H, KV_H, D, S_max, num_pages,
+                           scale, write_kv, workspace, stream, nullptr);
+}
+
+// The decode token's whole attention step in one launch: RoPE (rotate-half) of q and of the new K row, the
+// append of the new K / V rows to the cache (any layout; the q8 layouts quantise them) and the attention
+// itself.  Same results, bit for bit, as alloyb_rope_kv_append followed by alloyb_attn_decode with
+// write_kv = 0, except that q is left unrotated in memory.  Covers fp16 q, head_dim 128, up to eight
+// query heads per KV head, 16-byte-aligned q rows; anything else returns ALLOYB_NOT_TAKEN (1) and the
+// caller makes the two calls.  No counterpart in the reference, which rotates in the model code and
+// fuses only the cache write (metal/std/kv_quant.py:212-246).
+extern "C" int alloyb_attn_decode_rope(int layout, const void* q, int64_t q_batch_stride, int64_t q_head_stride,
+                                       void* k0, void* k1, void* v0, void* v1, const void* new_k, const void* new_v,
+                                       int64_t new_batch_stride, int64_t new_head_stride, const int32_t* pos,
+                                       int pos_count, const float* inv_freq, void* out, int B, int H, int KV_H,
+                                       int D, int S_max, int64_t num_pages, float scale, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
+    const int vrc = attn_decode_validate(layout, q, ALLOYB_F16, k0, k1, v0, v1, new_k, new_v, pos, pos_count, out, B,
+                                         H, KV_H, D, S_max, num_pages, 1, workspace, workspace_bytes);
+    if (vrc != ALLOYB_OK) return vrc;
+    if (!inv_freq) return ALLOYB_E_NULL;
+    if (D != 128 || H / KV_H > 8) return ALLOYB_NOT_TAKEN;
+    if ((reinterpret_cast<uintptr_t>(q) | static_cast<uintptr_t>(q_batch_stride * 2) |
+         static_cast<uintptr_t>(q_head_stride * 2)) & 15)
+        return ALLOYB_NOT_TAKEN;
+    AttnFuse fuse;
+    fuse.inv_freq = inv_freq;
+    fuse.new_k = static_cast<const __half*>(new_k);
+    fuse.new_v = static_cast<const __half*>(new_v);
+    fuse.new_bs = new_batch_stride;
+    fuse.new_hs = new_head_stride;
+    return attn_decode_run(layout, q, q_batch_stride, q_head_stride, ALLOYB_F16, k0, k1, v0, v1, new_k, new_v,
+                           new_batch_stride, new_head_stride, pos, pos_count, out, B, H, KV_H, D, S_max, num_pages,
+                           scale, 0, workspace, stream, &fuse);
 }
 
 // Zero the status word and completion counters of a fresh workspace (once after allocation).

@@ -15,6 +15,10 @@
 // afterwards and the +128 is taken out with sum(q) resp. sum(P') -- all in fp32.
 // The paged layout (34-byte blocks, 2-byte aligned) is staged per 16-token page through shared
 // memory with two bulk copies per tile; the other layouts are read straight from global memory.
+// Fused form: q is rotated (RoPE, rotate-half) in registers as it is loaded, and the CTA whose token range
+// holds the decode position rotates the new K row, appends it and the new V row to the cache (quantising
+// for the q8 layouts) before it starts on its tiles -- the arithmetic and rounding points of the separate
+// RoPE + append kernel, so results are bit-identical to the two-launch sequence.
 #include "kv.cuh"
 
 namespace alloyb {
@@ -50,6 +54,8 @@ struct Params {
     float* part_lse;
     unsigned int* counters;
     int* status;
+    AttnFuse fuse;           // valid when fused != 0: RoPE of q / new K and the K / V append happen in here
+    int fused;
 };
 
 __device__ __forceinline__ uint32_t s32(const void* p) {
@@ -65,6 +71,12 @@ __device__ __forceinline__ void mma(float (&c)[4], uint32_t a0, uint32_t a2, uin
     asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1));
+}
+// Cache loads: through the read-only path, or (fused form, where this kernel itself wrote the newest row)
+// from L2.
+template <typename T>
+__device__ __forceinline__ T ldkv(const T* p, bool from_l2) {
+    return from_l2 ? __ldcg(p) : __ldg(p);
 }
 __device__ __forceinline__ uint32_t lds32(const void* p) {
     uint32_t v;
@@ -165,24 +177,81 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
     __syncwarp();
     pdl_wait();
     int pos = P.pos[P.pos_count == 1 ? 0 : b];
+    const int pos_in = pos;                           // as given: the rotation angle and the append use it
     if (pos >= P.kv.S_max) {
         if (threadIdx.x == 0 && P.status) atomicOr(P.status, KV_STATUS_POS_RANGE);
         pos = P.kv.S_max - 1;
     }
     const int len = pos + 1;
+    const bool fresh = P.fused != 0;
+    // this CTA's token range (whole 64-token passes of the four warps per split)
+    int chunk = (len + P.splits - 1) / P.splits;
+    chunk = (chunk + 63) & ~63;
+    const int t0 = split * chunk;
+    const int t1 = min(len, t0 + chunk);
+    const int n_tiles = t1 > t0 ? (t1 - t0 + 15) / 16 : 0;
+
+    if (P.fused && pos_in >= t0 && pos_in < t0 + chunk && pos_in >= 0 && pos_in < P.kv.S_max) {
+        // ---- the decode token's K / V rows: rotate K, append both (this CTA reads them back below)
+        if (warp < 2) {
+            // pair-warp `warp`: rotation pairs (j, j + 64), j = 32 * warp + lane = blocks warp and warp + 2
+            const int j = 32 * warp + lane;
+            float sn, cs;
+            sincosf(static_cast<float>(pos_in) * P.fuse.inv_freq[j], &sn, &cs);
+            const __half* base = P.fuse.new_k + b * P.fuse.new_bs + kvh * P.fuse.new_hs;
+            const float x1 = __half2float(base[j]), x2 = __half2float(base[j + D / 2]);
+            store_kv_block<LAYOUT>(P.kv, 0, b, kvh, pos_in, warp, lane,
+                                   __float2half_rn(__fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn))), P.KV_H, D, P.status);
+            store_kv_block<LAYOUT>(P.kv, 0, b, kvh, pos_in, warp + 2, lane,
+                                   __float2half_rn(__fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn))), P.KV_H, D, P.status);
+        }
+        store_kv_block<LAYOUT>(P.kv, 1, b, kvh, pos_in, warp, lane,
+                               P.fuse.new_v[b * P.fuse.new_bs + kvh * P.fuse.new_hs + 32 * warp + lane], P.KV_H, D, P.status);
+        __threadfence();
+        asm volatile("fence.proxy.async.global;" ::: "memory");       // the paged tiles come in by bulk copies
+        __syncthreads();
+    }
 
     // ---- Q fragments (rows = heads of this group; rows >= G are zero) and per-block sums of q
     uint32_t qa[NKP][2][2];
     float qsum[NKP];
     const bool q_vec = P.q_dtype == ALLOYB_F16 && ((reinterpret_cast<uintptr_t>(P.q) | (P.q_bs * 2) | (P.q_hs * 2)) & 15) == 0;
+    uint4 qraw[NKP];
+    if (q_vec) {
+        // eight consecutive fp16 of head g per 32-dim block: one 16-byte load each
+#pragma unroll
+        for (int kp = 0; kp < NKP; ++kp) {
+            const int64_t base = b * P.q_bs + static_cast<int64_t>(kvh * G + g) * P.q_hs + 32 * kp + 8 * t;
+            qraw[kp] = make_uint4(0u, 0u, 0u, 0u);
+            if (g < G) qraw[kp] = __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(P.q) + base));
+        }
+        if (P.fused) {
+            // rotate-half RoPE in registers: dims d = 32 kp + 8 t + e (kp = 0, 1) pair with d + 64 (kp + 2).
+            // The eight lanes of a column t need the same eight angles: lane (g, t) evaluates e = g and
+            // the values go round by shuffles.
+#pragma unroll
+            for (int kp = 0; kp < 2; ++kp) {
+                __half* lo = reinterpret_cast<__half*>(&qraw[kp]);
+                __half* hi = reinterpret_cast<__half*>(&qraw[kp + 2]);
+                float sn_own, cs_own;
+                sincosf(static_cast<float>(pos_in) * __ldg(P.fuse.inv_freq + 32 * kp + 8 * t + g), &sn_own, &cs_own);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float sn = __shfl_sync(0xffffffffu, sn_own, e * 4 + t);
+                    const float cs = __shfl_sync(0xffffffffu, cs_own, e * 4 + t);
+                    const float x1 = __half2float(lo[e]), x2 = __half2float(hi[e]);
+                    lo[e] = __float2half_rn(__fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn)));
+                    hi[e] = __float2half_rn(__fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn)));
+                }
+            }
+        }
+    }
 #pragma unroll
     for (int kp = 0; kp < NKP; ++kp) {
         float s = 0.f;
         const int64_t base = b * P.q_bs + static_cast<int64_t>(kvh * G + g) * P.q_hs + 32 * kp + 8 * t;
         if (q_vec) {
-            // eight consecutive fp16 of head g: one 16-byte load
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (g < G) v = __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(P.q) + base));
+            const uint4 v = qraw[kp];
             qa[kp][0][0] = v.x;
             qa[kp][0][1] = v.y;
             qa[kp][1][0] = v.z;
@@ -206,13 +275,6 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
         s += __shfl_xor_sync(0xffffffffu, s, 2);
         qsum[kp] = s;
     }
-
-    // ---- this CTA's token range, in 16-token tiles
-    int chunk = (len + P.splits - 1) / P.splits;
-    chunk = (chunk + 63) & ~63;                       // whole tiles for each of the four warps
-    const int t0 = split * chunk;
-    const int t1 = min(len, t0 + chunk);
-    const int n_tiles = t1 > t0 ? (t1 - t0 + 15) / 16 : 0;
 
     float m_run = NEG_BIG, l_run = 0.f;               // for head g (replicated over t)
     float o[NKP * 4][2];                              // [(kp, e)][column 2t / 2t+1]
@@ -263,7 +325,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                 const uint4* kr = reinterpret_cast<const uint4*>(static_cast<const __half*>(P.kv.k0) + (head_row + tok) * D) + t;
 #pragma unroll
                 for (int kp = 0; kp < NKP; ++kp) {
-                    const uint4 kv = __ldg(kr + kp * 4);
+                    const uint4 kv = ldkv(kr + kp * 4, fresh);
                     mma(c, qa[kp][0][0], qa[kp][0][1], kv.x, kv.y);
                     mma(c, qa[kp][1][0], qa[kp][1][1], kv.z, kv.w);
                 }
@@ -285,13 +347,13 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                                         ? half_bits_to_f32(lds16(st->k[slot] + (8 * tb + 2 * t + e) * (NKP * KV_BLOCK_BYTES) + kp * KV_BLOCK_BYTES))
                                         : 0.f;
                     } else {
-                        const uint2 cw = __ldg(reinterpret_cast<const uint2*>(static_cast<const int8_t*>(P.kv.k0) + (head_row + tok) * D + 32 * kp + 8 * t));
+                        const uint2 cw = ldkv(reinterpret_cast<const uint2*>(static_cast<const int8_t*>(P.kv.k0) + (head_row + tok) * D + 32 * kp + 8 * t), fresh);
                         w0 = cw.x;
                         w1 = cw.y;
 #pragma unroll
                         for (int e = 0; e < 2; ++e) {
                             const int tk = min(tok0 + 8 * tb + 2 * t + e, t1 - 1);
-                            ks[e] = __half2float(__ldg(static_cast<const __half*>(P.kv.k1) + (head_row + tk) * NKP + kp));
+                            ks[e] = __half2float(ldkv(static_cast<const __half*>(P.kv.k1) + (head_row + tk) * NKP + kp, fresh));
                         }
                     }
                     const uint32_t u0 = w0 ^ 0x80808080u, u1 = w1 ^ 0x80808080u;
@@ -358,7 +420,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                 uint2 w[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
-                    w[i] = __ldg(reinterpret_cast<const uint2*>(static_cast<const __half*>(P.kv.v0) + (head_row + vtok[i]) * D + 32 * kp + 4 * g));
+                    w[i] = ldkv(reinterpret_cast<const uint2*>(static_cast<const __half*>(P.kv.v0) + (head_row + vtok[i]) * D + 32 * kp + 4 * g), fresh);
                 b0[0] = prmt(w[0].x, w[1].x, 0x5410u); b0[1] = prmt(w[0].x, w[1].x, 0x7632u);
                 b0[2] = prmt(w[0].y, w[1].y, 0x5410u); b0[3] = prmt(w[0].y, w[1].y, 0x7632u);
                 b1[0] = prmt(w[2].x, w[3].x, 0x5410u); b1[1] = prmt(w[2].x, w[3].x, 0x7632u);
@@ -374,8 +436,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                         lds_words_align2(row + 2 + 4 * g, w[i], dummy, false);
                         vs[i] = tok0 + (i >> 1) * 8 + 2 * t + (i & 1) < t1 ? half_bits_to_f32(lds16(row)) : 0.f;
                     } else {
-                        w[i] = __ldg(reinterpret_cast<const uint32_t*>(static_cast<const int8_t*>(P.kv.v0) + (head_row + vtok[i]) * D + 32 * kp + 4 * g));
-                        vs[i] = __half2float(__ldg(static_cast<const __half*>(P.kv.v1) + (head_row + vtok[i]) * NKP + kp));
+                        w[i] = ldkv(reinterpret_cast<const uint32_t*>(static_cast<const int8_t*>(P.kv.v0) + (head_row + vtok[i]) * D + 32 * kp + 4 * g), fresh);
+                        vs[i] = __half2float(ldkv(static_cast<const __half*>(P.kv.v1) + (head_row + vtok[i]) * NKP + kp, fresh));
                     }
                     w[i] ^= 0x80808080u;
                 }
@@ -562,8 +624,11 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
 int launch_attn_mma(int layout, const void* q, int64_t q_bs, int64_t q_hs, int q_dtype, const KVPtrs& kv,
                     const int32_t* pos, int pos_count, void* out, int B, int H, int KV_H, float scale_log2,
                     int splits, float* part_o, float* part_lse, unsigned int* counters, int* status,
-                    cudaStream_t st) {
+                    cudaStream_t st, const AttnFuse* fuse) {
     am::Params P;
+    P.fused = fuse ? 1 : 0;
+    if (fuse) P.fuse = *fuse;
+    else P.fuse = AttnFuse{nullptr, nullptr, nullptr, 0, 0};
     P.q = q; P.q_bs = q_bs; P.q_hs = q_hs; P.q_dtype = q_dtype;
     P.kv = kv; P.pos = pos; P.pos_count = pos_count; P.out = out;
     P.B = B; P.H = H; P.KV_H = KV_H; P.G = H / KV_H;

@@ -12,6 +12,9 @@
 
 namespace alloyb {
 
+constexpr int ALLOYB_NOT_TAKEN = 1;    // a fast path declined the shape: nothing was launched, take the general one
+
+
 constexpr int QK_K = 256;
 constexpr int Q4K_BYTES = 144;
 constexpr int Q6K_BYTES = 210;

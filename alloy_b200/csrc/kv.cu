@@ -9,23 +9,6 @@
 
 namespace alloyb {
 
-struct Q8Block {
-    int code;
-    __half scale;
-};
-
-// All 32 lanes of a warp hold one element each of the same block.
-__device__ __forceinline__ Q8Block quantize_block_q8(float x) {
-    const float m = warp_max(fabsf(x));
-    const float inv = (m > 0.f) ? __fdiv_rn(127.0f, m) : 0.f;
-    const float q = __fmul_rn(x, inv);
-    const float mag = floorf(__fadd_rn(fabsf(q), 0.5f));
-    Q8Block r;
-    r.code = static_cast<int>(copysignf(mag, q));
-    r.scale = __float2half_rn(__fdiv_rn(m, 127.0f));
-    return r;
-}
-
 // Range quantise into the split layout; one warp per (b, h, token, block).
 __global__ void kv_quantize_range_kernel(const __half* __restrict__ src, int64_t sb, int64_t sh,
                                          int64_t stok, int8_t* __restrict__ codes,
@@ -48,36 +31,6 @@ __global__ void kv_quantize_range_kernel(const __half* __restrict__ src, int64_t
     const int64_t row = (static_cast<int64_t>(b) * KV_H + h) * S_max + (start + t);
     codes[row * D + blk * 32 + lane] = static_cast<int8_t>(qb.code);
     if (lane == 0) scales[row * nblk + blk] = qb.scale;
-}
-
-// One 32-element block of a new K (which = 0) or V (1) row at position p, one element per lane, into
-// the cache of any layout (q8 layouts quantise it).
-template <int LAYOUT>
-__device__ __forceinline__ void store_kv_block(const KVPtrs& kv, int which, int b, int h, int p, int blk, int lane,
-                                               __half xin, int KV_H, int D, int* status) {
-    const int nblk = D / 32;
-    if (LAYOUT == ALLOYB_KV_F16) {
-        __half* cache = static_cast<__half*>(which ? kv.v0 : kv.k0);
-        cache[((static_cast<int64_t>(b) * KV_H + h) * kv.S_max + p) * D + blk * 32 + lane] = xin;
-        return;
-    }
-    const Q8Block qb = quantize_block_q8(__half2float(xin));
-    if (LAYOUT == ALLOYB_KV_Q8_SPLIT) {
-        const int64_t row = (static_cast<int64_t>(b) * KV_H + h) * kv.S_max + p;
-        static_cast<int8_t*>(which ? kv.v0 : kv.k0)[row * D + blk * 32 + lane] = static_cast<int8_t>(qb.code);
-        if (lane == 0) static_cast<__half*>(which ? kv.v1 : kv.k1)[row * nblk + blk] = qb.scale;
-    } else {
-        const int32_t* table = static_cast<const int32_t*>(kv.k1);
-        const int64_t page = table[static_cast<int64_t>(b) * kv.max_pages + p / PAGE_TOKENS];
-        if (page < 0 || page >= kv.num_pages) {
-            if (lane == 0 && status) atomicOr(status, KV_STATUS_PAGE_RANGE);
-            return;
-        }
-        uint8_t* dst = static_cast<uint8_t*>(kv.k0) + paged_row_offset(page, which, h, p % PAGE_TOKENS, KV_H, D) +
-                       blk * KV_BLOCK_BYTES;
-        if (lane == 0) *reinterpret_cast<__half*>(dst) = qb.scale;
-        reinterpret_cast<int8_t*>(dst + 2)[lane] = static_cast<int8_t>(qb.code);
-    }
 }
 
 // One new token per sequence, any layout; one warp per (b, h, K|V, block).

@@ -5,7 +5,6 @@
 namespace alloyb {
 
 constexpr int MAX_SEGS = 4;            // weight matrices per launch (q/k/v + one spare)
-constexpr int ALLOYB_NOT_TAKEN = 1;    // a fast path declined the shape; use the row kernels
 
 struct WeightSeg {
     int format;

@@ -339,19 +339,15 @@ class QuantLlamaDecoder:
             q3 = q.view(b, self.heads_l, s.head_dim)
             k3 = k.view(b, self.kv_heads_l, s.head_dim)
             v3 = v.view(b, self.kv_heads_l, s.head_dim)
-            q4, k4, v4 = q3.unsqueeze(2), k3.unsqueeze(2), v3.unsqueeze(2)
-            # RoPE of q and k and the cache append in one launch; attention then only reads
+            # RoPE of q and k, the cache append and the attention in one launch
             if self.kv_kind == "f16":
-                ops.rope_kv_append(q3, k3, v3, self.pos, self.inv_freq, k_cache=self.k_cache[li],
-                                   v_cache=self.v_cache[li])
-                a = torch.ops.alloy.attention_cache(q4, k4, v4, self.pos, self.k_cache[li],
-                                                    self.v_cache[li], scale, 0, False)
+                a = ops.rope_attention_decode(q3, k3, v3, self.pos, self.inv_freq, k_cache=self.k_cache[li],
+                                              v_cache=self.v_cache[li], scale=scale)
             else:
                 pool = self.pools[li]
-                ops.rope_kv_append(q3, k3, v3, self.seq_pos, self.inv_freq, paged=(pool.page_table, pool.pool))
-                a = torch.ops.alloy.attention_cache_q8_paged(q4, k4, v4, self.seq_pos, pool.page_table,
-                                                             pool.pool, -1.0, False)
-            a2 = a.transpose(1, 2).reshape(b, self.heads_l * s.head_dim)
+                a = ops.rope_attention_decode(q3, k3, v3, self.seq_pos, self.inv_freq,
+                                              paged=(pool.page_table, pool.pool))
+            a2 = a.reshape(b, self.heads_l * s.head_dim)
             if self.tp_size == 1:
                 h = torch.ops.alloy.linear_residual(a2, lw.wo, None, h, lw.fmt["wo"])
             else:

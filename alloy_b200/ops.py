@@ -806,6 +806,53 @@ def rope_kv_append(q: torch.Tensor, new_k: torch.Tensor, new_v: torch.Tensor, po
                                   ws.data_ptr(), _stream()), "alloyb_rope_kv_append")
 
 
+def rope_attention_decode(q: torch.Tensor, new_k: torch.Tensor, new_v: torch.Tensor, pos: torch.Tensor,
+                          inv_freq: torch.Tensor, *, k_cache: torch.Tensor | None = None,
+                          v_cache: torch.Tensor | None = None, q8_split: tuple | None = None,
+                          paged: tuple | None = None, scale: float | None = None) -> torch.Tensor:
+    """The decode token's attention step in ONE launch (``alloyb_attn_decode_rope``): RoPE of q and k, the
+    append of k / v at ``pos`` to the cache, attention over the cache.  Arguments as ``rope_kv_append``
+    (q fp16 (B, H, D), left unrotated); returns (B, H, D).  Same numbers, bit for bit, as
+    ``rope_kv_append`` followed by the cache-attention op with ``write_kv=False``; shapes the fused
+    kernel does not cover take exactly that route."""
+    b, h, d = q.shape
+    kv_h = new_k.shape[1]
+    if q.dtype != torch.float16 or q.stride(2) != 1:
+        raise ValueError("q must be float16 (B, H, D) with unit inner stride")
+    for name, t in (("new_k", new_k), ("new_v", new_v)):
+        if t.dtype != torch.float16 or tuple(t.shape) != (b, kv_h, d) or t.stride(2) != 1:
+            raise ValueError(f"{name} must be float16 {(b, kv_h, d)} with unit inner stride")
+    if new_k.stride() != new_v.stride():
+        new_k, new_v = new_k.contiguous(), new_v.contiguous()
+    pos = _pos_i32(pos.reshape(-1))
+    if k_cache is not None:
+        layout, ptrs, s_max, n_pages = _lib.KV_F16, (k_cache, None, v_cache, None), k_cache.shape[2], 0
+    elif q8_split is not None:
+        layout, ptrs, s_max, n_pages = _lib.KV_Q8_SPLIT, tuple(q8_split), q8_split[0].shape[2], 0
+    elif paged is not None:
+        table, pool = paged
+        layout, ptrs, s_max, n_pages = _lib.KV_Q8_PAGED, (pool, table, None, None), table.shape[1] * 16, pool.shape[0]
+    else:
+        raise ValueError("one cache must be given")
+    ws = attn_workspace(q.device, b, h, d)
+    out = torch.empty((b, h, d), dtype=q.dtype, device=q.device)
+    L = _lib.load()
+    rc = L.alloyb_attn_decode_rope(layout, q.data_ptr(), q.stride(0), q.stride(1),
+                                   *[t.data_ptr() if t is not None else None for t in ptrs],
+                                   new_k.data_ptr(), new_v.data_ptr(), new_k.stride(0), new_k.stride(1),
+                                   pos.data_ptr(), pos.numel(), inv_freq.data_ptr(), out.data_ptr(), b, h, kv_h, d,
+                                   s_max, n_pages, float(scale) if scale is not None else -1.0, ws.data_ptr(),
+                                   ws.numel(), _stream())
+    if rc == 1:          # not a shape of the fused kernel: the two launches it stands for
+        q = q.contiguous()
+        rope_kv_append(q, new_k, new_v, pos, inv_freq, k_cache=k_cache, v_cache=v_cache, q8_split=q8_split, paged=paged)
+        k0, k1, v0, v1 = ptrs
+        return _cache_attention(layout, q.unsqueeze(2), new_k.unsqueeze(2), new_v.unsqueeze(2), pos, k0, k1, v0, v1,
+                                s_max, n_pages, scale, False).squeeze(2)
+    check(rc, "alloyb_attn_decode_rope")
+    return out
+
+
 def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     y = torch.empty_like(gate)
     L = _lib.load()

@@ -288,6 +288,20 @@ int alloyb_attn_decode(int layout, const void* q, int64_t q_batch_stride, int64_
                        int S_max, int64_t num_pages, float scale, int write_kv, void* workspace,
                        size_t workspace_bytes, void* stream);
 
+/* The decode token's whole attention step in ONE launch: rotate-half RoPE of q and of the new K row, the
+ * append of the new K / V rows (any layout; q8 layouts quantise) and the attention.  Bit-identical to
+ * alloyb_rope_kv_append followed by alloyb_attn_decode(write_kv = 0), except that q is left unrotated
+ * in memory.  fp16 q with 16-byte-aligned rows, head_dim 128, at most eight query heads per KV head;
+ * other shapes return ALLOYB_NOT_TAKEN (1) and nothing is launched.  No reference counterpart: the
+ * reference rotates in model code and fuses only the cache write
+ * (packages/alloy-metal/src/alloy/std/kv_quant.py:212-246). */
+int alloyb_attn_decode_rope(int layout, const void* q, int64_t q_batch_stride, int64_t q_head_stride,
+                            void* k0, void* k1, void* v0, void* v1, const void* new_k, const void* new_v,
+                            int64_t new_batch_stride, int64_t new_head_stride, const int32_t* pos,
+                            int pos_count, const float* inv_freq, void* out, int B, int H, int KV_H, int D,
+                            int S_max, int64_t num_pages, float scale, void* workspace,
+                            size_t workspace_bytes, void* stream);
+
 /* Decode attention that allocates nothing and needs no workspace from the caller (no
  * counterpart in the reference, whose runtime owns its scratch buffers).  For hosts that may
  * not allocate device memory where the decode step runs -- a serving loop with a frozen

@@ -348,6 +348,19 @@ def test_rope_kv_append_equals_rope_then_append(layout):
     for x, y in zip(a, bb):
         assert torch.equal(x, y)
     assert torch.equal(out1, out2)
+    # all three steps in one launch: same cache, same output, q left unrotated
+    c3 = caches()
+    q3 = q.clone()
+    if layout == "f16":
+        out3 = ops.rope_attention_decode(q3, nk, nv, p_arg, inv, k_cache=c3[0], v_cache=c3[1])
+    elif layout == "q8_split":
+        out3 = ops.rope_attention_decode(q3, nk, nv, p_arg, inv, q8_split=tuple(c3))
+    else:
+        out3 = ops.rope_attention_decode(q3, nk, nv, p_arg, inv, paged=(c3[0].page_table, c3[0].pool))
+    assert torch.equal(q3, q)
+    for x, y in zip(a, [t if isinstance(t, torch.Tensor) else t.pool for t in c3]):
+        assert torch.equal(x, y)
+    assert torch.equal(out1.squeeze(2), out3)
 
 
 def test_paged_append_entry_and_bad_page_is_skipped():
@@ -387,3 +400,28 @@ def test_attention_argument_errors():
         torch.ops.alloy.attention_cache_q8(q, z, z, torch.tensor([0], device=DEV), c, s, c, s)
     with pytest.raises(ValueError):
         torch.ops.alloy.attention_cache_q8(q[0], z, z, torch.tensor([0], device=DEV), c, s, c, s)
+
+
+@pytest.mark.parametrize("pos0", [0, 63, 64, 2047])
+def test_rope_attention_decode_positions_and_fallback(pos0):
+    """The one-launch attention step at the first position, at both sides of a split boundary and at the
+    last position of the cache; a head_dim the fused kernel does not cover takes the two-launch route."""
+    rng = np.random.default_rng(pos0)
+    b, kv_h, group, s_max = 2, 2, 4, 2048
+    for d in (128, 64):
+        h = kv_h * group
+        q = torch.from_numpy(synth.activations(rng, b * h, d).reshape(b, h, d)).to(DEV)
+        nk = torch.from_numpy(synth.kv_rows(rng, (b, kv_h, d))).to(DEV)
+        nv = torch.from_numpy(synth.kv_rows(rng, (b, kv_h, d))).to(DEV)
+        inv = (1.0 / (500000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(DEV)
+        pos = torch.tensor([pos0], dtype=torch.int32, device=DEV)
+        g = torch.Generator(device=DEV).manual_seed(11)
+        base = [torch.randn((b, kv_h, s_max, d), device=DEV, generator=g).half() for _ in range(2)]
+        c1, c2 = [t.clone() for t in base], [t.clone() for t in base]
+        q1 = q.clone()
+        ops.rope_kv_append(q1, nk, nv, pos, inv, k_cache=c1[0], v_cache=c1[1])
+        want = torch.ops.alloy.attention_cache(q1.unsqueeze(2), nk.unsqueeze(2), nv.unsqueeze(2), pos, c1[0], c1[1],
+                                               -1.0, 0, False).squeeze(2)
+        got = ops.rope_attention_decode(q, nk, nv, pos, inv, k_cache=c2[0], v_cache=c2[1])
+        assert torch.equal(c1[0], c2[0]) and torch.equal(c1[1], c2[1])
+        assert torch.equal(want, got)
