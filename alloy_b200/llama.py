@@ -132,13 +132,15 @@ class QuantLlamaDecoder:
     def __init__(self, shape: LlamaShape, batch: int, context: int, *, device="cuda", seed: int = 0,
                  kv: str = "f16", tp_rank: int = 0, tp_size: int = 1, process_group=None,
                  dtype: torch.dtype = torch.float16, d_scale: float = 1.0, centered: bool = False, peer_allreduce: bool = True,
-                 tp_dry: bool = False, weights=None, one_launch: bool | None = None) -> None:
+                 tp_dry: bool = False, weights=None, one_launch: bool | None = None,
+                 fused_attention: bool = True) -> None:
         if kv not in ("f16", "q8_paged"):
             raise ValueError(f"kv must be 'f16' or 'q8_paged', got {kv!r}")
         if shape.heads % tp_size or shape.kv_heads % tp_size or shape.ffn % (256 * tp_size) \
                 or (shape.heads * shape.head_dim) % (256 * tp_size) or shape.vocab % tp_size:
             raise ValueError(f"shape does not shard {tp_size} ways")
         self.shape, self.batch, self.context = shape, int(batch), int(context)
+        self.fused_attention = bool(fused_attention)
         self.device, self.dtype, self.kv_kind = torch.device(device), dtype, kv
         self.tp_rank, self.tp_size, self.pg = tp_rank, tp_size, process_group
         # row-parallel outputs are summed inside the GEMV launch over peer memory (NCCL only sets
@@ -339,14 +341,23 @@ class QuantLlamaDecoder:
             q3 = q.view(b, self.heads_l, s.head_dim)
             k3 = k.view(b, self.kv_heads_l, s.head_dim)
             v3 = v.view(b, self.kv_heads_l, s.head_dim)
-            # RoPE of q and k, the cache append and the attention in one launch
-            if self.kv_kind == "f16":
-                a = ops.rope_attention_decode(q3, k3, v3, self.pos, self.inv_freq, k_cache=self.k_cache[li],
-                                              v_cache=self.v_cache[li], scale=scale)
+            # RoPE of q and k, the cache append and the attention in one launch (or, on request, RoPE +
+            # append as a launch of their own before an attention that only reads)
+            kv_args = (dict(k_cache=self.k_cache[li], v_cache=self.v_cache[li]) if self.kv_kind == "f16"
+                       else dict(paged=(self.pools[li].page_table, self.pools[li].pool)))
+            p_arg = self.pos if self.kv_kind == "f16" else self.seq_pos
+            if self.fused_attention:
+                a = ops.rope_attention_decode(q3, k3, v3, p_arg, self.inv_freq, scale=scale, **kv_args)
             else:
-                pool = self.pools[li]
-                a = ops.rope_attention_decode(q3, k3, v3, self.seq_pos, self.inv_freq,
-                                              paged=(pool.page_table, pool.pool))
+                ops.rope_kv_append(q3, k3, v3, p_arg, self.inv_freq, **kv_args)
+                q4, k4, v4 = q3.unsqueeze(2), k3.unsqueeze(2), v3.unsqueeze(2)
+                if self.kv_kind == "f16":
+                    a = torch.ops.alloy.attention_cache(q4, k4, v4, self.pos, self.k_cache[li], self.v_cache[li],
+                                                        scale, 0, False)
+                else:
+                    a = torch.ops.alloy.attention_cache_q8_paged(q4, k4, v4, self.seq_pos, self.pools[li].page_table,
+                                                                 self.pools[li].pool, -1.0, False)
+                a = a.transpose(1, 2)
             a2 = a.reshape(b, self.heads_l * s.head_dim)
             if self.tp_size == 1:
                 h = torch.ops.alloy.linear_residual(a2, lw.wo, None, h, lw.fmt["wo"])

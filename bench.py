@@ -322,7 +322,8 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
                                     tp_rank=0 if solo else rank, tp_size=1 if solo else (dry or world),
                                     process_group=None if solo else pg, tp_dry=bool(dry) and not solo,
                                     d_scale=WEIGHT_D_SCALE, centered=True,
-                                    one_launch=one_launch if fused is None else fused)
+                                    one_launch=one_launch if fused is None else fused,
+                                    fused_attention=not args.split_attention)
         torch.cuda.synchronize()
         note("weights ready; capturing")
         d.capture()
@@ -593,6 +594,8 @@ def main() -> None:
     ap.add_argument("--step", default="auto", choices=["auto", "one-launch", "per-op"],
                     help="batch 1: the whole step as one persistent launch, or op by op (auto: op by op, with the "
                          "one-launch step timed beside it at N = 1)")
+    ap.add_argument("--split-attention", action="store_true",
+                    help="RoPE + KV append as a launch of their own instead of inside the attention kernel")
     ap.add_argument("--no-sweep", action="store_true", help="skip the batch sweep")
     ap.add_argument("--no-extras", action="store_true", help="N = 1: skip the config 0 / 2 / 3 kernel timings")
     ap.add_argument("--no-tp1", action="store_true", help="N > 1: skip the one-GPU run of the same step")
