@@ -895,6 +895,51 @@ static int launch_bm(int BM, const Maps& maps, const Params& P, int grid, int de
 
 }  // namespace tc
 
+namespace tc {
+
+// y = type(residual + y), rows of N elements `ld` apart, eight elements per thread where the row allows.
+template <bool BF16>
+__global__ void residual_add_kernel(uint16_t* __restrict__ y, const uint16_t* __restrict__ res, int M, int N, int64_t ld) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int per_row = (N + 7) / 8;
+    const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (i >= static_cast<int64_t>(M) * per_row) return;
+    const int m = static_cast<int>(i / per_row), c = static_cast<int>(i % per_row) * 8;
+    uint16_t* yp = y + m * ld + c;
+    const uint16_t* rp = res + m * ld + c;
+    if (c + 8 <= N && ((reinterpret_cast<uintptr_t>(yp) | reinterpret_cast<uintptr_t>(rp)) & 15) == 0) {
+        uint4 a = *reinterpret_cast<const uint4*>(yp);
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(rp));
+        uint16_t* ah = reinterpret_cast<uint16_t*>(&a);
+        const uint16_t* bh = reinterpret_cast<const uint16_t*>(&b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ah[e] = to_16<BF16>(to_f32<BF16>(bh[e]) + to_f32<BF16>(ah[e]));
+        *reinterpret_cast<uint4*>(yp) = a;
+    } else {
+        for (int e = 0; e < 8 && c + e < N; ++e) yp[e] = to_16<BF16>(to_f32<BF16>(rp[e]) + to_f32<BF16>(yp[e]));
+    }
+}
+
+}  // namespace tc
+
+// Beyond this many tokens the residual is added by a kernel of its own after the GEMM: the GEMM's epilogue
+// holds one weight row per thread and fetches its residual values token by token (strided), which a single
+// tile per CTA hides and a walk over many tiles does not.
+constexpr int GEMM_FUSED_RESIDUAL_MAX_M = 128;
+
+int gemm_tc_residual_add(void* y, const void* residual, int M, int N, int64_t ldy, int dtype, cudaStream_t st) {
+    const int64_t threads = static_cast<int64_t>(M) * ((N + 7) / 8);
+    const dim3 grid(static_cast<unsigned int>((threads + 255) / 256));
+    if (dtype == ALLOYB_BF16)
+        launch_pdl(tc::residual_add_kernel<true>, grid, dim3(256), 0, st, static_cast<uint16_t*>(y),
+                   static_cast<const uint16_t*>(residual), M, N, ldy);
+    else
+        launch_pdl(tc::residual_add_kernel<false>, grid, dim3(256), 0, st, static_cast<uint16_t*>(y),
+                   static_cast<const uint16_t*>(residual), M, N, ldy);
+    return check_launch();
+}
+
 // C = X * deq(W)^T (+ residual) for one packed matrix, or act(X G^T) * (X U^T) for a gate/up pair
 // (`up` non-null; both matrices in seg's format and shape, M <= 128).  NOT_TAKEN unless the shape and
 // the alignment are the kind the kernel is built for.
@@ -952,7 +997,8 @@ int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, co
     Params P;
     P.format = seg.format;
     P.y = seg.y;
-    P.residual = residual;
+    const bool add_after = residual && M > GEMM_FUSED_RESIDUAL_MAX_M;
+    P.residual = add_after ? nullptr : residual;
     P.ldy = seg.ldy;
     P.M = M;
     P.N = seg.N;
@@ -964,7 +1010,9 @@ int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, co
     // persistent: one CTA per SM walks the items (weight-row tile fastest, so neighbours share a token tile)
     const int n_items = tiles_n * tiles_m * splits;
     const int grid = n_items < sms ? n_items : sms;
-    return dtype == ALLOYB_BF16 ? launch_bm<true>(BM, maps, P, grid, dev, st) : launch_bm<false>(BM, maps, P, grid, dev, st);
+    const int rc = dtype == ALLOYB_BF16 ? launch_bm<true>(BM, maps, P, grid, dev, st) : launch_bm<false>(BM, maps, P, grid, dev, st);
+    if (rc != ALLOYB_OK || !add_after) return rc;
+    return gemm_tc_residual_add(seg.y, residual, M, seg.N, seg.ldy, dtype, st);
 }
 
 }  // namespace alloyb

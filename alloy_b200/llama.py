@@ -46,6 +46,12 @@ class LlamaShape:
         norms = (2 * self.layers + 1) * self.hidden * 2
         return layer * self.layers + q6(self.vocab, self.hidden) + norms
 
+    def layer_weight_elems(self) -> int:
+        """Weights of the per-layer linears (what every prompt token is multiplied by in prefill)."""
+        hd = self.heads * self.head_dim
+        kvd = self.kv_heads * self.head_dim
+        return self.layers * (hd * self.hidden + 2 * kvd * self.hidden + self.hidden * hd + 3 * self.ffn * self.hidden)
+
 
 LLAMA3_8B = LlamaShape(layers=32, hidden=4096, ffn=14336, heads=32, kv_heads=8, head_dim=128,
                        vocab=128256)
@@ -379,6 +385,73 @@ class QuantLlamaDecoder:
         self.logits = logits
         self.next_ids.copy_(ops.argmax(logits))
         self.launches_per_step = ops.launch_count() - n0
+
+    # ------------------------------------------------------------------ prefill
+
+    def prefill(self, ids: torch.Tensor, start: int = 0) -> torch.Tensor:
+        """Run ``ids`` (B, S) through the model as ONE chunk at positions ``start .. start + S - 1``: the
+        linears see B * S tokens at once (tensor-core GEMM from 28 tokens up), every layer writes its S
+        new K / V rows per sequence to the cache (quantised for the q8 pool) and attends causally over
+        the cache (``attention_cache*`` with ``seq_len > 1``).  Returns the logits of each sequence's
+        last token (B, vocab) and leaves ``pos`` at ``start + S``, so ``step()`` continues from there --
+        the prefill half of the reference's serving loop (model forward over the prompt chunk,
+        ``server/models/attention.py:281-342``)."""
+        s, b = self.shape, self.batch
+        if ids.ndim != 2 or ids.shape[0] != b:
+            raise ValueError(f"ids must be ({b}, S), got {tuple(ids.shape)}")
+        n = int(ids.shape[1])
+        if n < 1 or start < 0 or start + n > self.context:
+            raise ValueError(f"positions {start}..{start + n - 1} do not fit a cache of {self.context}")
+        if self._graph is not None:
+            raise RuntimeError("prefill runs eagerly: call it before capture()")
+        dev = self.device
+        m = b * n
+        x = ops._embedding(ids.to(dev).reshape(-1), ops._FORMATS[self.embed_fmt], self.embed, None, out_dtype=self.dtype)
+        rows_pos = (start + torch.arange(n, dtype=torch.int32, device=dev)).repeat(b)       # position of token row
+        start_t = torch.full((b,), start, dtype=torch.int32, device=dev)
+        scale = 1.0 / (s.head_dim ** 0.5)
+        self._enter_together()
+        for li, lw in enumerate(self.layers):
+            xn = ops.rms_norm(x, lw.norm_in, s.eps)
+            q, k, v = ops.linear_multi(xn, [(lw.fmt["wq"], lw.wq, None), (lw.fmt["wk"], lw.wk, None),
+                                            (lw.fmt["wv"], lw.wv, None)])
+            q3 = q.view(m, self.heads_l, s.head_dim)
+            k3 = k.view(m, self.kv_heads_l, s.head_dim)
+            ops.rope_inplace(q3, k3, rows_pos, self.inv_freq)
+            q4 = q3.view(b, n, self.heads_l, s.head_dim).transpose(1, 2)
+            k4 = k3.view(b, n, self.kv_heads_l, s.head_dim).transpose(1, 2)
+            v4 = v.view(b, n, self.kv_heads_l, s.head_dim).transpose(1, 2)
+            if self.kv_kind == "f16":
+                a = torch.ops.alloy.attention_cache(q4, k4, v4, start_t[:1], self.k_cache[li], self.v_cache[li],
+                                                    scale, 0, True)
+            else:
+                pool = self.pools[li]
+                a = torch.ops.alloy.attention_cache_q8_paged(q4, k4, v4, start_t, pool.page_table, pool.pool, -1.0, True)
+            a2 = a.transpose(1, 2).reshape(m, self.heads_l * s.head_dim)
+            if self.tp_size == 1:
+                x = torch.ops.alloy.linear_residual(a2, lw.wo, None, x, lw.fmt["wo"])
+            else:
+                x = self._row_parallel(a2, lw.fmt["wo"], lw.wo, x)
+            xn = ops.rms_norm(x, lw.norm_post, s.eps)
+            if lw.fmt["wg"] == "q4_k" and lw.fmt["wu"] == "q4_k":
+                act = torch.ops.alloy.gguf_q4_k_silu(xn, lw.wg, lw.wu)
+            else:
+                gate, up = ops.linear_multi(xn, [(lw.fmt["wg"], lw.wg, None), (lw.fmt["wu"], lw.wu, None)])
+                act = ops.silu_mul(gate, up)
+            if self.tp_size == 1:
+                x = torch.ops.alloy.linear_residual(act, lw.wd, None, x, lw.fmt["wd"])
+            else:
+                x = self._row_parallel(act, lw.fmt["wd"], lw.wd, x)
+        last = x.view(b, n, s.hidden)[:, -1].contiguous()
+        logits = ops.linear_multi(last, [(self.head_fmt, self.head, None)], norm=(self.norm_final, s.eps))[0]
+        if self.tp_size > 1 and not self.tp_dry:
+            logits = tp.gather_columns(logits, self.pg)
+        self.logits = logits
+        self.next_ids.copy_(ops.argmax(logits))
+        self.pos.fill_(start + n)
+        if hasattr(self, "seq_pos"):
+            self.seq_pos.fill_(start + n)
+        return logits
 
     def capture(self) -> None:
         """Warm up once eagerly, then record the step into a CUDA graph."""

@@ -798,6 +798,7 @@ def rope_kv_append(q: torch.Tensor, new_k: torch.Tensor, new_v: torch.Tensor, po
         layout, ptrs, s_max, n_pages = _lib.KV_Q8_PAGED, (pool, table, None, None), table.shape[1] * 16, pool.shape[0]
     else:
         raise ValueError("one cache must be given")
+    _check_cache(layout, b, kv_h, d, *ptrs)
     ws = attn_workspace(q.device, b, h, d)
     L = _lib.load()
     check(L.alloyb_rope_kv_append(layout, q.data_ptr(), new_k.data_ptr(), new_v.data_ptr(), new_k.stride(0),
@@ -834,6 +835,7 @@ def rope_attention_decode(q: torch.Tensor, new_k: torch.Tensor, new_v: torch.Ten
         layout, ptrs, s_max, n_pages = _lib.KV_Q8_PAGED, (pool, table, None, None), table.shape[1] * 16, pool.shape[0]
     else:
         raise ValueError("one cache must be given")
+    _check_cache(layout, b, kv_h, d, *ptrs)
     ws = attn_workspace(q.device, b, h, d)
     out = torch.empty((b, h, d), dtype=q.dtype, device=q.device)
     L = _lib.load()

@@ -466,6 +466,27 @@ def run_ours(args, shape_name: str, wl: dict, workload: str) -> None:
             except Exception as e:  # noqa: BLE001
                 one_launch_cmp = {"error": repr(e)}
             torch.cuda.empty_cache()
+        # the prompt side of the same model: one chunk of `context` tokens through prefill() (tensor-core
+        # GEMMs, causal chunk attention, K/V written to the cache), eager, timed with CUDA events
+        try:
+            pre = llama.QuantLlamaDecoder(shape, 1, wl["context"], device=dev, seed=0, kv=wl["kv"],
+                                          d_scale=WEIGHT_D_SCALE, centered=True)
+            gen = torch.Generator().manual_seed(2)
+            prompt = torch.randint(0, shape.vocab, (1, wl["context"]), generator=gen)
+            pre.prefill(prompt)                                    # warm-up
+            torch.cuda.synchronize()
+            pms = min(_event_ms(lambda: pre.prefill(prompt)) for _ in range(3))
+            flop = 2.0 * shape.layer_weight_elems() * wl["context"]          # the layers' linears only
+            extras["prefill"] = {"tokens": wl["context"], "ms": pms, "tokens_per_s": wl["context"] / (pms * 1e-3),
+                                 "logits_finite": bool(torch.isfinite(pre.logits.float()).all().item()),
+                                 "device_error": pre.device_error()}
+            if flop:
+                extras["prefill"]["linear_tflops"] = flop / pms / 1e9
+                extras["prefill"]["frac_of_bf16_burst"] = flop / pms / 1e9 / peaks["bf16_tflops"]
+            del pre
+        except Exception as e:  # noqa: BLE001
+            extras["prefill"] = {"error": repr(e)}
+        torch.cuda.empty_cache()
 
     if rank != 0:
         _leave(world)
