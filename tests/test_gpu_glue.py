@@ -35,12 +35,21 @@ def test_rope_inplace():
         assert_close(to_np(got), ref.astype(np.float64), torch.float16, "rope")
 
 
-def test_silu_mul():
+@pytest.mark.parametrize("shape,dt", [((4, 1000), torch.float16), ((3, 1001), torch.float16), ((64, 1024), torch.bfloat16),
+                                      ((5, 333), torch.float32)])
+def test_silu_mul(shape, dt):
+    """Whole multiples of eight 16-bit elements take the 16-byte-vector kernel, the rest one element per
+    thread: same numbers."""
     rng = np.random.default_rng(6)
-    g = rng.standard_normal((4, 1000)).astype(np.float16)
-    u = rng.standard_normal((4, 1000)).astype(np.float16)
-    y = ops.silu_mul(torch.from_numpy(g).to(DEV), torch.from_numpy(u).to(DEV))
-    assert_close(to_np(y), O.silu(g.astype(np.float64)) * u.astype(np.float64), torch.float16, "silu_mul")
+    g = torch.from_numpy(rng.standard_normal(shape).astype(np.float32)).to(dt)
+    u = torch.from_numpy(rng.standard_normal(shape).astype(np.float32)).to(dt)
+    y = ops.silu_mul(g.to(DEV), u.to(DEV))
+    ref = O.silu(g.double().numpy()) * u.double().numpy()
+    assert_close(to_np(y), ref, dt, "silu_mul")
+    # an unaligned view of the same data goes through the scalar kernel and agrees bit for bit
+    gp = torch.zeros(g.numel() + 1, dtype=dt, device=DEV)[1:].view(shape).copy_(g)
+    up = torch.zeros(u.numel() + 1, dtype=dt, device=DEV)[1:].view(shape).copy_(u)
+    assert torch.equal(ops.silu_mul(gp, up), y)
 
 
 @pytest.mark.parametrize("m,n,dt", [(1, 128256, torch.float16), (4, 32000, torch.float16), (3, 1000, torch.float32),
