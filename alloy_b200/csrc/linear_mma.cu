@@ -502,8 +502,11 @@ struct SmemHeader {
     uint64_t empty[MMA_STAGES];
 };
 
+// Two CTAs per SM (nine warps each) wherever the accumulators leave the registers for it: with one, the
+// warps wait on their activation loads with nobody to run meanwhile.  A gate/up pair with three or four
+// token groups would spill under that limit and keeps the SM to itself.
 template <typename XT, int RT, int NT, bool SB>
-__global__ void __launch_bounds__(MMA_THREADS) linear_mma_kernel(const MmaParams P) {
+__global__ void __launch_bounds__(MMA_THREADS, (RT == 2 && NT >= 3) ? 1 : 2) linear_mma_kernel(const MmaParams P) {
     static_assert(!SB || (std::is_same<XT, __half>::value && NT == 1), "one-token path: fp16, one token group");
     extern __shared__ __align__(128) uint8_t smem[];
     SmemHeader* hdr = reinterpret_cast<SmemHeader*>(smem);
