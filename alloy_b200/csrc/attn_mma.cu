@@ -88,17 +88,19 @@ __device__ __forceinline__ uint32_t lds16(const void* p) {
     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(s32(p)));
     return v;
 }
-// n (1 or 2) 32-bit words starting at a 2-byte-aligned shared address
+// n (1 or 2) 32-bit words starting at a 2-byte-aligned shared address.  Whether the address is 4-byte
+// aligned is known at compile time from the block index (a row of 34-byte blocks starts 4-byte aligned, the
+// codes of block kp at 34 * kp + 2): HALF = true reads across the word boundary with funnel shifts.
+template <bool HALF>
 __device__ __forceinline__ void lds_words_align2(const uint8_t* p, uint32_t& w0, uint32_t& w1, bool two) {
-    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-    const uint8_t* base = reinterpret_cast<const uint8_t*>(a & ~uintptr_t(3));
-    const uint32_t x0 = lds32(base), x1 = lds32(base + 4);
-    if (a & 2u) {
+    if (HALF) {
+        const uint8_t* base = p - 2;
+        const uint32_t x0 = lds32(base), x1 = lds32(base + 4);
         w0 = __funnelshift_r(x0, x1, 16);
         if (two) w1 = __funnelshift_r(x1, lds32(base + 8), 16);
     } else {
-        w0 = x0;
-        if (two) w1 = x1;
+        w0 = lds32(p);
+        if (two) w1 = lds32(p + 4);
     }
 }
 __device__ __forceinline__ void bar_init(uint64_t* b, uint32_t n) {
@@ -339,8 +341,9 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                     uint32_t w0, w1;
                     float ks[2];
                     if (PAGED) {
-                        lds_words_align2(st->k[slot] + (8 * tb + g) * (NKP * KV_BLOCK_BYTES) + kp * KV_BLOCK_BYTES + 2 + 8 * t,
-                                         w0, w1, true);
+                        const uint8_t* kc = st->k[slot] + (8 * tb + g) * (NKP * KV_BLOCK_BYTES) + kp * KV_BLOCK_BYTES + 2 + 8 * t;
+                        if (kp & 1) lds_words_align2<false>(kc, w0, w1, true);      // 34 * kp + 2 is a multiple of 4
+                        else lds_words_align2<true>(kc, w0, w1, true);
 #pragma unroll
                         for (int e = 0; e < 2; ++e)
                             ks[e] = tok0 + 8 * tb + 2 * t + e < t1
@@ -433,7 +436,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                     if (PAGED) {
                         const uint8_t* row = st->v[slot] + ((i >> 1) * 8 + 2 * t + (i & 1)) * (NKP * KV_BLOCK_BYTES) + kp * KV_BLOCK_BYTES;
                         uint32_t dummy;
-                        lds_words_align2(row + 2 + 4 * g, w[i], dummy, false);
+                        if (kp & 1) lds_words_align2<false>(row + 2 + 4 * g, w[i], dummy, false);
+                        else lds_words_align2<true>(row + 2 + 4 * g, w[i], dummy, false);
                         vs[i] = tok0 + (i >> 1) * 8 + 2 * t + (i & 1) < t1 ? half_bits_to_f32(lds16(row)) : 0.f;
                     } else {
                         w[i] = ldkv(reinterpret_cast<const uint32_t*>(static_cast<const int8_t*>(P.kv.v0) + (head_row + vtok[i]) * D + 32 * kp + 4 * g), fresh);
