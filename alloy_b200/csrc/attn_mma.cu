@@ -19,6 +19,8 @@
 // holds the decode position rotates the new K row, appends it and the new V row to the cache (quantising
 // for the q8 layouts) before it starts on its tiles -- the arithmetic and rounding points of the separate
 // RoPE + append kernel, so results are bit-identical to the two-launch sequence.
+#include <type_traits>
+
 #include "kv.cuh"
 
 namespace alloyb {
@@ -316,11 +318,15 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
             if (ok) ok = bar_wait(&sm_bar[warp][slot], (n_mine >> 1) & 1);
             if (!ok) continue;
         }
+        // A tile whose sixteen tokens all lie below t1 (every tile but the last one of the sequence) takes the
+        // FULL form of the body, without the per-token range tests and address clamps.
+        auto tile_body = [&](auto full_c) {
+        constexpr bool FULL = decltype(full_c)::value;
         // ---------------- S = Q K^T
         float s[2][2];
 #pragma unroll
         for (int tb = 0; tb < 2; ++tb) {
-            const int tok = min(tok0 + 8 * tb + g, t1 - 1);          // B column of this thread (clamped)
+            const int tok = FULL ? tok0 + 8 * tb + g : min(tok0 + 8 * tb + g, t1 - 1);   // B column of this thread
             float sc[2] = {0.f, 0.f};
             if (!Q8) {
                 float c[4] = {0.f, 0.f, 0.f, 0.f};
@@ -346,7 +352,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                         else lds_words_align2<true>(kc, w0, w1, true);
 #pragma unroll
                         for (int e = 0; e < 2; ++e)
-                            ks[e] = tok0 + 8 * tb + 2 * t + e < t1
+                            ks[e] = (FULL || tok0 + 8 * tb + 2 * t + e < t1)
                                         ? half_bits_to_f32(lds16(st->k[slot] + (8 * tb + 2 * t + e) * (NKP * KV_BLOCK_BYTES) + kp * KV_BLOCK_BYTES))
                                         : 0.f;
                     } else {
@@ -355,7 +361,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                         w1 = cw.y;
 #pragma unroll
                         for (int e = 0; e < 2; ++e) {
-                            const int tk = min(tok0 + 8 * tb + 2 * t + e, t1 - 1);
+                            const int tk = FULL ? tok0 + 8 * tb + 2 * t + e : min(tok0 + 8 * tb + 2 * t + e, t1 - 1);
                             ks[e] = __half2float(ldkv(static_cast<const __half*>(P.kv.k1) + (head_row + tk) * NKP + kp, fresh));
                         }
                     }
@@ -371,7 +377,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
             }
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const bool valid = tok0 + 8 * tb + 2 * t + e < t1;
+                const bool valid = FULL || tok0 + 8 * tb + 2 * t + e < t1;
                 s[tb][e] = valid ? sc[e] * P.scale_log2 : NEG_BIG;
             }
         }
@@ -387,7 +393,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
         for (int tb = 0; tb < 2; ++tb)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                p[tb][e] = s[tb][e] > 0.5f * NEG_BIG ? exp2f(s[tb][e] - m_new) : 0.f;
+                p[tb][e] = (FULL || s[tb][e] > 0.5f * NEG_BIG) ? exp2f(s[tb][e] - m_new) : 0.f;
                 ls += p[tb][e];
             }
         ls += __shfl_xor_sync(0xffffffffu, ls, 1);
@@ -406,7 +412,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
         // ---------------- O += P V
         int vtok[4];                                   // this thread's four contraction tokens
 #pragma unroll
-        for (int i = 0; i < 4; ++i) vtok[i] = min(tok0 + (i >> 1) * 8 + 2 * t + (i & 1), t1 - 1);
+        for (int i = 0; i < 4; ++i)
+            vtok[i] = FULL ? tok0 + (i >> 1) * 8 + 2 * t + (i & 1) : min(tok0 + (i >> 1) * 8 + 2 * t + (i & 1), t1 - 1);
         // P enters the tensor core as fp16 hi + lo halves (two products), which keeps ~22 bits of it
         const float pb[4] = {p[0][0] * P_BIAS, p[0][1] * P_BIAS, p[1][0] * P_BIAS, p[1][1] * P_BIAS};
         uint32_t pa0 = pack_h2(pb[0], pb[1]), pa2 = pack_h2(pb[2], pb[3]);
@@ -438,22 +445,19 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                         uint32_t dummy;
                         if (kp & 1) lds_words_align2<false>(row + 2 + 4 * g, w[i], dummy, false);
                         else lds_words_align2<true>(row + 2 + 4 * g, w[i], dummy, false);
-                        vs[i] = tok0 + (i >> 1) * 8 + 2 * t + (i & 1) < t1 ? half_bits_to_f32(lds16(row)) : 0.f;
+                        vs[i] = (FULL || tok0 + (i >> 1) * 8 + 2 * t + (i & 1) < t1) ? half_bits_to_f32(lds16(row)) : 0.f;
                     } else {
                         w[i] = ldkv(reinterpret_cast<const uint32_t*>(static_cast<const int8_t*>(P.kv.v0) + (head_row + vtok[i]) * D + 32 * kp + 4 * g), fresh);
                         vs[i] = __half2float(ldkv(static_cast<const __half*>(P.kv.v1) + (head_row + vtok[i]) * NKP + kp, fresh));
                     }
-                    w[i] ^= 0x80808080u;
                 }
-                // 4x4 byte transpose: T[e] = (w0.b[e], w1.b[e], w2.b[e], w3.b[e])
-                const uint32_t lo01 = prmt(w[0], w[1], 0x5140u), hi01 = prmt(w[0], w[1], 0x7362u);
-                const uint32_t lo23 = prmt(w[2], w[3], 0x5140u), hi23 = prmt(w[2], w[3], 0x7362u);
-                const uint32_t T[4] = {prmt(lo01, lo23, 0x5410u), prmt(lo01, lo23, 0x7632u),
-                                       prmt(hi01, hi23, 0x5410u), prmt(hi01, hi23, 0x7632u)};
+                // product e takes byte e of the four words: a byte permute puts the codes of two tokens into the
+                // low bytes of the two halves, one logic op clears the high bytes and adds the 128
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    b0[e] = prmt(T[e], 0u, 0x4140u);
-                    b1[e] = prmt(T[e], 0u, 0x4342u);
+                    const uint32_t sel = 0x4400u + 0x1111u * e;
+                    b0[e] = (prmt(w[0], w[1], sel) & 0x00ff00ffu) ^ 0x00800080u;
+                    b1[e] = (prmt(w[2], w[3], sel) & 0x00ff00ffu) ^ 0x00800080u;
                 }
                 // P' = p * (block scale of the token) as fp16 hi + lo; keep its sum for the +128
                 const float f0 = pb[0] * vs[0], f1 = pb[1] * vs[1], f2 = pb[2] * vs[2], f3 = pb[3] * vs[3];
@@ -462,8 +466,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                 const float2 r0 = unpack_h2(pa0), r2 = unpack_h2(pa2);
                 pl0 = pack_h2(f0 - r0.x, f1 - r0.y);
                 pl2 = pack_h2(f2 - r2.x, f3 - r2.y);
-                const float2 q0 = unpack_h2(pl0), q2 = unpack_h2(pl2);
-                ocorr[kp] += ((r0.x + r0.y) + (r2.x + r2.y)) + ((q0.x + q0.y) + (q2.x + q2.y));
+                // (hi + lo equals f to 2^-22: below what the offset's factor 128 could make visible)
+                ocorr[kp] += (f0 + f1) + (f2 + f3);
             }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -491,6 +495,9 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                 }
             }
         }
+        };
+        if (tok0 + 16 <= t1) tile_body(std::true_type{});
+        else tile_body(std::false_type{});
         __syncwarp();
     }
     if (PAGED && !ok) {

@@ -189,6 +189,11 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
         }
     }
 
+    // Q6_K without the cached fragments: the next super-block's activations are requested while this one is
+    // worked on (the sequence of super-blocks is the warp's slice, again for every tile)
+    uint2 xahead[2] = {};
+    if (KIND == Q6 && !CACHE && my_tiles > 0) load_xraw6(xahead, xsrc, sb_lo, g, t);
+
     bool ok = true;
     int c_slot = 0;
     uint32_t c_ph = 0;
@@ -215,7 +220,10 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
 #pragma unroll
                 for (int i = 0; i < SBS; ++i) {
                     if constexpr (KIND == Q6) {
-                        if (!CACHE) load_xfrag6(xc[0], xsrc, sb, g, t);
+                        if (!CACHE) {
+                            build_xfrag6(xc[0], xahead);
+                            load_xraw6(xahead, xsrc, sb + 1 < sb_lo + slice ? sb + 1 : sb_lo, g, t);
+                        }
                         const uint32_t off = static_cast<uint32_t>(sb * BLK) & 15u;
                         if (off & 2u) unit_q6k<false>(slot[0] + off, xc[0], g, t, acc[0][0], acc[0][1]);
                         else unit_q6k<true>(slot[0] + off, xc[0], g, t, acc[0][0], acc[0][1]);

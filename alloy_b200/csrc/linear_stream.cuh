@@ -291,11 +291,17 @@ struct XFrag6 {
     uint32_t b[2][2];        // [half][k slots (0, 2) | (1, 3)]
     float sx[2][2];          // [half][sub-block 2t, 2t+1 of the half]
 };
-__device__ __forceinline__ void load_xfrag6(XFrag6& f, const __half* x, int sb, int g, int t) {
+// The lane's eight activations of super-block sb as loaded (two 8-byte loads), and the fragments from them:
+// the loads are issued a super-block ahead of their use.
+__device__ __forceinline__ void load_xraw6(uint2 (&r)[2], const __half* x, int sb, int g, int t) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) r[h] = *reinterpret_cast<const uint2*>(x + sb * QK_K + 128 * h + 16 * g + 4 * t);
+}
+__device__ __forceinline__ void build_xfrag6(XFrag6& f, const uint2 (&r)[2]) {
     constexpr uint32_t ONE2 = 0x3C003C00u;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        const uint2 v = *reinterpret_cast<const uint2*>(x + sb * QK_K + 128 * h + 16 * g + 4 * t);
+        const uint2 v = r[h];
         f.b[h][0] = prmt(v.x, v.y, 0x5410u);
         f.b[h][1] = prmt(v.x, v.y, 0x7632u);
         float s[4];
@@ -303,6 +309,11 @@ __device__ __forceinline__ void load_xfrag6(XFrag6& f, const __half* x, int sb, 
         f.sx[h][0] = s[0];
         f.sx[h][1] = s[1];
     }
+}
+__device__ __forceinline__ void load_xfrag6(XFrag6& f, const __half* x, int sb, int g, int t) {
+    uint2 r[2];
+    load_xraw6(r, x, sb, g, t);
+    build_xfrag6(f, r);
 }
 
 // One super-block of 16 rows; `blk` = slot + the block's offset inside the aligned window.
