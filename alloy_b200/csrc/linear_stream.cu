@@ -44,7 +44,8 @@ template <int KIND, int RT, bool CACHE, int GW, bool GU = false>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     constexpr int SBS = Geom<KIND>::SBS, PITCH = Geom<KIND>::PITCH, SLOT = 16 * PITCH, BLK = Geom<KIND>::BLK;
-    using XF = typename std::conditional<KIND == Q6, XFrag6, XFrag>::type;
+    constexpr bool MIX = KIND == QMIX;             // Q4_K tiles (two super-blocks per slot) first, Q6_K tiles after them
+    static_assert(!MIX || (RT == 1 && !GU && GW > 1), "mixed formats: plain linears with a K split");
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int grp = warp / GW, wg = warp % GW;
@@ -76,53 +77,58 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     // when GW does not divide the count (one-super-block slots only)
     const int sb_lo = (wg * P.nsb) / GW;
     const int slice = ((wg + 1) * P.nsb) / GW - sb_lo;
-    const int spt = (slice / SBS) * RT;                              // stages per tile
-    int my_tiles = 0;
+    // stages per tile (a Q6_K tile of a mixed launch has one super-block per slot)
+    auto spt_of = [&](int seg) { return (MIX && P.seg[seg].q6) ? slice : (slice / SBS) * RT; };
+    int my_tiles = 0, n_stage = 0;
     {
         Cursor c = {0, 0, 0};
-        cursor_enter(c, P, lo, hi);
-        cursor_next(c, P, lo, hi, GU ? 0 : grp);
+        cursor_enter<MIX>(c, P, lo, hi);
+        cursor_next<MIX>(c, P, lo, hi, GU ? 0 : grp);
         while (c.seg < P.n_seg) {
             ++my_tiles;
-            cursor_next(c, P, lo, hi, tstep);
+            n_stage += spt_of(c.seg);
+            cursor_next<MIX>(c, P, lo, hi, tstep);
         }
     }
-    const int n_stage = my_tiles * spt;
 
     // producer side: stage sequence = for tile, for slot-sized step of the slice, for matrix
     Cursor pc = {0, 0, 0};
-    cursor_enter(pc, P, lo, hi);
-    cursor_next(pc, P, lo, hi, GU ? 0 : grp);
+    cursor_enter<MIX>(pc, P, lo, hi);
+    cursor_next<MIX>(pc, P, lo, hi, GU ? 0 : grp);
     int issued = 0, p_r = 0, p_slot = 0;
     auto issue = [&]() {
-        const int sb = sb_lo + (p_r / RT) * SBS, mt = p_r % RT;
+        // the geometry of this stage's tile (fixed by KIND unless the launch mixes formats)
+        const bool six = KIND == Q6 || (MIX && P.seg[pc.seg].q6);
+        const int sbs = MIX ? (six ? 1 : 2) : SBS, blk = MIX ? (six ? Q6K_BYTES : Q4K_BYTES) : BLK;
+        const int pitch = MIX ? (six ? Geom<Q6>::PITCH : Geom<Q4x2>::PITCH) : PITCH;
+        const int sb = sb_lo + (p_r / RT) * sbs, mt = p_r % RT;
         const int si = GU ? grp : (P.gated ? mt : pc.seg);
         const int nvalid = pc.lim - pc.row < 16 ? pc.lim - pc.row : 16;
         const uint32_t bar = bar0 + 8 * p_slot, dst = ring + p_slot * SLOT;
-        const int win = (sb * BLK) & ~15;                            // 16-byte-aligned start of the stage in a row
+        const int win = (sb * blk) & ~15;                            // 16-byte-aligned start of the stage in a row
         {
             if (nvalid == 16) {
                 if (lane == 0) {
-                    mbar_expect_tx(bar, SLOT);
+                    mbar_expect_tx(bar, 16 * pitch);
                     tma_2d(dst, &maps.m[si], win / 4, pc.row, bar);
                 }
             } else {
-                int bytes = SBS * BLK;
-                if (KIND == Q6) {
+                int bytes = sbs * blk;
+                if (six) {
                     const int left = static_cast<int>(P.seg[si].row_bytes) - win;
-                    bytes = left < PITCH ? left : PITCH;
+                    bytes = left < pitch ? left : pitch;
                 }
                 if (lane == 0) mbar_expect_tx(bar, nvalid * bytes);
                 __syncwarp();
                 if (lane < nvalid)
-                    bulk_g2s(dst + lane * PITCH, P.seg[si].data + (pc.row + lane) * P.seg[si].row_bytes + win, bytes, bar);
+                    bulk_g2s(dst + lane * pitch, P.seg[si].data + (pc.row + lane) * P.seg[si].row_bytes + win, bytes, bar);
             }
         }
         ++issued;
         if (++p_slot == D) p_slot = 0;
-        if (++p_r == spt) {
+        if (++p_r == spt_of(pc.seg)) {
             p_r = 0;
-            cursor_next(pc, P, lo, hi, tstep);
+            cursor_next<MIX>(pc, P, lo, hi, tstep);
         }
     };
     while (issued < n_stage && issued < D) issue();
@@ -180,12 +186,15 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     }
 
     const ScaleSel ss = make_scale_sel(t);
-    XF xc[CACHE ? SBS : 1];
+    // the token's fragments of this warp's slice, kept in registers where the slice is a single slot
+    XFrag xc[(CACHE && KIND != Q6) ? SBS : 1];
+    XFrag6 xc6;
     if (CACHE) {
+        if constexpr (KIND == Q6) {
+            load_xfrag6(xc6, xsrc, sb_lo, g, t);
+        } else {
 #pragma unroll
-        for (int i = 0; i < SBS; ++i) {
-            if constexpr (KIND == Q6) load_xfrag6(xc[i], xsrc, sb_lo + i, g, t);
-            else load_xfrag(xc[i], xsrc, sb_lo + i, g, t);
+            for (int i = 0; i < SBS; ++i) load_xfrag(xc[i], xsrc, sb_lo + i, g, t);
         }
     }
 
@@ -198,13 +207,17 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     int c_slot = 0;
     uint32_t c_ph = 0;
     Cursor cc = {0, 0, 0};
-    cursor_enter(cc, P, lo, hi);
-    cursor_next(cc, P, lo, hi, GU ? 0 : grp);
-    for (int it = 0; it < my_tiles; ++it) {
+    cursor_enter<MIX>(cc, P, lo, hi);
+    cursor_next<MIX>(cc, P, lo, hi, GU ? 0 : grp);
+    int it = 0;
+    // One tile of kind TK (the launch's own kind; a mixed launch runs its Q4_K tiles, then its Q6_K tiles).
+    auto run_tile = [&](auto kind_c) {
+        constexpr int TK = decltype(kind_c)::value;
+        constexpr int T_SBS = Geom<TK>::SBS, T_PITCH = Geom<TK>::PITCH, T_BLK = Geom<TK>::BLK;
         float acc[RT][2];
 #pragma unroll
         for (int m = 0; m < RT; ++m) acc[m][0] = acc[m][1] = 0.f;
-        for (int sb = sb_lo; sb < sb_lo + slice; sb += SBS) {
+        for (int sb = sb_lo; sb < sb_lo + slice; sb += T_SBS) {
             uint32_t slot[RT];
 #pragma unroll
             for (int mt = 0; mt < RT; ++mt) {
@@ -218,20 +231,23 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
             ok = __all_sync(0xffffffffu, ok);
             if (ok) {
 #pragma unroll
-                for (int i = 0; i < SBS; ++i) {
-                    if constexpr (KIND == Q6) {
-                        if (!CACHE) {
-                            build_xfrag6(xc[0], xahead);
+                for (int i = 0; i < T_SBS; ++i) {
+                    if constexpr (TK == Q6) {
+                        XFrag6 x6;
+                        if constexpr (KIND == Q6 && CACHE) {
+                            x6 = xc6;
+                        } else {
+                            build_xfrag6(x6, xahead);
                             load_xraw6(xahead, xsrc, sb + 1 < sb_lo + slice ? sb + 1 : sb_lo, g, t);
                         }
-                        const uint32_t off = static_cast<uint32_t>(sb * BLK) & 15u;
-                        if (off & 2u) unit_q6k<false>(slot[0] + off, xc[0], g, t, acc[0][0], acc[0][1]);
-                        else unit_q6k<true>(slot[0] + off, xc[0], g, t, acc[0][0], acc[0][1]);
+                        const uint32_t off = static_cast<uint32_t>(sb * T_BLK) & 15u;
+                        if (off & 2u) unit_q6k<false>(slot[0] + off, x6, g, t, acc[0][0], acc[0][1]);
+                        else unit_q6k<true>(slot[0] + off, x6, g, t, acc[0][0], acc[0][1]);
                     } else {
                         if (!CACHE) load_xfrag(xc[0], xsrc, sb + i, g, t);
 #pragma unroll
                         for (int mt = 0; mt < RT; ++mt)
-                            unit_q4k<PITCH>(slot[mt] + i * BLK, xc[CACHE ? i : 0], ss, g, t, acc[mt][0], acc[mt][1]);
+                            unit_q4k<T_PITCH>(slot[mt] + i * T_BLK, xc[CACHE ? i : 0], ss, g, t, acc[mt][0], acc[mt][1]);
                     }
                 }
             }
@@ -313,7 +329,15 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
                 store(tl, v, u);
             }
         }
-        cursor_next(cc, P, lo, hi, tstep);
+        cursor_next<MIX>(cc, P, lo, hi, tstep);
+        ++it;
+    };
+    if constexpr (MIX) {
+        while (it < my_tiles && !P.seg[cc.seg].q6) run_tile(std::integral_constant<int, Q4x2>{});
+        if (it < my_tiles) load_xraw6(xahead, xsrc, sb_lo, g, t);
+        while (it < my_tiles) run_tile(std::integral_constant<int, Q6>{});
+    } else {
+        while (it < my_tiles) run_tile(std::integral_constant<int, KIND>{});
     }
     if (RT == 1 && !GU && P.tp.world) {
         // ---- all-reduce of this CTA's rows: publish, wait for the same CTA of every rank, sum in
@@ -526,6 +550,52 @@ int try_gemv_stream(const void* x, int M, int K, int dtype, const WeightSeg* seg
 #undef ALLOYB_ST_LAUNCH
 }
 
+// Q4_K matrices and Q6_K matrices of one token in ONE launch (q/k and v of a decode step): the Q4_K rows
+// first, a Q6_K row counted Q6_ROW_COST times when the rows are shared out over the CTAs.  The caller has
+// checked formats, alignment and row lengths; K is a multiple of 16 super-blocks (eight K slices of whole
+// two-super-block slots).
+static int launch_mixed(const void* x, int K, const WeightSeg (*grp)[MAX_SEGS], const int* cnt, const void* norm_w,
+                        float eps, cudaStream_t stream) {
+    using namespace st;
+    const int nsb = K / QK_K;
+    Params P = {};
+    Maps maps;
+    P.x = static_cast<const __half*>(x);
+    P.norm_w = static_cast<const __half*>(norm_w);
+    P.eps = eps;
+    P.nsb = nsb;
+    P.depth = 2;
+    const EncodeFn encode = encoder();
+    if (!encode) { set_cuda_error(cudaErrorNotSupported); return ALLOYB_E_CUDA; }
+    int64_t units = 0;
+    int n = 0;
+    for (int f = 0; f < 2; ++f)
+        for (int i = 0; i < cnt[f]; ++i, ++n) {
+            const WeightSeg& w = grp[f][i];
+            P.seg[n].data = static_cast<const uint8_t*>(w.data);
+            P.seg[n].row_bytes = w.row_bytes;
+            P.seg[n].y = w.y;
+            P.seg[n].n_rows = w.N;
+            P.seg[n].row_base = static_cast<int>(units);
+            P.seg[n].q6 = f;
+            units += static_cast<int64_t>(w.N) * (f ? Q6_ROW_COST : 1);
+            if (units > (1 << 30)) return ALLOYB_NOT_TAKEN;
+            const int pitch = f ? Geom<Q6>::PITCH : Geom<Q4x2>::PITCH;
+            const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(w.row_bytes) / 4, static_cast<cuuint64_t>(w.N)};
+            const cuuint64_t gstr[1] = {static_cast<cuuint64_t>(w.row_bytes)};
+            const cuuint32_t box[2] = {static_cast<cuuint32_t>(pitch / 4), 16};
+            const cuuint32_t estr[2] = {1, 1};
+            const CUresult cr = encode(&maps.m[n], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(w.data), gdim, gstr, box,
+                                       estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (cr != CUDA_SUCCESS) { set_cuda_error(cudaErrorInvalidValue); return ALLOYB_E_CUDA; }
+        }
+    for (int i = n; i < MAX_SEG; ++i) maps.m[i] = maps.m[0];
+    P.n_seg = n;
+    P.total_rows = static_cast<int>(units);
+    return nsb == 16 ? launch<QMIX, 1, true, 8>(maps, P, stream) : launch<QMIX, 1, false, 8>(maps, P, stream);
+}
+
 int try_gemv_stream_mixed(const void* x, int M, int K, int dtype, const WeightSeg* seg, int n_seg, const void* residual,
                           const void* norm_w, float eps, cudaStream_t stream) {
     if (M != 1 || n_seg < 1 || n_seg > MAX_SEGS) return ALLOYB_NOT_TAKEN;
@@ -545,6 +615,10 @@ int try_gemv_stream_mixed(const void* x, int M, int K, int dtype, const WeightSe
         if (reinterpret_cast<uintptr_t>(seg[i].data) % 16 || seg[i].row_bytes % 16 || seg[i].N <= 0 ||
             seg[i].row_bytes < static_cast<int64_t>(K / QK_K) * (seg[i].format == ALLOYB_Q4_K ? Q4K_BYTES : Q6K_BYTES))
             return ALLOYB_NOT_TAKEN;
+    // one launch for both formats where the K split is whole slots (else one launch per format)
+    if ((K / QK_K) % 16 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(norm_w) % 16 == 0 &&
+        !(norm_w && K > 16384))
+        return launch_mixed(x, K, grp, cnt, norm_w, eps, stream);
     for (int f = 0; f < 2; ++f) {
         const int rc = try_gemv_stream(x, M, K, dtype, grp[f], cnt[f], false, 0, nullptr, norm_w, eps, stream, nullptr);
         if (rc != ALLOYB_OK) return rc == ALLOYB_NOT_TAKEN ? ALLOYB_E_SHAPE : rc;

@@ -32,11 +32,16 @@ constexpr int MAX_DEVICES = 64;
 //         the slot row is the 16-byte-aligned window [floor16(210 sb), +240) and the block sits
 //         at offset (210 sb) mod 16 inside it; pitch 240 = 60 words (28 mod 32: 32-bit reads of
 //         eight rows x four lanes are conflict-free).
-enum Kind { Q4x1 = 0, Q4x2 = 1, Q6 = 2 };
+//   QMIX: Q4_K matrices (as Q4x2) followed by Q6_K matrices in one launch (q/k and v of a decode step);
+//         a slot is as large as the larger of the two, every tile uses its own format's geometry.
+enum Kind { Q4x1 = 0, Q4x2 = 1, Q6 = 2, QMIX = 3 };
 template <int KIND> struct Geom;
 template <> struct Geom<Q4x1> { static constexpr int SBS = 1, PITCH = 144, BLK = Q4K_BYTES; };
 template <> struct Geom<Q4x2> { static constexpr int SBS = 2, PITCH = 304, BLK = Q4K_BYTES; };
 template <> struct Geom<Q6> { static constexpr int SBS = 1, PITCH = 240, BLK = Q6K_BYTES; };
+template <> struct Geom<QMIX> { static constexpr int SBS = 2, PITCH = 304, BLK = Q4K_BYTES; };
+// What a Q6_K row costs next to a Q4_K row (instructions and bytes) when a mixed launch shares its rows out.
+constexpr int Q6_ROW_COST = 2;
 
 static __device__ int g_error = 0;           // sticky: a bounded wait ran out (one word per translation unit)
 
@@ -58,6 +63,7 @@ struct Seg {
     void* y;
     int n_rows;
     int row_base;                            // first row of this matrix in the launch's stacked row space
+    int q6;                                  // mixed launches: 1 = Q6_K rows (stacked space in cost units)
 };
 struct Params {
     const __half* x;
@@ -81,11 +87,19 @@ struct Maps {
 struct Cursor {
     int seg, row, lim;
 };
+// COST: the stacked space counts a Q6_K row Q6_ROW_COST times (mixed launches); a row belongs to the range
+// its first unit falls into.
+template <bool COST = false>
 __device__ __forceinline__ void cursor_enter(Cursor& c, const Params& P, int lo, int hi) {
     while (c.seg < P.n_seg) {
         const int base = P.seg[c.seg].row_base, n = P.seg[c.seg].n_rows;
-        const int a = lo > base ? lo - base : 0;
-        const int b = hi - base < n ? hi - base : n;
+        int a = lo > base ? lo - base : 0;
+        int b = hi - base;
+        if (COST && P.seg[c.seg].q6) {
+            a = (a + Q6_ROW_COST - 1) / Q6_ROW_COST;
+            b = b > 0 ? (b + Q6_ROW_COST - 1) / Q6_ROW_COST : 0;
+        }
+        if (b > n) b = n;
         if (a < b) {
             c.row = a;
             c.lim = b;
@@ -94,12 +108,13 @@ __device__ __forceinline__ void cursor_enter(Cursor& c, const Params& P, int lo,
         ++c.seg;
     }
 }
+template <bool COST = false>
 __device__ __forceinline__ void cursor_next(Cursor& c, const Params& P, int lo, int hi, int steps) {
     for (int i = 0; i < steps && c.seg < P.n_seg; ++i) {
         c.row += 16;
         if (c.row >= c.lim) {
             ++c.seg;
-            cursor_enter(c, P, lo, hi);
+            cursor_enter<COST>(c, P, lo, hi);
         }
     }
 }

@@ -339,11 +339,10 @@ class QuantLlamaDecoder:
         h = ops._embedding(self.ids, ops._FORMATS[self.embed_fmt], self.embed, None, out_dtype=self.dtype)
         scale = 1.0 / (s.head_dim ** 0.5)
         for li, lw in enumerate(self.layers):
-            # q/k (Q4_K) and v (Q6_K) run as one streaming launch per format; the norm stays its own
-            # kernel here (folding it into both launches measured slower)
-            xn = ops.rms_norm(h, lw.norm_in, s.eps)
-            q, k, v = ops.linear_multi(xn, [(lw.fmt["wq"], lw.wq, None), (lw.fmt["wk"], lw.wk, None),
-                                            (lw.fmt["wv"], lw.wv, None)])
+            # q/k (Q4_K) and v (Q6_K) of one token run as ONE streaming launch that also applies the input
+            # RMSNorm (several tokens: the norm, then the projections)
+            q, k, v = ops.linear_multi(h, [(lw.fmt["wq"], lw.wq, None), (lw.fmt["wk"], lw.wk, None),
+                                           (lw.fmt["wv"], lw.wv, None)], norm=(lw.norm_in, s.eps))
             q3 = q.view(b, self.heads_l, s.head_dim)
             k3 = k.view(b, self.kv_heads_l, s.head_dim)
             v3 = v.view(b, self.kv_heads_l, s.head_dim)

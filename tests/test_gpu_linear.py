@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from alloy_b200 import ops, quant, synth
+from alloy_b200 import _lib, ops, quant, synth
 from oracle import blocks as O
 from tests._util import GEMM_MIN_TOKENS, assert_close, same_bits_f32, to_np
 
@@ -178,6 +178,39 @@ def test_linear_normed_qkv_and_gate_up(m, dt):
     y = ops.gated_normed(x.to(DEV), nw.to(DEV), eps, _dev(g), _dev(u))
     ref = O.silu(O.mm_ref_f64(xn, O.dequant_q4_k(g))) * O.mm_ref_f64(xn, O.dequant_q4_k(u))
     assert_close(to_np(y), ref, tdt, f"normed gate/up m={m} {dt}")
+
+
+# One token against Q4_K and Q6_K matrices in a single streaming launch (q/k and v of a decode step): rows
+# of both formats shared out by cost, ragged row counts, the Q6_K matrix named first, two matrices per
+# format, a K of 32 super-blocks (fragments not cached), with and without the fused RMSNorm.
+@pytest.mark.parametrize("k,q4_rows,q6_rows,normed", [
+    (4096, (4096, 1024), (1024,), True),
+    (4096, (200, 40), (7,), False),
+    (8192, (1024, 136), (520, 24), True),
+    (4096, (16,), (2048, 1000), False),
+])
+def test_mixed_formats_one_launch(k, q4_rows, q6_rows, normed):
+    rng = np.random.default_rng([k, len(q4_rows), q6_rows[0]])
+    eps = 1e-5
+    x = torch.from_numpy(2.0 * synth.activations(rng, 1, k, np.float32)).to(torch.float16)
+    w4 = [synth.q4k_blocks(rng, n, k) for n in q4_rows]
+    w6 = [synth.q6k_blocks(rng, n, k) for n in q6_rows]
+    # Q6_K first: the launch sorts by format, the outputs keep the caller's order
+    specs = [("q6_k", _dev(w), None) for w in w6] + [("q4_k", _dev(w), None) for w in w4]
+    refs = [O.dequant_q6_k(w) for w in w6] + [O.dequant_q4_k(w) for w in w4]
+    if normed:
+        nw = torch.from_numpy((1.0 + 0.1 * rng.standard_normal(k)).astype(np.float32)).to(torch.float16)
+        xr = (x.float() * torch.rsqrt((x.float() ** 2).mean(dim=1, keepdim=True) + eps)).to(torch.float16)
+        xin = (nw.float() * xr.float()).to(torch.float16).float().numpy()
+        outs = ops.linear_multi(x.to(DEV), specs, norm=(nw.to(DEV), eps))
+    else:
+        xin = x.float().numpy()
+        outs = ops.linear_multi(x.to(DEV), specs)
+    torch.cuda.synchronize()
+    assert _lib.load().alloyb_device_error(1) == 0
+    for y, wf in zip(outs, refs):
+        assert y.shape == (1, wf.shape[0])
+        assert_close(to_np(y), O.mm_ref_f64(xin, wf), torch.float16, f"mixed k={k} rows={wf.shape[0]}")
 
 
 # Row-parallel linear with the all-reduce inside the launch: with one rank the exchange
