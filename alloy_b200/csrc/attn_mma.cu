@@ -195,6 +195,24 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
     const int t1 = min(len, t0 + chunk);
     const int n_tiles = t1 > t0 ? (t1 - t0 + 15) / 16 : 0;
 
+    // q (and the angles' frequencies) are requested first: nothing below has to wait for them in turn
+    const bool q_vec = P.q_dtype == ALLOYB_F16 && ((reinterpret_cast<uintptr_t>(P.q) | (P.q_bs * 2) | (P.q_hs * 2)) & 15) == 0;
+    uint4 qraw[NKP];
+    float freq_own[2] = {0.f, 0.f};
+    if (q_vec) {
+        // eight consecutive fp16 of head g per 32-dim block: one 16-byte load each
+#pragma unroll
+        for (int kp = 0; kp < NKP; ++kp) {
+            const int64_t base = b * P.q_bs + static_cast<int64_t>(kvh * G + g) * P.q_hs + 32 * kp + 8 * t;
+            qraw[kp] = make_uint4(0u, 0u, 0u, 0u);
+            if (g < G) qraw[kp] = __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(P.q) + base));
+        }
+        if (P.fused) {
+#pragma unroll
+            for (int kp = 0; kp < 2; ++kp) freq_own[kp] = __ldg(P.fuse.inv_freq + 32 * kp + 8 * t + g);
+        }
+    }
+
     if (P.fused && pos_in >= t0 && pos_in < t0 + chunk && pos_in >= 0 && pos_in < P.kv.S_max) {
         // ---- the decode token's K / V rows: rotate K, append both (this CTA reads them back below)
         if (warp < 2) {
@@ -211,24 +229,19 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
         }
         store_kv_block<LAYOUT>(P.kv, 1, b, kvh, pos_in, warp, lane,
                                P.fuse.new_v[b * P.fuse.new_bs + kvh * P.fuse.new_hs + 32 * warp + lane], P.KV_H, D, P.status);
-        __threadfence();
-        asm volatile("fence.proxy.async.global;" ::: "memory");       // the paged tiles come in by bulk copies
+        // this CTA reads the rows back: the barrier orders its own loads behind its stores; the paged tiles come
+        // in by bulk copies, which sit behind a device-wide fence and one between the two memory proxies
+        if (PAGED) {
+            __threadfence();
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         __syncthreads();
     }
 
     // ---- Q fragments (rows = heads of this group; rows >= G are zero) and per-block sums of q
     uint32_t qa[NKP][2][2];
     float qsum[NKP];
-    const bool q_vec = P.q_dtype == ALLOYB_F16 && ((reinterpret_cast<uintptr_t>(P.q) | (P.q_bs * 2) | (P.q_hs * 2)) & 15) == 0;
-    uint4 qraw[NKP];
     if (q_vec) {
-        // eight consecutive fp16 of head g per 32-dim block: one 16-byte load each
-#pragma unroll
-        for (int kp = 0; kp < NKP; ++kp) {
-            const int64_t base = b * P.q_bs + static_cast<int64_t>(kvh * G + g) * P.q_hs + 32 * kp + 8 * t;
-            qraw[kp] = make_uint4(0u, 0u, 0u, 0u);
-            if (g < G) qraw[kp] = __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(P.q) + base));
-        }
         if (P.fused) {
             // rotate-half RoPE in registers: dims d = 32 kp + 8 t + e (kp = 0, 1) pair with d + 64 (kp + 2).
             // The eight lanes of a column t need the same eight angles: lane (g, t) evaluates e = g and
@@ -238,7 +251,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                 __half* lo = reinterpret_cast<__half*>(&qraw[kp]);
                 __half* hi = reinterpret_cast<__half*>(&qraw[kp + 2]);
                 float sn_own, cs_own;
-                sincosf(static_cast<float>(pos_in) * __ldg(P.fuse.inv_freq + 32 * kp + 8 * t + g), &sn_own, &cs_own);
+                sincosf(static_cast<float>(pos_in) * freq_own[kp], &sn_own, &cs_own);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     const float sn = __shfl_sync(0xffffffffu, sn_own, e * 4 + t);
@@ -569,18 +582,30 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
         const int64_t pi = (static_cast<int64_t>(b) * P.H + kvh * G + hg) * P.splits + split;
         *reinterpret_cast<float4*>(P.part_o + pi * D + d) = acc;
     }
-    __threadfence();
+    // One release-acquire count per CTA instead of a fence by every thread: the barrier puts the CTA's stores
+    // before thread 0's release, the last CTA's acquire (and its barrier) puts every split's stores before the
+    // loads below.
     __syncthreads();
     if (threadIdx.x == 0) {
-        const unsigned int prev = atomicAdd(P.counters + b * P.KV_H + kvh, 1u);
+        unsigned int prev;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(prev) : "l"(P.counters + b * P.KV_H + kvh) : "memory");
         s_last = (prev == static_cast<unsigned int>(P.splits) - 1u);
         if (s_last) P.counters[b * P.KV_H + kvh] = 0u;
     }
     __syncthreads();
     if (!s_last) return;
-    __threadfence();
     // split weights: one warp per head (lanes over the splits), then 16-byte loads of the partials
     float* wgt = reinterpret_cast<float*>(sm_buf);            // [G][splits], splits <= 64
+    // the first eight partials of this thread's output are requested before the weights are worked out
+    const bool mine = threadIdx.x < G * (D / 4);
+    const int my_hg = threadIdx.x / (D / 4), my_d = (threadIdx.x - my_hg * (D / 4)) * 4;
+    const float4* my_po =
+        reinterpret_cast<const float4*>(P.part_o + (static_cast<int64_t>(b) * P.H + kvh * G + my_hg) * P.splits * D + my_d);
+    float4 first[8];
+    if (mine && P.splits >= 8) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) first[u] = __ldcg(my_po + static_cast<int64_t>(u) * (D / 4));
+    }
     __syncthreads();
     for (int hg = warp; hg < G; hg += WARPS) {
         const float* lse = P.part_lse + (static_cast<int64_t>(b) * P.H + kvh * G + hg) * P.splits;
@@ -604,8 +629,13 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
         int s2 = 0;
         for (; s2 + 8 <= P.splits; s2 += 8) {
             float4 v[8];
+            if (s2 == 0 && i == threadIdx.x) {
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = __ldcg(po + static_cast<int64_t>(s2 + u) * (D / 4));
+                for (int u = 0; u < 8; ++u) v[u] = first[u];
+            } else {
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = __ldcg(po + static_cast<int64_t>(s2 + u) * (D / 4));
+            }
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 acc.x = fmaf(w[s2 + u], v[u].x, acc.x);
