@@ -187,7 +187,6 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
         pos = P.kv.S_max - 1;
     }
     const int len = pos + 1;
-    const bool fresh = P.fused != 0;
     // this CTA's token range (whole 64-token passes of the four warps per split)
     int chunk = (len + P.splits - 1) / P.splits;
     chunk = (chunk + 63) & ~63;
@@ -236,6 +235,35 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
             asm volatile("fence.proxy.async.global;" ::: "memory");
         }
         __syncthreads();
+    }
+
+    // fp16 cache: a tile's K and V words are requested a phase ahead of their use -- the first tile's before the
+    // q fragments are built, the next tile's K after this tile's scores, its V after this tile's products
+    const bool fresh = P.fused != 0;
+    const int64_t head_row = (static_cast<int64_t>(b) * P.KV_H + kvh) * P.kv.S_max;
+    uint4 kreg[2][NKP];
+    uint2 vreg[NKP][4];
+    auto load_k = [&](int tok0) {
+#pragma unroll
+        for (int tb = 0; tb < 2; ++tb) {
+            const int tok = min(tok0 + 8 * tb + g, t1 - 1);
+            const uint4* kr = reinterpret_cast<const uint4*>(static_cast<const __half*>(P.kv.k0) + (head_row + tok) * D) + t;
+#pragma unroll
+            for (int kp = 0; kp < NKP; ++kp) kreg[tb][kp] = ldkv(kr + kp * 4, fresh);
+        }
+    };
+    auto load_v = [&](int tok0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int vt = min(tok0 + (i >> 1) * 8 + 2 * t + (i & 1), t1 - 1);
+            const uint2* vr = reinterpret_cast<const uint2*>(static_cast<const __half*>(P.kv.v0) + (head_row + vt) * D + 4 * g);
+#pragma unroll
+            for (int kp = 0; kp < NKP; ++kp) vreg[kp][i] = ldkv(vr + kp * 8, fresh);
+        }
+    };
+    if (!Q8 && warp < n_tiles) {
+        load_k(t0 + warp * 16);
+        load_v(t0 + warp * 16);
     }
 
     // ---- Q fragments (rows = heads of this group; rows >= G are zero) and per-block sums of q
@@ -302,7 +330,6 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
 #pragma unroll
     for (int kp = 0; kp < NKP; ++kp) ocorr[kp] = 0.f;
 
-    const int64_t head_row = (static_cast<int64_t>(b) * P.KV_H + kvh) * P.kv.S_max;
     WarpStage* st = reinterpret_cast<WarpStage*>(sm_stage) + (PAGED ? warp : 0);
     const int32_t* table = static_cast<const int32_t*>(P.kv.k1) + static_cast<int64_t>(b) * P.kv.max_pages;
 
@@ -343,10 +370,9 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
             float sc[2] = {0.f, 0.f};
             if (!Q8) {
                 float c[4] = {0.f, 0.f, 0.f, 0.f};
-                const uint4* kr = reinterpret_cast<const uint4*>(static_cast<const __half*>(P.kv.k0) + (head_row + tok) * D) + t;
 #pragma unroll
                 for (int kp = 0; kp < NKP; ++kp) {
-                    const uint4 kv = ldkv(kr + kp * 4, fresh);
+                    const uint4 kv = kreg[tb][kp];
                     mma(c, qa[kp][0][0], qa[kp][0][1], kv.x, kv.y);
                     mma(c, qa[kp][1][0], qa[kp][1][1], kv.z, kv.w);
                 }
@@ -394,6 +420,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                 s[tb][e] = valid ? sc[e] * P.scale_log2 : NEG_BIG;
             }
         }
+        if (!Q8 && tile + WARPS < n_tiles) load_k(tok0 + WARPS * 16);
         // ---------------- online softmax for head g (the four lanes of a group hold the 16 tokens)
         float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -440,10 +467,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
         for (int kp = 0; kp < NKP; ++kp) {
             uint32_t b0[4], b1[4];                     // B fragments of the four products e = 0..3
             if (!Q8) {
-                uint2 w[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    w[i] = ldkv(reinterpret_cast<const uint2*>(static_cast<const __half*>(P.kv.v0) + (head_row + vtok[i]) * D + 32 * kp + 4 * g), fresh);
+                const uint2 (&w)[4] = vreg[kp];
                 b0[0] = prmt(w[0].x, w[1].x, 0x5410u); b0[1] = prmt(w[0].x, w[1].x, 0x7632u);
                 b0[2] = prmt(w[0].y, w[1].y, 0x5410u); b0[3] = prmt(w[0].y, w[1].y, 0x7632u);
                 b1[0] = prmt(w[2].x, w[3].x, 0x5410u); b1[1] = prmt(w[2].x, w[3].x, 0x7632u);
@@ -508,6 +532,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                 }
             }
         }
+        if (!Q8 && tile + WARPS < n_tiles) load_v(tok0 + WARPS * 16);
         };
         if (tok0 + 16 <= t1) tile_body(std::true_type{});
         else tile_body(std::false_type{});
