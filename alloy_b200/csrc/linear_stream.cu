@@ -70,9 +70,13 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
     __syncwarp();
     pdl_launch_dependents();
 
-    // this CTA's rows, this group's tiles (every n_groups-th), this warp's K slice
-    const int lo = static_cast<int>(static_cast<int64_t>(P.total_rows) * blockIdx.x / gridDim.x);
-    const int hi = static_cast<int>(static_cast<int64_t>(P.total_rows) * (blockIdx.x + 1) / gridDim.x);
+    // this CTA's rows (whole 16-row tiles of the stacked row space: a tile split between two CTAs would cost
+    // both of them a full tile's work), this group's tiles (every n_groups-th), this warp's K slice
+    constexpr int GRAIN = MIX ? 16 * Q6_ROW_COST : 16;
+    const int grains = (P.total_rows + GRAIN - 1) / GRAIN;
+    const int lo = static_cast<int>(static_cast<int64_t>(grains) * blockIdx.x / gridDim.x) * GRAIN;
+    const int hi_g = static_cast<int>(static_cast<int64_t>(grains) * (blockIdx.x + 1) / gridDim.x) * GRAIN;
+    const int hi = hi_g < P.total_rows ? hi_g : P.total_rows;
     // super-blocks [sb_lo, sb_lo + slice) of every tile; slices differ by at most one super-block
     // when GW does not divide the count (one-super-block slots only)
     const int sb_lo = (wg * P.nsb) / GW;
@@ -103,26 +107,13 @@ gemv_stream_kernel(const __grid_constant__ Maps maps, const Params P) {
         const int pitch = MIX ? (six ? Geom<Q6>::PITCH : Geom<Q4x2>::PITCH) : PITCH;
         const int sb = sb_lo + (p_r / RT) * sbs, mt = p_r % RT;
         const int si = GU ? grp : (P.gated ? mt : pc.seg);
-        const int nvalid = pc.lim - pc.row < 16 ? pc.lim - pc.row : 16;
         const uint32_t bar = bar0 + 8 * p_slot, dst = ring + p_slot * SLOT;
         const int win = (sb * blk) & ~15;                            // 16-byte-aligned start of the stage in a row
-        {
-            if (nvalid == 16) {
-                if (lane == 0) {
-                    mbar_expect_tx(bar, 16 * pitch);
-                    tma_2d(dst, &maps.m[si], win / 4, pc.row, bar);
-                }
-            } else {
-                int bytes = sbs * blk;
-                if (six) {
-                    const int left = static_cast<int>(P.seg[si].row_bytes) - win;
-                    bytes = left < pitch ? left : pitch;
-                }
-                if (lane == 0) mbar_expect_tx(bar, nvalid * bytes);
-                __syncwarp();
-                if (lane < nvalid)
-                    bulk_g2s(dst + lane * pitch, P.seg[si].data + (pc.row + lane) * P.seg[si].row_bytes + win, bytes, bar);
-            }
+        // one box of sixteen rows, also for the last tile of a matrix whose row count is no multiple of 16 (rows
+        // past the end come in as zeros) and for a tile cut short by the next CTA's range (its rows are read twice)
+        if (lane == 0) {
+            mbar_expect_tx(bar, 16 * pitch);
+            tma_2d(dst, &maps.m[si], win / 4, pc.row, bar);
         }
         ++issued;
         if (++p_slot == D) p_slot = 0;
