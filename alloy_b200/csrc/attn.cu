@@ -426,7 +426,7 @@ static int attn_decode_run(int layout, const void* q, int64_t q_batch_stride, in
     if (max_s < 1) max_s = 1;
     int splits = 1;
     int64_t best = INT64_MAX;
-    const int merge_w = layout == ALLOYB_KV_F16 ? 3 : 8;       // tokens' worth of merge time per split (measured)
+    const int merge_w = layout == ALLOYB_KV_F16 ? 3 : 4;       // tokens' worth of merge time per split (measured)
     for (int s = 1; s <= max_s; ++s) {
         const int64_t waves = (static_cast<int64_t>(ctas) * s + 148 * 3 - 1) / (148 * 3);
         const int64_t per = ((S_max + s - 1) / s + 63) / 64 * 64 + 256;
