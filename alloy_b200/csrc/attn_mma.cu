@@ -74,6 +74,13 @@ __device__ __forceinline__ void mma(float (&c)[4], uint32_t a0, uint32_t a2, uin
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1));
 }
+// The same product onto a zero accumulator (the zeros are the instruction's own operand: no register is set up).
+__device__ __forceinline__ void mma_z(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm("{\n\t.reg .f32 z;\n\tmov.f32 z, 0f00000000;\n\t"
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {z,z,z,z};\n\t}"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1));
+}
 // Cache loads: through the read-only path, or (fused form, where this kernel itself wrote the newest row)
 // from L2.
 template <typename T>
@@ -405,13 +412,11 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                         }
                     }
                     const uint32_t u0 = w0 ^ 0x80808080u, u1 = w1 ^ 0x80808080u;
-                    float c[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma(c, qa[kp][0][0], qa[kp][0][1], prmt(u0, 0u, 0x4140u), prmt(u0, 0u, 0x4342u));
+                    float c[4];
+                    mma_z(c, qa[kp][0][0], qa[kp][0][1], prmt(u0, 0u, 0x4140u), prmt(u0, 0u, 0x4342u));
                     mma(c, qa[kp][1][0], qa[kp][1][1], prmt(u1, 0u, 0x4140u), prmt(u1, 0u, 0x4342u));
                     sc[0] = fmaf(ks[0], fmaf(c[0], 16777216.0f, -128.0f * qsum[kp]), sc[0]);
                     sc[1] = fmaf(ks[1], fmaf(c[1], 16777216.0f, -128.0f * qsum[kp]), sc[1]);
-                    zz2 = c[2];
-                    zz3 = c[3];
                 }
             }
 #pragma unroll
@@ -514,13 +519,11 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                     // of tiles that bias reached 1e-3 of the output.  Each tile's product therefore
                     // starts from zero and is added to the running sum on the CUDA cores (round to
                     // nearest), where the offset is later taken out through ocorr.
-                    float c[4] = {0.f, 0.f, zz2, zz3};
-                    mma(c, pa0, pa2, b0[e], b1[e]);
+                    float c[4];
+                    mma_z(c, pa0, pa2, b0[e], b1[e]);
                     mma(c, pl0, pl2, b0[e], b1[e]);
                     o[kp * 4 + e][0] += c[0];
                     o[kp * 4 + e][1] += c[1];
-                    zz2 = c[2];
-                    zz3 = c[3];
                 } else {
                     float c[4] = {o[kp * 4 + e][0], o[kp * 4 + e][1], zz2, zz3};
                     mma(c, pa0, pa2, b0[e], b1[e]);
