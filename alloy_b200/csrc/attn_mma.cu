@@ -87,23 +87,25 @@ template <typename T>
 __device__ __forceinline__ T ldkv(const T* p, bool from_l2) {
     return from_l2 ? __ldcg(p) : __ldg(p);
 }
-__device__ __forceinline__ uint32_t lds32(const void* p) {
+// Shared loads by 32-bit shared-window address (a tile's base is converted once; the rest is 32-bit arithmetic
+// with constant offsets).
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(s32(p)));
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ uint32_t lds16(const void* p) {
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
     uint16_t v;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(s32(p)));
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
     return v;
 }
 // n (1 or 2) 32-bit words starting at a 2-byte-aligned shared address.  Whether the address is 4-byte
 // aligned is known at compile time from the block index (a row of 34-byte blocks starts 4-byte aligned, the
 // codes of block kp at 34 * kp + 2): HALF = true reads across the word boundary with funnel shifts.
 template <bool HALF>
-__device__ __forceinline__ void lds_words_align2(const uint8_t* p, uint32_t& w0, uint32_t& w1, bool two) {
+__device__ __forceinline__ void lds_words_align2(uint32_t p, uint32_t& w0, uint32_t& w1, bool two) {
     if (HALF) {
-        const uint8_t* base = p - 2;
+        const uint32_t base = p - 2;
         const uint32_t x0 = lds32(base), x1 = lds32(base + 4);
         w0 = __funnelshift_r(x0, x1, 16);
         if (two) w1 = __funnelshift_r(x1, lds32(base + 8), 16);
@@ -367,6 +369,11 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
         }
         // A tile whose sixteen tokens all lie below t1 (every tile but the last one of the sequence) takes the
         // FULL form of the body, without the per-token range tests and address clamps.
+        // paged tiles: the lane's base addresses inside this slot's two slabs
+        const uint32_t k_slab = PAGED ? s32(st->k[slot]) : 0u, v_slab = PAGED ? s32(st->v[slot]) : 0u;
+        const uint32_t k_code0 = k_slab + g * (NKP * KV_BLOCK_BYTES) + 2 + 8 * t;         // codes of token g, bytes 8t..
+        const uint32_t k_scale0 = k_slab + 2 * t * (NKP * KV_BLOCK_BYTES);               // scales of tokens 2t, 2t + 1
+        const uint32_t v_row0 = v_slab + 2 * t * (NKP * KV_BLOCK_BYTES);                 // rows of tokens 2t, 2t + 1
         auto tile_body = [&](auto full_c) {
         constexpr bool FULL = decltype(full_c)::value;
         // ---------------- S = Q K^T
@@ -393,13 +400,13 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
                     uint32_t w0, w1;
                     float ks[2];
                     if (PAGED) {
-                        const uint8_t* kc = st->k[slot] + (8 * tb + g) * (NKP * KV_BLOCK_BYTES) + kp * KV_BLOCK_BYTES + 2 + 8 * t;
+                        const uint32_t kc = k_code0 + (8 * tb) * (NKP * KV_BLOCK_BYTES) + kp * KV_BLOCK_BYTES;
                         if (kp & 1) lds_words_align2<false>(kc, w0, w1, true);      // 34 * kp + 2 is a multiple of 4
                         else lds_words_align2<true>(kc, w0, w1, true);
 #pragma unroll
                         for (int e = 0; e < 2; ++e)
                             ks[e] = (FULL || tok0 + 8 * tb + 2 * t + e < t1)
-                                        ? half_bits_to_f32(lds16(st->k[slot] + (8 * tb + 2 * t + e) * (NKP * KV_BLOCK_BYTES) + kp * KV_BLOCK_BYTES))
+                                        ? half_bits_to_f32(lds16(k_scale0 + (8 * tb + e) * (NKP * KV_BLOCK_BYTES) + kp * KV_BLOCK_BYTES))
                                         : 0.f;
                     } else {
                         const uint2 cw = ldkv(reinterpret_cast<const uint2*>(static_cast<const int8_t*>(P.kv.k0) + (head_row + tok) * D + 32 * kp + 8 * t), fresh);
@@ -483,7 +490,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const Params P) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     if (PAGED) {
-                        const uint8_t* row = st->v[slot] + ((i >> 1) * 8 + 2 * t + (i & 1)) * (NKP * KV_BLOCK_BYTES) + kp * KV_BLOCK_BYTES;
+                        const uint32_t row = v_row0 + ((i >> 1) * 8 + (i & 1)) * (NKP * KV_BLOCK_BYTES) + kp * KV_BLOCK_BYTES;
                         uint32_t dummy;
                         if (kp & 1) lds_words_align2<false>(row + 2 + 4 * g, w[i], dummy, false);
                         else lds_words_align2<true>(row + 2 + 4 * g, w[i], dummy, false);
