@@ -333,7 +333,7 @@ class QuantLlamaDecoder:
             if self.tp_size > 1 and not self.tp_dry:
                 logits = tp.gather_columns(logits, self.pg)
             self.logits = logits
-            self.next_ids.copy_(ops.argmax(logits))
+            ops.argmax(logits, out=self.next_ids)
             self.launches_per_step = ops.launch_count() - n0
             return
         h = ops._embedding(self.ids, ops._FORMATS[self.embed_fmt], self.embed, None, out_dtype=self.dtype)
@@ -382,7 +382,7 @@ class QuantLlamaDecoder:
         if self.tp_size > 1 and not self.tp_dry:
             logits = tp.gather_columns(logits, self.pg)
         self.logits = logits
-        self.next_ids.copy_(ops.argmax(logits))
+        ops.argmax(logits, out=self.next_ids)
         self.launches_per_step = ops.launch_count() - n0
 
     # ------------------------------------------------------------------ prefill
@@ -446,7 +446,7 @@ class QuantLlamaDecoder:
         if self.tp_size > 1 and not self.tp_dry:
             logits = tp.gather_columns(logits, self.pg)
         self.logits = logits
-        self.next_ids.copy_(ops.argmax(logits))
+        ops.argmax(logits, out=self.next_ids)
         self.pos.fill_(start + n)
         if hasattr(self, "seq_pos"):
             self.seq_pos.fill_(start + n)

@@ -863,9 +863,12 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return y
 
 
-def argmax(logits: torch.Tensor) -> torch.Tensor:
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     m, n = logits.shape
-    out = torch.empty((m,), dtype=torch.int64, device=logits.device)
+    if out is None:
+        out = torch.empty((m,), dtype=torch.int64, device=logits.device)
+    elif out.shape != (m,) or out.dtype != torch.int64 or not out.is_contiguous() or out.device != logits.device:
+        raise ValueError(f"out must be a contiguous int64 tensor of shape ({m},) on {logits.device}")
     L = _lib.load()
     check(L.alloyb_argmax(logits.data_ptr(), out.data_ptr(), m, n, _dtype_code(logits), _stream()),
           "alloyb_argmax")
