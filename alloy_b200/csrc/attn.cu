@@ -417,9 +417,11 @@ static int attn_decode_run(int layout, const void* q, int64_t q_batch_stride, in
     ws += align_up(bh * ATTN_MAX_SPLITS * sizeof(float), 256);
     P.part_o = reinterpret_cast<float*>(ws);
 
-    // Split count: the (b, kv head) pairs times the splits run in waves of about three CTAs per
-    // SM; a split costs its tokens (whole 64-token passes of the four warps) plus a fixed start-up
-    // and merge share, and every extra split lengthens the final merge.  Take the cheapest.
+    // Split count: the (b, kv head) pairs times the splits run in waves of as many CTAs per SM as the
+    // layout's kernel keeps resident (registers: 2 for the fp16 cache, whose tiles are staged in registers,
+    // 3 for the split q8_0 cache, 4 for the paged pool); a split costs its tokens (whole 64-token passes of
+    // the four warps) plus a fixed start-up and merge share, and every extra split lengthens the final
+    // merge.  Take the cheapest.
     const int ctas = B * KV_H;
     const int by_len = (S_max + 63) / 64;
     int max_s = by_len < ATTN_MAX_SPLITS ? by_len : ATTN_MAX_SPLITS;
@@ -427,8 +429,9 @@ static int attn_decode_run(int layout, const void* q, int64_t q_batch_stride, in
     int splits = 1;
     int64_t best = INT64_MAX;
     const int merge_w = layout == ALLOYB_KV_F16 ? 3 : 4;       // tokens' worth of merge time per split (measured)
+    const int resident = 148 * (layout == ALLOYB_KV_F16 ? 2 : (layout == ALLOYB_KV_Q8_SPLIT ? 3 : 4));
     for (int s = 1; s <= max_s; ++s) {
-        const int64_t waves = (static_cast<int64_t>(ctas) * s + 148 * 3 - 1) / (148 * 3);
+        const int64_t waves = (static_cast<int64_t>(ctas) * s + resident - 1) / resident;
         const int64_t per = ((S_max + s - 1) / s + 63) / 64 * 64 + 256;
         const int64_t cost = waves * per + merge_w * s;
         if (cost < best) { best = cost; splits = s; }
