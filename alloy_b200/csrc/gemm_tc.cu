@@ -769,34 +769,54 @@ gemm_tc_kernel(const __grid_constant__ Maps maps, const Params P) {
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 }
                 bar_arrive(&bars->acc_empty);
-                // the last item of the tile to get here finishes it
-                __threadfence();
+                // The last item of the tile to get here finishes it.  One release-acquire count per CTA: the
+                // barrier puts the epilogue threads' reductions before thread 0's release, the last CTA's acquire
+                // and its barrier put every item's reductions before the loads below.
                 asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
                 if (et == 0) {
-                    const unsigned int old = atomicAdd(&g_split_count[im.tile_n], 1u);
+                    unsigned int old;
+                    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(&g_split_count[im.tile_n]) : "memory");
                     bars->last = old == static_cast<unsigned int>(P.splits - 1) ? 1u : 0u;
                     if (bars->last) g_split_count[im.tile_n] = 0u;
                 }
                 asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
                 if (bars->last && ok) {
-                    __threadfence();
                     if (n < P.N) {
                         uint16_t* col = static_cast<uint16_t*>(P.y) + static_cast<int64_t>(tok0) * P.ldy + n;
                         const uint16_t* res = P.residual ? static_cast<const uint16_t*>(P.residual) +
                                                                static_cast<int64_t>(tok0) * P.ldy + n
                                                          : nullptr;
-                        for (int e = 0; e < HT; ++e) {
-                            if (tok0 + e >= P.M) break;
-                            float* a = sum + static_cast<int64_t>(e) * pitch;
-                            float v = __ldcg(a);
-                            __stcg(a, 0.0f);
-                            if (P.gated) {
-                                v = apply_act(v, P.act) * __ldcg(a + plane);
-                                __stcg(a + plane, 0.0f);
+                        // eight tokens' sums (and residuals) are requested together, then finished: one round
+                        // trip to L2 per eight tokens instead of one per token
+                        constexpr int FB = HT < 8 ? HT : 8;
+#pragma unroll 1
+                        for (int e0 = 0; e0 < HT; e0 += FB) {
+                            float v[FB], u[FB], r[FB];
+#pragma unroll
+                            for (int j = 0; j < FB; ++j) {
+                                const int e = e0 + j;
+                                const bool live = tok0 + e < P.M;
+                                const float* a = sum + static_cast<int64_t>(e) * pitch;
+                                v[j] = live ? __ldcg(a) : 0.f;
+                                u[j] = (live && P.gated) ? __ldcg(a + plane) : 0.f;
+                                r[j] = (live && res) ? to_f32<BF16>(res[static_cast<int64_t>(e) * P.ldy]) : 0.f;
                             }
-                            uint16_t o = to_16<BF16>(v);
-                            if (res) o = to_16<BF16>(to_f32<BF16>(res[static_cast<int64_t>(e) * P.ldy]) + to_f32<BF16>(o));
-                            col[static_cast<int64_t>(e) * P.ldy] = o;
+#pragma unroll
+                            for (int j = 0; j < FB; ++j) {
+                                const int e = e0 + j;
+                                if (tok0 + e < P.M) {
+                                    float* a = sum + static_cast<int64_t>(e) * pitch;
+                                    __stcg(a, 0.0f);
+                                    float val = v[j];
+                                    if (P.gated) {
+                                        val = apply_act(val, P.act) * u[j];
+                                        __stcg(a + plane, 0.0f);
+                                    }
+                                    uint16_t o = to_16<BF16>(val);
+                                    if (res) o = to_16<BF16>(r[j] + to_f32<BF16>(o));
+                                    col[static_cast<int64_t>(e) * P.ldy] = o;
+                                }
+                            }
                         }
                     }
                 }
