@@ -37,6 +37,8 @@
 // tensor memory and returns.
 #include <cuda.h>
 
+#include <climits>
+
 #include "linear.cuh"
 
 namespace alloyb {
@@ -123,6 +125,11 @@ struct Params {
     int M, N, K;
     int splits;               // K ranges per row tile (1: the item owns its output tile)
     int gated, act;           // gate/up pair: y = act(gate) * up
+    // Two matrices that lie back to back in memory run as one: rows from n_split on belong to the second
+    // one and go to its own output (INT_MAX: a single matrix).
+    int n_split;
+    void* y2;
+    int64_t ldy2;
 };
 
 __device__ __forceinline__ uint32_t s32(const void* p) {
@@ -736,7 +743,10 @@ gemm_tc_kernel(const __grid_constant__ Maps maps, const Params P) {
                 }
                 bar_arrive(&bars->acc_empty);               // the accumulators are free: the next item may start
                 if (ok && n < P.N) {
-                    uint16_t* col = static_cast<uint16_t*>(P.y) + static_cast<int64_t>(tok0) * P.ldy + n;
+                    const bool second = n >= P.n_split;                 // the second of two stacked matrices
+                    const int64_t ld = second ? P.ldy2 : P.ldy;
+                    uint16_t* col = static_cast<uint16_t*>(second ? P.y2 : P.y) + static_cast<int64_t>(tok0) * ld +
+                                    (second ? n - P.n_split : n);
                     const uint16_t* res =
                         P.residual ? static_cast<const uint16_t*>(P.residual) + static_cast<int64_t>(tok0) * P.ldy + n : nullptr;
 #pragma unroll
@@ -745,7 +755,7 @@ gemm_tc_kernel(const __grid_constant__ Maps maps, const Params P) {
                             uint16_t o = static_cast<uint16_t>(e & 1 ? acc[e >> 1] >> 16 : acc[e >> 1] & 0xffffu);
                             // residual: dtype(residual + dtype(acc))
                             if (res) o = to_16<BF16>(to_f32<BF16>(res[static_cast<int64_t>(e) * P.ldy]) + to_f32<BF16>(o));
-                            col[static_cast<int64_t>(e) * P.ldy] = o;
+                            col[static_cast<int64_t>(e) * ld] = o;
                         }
                     }
                 }
@@ -782,7 +792,10 @@ gemm_tc_kernel(const __grid_constant__ Maps maps, const Params P) {
                 asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
                 if (bars->last && ok) {
                     if (n < P.N) {
-                        uint16_t* col = static_cast<uint16_t*>(P.y) + static_cast<int64_t>(tok0) * P.ldy + n;
+                        const bool second = n >= P.n_split;
+                        const int64_t ld = second ? P.ldy2 : P.ldy;
+                        uint16_t* col = static_cast<uint16_t*>(second ? P.y2 : P.y) + static_cast<int64_t>(tok0) * ld +
+                                        (second ? n - P.n_split : n);
                         const uint16_t* res = P.residual ? static_cast<const uint16_t*>(P.residual) +
                                                                static_cast<int64_t>(tok0) * P.ldy + n
                                                          : nullptr;
@@ -814,7 +827,7 @@ gemm_tc_kernel(const __grid_constant__ Maps maps, const Params P) {
                                     }
                                     uint16_t o = to_16<BF16>(val);
                                     if (res) o = to_16<BF16>(r[j] + to_f32<BF16>(o));
-                                    col[static_cast<int64_t>(e) * P.ldy] = o;
+                                    col[static_cast<int64_t>(e) * ld] = o;
                                 }
                             }
                         }
@@ -964,7 +977,7 @@ int gemm_tc_residual_add(void* y, const void* residual, int M, int N, int64_t ld
 // (`up` non-null; both matrices in seg's format and shape, M <= 128).  NOT_TAKEN unless the shape and
 // the alignment are the kind the kernel is built for.
 int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, const void* residual, const void* up,
-                const void* up_scales, int act, cudaStream_t st) {
+                const void* up_scales, int act, cudaStream_t st, const WeightSeg* tail) {
     using namespace tc;
     if (dtype != ALLOYB_F16 && dtype != ALLOYB_BF16) return ALLOYB_NOT_TAKEN;
     if (seg.format != ALLOYB_Q4_K && seg.format != ALLOYB_Q6_K && seg.format != ALLOYB_Q8_0) return ALLOYB_NOT_TAKEN;
@@ -984,7 +997,11 @@ int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, co
     if (!sms) { set_cuda_error(cudaErrorInvalidValue); return ALLOYB_E_CUDA; }
 
     const int BM = M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
-    const int tiles_n = (seg.N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM, nsb = K / QK_K;
+    // `tail`: a second matrix of the same format whose rows follow seg's in memory (the caller has checked
+    // that, and that seg.N is a whole number of row tiles); no residual, no gate/up pair, not Q8_0
+    if (tail && (residual || up || q8 || seg.N % BN)) return ALLOYB_NOT_TAKEN;
+    const int n_rows = seg.N + (tail ? tail->N : 0);
+    const int tiles_n = (n_rows + BN - 1) / BN, tiles_m = (M + BM - 1) / BM, nsb = K / QK_K;
     // too few row tiles for the SMs and one token tile: split K (the sums live in a fixed scratch)
     int splits = 1;
     if (tiles_m == 1 && BM <= SPLIT_MAX_BM && tiles_n <= SPLIT_MAX_TILES && 2 * tiles_n <= sms) {
@@ -1005,7 +1022,7 @@ int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, co
                  map2d(encode, &maps.s[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, scs[i], static_cast<uint64_t>(K / Q8_BLOCK) * 2,
                        seg.N, static_cast<uint64_t>(K / Q8_BLOCK) * 2, 16, PACK_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
         } else {
-            ok = map2d(encode, &maps.w[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, mats[i], seg.row_bytes, seg.N, seg.row_bytes,
+            ok = map2d(encode, &maps.w[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, mats[i], seg.row_bytes, n_rows, seg.row_bytes,
                        seg.format == ALLOYB_Q4_K ? Q4_ROW : Q6_ROW, PACK_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
             maps.s[i] = maps.w[i];
         }
@@ -1021,7 +1038,10 @@ int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, co
     P.residual = add_after ? nullptr : residual;
     P.ldy = seg.ldy;
     P.M = M;
-    P.N = seg.N;
+    P.N = n_rows;
+    P.n_split = tail ? seg.N : INT_MAX;
+    P.y2 = tail ? tail->y : nullptr;
+    P.ldy2 = tail ? tail->ldy : 0;
     P.K = K;
     P.splits = splits;
     P.gated = up ? 1 : 0;

@@ -201,6 +201,21 @@ extern "C" int alloyb_linear(const void* x, int M, int K, int dtype, const alloy
         // more than a handful of tokens: one tcgen05 GEMM per matrix; a matrix it does not take (type,
         // alignment) goes through the kernels below on its own
         for (int i = 0; i < segs.n_seg; ++i) {
+            // two matrices of one format that lie back to back in one buffer (q and k of a layer) run as ONE
+            // GEMM; its epilogue sends the second matrix's rows to their own output
+            const WeightSeg& a = segs.seg[i];
+            if (i + 1 < segs.n_seg && !residual && a.format != ALLOYB_Q8_0 && a.N % 128 == 0) {
+                const WeightSeg& b = segs.seg[i + 1];
+                if (b.format == a.format && b.row_bytes == a.row_bytes &&
+                    static_cast<const uint8_t*>(b.data) == static_cast<const uint8_t*>(a.data) + static_cast<int64_t>(a.N) * a.row_bytes) {
+                    rc = try_gemm_tc(x, M, K, dtype, a, nullptr, nullptr, nullptr, 0, st, &b);
+                    if (rc == ALLOYB_OK) {
+                        ++i;
+                        continue;
+                    }
+                    if (rc != ALLOYB_NOT_TAKEN) return rc;
+                }
+            }
             rc = try_gemm_tc(x, M, K, dtype, segs.seg[i], residual, nullptr, nullptr, 0, st);
             if (rc == ALLOYB_NOT_TAKEN) {
                 RowSegs one;

@@ -45,8 +45,10 @@ int try_q8_gemv(const void* x, int M, int K, int dtype, const void* w0, const vo
 // 2.4e12 weights/s whatever the token count (35 us for 14336 x 4096), and below this the tokens-as-columns
 // GEMV, whose cost grows with the token count, is still ahead.
 constexpr int GEMM_TC_MIN_M = 28;
+// `tail`: a second matrix whose packed rows follow seg's in memory, run in the same launch (its rows go to its
+// own output).
 int try_gemm_tc(const void* x, int M, int K, int dtype, const WeightSeg& seg, const void* residual, const void* up,
-                const void* up_scales, int act, cudaStream_t st);
+                const void* up_scales, int act, cudaStream_t st, const WeightSeg* tail = nullptr);
 int gemm_tc_device_error(int clear);
 
 }  // namespace alloyb

@@ -220,6 +220,13 @@ class QuantLlamaDecoder:
                 self.layers.append(lw)
             self.norm_final = self._norm_weight(gen)
             self.head = rows(synth.q6k_blocks_device(s.vocab, s.hidden, gen, self.device, d_scale), self.vocab_l)
+        # q and k of a layer share a format: their packed rows are kept back to back in ONE buffer (wq and wk are
+        # views of it), which lets the library run the two projections of several tokens as a single GEMM
+        for lw in self.layers:
+            if lw.fmt["wq"] == lw.fmt["wk"] and lw.wq.shape[1:] == lw.wk.shape[1:] and lw.wq.dtype == lw.wk.dtype:
+                nq = lw.wq.shape[0]
+                qk = torch.cat([lw.wq, lw.wk], 0)
+                lw.wq, lw.wk = qk[:nq], qk[nq:]
         self.inv_freq = (1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, dtype=torch.float32) /
                                                  s.head_dim))).to(self.device)
         self._init_kv(gen)

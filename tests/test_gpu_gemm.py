@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 import torch
 
-from alloy_b200 import _lib, synth
+from alloy_b200 import _lib, ops, synth
 from oracle import blocks as O
 from tests._util import assert_close, to_np
 
@@ -182,3 +182,22 @@ def test_gemm_gated_q8_few_tokens():
     ref = O.silu(_ref(x, O.dequant_q8_0(gc, gs), torch.float16)) * _ref(x, O.dequant_q8_0(uc, us), torch.float16)
     assert_close(to_np(y), ref, torch.float16, "q8 gated gemm")
     assert _lib.load().alloyb_device_error(0) == 0
+
+
+# Two matrices of one format whose packed rows lie back to back in one buffer (q and k of a layer) run as ONE
+# GEMM with two outputs: each output against the oracle, with and without a K split, ragged second matrix.
+@pytest.mark.parametrize("fmt,m,nq,nk,k", [("q4_k", 40, 256, 200, 1024), ("q4_k", 64, 4096, 1024, 4096),
+                                           ("q6_k", 33, 128, 72, 2048), ("q4_k", 200, 384, 128, 512)])
+def test_gemm_two_stacked_matrices_one_launch(fmt, m, nq, nk, k):
+    rng = np.random.default_rng([m, nq, nk, k])
+    make = synth.q4k_blocks if fmt == "q4_k" else synth.q6k_blocks
+    deq = O.dequant_q4_k if fmt == "q4_k" else O.dequant_q6_k
+    wq, wk = make(rng, nq, k), make(rng, nk, k)
+    both = torch.from_numpy(np.concatenate([wq, wk], 0)).to(DEV)
+    x = torch.from_numpy(synth.activations(rng, m, k, np.float32)).to(torch.float16)
+    yq, yk = ops.linear_multi(x.to(DEV), [(fmt, both[:nq], None), (fmt, both[nq:], None)])
+    torch.cuda.synchronize()
+    assert _lib.load().alloyb_device_error(1) == 0
+    for y, w in ((yq, wq), (yk, wk)):
+        assert y.shape == (m, w.shape[0])
+        assert_close(to_np(y), _ref(x, deq(w), torch.float16), torch.float16, f"stacked {fmt} m={m} rows={w.shape[0]}")
