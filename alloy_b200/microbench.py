@@ -14,6 +14,8 @@ graph; the figure printed is the mean device time per launch and the algorithmic
     python -m alloy_b200.microbench --op attn_paged --batch 64 --ctx-lo 4096 --ctx-hi 32768
     python -m alloy_b200.microbench --op gemm_q4k --m 4096 --n 14336 --k 4096 --dtype bf16
     python -m alloy_b200.microbench --op q8_mm --n 4096 --k 4096 --m 1
+    python -m alloy_b200.microbench --op layer_ops --batch 1            # the 8B decode step's five launches per layer
+    python -m alloy_b200.microbench --op layer_ops --model 70b --tp-dry 8
 """
 
 from __future__ import annotations
@@ -144,23 +146,93 @@ def bench_attn_paged(batch: int, lo: int, hi: int, sweeps: int, kv_heads: int = 
             "gbs_median": alg / med / 1e6, "gbs_best": alg / min(ms) / 1e6}
 
 
+def bench_layer_ops(model: str, batch: int, tp_dry: int, sweeps: int) -> dict:
+    """The decode step's per-layer launches, each kind timed on its own: one CUDA graph runs the op of all
+    layers back to back (every layer's own weights and cache, so nothing comes from L2), and the figure is the
+    mean device time per launch.  The sum over the kinds is what a step would take if its launches followed
+    each other as smoothly as launches of one kind do; the step itself is timed beside it."""
+    from . import llama
+
+    shape = llama.LLAMA3_70B if model == "70b" else llama.LLAMA3_8B
+    context, kv = (4096, "q8_paged") if model == "70b" else (2048, "f16")
+    extra = dict(tp_rank=0, tp_size=tp_dry, tp_dry=True) if tp_dry > 1 else {}
+    d = llama.QuantLlamaDecoder(shape, batch, context, seed=0, d_scale=0.1, centered=True, kv=kv, **extra)
+    d.capture()
+    s, n_layers = d.shape, len(d.layers)
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    rnd = lambda *sh: (torch.randn(sh, device="cuda", generator=gen) * 0.1).half()
+    h, a2, act = rnd(batch, s.hidden), rnd(batch, d.heads_l * s.head_dim), rnd(batch, d.ffn_l)
+    q3, k3, v3 = rnd(batch, d.heads_l, s.head_dim), rnd(batch, d.kv_heads_l, s.head_dim), rnd(batch, d.kv_heads_l, s.head_dim)
+    scale = 1.0 / s.head_dim ** 0.5
+
+    def qkv():
+        for lw in d.layers:
+            ops.linear_multi(h, [(lw.fmt["wq"], lw.wq, None), (lw.fmt["wk"], lw.wk, None), (lw.fmt["wv"], lw.wv, None)],
+                             norm=(lw.norm_in, s.eps))
+
+    def attn():
+        for li in range(n_layers):
+            if kv == "f16":
+                ops.rope_attention_decode(q3, k3, v3, d.pos, d.inv_freq, scale=scale, k_cache=d.k_cache[li],
+                                          v_cache=d.v_cache[li])
+            else:
+                ops.rope_attention_decode(q3, k3, v3, d.seq_pos, d.inv_freq, scale=scale,
+                                          paged=(d.pools[li].page_table, d.pools[li].pool))
+
+    def row_parallel(x, name):
+        for lw in d.layers:
+            w = getattr(lw, name)
+            if d.tp_size == 1:
+                torch.ops.alloy.linear_residual(x, w, None, h, lw.fmt[name])
+            else:
+                d._row_parallel(x, lw.fmt[name], w, h)
+
+    def gate_up():
+        for lw in d.layers:
+            ops.gated_normed(h, lw.norm_post, s.eps, lw.wg, lw.wu)
+
+    kinds = [("qkv", qkv), ("attention", attn), ("o", lambda: row_parallel(a2, "wo")), ("gate_up", gate_up),
+             ("down", lambda: row_parallel(act, "wd"))]
+    res = {"op": "layer_ops", "model": model, "batch": batch, "tp_dry": tp_dry, "layers": n_layers, "us_per_launch": {}}
+    for name, fn in kinds:
+        ms = _time_graph(fn, sweeps)
+        res["us_per_launch"][name] = statistics.median(ms) * 1e3 / n_layers
+    res["sum_us_per_layer"] = sum(res["us_per_launch"].values())
+    for _ in range(3):
+        d.step()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(20):
+        d.step()
+    b.record()
+    torch.cuda.synchronize()
+    res["step_ms"] = a.elapsed_time(b) / 20
+    return res
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", required=True,
-                    choices=["q4k_mm", "q6k_mm", "q8_mm", "gated", "attn_paged", "gemm_q4k", "gemm_q6k", "gemm_q8"])
+                    choices=["q4k_mm", "q6k_mm", "q8_mm", "gated", "attn_paged", "gemm_q4k", "gemm_q6k", "gemm_q8",
+                             "layer_ops"])
+    ap.add_argument("--model", default="8b", choices=["8b", "70b"])
+    ap.add_argument("--tp-dry", type=int, default=1, help="layer_ops: one rank's share of an N-way split, nobody to exchange with")
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--dtype", default="f16", choices=["f16", "bf16"])
     ap.add_argument("--ring-mb", type=int, default=512)
     ap.add_argument("--sweeps", type=int, default=20)
-    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--batch", type=int, default=None, help="attn_paged: sequences (default 64); layer_ops: tokens per step (default 1)")
     ap.add_argument("--ctx-lo", type=int, default=4096)
     ap.add_argument("--ctx-hi", type=int, default=32768)
     a = ap.parse_args()
     dt = torch.float16 if a.dtype == "f16" else torch.bfloat16
-    if a.op == "attn_paged":
-        res = bench_attn_paged(a.batch, a.ctx_lo, a.ctx_hi, a.sweeps)
+    if a.op == "layer_ops":
+        res = bench_layer_ops(a.model, a.batch or 1, a.tp_dry, min(a.sweeps, 10))
+    elif a.op == "attn_paged":
+        res = bench_attn_paged(a.batch or 64, a.ctx_lo, a.ctx_hi, a.sweeps)
     elif a.op.startswith("gemm_"):
         res = bench_gemm(a.op[5:], a.m, a.n, a.k, a.sweeps, dt)
     else:
