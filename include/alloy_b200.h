@@ -106,7 +106,10 @@ typedef struct alloyb_weight {
 
 /* Generic entry: n_w matrices sharing activations x (M,K).
  * residual (may be NULL): same shape/pitch as y of matrix 0, added in the
- * epilogue as dtype(residual + dtype(acc)); only with n_w == 1. */
+ * epilogue as dtype(residual + dtype(acc)); only with n_w == 1.
+ * One fp16 token against Q4_K and Q6_K matrices (q/k and v of a decode step) is one launch; from 28 tokens
+ * up two consecutive descriptors of one format whose packed rows lie back to back in memory (the second's
+ * data = the first's data + N * row_bytes, N a multiple of 128) run as one GEMM, each with its own output. */
 int alloyb_linear(const void* x, int M, int K, int dtype, const alloyb_weight* w, int n_w,
                   const void* residual, void* stream);
 
